@@ -1,0 +1,156 @@
+/*
+ * wsl.h -- C ABI of the B200 (sm_100a) shared-W + LoRA linear hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (a cudaStream_t passed as void*), enqueues its kernels on that stream and
+ * returns an int status (WSL_OK or a negative WSL_ERR_*). Nothing here
+ * allocates, frees or synchronises, and nothing throws; the caller owns all
+ * memory. There is no CPU fallback: on a machine without an sm_100 device
+ * every compute entry point returns WSL_ERR_DEVICE.
+ *
+ * The reference (muchanem/weightshared_torchtitan) has no FFI of its own; its
+ * interface for this path is Python (nn.Module + autograd). Each declaration
+ * below names the reference lines whose arithmetic it replaces. File paths are
+ * relative to the reference project root.
+ *
+ * Conventions
+ *   - matrices are row-major, last dimension contiguous; `ld*` arguments are row
+ *     pitches in ELEMENTS (pass the number of columns for a packed matrix);
+ *   - dtype WSL_BF16: activations/weights are bf16, accumulation is fp32 on the
+ *     tcgen05 tensor cores, gradients of parameters (dW, dA, dB, dE, dP) are fp32;
+ *   - dtype WSL_F32 : everything is fp32 and runs on the CUDA cores (the
+ *     correctness mode of the reference's CPU-runnable configuration);
+ *   - bf16 matrices must be 16-byte aligned with pitches that are multiples of
+ *     8 elements (TMA requirement); violations return WSL_ERR_ALIGN;
+ *   - s is the LoRA scale alpha/rank (the reference fixes alpha = 2*rank, so s = 2).
+ */
+#ifndef WSL_H_
+#define WSL_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WSL_OK 0
+#define WSL_ERR_BAD_ARG (-1)   /* null pointer, non-positive or unsupported size */
+#define WSL_ERR_ALIGN (-2)     /* pointer or pitch breaks the 16-byte rule */
+#define WSL_ERR_DEVICE (-3)    /* no CUDA device, or the current device is not sm_100 */
+#define WSL_ERR_CUDA (-4)      /* a CUDA runtime call or kernel launch failed */
+#define WSL_ERR_TIMEOUT (-5)   /* a bounded device-side wait ran out (see wsl_poll_status) */
+#define WSL_ERR_DRIVER (-6)    /* cuTensorMapEncodeTiled unavailable or refused the tensor */
+#define WSL_ERR_TOO_LARGE (-7) /* size beyond a documented fixed limit */
+
+#define WSL_BF16 0
+#define WSL_F32 1
+
+#define WSL_MAX_PROJ 3 /* projections that can share one input in wsl_lora_linear_bwd_dx */
+
+/* Library version, (major << 16) | minor. */
+int wsl_version(void);
+
+/* Static, NUL-terminated description of a status code. */
+const char* wsl_status_string(int status);
+
+/* Number of kernel launches the library has enqueued since it was loaded. */
+unsigned long long wsl_launch_count(void);
+
+/*
+ * Device-side status words of the CURRENT device: words[0] = 0 or the first
+ * recorded WSL_ERR_TIMEOUT, words[1] = role that gave up (1 producer, 2 MMA
+ * issuer, 3 epilogue), words[2] = block index, words[3] = tile index.
+ * Copies from the device, so it waits for work already enqueued on the legacy
+ * default stream's peers to the extent cudaMemcpyFromSymbol does; call it
+ * after synchronising the stream of interest. Returns words[0].
+ * Replaces: the reference reports errors by Python exceptions/asserts
+ * (torchtitan/models/llama3/model/model.py:126).
+ */
+int wsl_poll_status(int words[4]);
+int wsl_reset_status(void);
+
+/*
+ * y[M,N] = x[M,K] * W[N,K]^T           (plain projection, no adapter)
+ * Replaces F.linear of the base projections: torchtitan/models/llama3/model/
+ * model.py:392-394 and torchtitan/experiments/qwen3/model/model.py:184,218,251.
+ * out_f32 != 0 writes fp32 instead of bf16 (bf16 mode only).
+ */
+int wsl_linear_fwd(const void* x, long long ldx, const void* W, void* y, long long ldy,
+                   long long M, long long N, long long K, int out_f32, int dtype, void* stream);
+
+/*
+ * T[M,r_tot] = s * x[M,K] * A_cat[r_tot,K]^T
+ * The rank-r pre-pass of the adapter. A_cat may stack the A matrices of all
+ * projections that read the same x (q|k|v, gate|up), so x is read once.
+ * The scale s is folded in here; wsl_lora_linear_fwd and wsl_lora_linear_bwd_dw
+ * expect this scaled T.
+ * Replaces self.w_a(x) and the "* (alpha/rank)" of LoRAModule.forward:
+ * torchtitan/models/llama3/model/model.py:189-192.
+ */
+int wsl_lora_prepass(const void* x, long long ldx, const void* A_cat, void* T, long long ldt,
+                     long long M, long long K, long long r_tot, float s, int dtype, void* stream);
+
+/*
+ * y[M,N] = x[M,K] * W[N,K]^T + T[M,r] * B[N,r]^T
+ * One GEMM whose contraction runs over the concatenation [x | T] . [W | B]^T,
+ * accumulated in fp32, rounded once. T is the scaled pre-pass output (column
+ * slice of T_cat with pitch ldt).
+ * Replaces base(x) + LoRAModule.forward(x) joined by broadcast_add with equal
+ * widths: torchtitan/models/llama3/model/model.py:111-145,189-192,392-398.
+ */
+int wsl_lora_linear_fwd(const void* x, long long ldx, const void* W, const void* T,
+                        long long ldt, const void* B, void* y, long long ldy, long long M,
+                        long long N, long long K, long long r, int dtype, void* stream);
+
+/*
+ * U[M,r] = s * dY[M,N] * B[N,r]
+ * Backward pre-pass (the autograd MmBackward of w_b together with the
+ * MulBackward of the scale): torchtitan/models/llama3/model/model.py:191.
+ */
+int wsl_lora_bwd_prepass(const void* dY, long long lddy, const void* B, void* U, long long ldu,
+                         long long M, long long N, long long r, float s, int dtype, void* stream);
+
+/*
+ * dX[M,K] = sum_{p < nproj} ( dY_p[M,N_p] * W_p[N_p,K] + U_p[M,r_p] * A_p[r_p,K] )
+ * Input gradient of up to WSL_MAX_PROJ projections that read the same x (q,k,v or
+ * gate,up), summed inside one fp32 accumulator and rounded once.
+ * Replaces the two MmBackward nodes per projection and the AddBackward at the
+ * shared input: autograd of torchtitan/models/llama3/model/model.py:191,392-398.
+ */
+int wsl_lora_linear_bwd_dx(int nproj, const void* const* dY, const long long* lddy,
+                           const void* const* U, const long long* ldu, const void* const* W,
+                           const void* const* A, const long long* N, const long long* r, void* dX,
+                           long long lddx, long long M, long long K, int dtype, void* stream);
+
+/*
+ * dW[N,K] += dY^T x ;  dA[r,K] += U^T x ;  dB[N,r] += dY^T T      (all fp32, in place)
+ * U and T carry the scale s already. dW is the gradient buffer of the SHARED
+ * base weight: every layer that reuses W adds into the same fp32 buffer. Any of
+ * dW, dA, dB may be NULL to skip that product.
+ * Replaces the MmBackward weight gradients and AccumulateGrad of
+ * torchtitan/models/llama3/model/model.py:191,392-394 (one dW per use, cast and
+ * added into W.grad by autograd in the reference).
+ */
+int wsl_lora_linear_bwd_dw(const void* dY, long long lddy, const void* U, long long ldu,
+                           const void* x, long long ldx, const void* T, long long ldt, float* dW,
+                           float* dA, float* dB, long long M, long long N, long long K,
+                           long long r, int dtype, void* stream);
+
+/*
+ * G[M,r_e] = E_small[tokens[m], :]          (bit-exact row gather)
+ * tokens are int64 in [0, V). Replaces aten::embedding behind
+ * nn.Embedding: torchtitan/experiments/qwen3/model/model.py:350,441.
+ */
+int wsl_embed_gather(const long long* tokens, const void* E_small, void* G, long long M,
+                     long long V, long long r_e, int dtype, void* stream);
+
+/*
+ * dE[tokens[m], :] += dG[m, :]              (fp32 scatter-add, atomics)
+ * dG is bf16 (WSL_BF16) or fp32 (WSL_F32); dE is fp32 [V, r_e].
+ * Replaces embedding_dense_backward behind nn.Embedding (same lines).
+ */
+int wsl_embed_scatter_add(const long long* tokens, const void* dG, float* dE, long long M,
+                          long long V, long long r_e, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WSL_H_ */

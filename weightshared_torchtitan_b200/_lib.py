@@ -1,0 +1,94 @@
+"""ctypes binding of libwsl.so (include/wsl.h). No torch types cross this boundary:
+pointers are passed as integers, sizes as 64-bit ints, the stream as a raw handle.
+
+There is no fallback: if the library is missing the first call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libwsl.so")
+
+WSL_BF16 = 0
+WSL_F32 = 1
+WSL_OK = 0
+WSL_ERR_BAD_ARG = -1
+WSL_ERR_ALIGN = -2
+WSL_ERR_DEVICE = -3
+WSL_ERR_CUDA = -4
+WSL_ERR_TIMEOUT = -5
+WSL_ERR_DRIVER = -6
+WSL_ERR_TOO_LARGE = -7
+
+_vp = ctypes.c_void_p
+_ll = ctypes.c_longlong
+_i = ctypes.c_int
+_f = ctypes.c_float
+_vpp = ctypes.POINTER(ctypes.c_void_p)
+_llp = ctypes.POINTER(ctypes.c_longlong)
+
+# name -> (restype, argtypes); mirrors include/wsl.h one to one.
+SIGNATURES = {
+    "wsl_version": (_i, []),
+    "wsl_status_string": (ctypes.c_char_p, [_i]),
+    "wsl_launch_count": (ctypes.c_ulonglong, []),
+    "wsl_poll_status": (_i, [ctypes.POINTER(_i)]),
+    "wsl_reset_status": (_i, []),
+    "wsl_linear_fwd": (_i, [_vp, _ll, _vp, _vp, _ll, _ll, _ll, _ll, _i, _i, _vp]),
+    "wsl_lora_prepass": (_i, [_vp, _ll, _vp, _vp, _ll, _ll, _ll, _ll, _f, _i, _vp]),
+    "wsl_lora_linear_fwd": (_i, [_vp, _ll, _vp, _vp, _ll, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _i, _vp]),
+    "wsl_lora_bwd_prepass": (_i, [_vp, _ll, _vp, _vp, _ll, _ll, _ll, _ll, _f, _i, _vp]),
+    "wsl_lora_linear_bwd_dx": (_i, [_i, _vpp, _llp, _vpp, _llp, _vpp, _vpp, _llp, _llp, _vp, _ll, _ll, _ll, _i, _vp]),
+    "wsl_lora_linear_bwd_dw": (_i, [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _i, _vp]),
+    "wsl_embed_gather": (_i, [_vp, _vp, _vp, _ll, _ll, _ll, _i, _vp]),
+    "wsl_embed_scatter_add": (_i, [_vp, _vp, _vp, _ll, _ll, _ll, _i, _vp]),
+}
+
+_LIB = None
+
+
+class WslError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        super().__init__(f"{where}: wsl status {status}: {status_string(status)}")
+
+
+def lib() -> ctypes.CDLL:
+    """Load libwsl.so once. Raises if it has not been built (no CPU fallback exists)."""
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with "
+                "`python -m weightshared_torchtitan_b200.build` (needs nvcc); "
+                "this package has no fallback path"
+            )
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _LIB = handle
+    return _LIB
+
+
+def status_string(status: int) -> str:
+    return lib().wsl_status_string(status).decode()
+
+
+def check(status: int, where: str) -> None:
+    if status != WSL_OK:
+        raise WslError(status, where)
+
+
+def poll_status():
+    """(status, [4 words]) of the current device; see wsl_poll_status in include/wsl.h."""
+    words = (ctypes.c_int * 4)()
+    st = lib().wsl_poll_status(words)
+    return st, list(words)
+
+
+def launch_count() -> int:
+    return int(lib().wsl_launch_count())

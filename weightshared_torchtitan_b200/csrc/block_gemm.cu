@@ -1,0 +1,509 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   out_region[mo, no] (op)= alpha * sum over segments  A_seg * B_seg^T
+//
+// One launch covers up to kMaxRegion output regions that share the contraction,
+// and the contraction is a concatenation of up to kMaxSeg segments, each with
+// its own pair of TMA tensor maps. That one shape serves every GEMM on the
+// shared-W + LoRA path:
+//   forward   y  = [x | T] . [W | B]^T                    2 segments, K-major / K-major
+//   dX        dX = [dY_q | U_q | dY_k | ...] . [...]      2 per projection, K-major / MN-major
+//   dW,dA,dB  [dY | U]^T . [x | T]                        3 regions, MN-major / MN-major
+//   pre-pass  T  = s x A^T,  U = s dY B                    1 segment, narrow N tile
+//
+// CTA layout (192 threads, one CTA per SM, grid = min(#SM, #tiles)):
+//   warp 0    TMA producer: fills a 4-stage ring of [128 x 64] A and [bn x 64] B
+//             bf16 tiles, 128-byte swizzled, completion on `full` mbarriers
+//   warp 1    allocates 512 TMEM columns, one lane issues tcgen05.mma
+//             (M=128, N=bn<=256, K=16 per instruction) into one of two fp32
+//             accumulators; tcgen05.commit frees ring stages and publishes tiles
+//   warps 2-5 epilogue: tcgen05.ld of their 32-lane quarter, scale, convert,
+//             store/accumulate to global, then hand the accumulator back
+// Every mbarrier wait is bounded; a wait that runs out records WSL_ERR_TIMEOUT in
+// g_wsl_status and all roles fall through to the common tear-down.
+#include "block_gemm.cuh"
+#include "ptx_sm100.cuh"
+#include "status.cuh"
+
+#include <cuda_bf16.h>
+#include <cudaTypedefs.h>
+#include <cstdio>
+#include <cstdlib>
+
+#include "../../include/wsl.h"
+
+namespace wsl {
+
+constexpr int BM = 128;
+constexpr int BN_MAX = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;       // 16 KiB
+constexpr int B_STAGE_BYTES = BN_MAX * BK * 2;   // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int SLAB_BYTES = 64 * BK * 2;          // one MN-major slab: 64 k-rows of 128 B
+constexpr int SMEM_DYN_BYTES = STAGES * STAGE_BYTES + 1024;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int RASTER_GROUP = 16;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+
+struct Region {
+  signed char a_map[kMaxSeg];
+  signed char b_map[kMaxSeg];
+  int m_tiles;
+  int n_tiles;
+  int tile_begin;
+  int bn;
+  int rows;
+  int cols;
+  void* out;
+  long long ld;
+  int mode;
+  float alpha;
+};
+
+struct GemmParams {
+  alignas(64) CUtensorMap maps[kMaxMaps];
+  Region reg[kMaxRegion];
+  int seg_k[kMaxSeg];
+  int nseg;
+  int nregion;
+  int total_tiles;
+  int mn_lbo;   // descriptor offsets of MN-major operand tiles (bytes)
+  int mn_sbo;
+};
+
+struct TileInfo {
+  int r;
+  int m0;
+  int n0;
+};
+
+__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int t) {
+  int r = 0;
+  while (r + 1 < p.nregion && t >= p.reg[r + 1].tile_begin) ++r;
+  const Region& R = p.reg[r];
+  const int lt = t - R.tile_begin;
+  const int per_group = RASTER_GROUP * R.n_tiles;
+  const int g = lt / per_group;
+  const int first_m = g * RASTER_GROUP;
+  const int gsz = min(R.m_tiles - first_m, RASTER_GROUP);
+  const int rem = lt - g * per_group;
+  const int mt = first_m + rem % gsz;
+  const int nt = rem / gsz;
+  return {r, mt * BM, nt * R.bn};
+}
+
+__device__ __forceinline__ void record_timeout(int role, int tile) {
+  if (atomicCAS(&g_wsl_status[0], 0, WSL_ERR_TIMEOUT) == 0) {
+    g_wsl_status[1] = role;
+    g_wsl_status[2] = static_cast<int>(blockIdx.x);
+    g_wsl_status[3] = tile;
+  }
+}
+
+template <int NV>
+__device__ __forceinline__ void epilogue_store(const Region& R, int row, int col0,
+                                               const uint32_t (&v)[NV]) {
+  if (row >= R.rows) return;
+  const float alpha = R.alpha;
+  if (R.mode == kEpiStoreBf16) {
+    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(R.out) + static_cast<long long>(row) * R.ld + col0;
+#pragma unroll
+    for (int j = 0; j < NV; j += 8) {
+      if (col0 + j < R.cols) {
+        uint4 pk;
+        uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float lo = alpha * __uint_as_float(v[j + 2 * e]);
+          const float hi = alpha * __uint_as_float(v[j + 2 * e + 1]);
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(lo, hi);
+          w[e] = *reinterpret_cast<uint32_t*>(&h2);
+        }
+        *reinterpret_cast<uint4*>(o + j) = pk;
+      }
+    }
+  } else {
+    float* o = static_cast<float*>(R.out) + static_cast<long long>(row) * R.ld + col0;
+    const bool acc = (R.mode == kEpiAccumF32);
+#pragma unroll
+    for (int j = 0; j < NV; j += 4) {
+      if (col0 + j < R.cols) {
+        float4 f;
+        f.x = alpha * __uint_as_float(v[j]);
+        f.y = alpha * __uint_as_float(v[j + 1]);
+        f.z = alpha * __uint_as_float(v[j + 2]);
+        f.w = alpha * __uint_as_float(v[j + 3]);
+        float4* dst = reinterpret_cast<float4*>(o + j);
+        if (acc) {
+          const float4 old = *dst;
+          f.x += old.x;
+          f.y += old.y;
+          f.z += old.z;
+          f.w += old.w;
+        }
+        *dst = f;
+      }
+    }
+  }
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+block_gemm_kernel(const __grid_constant__ GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_dyn[];
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+  volatile int* abortp = &abort_flag;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);
+    }
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_smem), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_base_smem);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int i = 0; i < p.nregion * p.nseg * 2 && i < kMaxMaps; ++i) tma_prefetch_desc(&p.maps[i]);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+        const TileInfo ti = decode_tile(p, t);
+        const Region& R = p.reg[ti.r];
+        const int b_slabs = (R.bn + 63) >> 6;
+        const uint32_t tx = A_STAGE_BYTES + (B_MN ? b_slabs * SLAB_BYTES : R.bn * BK * 2);
+        for (int sg = 0; ok && sg < p.nseg; ++sg) {
+          const CUtensorMap* ma = &p.maps[R.a_map[sg]];
+          const CUtensorMap* mb = &p.maps[R.b_map[sg]];
+          const int klen = p.seg_k[sg];
+          for (int kk = 0; kk < klen; kk += BK) {
+            if (!mbar_wait(empty_bar(s), ph ^ 1u, abortp, WAIT_LIMIT_NS)) {
+              record_timeout(1, t);
+              ok = false;
+              break;
+            }
+            const uint32_t fb = full_bar(s);
+            mbar_arrive_expect_tx(fb, tx);
+            const uint32_t sa = smem_base + s * STAGE_BYTES;
+            const uint32_t sb = sa + A_STAGE_BYTES;
+            if (A_MN) {
+              tma_load_2d(sa, ma, fb, ti.m0, kk);
+              tma_load_2d(sa + SLAB_BYTES, ma, fb, ti.m0 + 64, kk);
+            } else {
+              tma_load_2d(sa, ma, fb, kk, ti.m0);
+            }
+            if (B_MN) {
+              for (int j = 0; j < b_slabs; ++j)
+                tma_load_2d(sb + j * SLAB_BYTES, mb, fb, ti.n0 + 64 * j, kk);
+            } else {
+              tma_load_2d(sb, mb, fb, kk, ti.n0);
+            }
+            if (++s == STAGES) {
+              s = 0;
+              ph ^= 1u;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x, ++it) {
+        const TileInfo ti = decode_tile(p, t);
+        const Region& R = p.reg[ti.r];
+        const uint32_t idesc = umma_idesc_bf16(BM, R.bn, A_MN ? 1 : 0, B_MN ? 1 : 0);
+        const int buf = it & 1;
+        const uint32_t tph = (static_cast<uint32_t>(it) >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(buf), tph ^ 1u, abortp, WAIT_LIMIT_NS)) {
+          record_timeout(2, t);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN_MAX);
+        uint32_t accumulate = 0;
+        for (int sg = 0; ok && sg < p.nseg; ++sg) {
+          const int klen = p.seg_k[sg];
+          for (int kk = 0; kk < klen; kk += BK) {
+            if (!mbar_wait(full_bar(s), ph, abortp, WAIT_LIMIT_NS)) {
+              record_timeout(2, t);
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const int kvalid = min(BK, klen - kk);
+            const int nk = (kvalid + 15) >> 4;
+            const uint32_t sa = smem_base + s * STAGE_BYTES;
+            const uint32_t sb = sa + A_STAGE_BYTES;
+            for (int k = 0; k < nk; ++k) {
+              // K-major: 16 bf16 = 32 B further along the 128-B swizzled row.
+              // MN-major: 16 k-rows of 128 B further; slabs of 64 MN elements are
+              // SLAB_BYTES apart (leading offset), 8-row groups 1024 B (stride offset).
+              const uint64_t adesc = A_MN ? smem_desc_sw128(sa + k * 2048, p.mn_lbo, p.mn_sbo)
+                                          : smem_desc_sw128(sa + k * 32, 16, 1024);
+              const uint64_t bdesc = B_MN ? smem_desc_sw128(sb + k * 2048, p.mn_lbo, p.mn_sbo)
+                                          : smem_desc_sw128(sb + k * 32, 16, 1024);
+              umma_bf16(d_tmem, adesc, bdesc, idesc, accumulate);
+              accumulate = 1;
+            }
+            umma_commit(empty_bar(s));
+            if (++s == STAGES) {
+              s = 0;
+              ph ^= 1u;
+            }
+          }
+        }
+        if (ok) umma_commit(tfull_bar(buf));
+      }
+    }
+  } else {
+    // --------------------------------------------------------------- epilogue
+    const int q = warp & 3;   // TMEM lane quarter this warp may read
+    int it = 0;
+    for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++it) {
+      const TileInfo ti = decode_tile(p, t);
+      const Region& R = p.reg[ti.r];
+      const int buf = it & 1;
+      const uint32_t tph = (static_cast<uint32_t>(it) >> 1) & 1u;
+      bool ok = mbar_wait(tfull_bar(buf), tph, abortp, WAIT_LIMIT_NS);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) record_timeout(3, t);
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = ti.m0 + q * 32 + lane;
+      const uint32_t taddr =
+          tmem_base + static_cast<uint32_t>(buf * BN_MAX) + (static_cast<uint32_t>(q * 32) << 16);
+      for (int c = 0; c < R.bn; c += 32) {
+        if (R.bn - c >= 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+          epilogue_store<32>(R, row, ti.n0 + c, v);
+        } else {
+          uint32_t v[16];
+          tmem_ld_32x16(taddr + c, v);
+          tmem_ld_wait();
+          epilogue_store<16>(R, row, ti.n0 + c, v);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(buf));
+    }
+  }
+
+  // ---------------------------------------------------------------- tear-down
+  if (*abortp != 0) {
+    // Give TMA copies that are still in flight time to land before the CTA's
+    // shared memory is released.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ============================================================== host side
+unsigned long long g_launch_count = 0;
+
+static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+static int g_num_sms = 0;
+static int g_device_ok = 0;   // 0 unknown, 1 ok, -1 not sm_100 / no device
+
+static int ensure_device() {
+  if (g_device_ok != 0) return g_device_ok > 0 ? WSL_OK : WSL_ERR_DEVICE;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    g_device_ok = -1;
+    return WSL_ERR_DEVICE;
+  }
+  int major = 0, sms = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    cudaGetLastError();
+    g_device_ok = -1;
+    return WSL_ERR_DEVICE;
+  }
+  if (major != 10) {
+    g_device_ok = -1;
+    return WSL_ERR_DEVICE;
+  }
+  g_num_sms = sms;
+  g_device_ok = 1;
+  return WSL_OK;
+}
+
+int device_check() { return ensure_device(); }
+int device_sm_count() { return g_num_sms; }
+
+static int ensure_encode() {
+  if (g_encode) return WSL_OK;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000, cudaEnableDefault,
+                                       &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+    cudaGetLastError();
+    return WSL_ERR_DRIVER;
+  }
+  g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  return WSL_OK;
+}
+
+// Tensor map over a row-major bf16 matrix [rows, cols] (pitch ld elements) with a
+// box of box_cols (<= 64) x box_rows, 128-byte swizzle, zero fill outside.
+static int make_map_bf16(CUtensorMap* m, const Mat& t, int box_cols, int box_rows) {
+  if (t.ptr == nullptr || t.rows <= 0 || t.cols <= 0) return WSL_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(t.ptr) & 15u) != 0 || (t.ld % 8) != 0 || t.ld < t.cols)
+    return WSL_ERR_ALIGN;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(t.cols), static_cast<cuuint64_t>(t.rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(t.ld) * 2u};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(t.ptr), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? WSL_OK : WSL_ERR_DRIVER;
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_variant(const GemmParams& p, int grid, cudaStream_t stream) {
+  static bool attr_set = false;   // per instantiation
+  auto kern = block_gemm_kernel<A_MN, B_MN>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN_BYTES) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return WSL_ERR_CUDA;
+    }
+    attr_set = true;
+  }
+  kern<<<grid, NUM_THREADS, SMEM_DYN_BYTES, stream>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
+  ++g_launch_count;
+  return WSL_OK;
+}
+
+int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
+  int st = ensure_device();
+  if (st != WSL_OK) return st;
+  st = ensure_encode();
+  if (st != WSL_OK) return st;
+  if (g.nseg < 1 || g.nseg > kMaxSeg || g.nregion < 1 || g.nregion > kMaxRegion)
+    return WSL_ERR_BAD_ARG;
+  if (g.nseg * g.nregion * 2 > kMaxMaps) return WSL_ERR_BAD_ARG;
+
+  GemmParams p;
+  p.nseg = g.nseg;
+  p.nregion = g.nregion;
+  for (int s = 0; s < kMaxSeg; ++s) p.seg_k[s] = s < g.nseg ? g.seg_k[s] : 0;
+  for (int s = 0; s < g.nseg; ++s)
+    if (g.seg_k[s] <= 0) return WSL_ERR_BAD_ARG;
+
+  int nmaps = 0;
+  long long tiles = 0;
+  for (int r = 0; r < g.nregion; ++r) {
+    const RegionDesc& rd = g.region[r];
+    Region& R = p.reg[r];
+    if (rd.mo <= 0 || rd.no <= 0 || rd.out == nullptr) return WSL_ERR_BAD_ARG;
+    const int vec = rd.mode == kEpiStoreBf16 ? 8 : 4;
+    if ((rd.no % vec) != 0 || (rd.ld_out % vec) != 0 || rd.ld_out < rd.no ||
+        (reinterpret_cast<uintptr_t>(rd.out) & 15u) != 0)
+      return WSL_ERR_ALIGN;
+    const long long n_tiles = (rd.no + BN_MAX - 1) / BN_MAX;
+    long long bn = (rd.no + n_tiles - 1) / n_tiles;
+    bn = (bn + 15) / 16 * 16;
+    const long long m_tiles = (rd.mo + BM - 1) / BM;
+    if (m_tiles * n_tiles + tiles > 0x7fffffffLL) return WSL_ERR_TOO_LARGE;
+    R.m_tiles = static_cast<int>(m_tiles);
+    R.n_tiles = static_cast<int>(n_tiles);
+    R.tile_begin = static_cast<int>(tiles);
+    R.bn = static_cast<int>(bn);
+    R.rows = static_cast<int>(rd.mo);
+    R.cols = static_cast<int>(rd.no);
+    R.out = rd.out;
+    R.ld = rd.ld_out;
+    R.mode = rd.mode;
+    R.alpha = rd.alpha;
+    tiles += m_tiles * n_tiles;
+    for (int s = 0; s < kMaxSeg; ++s) {
+      R.a_map[s] = 0;
+      R.b_map[s] = 0;
+    }
+    for (int s = 0; s < g.nseg; ++s) {
+      const Mat& a = rd.a[s];
+      const Mat& b = rd.b[s];
+      // Shape checks: K-major operand is [mo|no, k]; MN-major operand is [k, mo|no].
+      if (g.a_mn ? (a.rows != g.seg_k[s] || a.cols != rd.mo) : (a.rows != rd.mo || a.cols != g.seg_k[s]))
+        return WSL_ERR_BAD_ARG;
+      if (g.b_mn ? (b.rows != g.seg_k[s] || b.cols != rd.no) : (b.rows != rd.no || b.cols != g.seg_k[s]))
+        return WSL_ERR_BAD_ARG;
+      st = g.a_mn ? make_map_bf16(&p.maps[nmaps], a, 64, BK) : make_map_bf16(&p.maps[nmaps], a, BK, BM);
+      if (st != WSL_OK) return st;
+      R.a_map[s] = static_cast<signed char>(nmaps++);
+      st = g.b_mn ? make_map_bf16(&p.maps[nmaps], b, 64, BK)
+                  : make_map_bf16(&p.maps[nmaps], b, BK, static_cast<int>(bn));
+      if (st != WSL_OK) return st;
+      R.b_map[s] = static_cast<signed char>(nmaps++);
+    }
+  }
+  p.total_tiles = static_cast<int>(tiles);
+  p.mn_lbo = SLAB_BYTES;
+  p.mn_sbo = 1024;
+  if (const char* e = getenv("WSL_DBG_MN_SWAP")) {
+    if (e[0] == '1') {
+      p.mn_lbo = 1024;
+      p.mn_sbo = SLAB_BYTES;
+    }
+  }
+  const int grid = static_cast<int>(tiles < g_num_sms ? tiles : g_num_sms);
+
+  if (g.a_mn && g.b_mn) return launch_variant<true, true>(p, grid, stream);
+  if (!g.a_mn && g.b_mn) return launch_variant<false, true>(p, grid, stream);
+  if (!g.a_mn && !g.b_mn) return launch_variant<false, false>(p, grid, stream);
+  return launch_variant<true, false>(p, grid, stream);
+}
+
+}  // namespace wsl

@@ -1,0 +1,58 @@
+// Host-side description of one launch of the tcgen05 block GEMM
+// (see block_gemm.cu). Internal to the library: the C-ABI in include/wsl.h is
+// the public surface.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace wsl {
+
+constexpr int kMaxMaps = 16;    // tensor maps carried in the kernel parameters
+constexpr int kMaxSeg = 6;      // contraction segments (K-concatenation)
+constexpr int kMaxRegion = 3;   // output regions sharing one launch
+
+enum EpilogueMode : int {
+  kEpiStoreBf16 = 0,   // out(bf16)  = alpha * acc
+  kEpiStoreF32 = 1,    // out(fp32)  = alpha * acc
+  kEpiAccumF32 = 2,    // out(fp32) += alpha * acc   (tiles own their outputs: plain RMW)
+};
+
+// A row-major bf16 matrix in device memory: `rows` x `cols`, row pitch `ld` elements.
+struct Mat {
+  const void* ptr;
+  long long rows;
+  long long cols;
+  long long ld;
+};
+
+// One output region: out[mo, no] (op)= alpha * sum_seg A_seg * B_seg^T.
+// With K-major operands A_seg is stored [mo, k_seg] and B_seg [no, k_seg];
+// with MN-major operands A_seg is stored [k_seg, mo] and B_seg [k_seg, no].
+struct RegionDesc {
+  Mat a[kMaxSeg];
+  Mat b[kMaxSeg];
+  long long mo;
+  long long no;
+  void* out;
+  long long ld_out;
+  int mode;
+  float alpha;
+};
+
+struct GemmDesc {
+  bool a_mn;   // A operands are MN-major (contraction index is the slow one in memory)
+  bool b_mn;
+  int nseg;
+  int seg_k[kMaxSeg];   // contraction length of each segment (same for all regions)
+  int nregion;
+  RegionDesc region[kMaxRegion];
+};
+
+// Enqueues the GEMM on `stream`. Returns a WSL_* status code (include/wsl.h).
+int launch_block_gemm(const GemmDesc& g, cudaStream_t stream);
+
+// Number of kernel launches this library has enqueued since load (all kernels).
+extern unsigned long long g_launch_count;
+
+}  // namespace wsl

@@ -1,0 +1,318 @@
+// The extern "C" surface declared in include/wsl.h. This file is the single
+// translation unit of libwsl.so: it pulls in the kernel sources so that the
+// device-side status words are one definition without relocatable device code.
+#include "block_gemm.cu"
+#include "simt_gemm.cu"
+#include "embed.cu"
+
+namespace wsl {
+int launch_simt_gemm_f32(const float* A, long long sai, long long sak, const float* B,
+                         long long sbj, long long sbk, float* C, long long ldc, long long M,
+                         long long N, long long K, float alpha, int accumulate,
+                         cudaStream_t stream);
+
+static inline Mat mat(const void* p, long long rows, long long cols, long long ld) {
+  Mat m;
+  m.ptr = p;
+  m.rows = rows;
+  m.cols = cols;
+  m.ld = ld;
+  return m;
+}
+static inline bool bad_dtype(int dtype) { return dtype != WSL_BF16 && dtype != WSL_F32; }
+static inline const float* f32(const void* p) { return static_cast<const float*>(p); }
+}  // namespace wsl
+
+using namespace wsl;
+
+extern "C" {
+
+int wsl_version(void) { return (0 << 16) | 3; }
+
+const char* wsl_status_string(int status) {
+  switch (status) {
+    case WSL_OK: return "ok";
+    case WSL_ERR_BAD_ARG: return "bad argument (null pointer, non-positive or inconsistent size)";
+    case WSL_ERR_ALIGN: return "pointer or pitch violates the 16-byte alignment rule";
+    case WSL_ERR_DEVICE: return "no CUDA device or current device is not sm_100";
+    case WSL_ERR_CUDA: return "CUDA runtime call or kernel launch failed";
+    case WSL_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case WSL_ERR_DRIVER: return "cuTensorMapEncodeTiled unavailable or rejected the tensor";
+    case WSL_ERR_TOO_LARGE: return "size beyond a fixed limit of the library";
+    default: return "unknown status";
+  }
+}
+
+unsigned long long wsl_launch_count(void) { return g_launch_count; }
+
+int wsl_poll_status(int words[4]) {
+  int st = device_check();
+  if (st != WSL_OK) return st;
+  int w[4] = {0, 0, 0, 0};
+  if (cudaMemcpyFromSymbol(w, g_wsl_status, sizeof(w)) != cudaSuccess) {
+    cudaGetLastError();
+    return WSL_ERR_CUDA;
+  }
+  if (words)
+    for (int i = 0; i < 4; ++i) words[i] = w[i];
+  return w[0];
+}
+
+int wsl_reset_status(void) {
+  int st = device_check();
+  if (st != WSL_OK) return st;
+  const int w[4] = {0, 0, 0, 0};
+  if (cudaMemcpyToSymbol(g_wsl_status, w, sizeof(w)) != cudaSuccess) {
+    cudaGetLastError();
+    return WSL_ERR_CUDA;
+  }
+  return WSL_OK;
+}
+
+int wsl_linear_fwd(const void* x, long long ldx, const void* W, void* y, long long ldy,
+                   long long M, long long N, long long K, int out_f32, int dtype, void* stream) {
+  if (bad_dtype(dtype) || !x || !W || !y || M <= 0 || N <= 0 || K <= 0) return WSL_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == WSL_F32)
+    return launch_simt_gemm_f32(f32(x), ldx, 1, f32(W), K, 1, static_cast<float*>(y), ldy, M, N, K,
+                                1.f, 0, s);
+  GemmDesc g = {};
+  g.a_mn = false;
+  g.b_mn = false;
+  g.nseg = 1;
+  g.seg_k[0] = static_cast<int>(K);
+  g.nregion = 1;
+  RegionDesc& r0 = g.region[0];
+  r0.a[0] = mat(x, M, K, ldx);
+  r0.b[0] = mat(W, N, K, K);
+  r0.mo = M;
+  r0.no = N;
+  r0.out = y;
+  r0.ld_out = ldy;
+  r0.mode = out_f32 ? kEpiStoreF32 : kEpiStoreBf16;
+  r0.alpha = 1.f;
+  return launch_block_gemm(g, s);
+}
+
+int wsl_lora_prepass(const void* x, long long ldx, const void* A_cat, void* T, long long ldt,
+                     long long M, long long K, long long r_tot, float sc, int dtype,
+                     void* stream) {
+  if (bad_dtype(dtype) || !x || !A_cat || !T || M <= 0 || K <= 0 || r_tot <= 0)
+    return WSL_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == WSL_F32)
+    return launch_simt_gemm_f32(f32(x), ldx, 1, f32(A_cat), K, 1, static_cast<float*>(T), ldt, M,
+                                r_tot, K, sc, 0, s);
+  GemmDesc g = {};
+  g.nseg = 1;
+  g.seg_k[0] = static_cast<int>(K);
+  g.nregion = 1;
+  RegionDesc& r0 = g.region[0];
+  r0.a[0] = mat(x, M, K, ldx);
+  r0.b[0] = mat(A_cat, r_tot, K, K);
+  r0.mo = M;
+  r0.no = r_tot;
+  r0.out = T;
+  r0.ld_out = ldt;
+  r0.mode = kEpiStoreBf16;
+  r0.alpha = sc;
+  return launch_block_gemm(g, s);
+}
+
+int wsl_lora_linear_fwd(const void* x, long long ldx, const void* W, const void* T,
+                        long long ldt, const void* B, void* y, long long ldy, long long M,
+                        long long N, long long K, long long r, int dtype, void* stream) {
+  if (bad_dtype(dtype) || !x || !W || !y || M <= 0 || N <= 0 || K <= 0 || r < 0)
+    return WSL_ERR_BAD_ARG;
+  if (r > 0 && (!T || !B)) return WSL_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == WSL_F32) {
+    int st = launch_simt_gemm_f32(f32(x), ldx, 1, f32(W), K, 1, static_cast<float*>(y), ldy, M, N,
+                                  K, 1.f, 0, s);
+    if (st != WSL_OK || r == 0) return st;
+    return launch_simt_gemm_f32(f32(T), ldt, 1, f32(B), r, 1, static_cast<float*>(y), ldy, M, N, r,
+                                1.f, 1, s);
+  }
+  GemmDesc g = {};
+  g.nseg = r > 0 ? 2 : 1;
+  g.seg_k[0] = static_cast<int>(K);
+  g.seg_k[1] = static_cast<int>(r);
+  g.nregion = 1;
+  RegionDesc& r0 = g.region[0];
+  r0.a[0] = mat(x, M, K, ldx);
+  r0.b[0] = mat(W, N, K, K);
+  if (r > 0) {
+    r0.a[1] = mat(T, M, r, ldt);
+    r0.b[1] = mat(B, N, r, r);
+  }
+  r0.mo = M;
+  r0.no = N;
+  r0.out = y;
+  r0.ld_out = ldy;
+  r0.mode = kEpiStoreBf16;
+  r0.alpha = 1.f;
+  return launch_block_gemm(g, s);
+}
+
+int wsl_lora_bwd_prepass(const void* dY, long long lddy, const void* B, void* U, long long ldu,
+                         long long M, long long N, long long r, float sc, int dtype,
+                         void* stream) {
+  if (bad_dtype(dtype) || !dY || !B || !U || M <= 0 || N <= 0 || r <= 0) return WSL_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == WSL_F32)   // U[m,j] = s * sum_n dY[m,n] * B[n,j]
+    return launch_simt_gemm_f32(f32(dY), lddy, 1, f32(B), 1, r, static_cast<float*>(U), ldu, M, r,
+                                N, sc, 0, s);
+  GemmDesc g = {};
+  g.a_mn = false;
+  g.b_mn = true;
+  g.nseg = 1;
+  g.seg_k[0] = static_cast<int>(N);
+  g.nregion = 1;
+  RegionDesc& r0 = g.region[0];
+  r0.a[0] = mat(dY, M, N, lddy);
+  r0.b[0] = mat(B, N, r, r);
+  r0.mo = M;
+  r0.no = r;
+  r0.out = U;
+  r0.ld_out = ldu;
+  r0.mode = kEpiStoreBf16;
+  r0.alpha = sc;
+  return launch_block_gemm(g, s);
+}
+
+int wsl_lora_linear_bwd_dx(int nproj, const void* const* dY, const long long* lddy,
+                           const void* const* U, const long long* ldu, const void* const* W,
+                           const void* const* A, const long long* N, const long long* r, void* dX,
+                           long long lddx, long long M, long long K, int dtype, void* stream) {
+  if (bad_dtype(dtype) || nproj < 1 || nproj > WSL_MAX_PROJ || !dY || !lddy || !W || !N || !r ||
+      !dX || M <= 0 || K <= 0)
+    return WSL_ERR_BAD_ARG;
+  for (int p = 0; p < nproj; ++p) {
+    if (!dY[p] || !W[p] || N[p] <= 0 || r[p] < 0) return WSL_ERR_BAD_ARG;
+    if (r[p] > 0 && (!U || !ldu || !A || !U[p] || !A[p])) return WSL_ERR_BAD_ARG;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == WSL_F32) {
+    int acc = 0;
+    for (int p = 0; p < nproj; ++p) {
+      // dX[m,k] += sum_n dY[m,n] * W[n,k]
+      int st = launch_simt_gemm_f32(f32(dY[p]), lddy[p], 1, f32(W[p]), 1, K,
+                                    static_cast<float*>(dX), lddx, M, K, N[p], 1.f, acc, s);
+      if (st != WSL_OK) return st;
+      acc = 1;
+      if (r[p] > 0) {
+        st = launch_simt_gemm_f32(f32(U[p]), ldu[p], 1, f32(A[p]), 1, K, static_cast<float*>(dX),
+                                  lddx, M, K, r[p], 1.f, 1, s);
+        if (st != WSL_OK) return st;
+      }
+    }
+    return WSL_OK;
+  }
+  GemmDesc g = {};
+  g.a_mn = false;
+  g.b_mn = true;
+  g.nregion = 1;
+  RegionDesc& r0 = g.region[0];
+  int ns = 0;
+  for (int p = 0; p < nproj; ++p) {
+    g.seg_k[ns] = static_cast<int>(N[p]);
+    r0.a[ns] = mat(dY[p], M, N[p], lddy[p]);
+    r0.b[ns] = mat(W[p], N[p], K, K);
+    ++ns;
+    if (r[p] > 0) {
+      g.seg_k[ns] = static_cast<int>(r[p]);
+      r0.a[ns] = mat(U[p], M, r[p], ldu[p]);
+      r0.b[ns] = mat(A[p], r[p], K, K);
+      ++ns;
+    }
+  }
+  g.nseg = ns;
+  r0.mo = M;
+  r0.no = K;
+  r0.out = dX;
+  r0.ld_out = lddx;
+  r0.mode = kEpiStoreBf16;
+  r0.alpha = 1.f;
+  return launch_block_gemm(g, s);
+}
+
+int wsl_lora_linear_bwd_dw(const void* dY, long long lddy, const void* U, long long ldu,
+                           const void* x, long long ldx, const void* T, long long ldt, float* dW,
+                           float* dA, float* dB, long long M, long long N, long long K,
+                           long long r, int dtype, void* stream) {
+  if (bad_dtype(dtype) || M <= 0 || N <= 0 || K <= 0 || r < 0) return WSL_ERR_BAD_ARG;
+  if (r == 0 && (dA || dB)) return WSL_ERR_BAD_ARG;
+  if (!dW && !dA && !dB) return WSL_ERR_BAD_ARG;
+  if ((dW || dB) && !dY) return WSL_ERR_BAD_ARG;
+  if ((dW || dA) && !x) return WSL_ERR_BAD_ARG;
+  if (dA && !U) return WSL_ERR_BAD_ARG;
+  if (dB && !T) return WSL_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == WSL_F32) {
+    int st = WSL_OK;
+    if (dW)   // dW[n,k] += sum_m dY[m,n] * x[m,k]
+      st = launch_simt_gemm_f32(f32(dY), 1, lddy, f32(x), 1, ldx, dW, K, N, K, M, 1.f, 1, s);
+    if (st == WSL_OK && dB)
+      st = launch_simt_gemm_f32(f32(dY), 1, lddy, f32(T), 1, ldt, dB, r, N, r, M, 1.f, 1, s);
+    if (st == WSL_OK && dA)
+      st = launch_simt_gemm_f32(f32(U), 1, ldu, f32(x), 1, ldx, dA, K, r, K, M, 1.f, 1, s);
+    return st;
+  }
+  GemmDesc g = {};
+  g.a_mn = true;
+  g.b_mn = true;
+  g.nseg = 1;
+  g.seg_k[0] = static_cast<int>(M);
+  int nr = 0;
+  if (dW) {
+    RegionDesc& rd = g.region[nr++];
+    rd.a[0] = mat(dY, M, N, lddy);
+    rd.b[0] = mat(x, M, K, ldx);
+    rd.mo = N;
+    rd.no = K;
+    rd.out = dW;
+    rd.ld_out = K;
+    rd.mode = kEpiAccumF32;
+    rd.alpha = 1.f;
+  }
+  if (dB) {
+    RegionDesc& rd = g.region[nr++];
+    rd.a[0] = mat(dY, M, N, lddy);
+    rd.b[0] = mat(T, M, r, ldt);
+    rd.mo = N;
+    rd.no = r;
+    rd.out = dB;
+    rd.ld_out = r;
+    rd.mode = kEpiAccumF32;
+    rd.alpha = 1.f;
+  }
+  if (dA) {
+    RegionDesc& rd = g.region[nr++];
+    rd.a[0] = mat(U, M, r, ldu);
+    rd.b[0] = mat(x, M, K, ldx);
+    rd.mo = r;
+    rd.no = K;
+    rd.out = dA;
+    rd.ld_out = K;
+    rd.mode = kEpiAccumF32;
+    rd.alpha = 1.f;
+  }
+  g.nregion = nr;
+  return launch_block_gemm(g, s);
+}
+
+int wsl_embed_gather(const long long* tokens, const void* E_small, void* G, long long M,
+                     long long V, long long r_e, int dtype, void* stream) {
+  if (bad_dtype(dtype)) return WSL_ERR_BAD_ARG;
+  return launch_embed_gather(tokens, E_small, G, M, V, r_e, dtype == WSL_F32 ? 4 : 2,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int wsl_embed_scatter_add(const long long* tokens, const void* dG, float* dE, long long M,
+                          long long V, long long r_e, int dtype, void* stream) {
+  if (bad_dtype(dtype)) return WSL_ERR_BAD_ARG;
+  return launch_embed_scatter_add(tokens, dG, dE, M, V, r_e, dtype == WSL_F32 ? 1 : 0,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

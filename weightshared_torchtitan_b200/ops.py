@@ -1,0 +1,222 @@
+"""Tensor-level wrappers of the C ABI (include/wsl.h).
+
+PyTorch is plumbing here: it owns device memory and the current stream; every function
+below extracts raw pointers, pitches and the stream handle and calls straight into
+libwsl.so. All launches go on ``torch.cuda.current_stream()``; nothing synchronises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import WSL_BF16, WSL_F32
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return WSL_BF16
+    if t.dtype == torch.float32:
+        return WSL_F32
+    raise TypeError(f"wsl kernels take bfloat16 or float32 tensors, got {t.dtype}")
+
+
+def _mat(t: torch.Tensor, name: str) -> torch.Tensor:
+    """A 2-D CUDA matrix whose last dimension is contiguous (row pitch may exceed width)."""
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: the wsl path has no CPU implementation")
+    if t.dim() != 2:
+        raise ValueError(f"{name} must be 2-D, got shape {tuple(t.shape)}")
+    if t.shape[1] > 1 and t.stride(1) != 1:
+        t = t.contiguous()
+    elif t.shape[0] > 1 and t.stride(0) < t.shape[1]:
+        t = t.contiguous()
+    return t
+
+
+def _ld(t: torch.Tensor) -> int:
+    return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _same(code: int, *ts: torch.Tensor) -> None:
+    for t in ts:
+        if _dtype_code(t) != code:
+            raise TypeError("all matrices of one wsl call must share a dtype")
+
+
+def linear_fwd(x: torch.Tensor, W: torch.Tensor, out_f32: bool = False) -> torch.Tensor:
+    """y = x @ W.T (wsl_linear_fwd)."""
+    x, W = _mat(x, "x"), _mat(W, "W").contiguous()
+    code = _dtype_code(x)
+    _same(code, W)
+    M, K = x.shape
+    N = W.shape[0]
+    if W.shape[1] != K:
+        raise ValueError("W must be [N, K]")
+    y = torch.empty((M, N), device=x.device,
+                    dtype=torch.float32 if (out_f32 or code == WSL_F32) else torch.bfloat16)
+    st = _lib.lib().wsl_linear_fwd(x.data_ptr(), _ld(x), W.data_ptr(), y.data_ptr(), N, M, N, K,
+                                   int(bool(out_f32)), code, _stream())
+    _lib.check(st, "wsl_linear_fwd")
+    return y
+
+
+def lora_prepass(x: torch.Tensor, A_cat: torch.Tensor, s: float) -> torch.Tensor:
+    """T = s * x @ A_cat.T (wsl_lora_prepass)."""
+    x, A_cat = _mat(x, "x"), _mat(A_cat, "A_cat").contiguous()
+    code = _dtype_code(x)
+    _same(code, A_cat)
+    M, K = x.shape
+    r_tot = A_cat.shape[0]
+    if A_cat.shape[1] != K:
+        raise ValueError("A_cat must be [r_tot, K]")
+    T = torch.empty((M, r_tot), device=x.device, dtype=x.dtype)
+    st = _lib.lib().wsl_lora_prepass(x.data_ptr(), _ld(x), A_cat.data_ptr(), T.data_ptr(), r_tot,
+                                     M, K, r_tot, float(s), code, _stream())
+    _lib.check(st, "wsl_lora_prepass")
+    return T
+
+
+def lora_linear_fwd(x: torch.Tensor, W: torch.Tensor, T: Optional[torch.Tensor],
+                    B: Optional[torch.Tensor]) -> torch.Tensor:
+    """y = x @ W.T + T @ B.T with T the scaled pre-pass output (wsl_lora_linear_fwd)."""
+    x, W = _mat(x, "x"), _mat(W, "W").contiguous()
+    code = _dtype_code(x)
+    _same(code, W)
+    M, K = x.shape
+    N = W.shape[0]
+    r = 0
+    tp = bp = None
+    ldt = 0
+    if T is not None:
+        T, B = _mat(T, "T"), _mat(B, "B").contiguous()
+        _same(code, T, B)
+        r = B.shape[1]
+        if T.shape != (M, r) or B.shape[0] != N:
+            raise ValueError("T must be [M, r] and B [N, r]")
+        tp, bp, ldt = T.data_ptr(), B.data_ptr(), _ld(T)
+    y = torch.empty((M, N), device=x.device, dtype=x.dtype)
+    st = _lib.lib().wsl_lora_linear_fwd(x.data_ptr(), _ld(x), W.data_ptr(), tp, ldt, bp,
+                                        y.data_ptr(), N, M, N, K, r, code, _stream())
+    _lib.check(st, "wsl_lora_linear_fwd")
+    return y
+
+
+def lora_bwd_prepass(dY: torch.Tensor, B: torch.Tensor, s: float) -> torch.Tensor:
+    """U = s * dY @ B (wsl_lora_bwd_prepass)."""
+    dY, B = _mat(dY, "dY"), _mat(B, "B").contiguous()
+    code = _dtype_code(dY)
+    _same(code, B)
+    M, N = dY.shape
+    r = B.shape[1]
+    if B.shape[0] != N:
+        raise ValueError("B must be [N, r]")
+    U = torch.empty((M, r), device=dY.device, dtype=dY.dtype)
+    st = _lib.lib().wsl_lora_bwd_prepass(dY.data_ptr(), _ld(dY), B.data_ptr(), U.data_ptr(), r,
+                                         M, N, r, float(s), code, _stream())
+    _lib.check(st, "wsl_lora_bwd_prepass")
+    return U
+
+
+def lora_linear_bwd_dx(dYs: Sequence[torch.Tensor], Us: Sequence[Optional[torch.Tensor]],
+                       Ws: Sequence[torch.Tensor], As: Sequence[Optional[torch.Tensor]]) -> torch.Tensor:
+    """dX = sum_p dY_p @ W_p + U_p @ A_p for projections that read the same x."""
+    n = len(dYs)
+    dYs = [_mat(t, "dY") for t in dYs]
+    Ws = [_mat(t, "W").contiguous() for t in Ws]
+    code = _dtype_code(dYs[0])
+    M = dYs[0].shape[0]
+    K = Ws[0].shape[1]
+    keep = []
+    vp = ctypes.c_void_p * n
+    ll = ctypes.c_longlong * n
+    dy_p, u_p, w_p, a_p = vp(), vp(), vp(), vp()
+    lddy, ldu, Ns, rs = ll(), ll(), ll(), ll()
+    for p in range(n):
+        _same(code, dYs[p], Ws[p])
+        if dYs[p].shape[0] != M or Ws[p].shape != (dYs[p].shape[1], K):
+            raise ValueError("dY_p must be [M, N_p] and W_p [N_p, K]")
+        dy_p[p], lddy[p] = dYs[p].data_ptr(), _ld(dYs[p])
+        w_p[p], Ns[p] = Ws[p].data_ptr(), Ws[p].shape[0]
+        if Us[p] is not None:
+            U, A = _mat(Us[p], "U"), _mat(As[p], "A").contiguous()
+            _same(code, U, A)
+            if U.shape != (M, A.shape[0]) or A.shape[1] != K:
+                raise ValueError("U_p must be [M, r_p] and A_p [r_p, K]")
+            keep += [U, A]
+            u_p[p], ldu[p], a_p[p], rs[p] = U.data_ptr(), _ld(U), A.data_ptr(), A.shape[0]
+        else:
+            u_p[p], ldu[p], a_p[p], rs[p] = None, 0, None, 0
+    dX = torch.empty((M, K), device=dYs[0].device, dtype=dYs[0].dtype)
+    st = _lib.lib().wsl_lora_linear_bwd_dx(n, dy_p, lddy, u_p, ldu, w_p, a_p, Ns, rs, dX.data_ptr(),
+                                           K, M, K, code, _stream())
+    _lib.check(st, "wsl_lora_linear_bwd_dx")
+    return dX
+
+
+def lora_linear_bwd_dw(dY: torch.Tensor, U: Optional[torch.Tensor], x: torch.Tensor,
+                       T: Optional[torch.Tensor], dW: Optional[torch.Tensor],
+                       dA: Optional[torch.Tensor], dB: Optional[torch.Tensor]) -> None:
+    """dW += dY.T @ x, dA += U.T @ x, dB += dY.T @ T, in place into fp32 buffers."""
+    dY, x = _mat(dY, "dY"), _mat(x, "x")
+    code = _dtype_code(dY)
+    _same(code, x)
+    M, N = dY.shape
+    K = x.shape[1]
+    if x.shape[0] != M:
+        raise ValueError("x must be [M, K]")
+    r = 0
+    up = tp = None
+    ldu = ldt = 0
+    if U is not None:
+        U = _mat(U, "U")
+        _same(code, U)
+        r, up, ldu = U.shape[1], U.data_ptr(), _ld(U)
+    if T is not None:
+        T = _mat(T, "T")
+        _same(code, T)
+        r, tp, ldt = T.shape[1], T.data_ptr(), _ld(T)
+    for g, shape, nm in ((dW, (N, K), "dW"), (dA, (r, K), "dA"), (dB, (N, r), "dB")):
+        if g is not None:
+            if g.dtype != torch.float32 or not g.is_contiguous() or tuple(g.shape) != shape:
+                raise ValueError(f"{nm} must be a contiguous float32 tensor of shape {shape}")
+    st = _lib.lib().wsl_lora_linear_bwd_dw(
+        dY.data_ptr(), _ld(dY), up, ldu, x.data_ptr(), _ld(x), tp, ldt,
+        dW.data_ptr() if dW is not None else None,
+        dA.data_ptr() if dA is not None else None,
+        dB.data_ptr() if dB is not None else None,
+        M, N, K, r, code, _stream())
+    _lib.check(st, "wsl_lora_linear_bwd_dw")
+
+
+def embed_gather(tokens: torch.Tensor, E_small: torch.Tensor) -> torch.Tensor:
+    """G[m] = E_small[tokens[m]] (bit-exact row copy)."""
+    tok = tokens.reshape(-1)
+    if tok.dtype != torch.int64 or not tok.is_cuda:
+        raise TypeError("tokens must be a CUDA int64 tensor")
+    tok = tok.contiguous()
+    E = _mat(E_small, "E_small").contiguous()
+    V, r_e = E.shape
+    G = torch.empty((tok.numel(), r_e), device=E.device, dtype=E.dtype)
+    st = _lib.lib().wsl_embed_gather(tok.data_ptr(), E.data_ptr(), G.data_ptr(), tok.numel(), V, r_e,
+                                     _dtype_code(E), _stream())
+    _lib.check(st, "wsl_embed_gather")
+    return G
+
+
+def embed_scatter_add(tokens: torch.Tensor, dG: torch.Tensor, dE: torch.Tensor) -> None:
+    """dE[tokens[m]] += dG[m] into a contiguous fp32 [V, r_e] buffer."""
+    tok = tokens.reshape(-1).contiguous()
+    dG = _mat(dG, "dG").contiguous()
+    if dE.dtype != torch.float32 or not dE.is_contiguous():
+        raise ValueError("dE must be contiguous float32")
+    V, r_e = dE.shape
+    st = _lib.lib().wsl_embed_scatter_add(tok.data_ptr(), dG.data_ptr(), dE.data_ptr(), tok.numel(),
+                                          V, r_e, _dtype_code(dG), _stream())
+    _lib.check(st, "wsl_embed_scatter_add")
