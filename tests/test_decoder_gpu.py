@@ -1,0 +1,178 @@
+"""GPU tests of the module surface and of the weight-shared decoder around the kernels."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import lora_oracle as O
+from tests.test_oracle_golden import tiny_decoder_params
+
+pytestmark = pytest.mark.gpu
+
+
+def _t(a):
+    return torch.from_numpy(np.asarray(a))
+
+
+def rel(a, b):
+    return O.max_rel_err(a, b)
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _cuda():
+    if not torch.cuda.is_available():
+        pytest.fail("gpu tests need a CUDA device")
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    yield
+    from weightshared_torchtitan_b200 import _lib
+    torch.cuda.synchronize()
+    st, words = _lib.poll_status()
+    assert st == 0, (st, words)
+
+
+def test_lora_module_matches_reference_semantics():
+    """LoRAModule: same attributes and forward = s * B(A(x)) with s = alpha/rank = 2."""
+    from weightshared_torchtitan_b200.modules import LoRAModule
+    m = LoRAModule(256, 384, rank=16).cuda()
+    assert (m.in_dim, m.out_dim, m.rank, m.alpha, m.bias) == (256, 384, 16, 32, False)
+    assert [n for n, _ in m.named_parameters()] == ["w_a.weight", "w_b.weight"]
+    m.reset_parameters()
+    assert m.w_b.weight.abs().max().item() == 0.0
+    with torch.no_grad():
+        m.w_b.weight.normal_(0, 0.02)
+    x = torch.randn(3, 50, 256, device="cuda", requires_grad=True)
+    y = m(x)
+    y.backward(torch.ones_like(y))
+    xo = x.detach().cpu().requires_grad_(True)
+    A, B = m.w_a.weight.detach().cpu().requires_grad_(True), m.w_b.weight.detach().cpu().requires_grad_(True)
+    yo = O.lora_delta(xo, A, B)
+    yo.backward(torch.ones_like(yo))
+    assert rel(y, yo) < 1e-5 and rel(x.grad, xo.grad) < 1e-5
+    assert rel(m.w_a.weight.grad, A.grad) < 1e-5 and rel(m.w_b.weight.grad, B.grad) < 1e-5
+    # sharing an nn.Linear between adapters, as w_a_override does in the reference
+    m2 = LoRAModule(256, 384, rank=16, w_a_override=m.w_a)
+    assert m2.w_a is m.w_a
+
+
+def test_broadcast_add_product_matches_oracle():
+    from weightshared_torchtitan_b200.modules import broadcast_add
+    g = torch.Generator().manual_seed(2)
+    for gg, H, D in ((1, 4, 8), (2, 8, 4), (4, 4, 16)):
+        base = torch.randn(2, 7, gg * D, generator=g).cuda()
+        delta = torch.randn(2, 7, H * D, generator=g).cuda()
+        assert torch.equal(broadcast_add(base, delta, dim=-1, g=gg).cpu(),
+                           O.broadcast_add(base.cpu(), delta.cpu(), dim=-1, g=gg))
+
+
+@pytest.mark.parametrize("mode", ["f32", "bf16"])
+def test_shared_base_across_layers_in_place(mode):
+    """Four SharedLoRALinear modules referencing ONE nn.Linear: the base gradient is the sum
+    of all users' contributions, accumulated in place (configuration 0 through the modules)."""
+    import torch.nn as nn
+    from weightshared_torchtitan_b200.modules import LoRAModule, SharedLoRALinear
+    inp = O.config0_inputs(M=512, K=256, N=384, r=16, L=4)
+    base = nn.Linear(256, 384, bias=False).cuda()
+    with torch.no_grad():
+        base.weight.copy_(inp["W"])
+    layers = []
+    for l in range(4):
+        off = LoRAModule(256, 384, rank=16).cuda()
+        with torch.no_grad():
+            off.w_a.weight.copy_(inp["As"][l])
+            off.w_b.weight.copy_(inp["Bs"][l])
+        layers.append(SharedLoRALinear(base, off, grad_in_place=True))
+    dt = torch.float32 if mode == "f32" else torch.bfloat16
+    tol = 1e-5 if mode == "f32" else 1e-2
+    xs = [x.cuda().to(dt).requires_grad_(True) for x in inp["xs"]]
+    ys = [m(x) for m, x in zip(layers, xs)]
+    total = sum((y.float() * dY.cuda()).sum() for y, dY in zip(ys, inp["dYs"]))
+    total.backward()
+    rd = (lambda t: t.to(dt).float()) if mode == "bf16" else (lambda t: t)
+    ys_o, dXs_o, dW_o, dAs_o, dBs_o = O.shared_w_layers_fwd_bwd(
+        [rd(x) for x in inp["xs"]], rd(inp["W"]), [rd(a) for a in inp["As"]], [rd(b) for b in inp["Bs"]],
+        [rd(d) for d in inp["dYs"]])
+    assert base.weight.grad.dtype == torch.float32
+    assert rel(base.weight.grad, dW_o) < tol
+    for l in range(4):
+        assert rel(ys[l], ys_o[l]) < tol
+        assert rel(xs[l].grad, dXs_o[l]) < tol
+        assert rel(layers[l].offset.w_a.weight.grad, dAs_o[l]) < tol
+        assert rel(layers[l].offset.w_b.weight.grad, dBs_o[l]) < tol
+
+
+def _build_tiny(dtype):
+    from weightshared_torchtitan_b200.decoder import DecoderConfig, WeightSharedDecoder
+    a, p = tiny_decoder_params()
+    c = DecoderConfig(dim=a.dim, hidden_dim=a.hidden_dim, n_layers=a.n_layers, n_unique=a.n_unique,
+                      n_heads=a.n_heads, n_kv_heads=a.n_kv_heads, head_dim=a.head_dim, rank=a.rank,
+                      vocab_size=a.vocab_size, embed_rank=a.embed_rank, max_seq_len=a.max_seq_len,
+                      loss_chunk=16)
+    m = WeightSharedDecoder(c).cuda()
+    m.load_oracle_params({k: v.cuda() for k, v in p.items()})
+    m.compute_dtype = dtype
+    return a, p, m
+
+
+def _grad_of(m, name):
+    if name.startswith("blocks."):
+        _, u, proj, _ = name.split(".")
+        return getattr(m.blocks[int(u)], proj).weight.grad
+    if name.startswith("layers."):
+        _, l, rest = name.split(".", 2)
+        lyr = m.layers[int(l)]
+        if "." in rest:
+            proj, ab = rest.split(".")
+            return getattr(getattr(lyr, f"{proj}_offset"), ab).weight.grad
+        return getattr(lyr, rest).weight.grad
+    if name == "embed.P":
+        return m.tok_embeddings.proj.weight.grad
+    raise KeyError(name)
+
+
+def test_tiny_decoder_fp32_matches_reference_golden(golden_dir):
+    """fp32 mode of the decoder against the fixture produced by the reference's own blocks."""
+    g = np.load(os.path.join(golden_dir, "decoder_tiny.npz"))
+    a, p, m = _build_tiny(torch.float32)
+    tokens, labels = _t(g["tokens"]).cuda(), _t(g["labels"]).cuda()
+    with torch.no_grad():
+        logits = m(tokens)
+    assert rel(logits[:, ::5, ::37], _t(g["logits_s"])) < 1e-4
+    loss = m.loss(tokens, labels)
+    assert abs(loss.item() - float(g["loss"])) < 1e-4 * float(g["loss"])
+    loss.backward()
+    for key in g.files:
+        if not key.startswith("g."):
+            continue
+        name = key[2:]
+        if name == "embed.E_small_rows":
+            got = m.tok_embeddings.embed.weight.grad[tokens.flatten()[:8]]
+        elif name == "output_s":
+            got = m.output.weight.grad[::17, ::3]
+        else:
+            got = _grad_of(m, name)
+        assert rel(got, _t(g[key])) < 2e-4, (key, rel(got, _t(g[key])))
+
+
+def test_tiny_decoder_bf16_close_to_reference_golden(golden_dir):
+    g = np.load(os.path.join(golden_dir, "decoder_tiny.npz"))
+    a, p, m = _build_tiny(torch.bfloat16)
+    tokens, labels = _t(g["tokens"]).cuda(), _t(g["labels"]).cuda()
+    loss = m.loss(tokens, labels)
+    assert abs(loss.item() - float(g["loss"])) < 1e-2 * float(g["loss"])
+    loss.backward()
+    for key in ("g.blocks.0.wq.weight", "g.blocks.1.w2.weight", "g.layers.0.wq.w_a", "g.layers.3.w2.w_b", "g.embed.P"):
+        assert rel(_grad_of(m, key[2:]), _t(g[key])) < 6e-2, (key, rel(_grad_of(m, key[2:]), _t(g[key])))
+
+
+def test_train_step_reduces_loss():
+    from weightshared_torchtitan_b200.train_step import TrainStep
+    a, p, m = _build_tiny(torch.bfloat16)
+    step = TrainStep(m, lr=3e-3, weight_decay=0.0)
+    g = torch.Generator().manual_seed(0)
+    tokens = torch.randint(0, a.vocab_size, (4, a.max_seq_len), generator=g).cuda()
+    labels = torch.randint(0, a.vocab_size, (4, a.max_seq_len), generator=g).cuda()
+    losses = [step(tokens, labels).item() for _ in range(8)]
+    step.arena.check_attached()
+    assert all(np.isfinite(losses)) and losses[-1] < losses[0]

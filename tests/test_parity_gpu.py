@@ -1,0 +1,334 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the oracle and the
+golden fixtures on the same seeded inputs.
+
+Tolerances (per-tensor max|a-b| / max|b|, the metric of the baseline):
+  bf16 inputs, fp32 accumulation : 1e-2
+  fp32 mode                      : 1e-5
+  embedding gather               : bit-exact
+"""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import lora_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL_BF16 = 1e-2
+TOL_F32 = 1e-5
+
+
+@pytest.fixture(scope="module")
+def wsl():
+    if not torch.cuda.is_available():
+        pytest.fail("gpu tests need a CUDA device")
+    from weightshared_torchtitan_b200 import _lib, ops
+    _lib.lib()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    yield ops
+    torch.cuda.synchronize()
+    st, words = _lib.poll_status()
+    assert st == 0, f"device status {st} {words}"
+
+
+def _t(a):
+    return torch.from_numpy(np.asarray(a))
+
+
+def rel(a, b):
+    return O.max_rel_err(a, b)
+
+
+def run_projection(ops, x, W, A, B, dY, s=2.0):
+    """The five kernels of one projection; returns y, dX, dW, dA, dB (fp32 grads, from zero)."""
+    T = ops.lora_prepass(x, A, s)
+    y = ops.lora_linear_fwd(x, W, T, B)
+    U = ops.lora_bwd_prepass(dY, B, s)
+    dX = ops.lora_linear_bwd_dx([dY], [U], [W], [A])
+    dW = torch.zeros(W.shape, device=x.device)
+    dA = torch.zeros(A.shape, device=x.device)
+    dB = torch.zeros(B.shape, device=x.device)
+    ops.lora_linear_bwd_dw(dY, U, x, T, dW, dA, dB)
+    return y, dX, dW, dA, dB
+
+
+def oracle_projection(x, W, A, B, dY):
+    return O.lora_linear_fwd_bwd(x.float().cpu(), W.float().cpu(), A.float().cpu(), B.float().cpu(),
+                                 dY.float().cpu())
+
+
+# ------------------------------------------------------------------ golden fixtures
+@pytest.mark.parametrize("mode", ["f32", "bf16"])
+def test_golden_small(wsl, golden_dir, mode):
+    g = np.load(os.path.join(golden_dir, "lora_small.npz"))
+    dt = torch.float32 if mode == "f32" else torch.bfloat16
+    ins = [_t(g[k]).cuda().to(dt) for k in ("x", "W", "A", "B", "dY")]
+    outs = run_projection(wsl, *ins)
+    if mode == "f32":
+        want = [_t(g[k]) for k in ("y", "dX", "dW", "dA", "dB")]
+        tol = TOL_F32
+    else:   # compare against the oracle evaluated on the bf16-rounded inputs
+        want = oracle_projection(*ins)
+        tol = TOL_BF16
+    for got, w, name in zip(outs, want, ("y", "dX", "dW", "dA", "dB")):
+        assert rel(got, w) < tol, (name, rel(got, w))
+
+
+def test_golden_config0_fp32(wsl, golden_dir):
+    """Baseline configuration 0 in fp32 mode: four layers share W and accumulate into ONE dW."""
+    g = np.load(os.path.join(golden_dir, "lora_cfg0.npz"))
+    inp = O.config0_inputs()
+    W = inp["W"].cuda()
+    dW = torch.zeros_like(W)
+    for l in range(4):
+        x, A, B, dY = (inp[k][l].cuda() for k in ("xs", "As", "Bs", "dYs"))
+        T = wsl.lora_prepass(x, A, 2.0)
+        y = wsl.lora_linear_fwd(x, W, T, B)
+        U = wsl.lora_bwd_prepass(dY, B, 2.0)
+        dX = wsl.lora_linear_bwd_dx([dY], [U], [W], [A])
+        dA = torch.zeros_like(A)
+        dB = torch.zeros_like(B)
+        wsl.lora_linear_bwd_dw(dY, U, x, T, dW, dA, dB)
+        assert rel(y[::97, ::89], _t(g[f"y{l}_s"])) < TOL_F32
+        assert rel(dX[::97, ::89], _t(g[f"dX{l}_s"])) < TOL_F32
+        assert rel(dA[:, ::7], _t(g[f"dA{l}"])) < TOL_F32
+        assert rel(dB[::7], _t(g[f"dB{l}"])) < TOL_F32
+        for t, key in ((y, f"y{l}_c"), (dX, f"dX{l}_c")):
+            c = g[key]
+            assert abs(t.double().abs().sum().item() - c[1]) <= 1e-5 * c[1], key
+    assert rel(dW[::31, ::29], _t(g["dW_s"])) < TOL_F32
+    c = g["dW_c"]
+    assert abs(dW.double().abs().sum().item() - c[1]) <= 1e-5 * c[1]
+
+
+def test_config0_bf16_against_oracle(wsl):
+    inp = O.config0_inputs()
+    bf = torch.bfloat16
+    W = inp["W"].cuda().to(bf)
+    dW = torch.zeros(W.shape, device="cuda")
+    xs = [t.cuda().to(bf) for t in inp["xs"]]
+    As = [t.cuda().to(bf) for t in inp["As"]]
+    Bs = [t.cuda().to(bf) for t in inp["Bs"]]
+    dYs = [t.cuda().to(bf) for t in inp["dYs"]]
+    ys_o, dXs_o, dW_o, dAs_o, dBs_o = O.shared_w_layers_fwd_bwd(
+        [t.float().cpu() for t in xs], W.float().cpu(), [t.float().cpu() for t in As],
+        [t.float().cpu() for t in Bs], [t.float().cpu() for t in dYs])
+    for l in range(4):
+        T = wsl.lora_prepass(xs[l], As[l], 2.0)
+        y = wsl.lora_linear_fwd(xs[l], W, T, Bs[l])
+        U = wsl.lora_bwd_prepass(dYs[l], Bs[l], 2.0)
+        dX = wsl.lora_linear_bwd_dx([dYs[l]], [U], [W], [As[l]])
+        dA = torch.zeros(As[l].shape, device="cuda")
+        dB = torch.zeros(Bs[l].shape, device="cuda")
+        wsl.lora_linear_bwd_dw(dYs[l], U, xs[l], T, dW, dA, dB)
+        for got, want, name in ((y, ys_o[l], "y"), (dX, dXs_o[l], "dX"), (dA, dAs_o[l], "dA"), (dB, dBs_o[l], "dB")):
+            assert rel(got, want) < TOL_BF16, (l, name, rel(got, want))
+    assert rel(dW, dW_o) < TOL_BF16
+
+
+# ----------------------------------------------------------------- shapes and edges
+SHAPES = [
+    # M, N, K, r     (ragged M, narrow and wide N, every rank of the sweep, single row)
+    (1, 64, 64, 8),
+    (127, 1024, 1024, 16),
+    (200, 328, 264, 8),
+    (333, 3072, 1024, 16),
+    (512, 1024, 3072, 32),
+    (640, 2048, 2048, 64),
+    (300, 2560, 1024, 128),
+    (1000, 1024, 512, 48),
+]
+
+
+@pytest.mark.parametrize("M,N,K,r", SHAPES)
+def test_projection_bf16_shapes(wsl, M, N, K, r):
+    ins = [t.cuda().to(torch.bfloat16) for t in O.projection_inputs(100 + M + r, M, N, K, r)]
+    outs = run_projection(wsl, *ins)
+    want = oracle_projection(*ins)
+    for got, w, name in zip(outs, want, ("y", "dX", "dW", "dA", "dB")):
+        assert rel(got, w) < TOL_BF16, (name, rel(got, w))
+
+
+@pytest.mark.parametrize("M,N,K,r", [(1, 64, 64, 8), (200, 328, 264, 8), (257, 520, 136, 20)])
+def test_projection_fp32_shapes(wsl, M, N, K, r):
+    ins = [t.cuda() for t in O.projection_inputs(7 + M, M, N, K, r)]
+    outs = run_projection(wsl, *ins)
+    want = oracle_projection(*ins)
+    for got, w, name in zip(outs, want, ("y", "dX", "dW", "dA", "dB")):
+        assert rel(got, w) < TOL_F32, (name, rel(got, w))
+
+
+def test_grouped_dx_sums_projections(wsl):
+    """q|k|v: one dX kernel contracts over all three projections (fp32 accumulate, one rounding)."""
+    M, K, r = 384, 1024, 16
+    g = torch.Generator().manual_seed(11)
+    bf = torch.bfloat16
+    Ns = (2048, 1024, 1024)
+    dYs = [torch.randn(M, n, generator=g).cuda().to(bf) for n in Ns]
+    Ws = [(torch.randn(n, K, generator=g) * 0.02).cuda().to(bf) for n in Ns]
+    Us = [torch.randn(M, r, generator=g).cuda().to(bf) for _ in Ns]
+    As = [(torch.randn(r, K, generator=g) * 0.03).cuda().to(bf) for _ in Ns]
+    dX = wsl.lora_linear_bwd_dx(dYs, Us, Ws, As)
+    want = sum(d.float().cpu() @ w.float().cpu() + u.float().cpu() @ a.float().cpu()
+               for d, w, u, a in zip(dYs, Ws, Us, As))
+    assert rel(dX, want) < TOL_BF16
+
+
+def test_zero_B_and_scale_linearity(wsl):
+    x, W, A, B, dY = [t.cuda().to(torch.bfloat16) for t in O.projection_inputs(5, 256, 512, 256, 16)]
+    y0, _, _, dA0, _ = run_projection(wsl, x, W, A, torch.zeros_like(B), dY)
+    assert torch.equal(y0, wsl.linear_fwd(x, W))       # B = 0: exactly the base projection
+    assert dA0.abs().max().item() == 0.0               # and A receives no gradient
+    # the adapter term is linear in s (s = 2 and s = 4 are exact scalings in bf16)
+    T2, T4 = wsl.lora_prepass(x, A, 2.0), wsl.lora_prepass(x, A, 4.0)
+    assert torch.equal(T4.float(), 2.0 * T2.float())
+
+
+def test_rank_padding_invariance(wsl):
+    """Zero-padding the adapter from r=8 to r=16 must not change any result."""
+    x, W, A, B, dY = [t.cuda().to(torch.bfloat16) for t in O.projection_inputs(9, 256, 384, 320, 8)]
+    A2 = torch.cat([A, torch.zeros_like(A)], 0)
+    B2 = torch.cat([B, torch.zeros_like(B)], 1).contiguous()
+    y, dX, dW, dA, dB = run_projection(wsl, x, W, A, B, dY)
+    y2, dX2, dW2, dA2, dB2 = run_projection(wsl, x, W, A2, B2, dY)
+    assert torch.equal(y, y2) and torch.equal(dX, dX2) and torch.equal(dW, dW2)
+    assert torch.equal(dA, dA2[:8]) and dA2[8:].abs().max().item() == 0.0
+    assert torch.equal(dB, dB2[:, :8]) and dB2[:, 8:].abs().max().item() == 0.0
+
+
+def test_guard_bands_and_repeatability(wsl):
+    """Outputs live inside larger sentinel-filled buffers: nothing outside the result may be
+    written, and two runs on the same inputs must agree bit for bit."""
+    M, N, K, r = 200, 328, 264, 8
+    x, W, A, B, dY = [t.cuda().to(torch.bfloat16) for t in O.projection_inputs(21, M, N, K, r)]
+    from weightshared_torchtitan_b200 import _lib
+    lib = _lib.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    pad = 16
+
+    def guarded(rows, cols, dtype, fill):
+        buf = torch.full((rows + 2 * pad, cols + 2 * pad), fill, device="cuda", dtype=dtype)
+        return buf, buf[pad:pad + rows, pad:pad + cols]
+
+    results = []
+    for _ in range(2):
+        Tb, T = guarded(M, r, torch.bfloat16, 7.0)
+        yb, y = guarded(M, N, torch.bfloat16, 7.0)
+        dWb, dW = guarded(N, K, torch.float32, 0.0)
+        st = lib.wsl_lora_prepass(x.data_ptr(), K, A.data_ptr(), T.data_ptr(), Tb.stride(0), M, K, r, 2.0, 0, stream)
+        assert st == 0
+        st = lib.wsl_lora_linear_fwd(x.data_ptr(), K, W.data_ptr(), T.data_ptr(), Tb.stride(0), B.data_ptr(),
+                                     y.data_ptr(), yb.stride(0), M, N, K, r, 0, stream)
+        assert st == 0
+        torch.cuda.synchronize()
+        for buf, inner_rows, inner_cols in ((Tb, M, r), (yb, M, N)):
+            mask = torch.ones_like(buf, dtype=torch.bool)
+            mask[pad:pad + inner_rows, pad:pad + inner_cols] = False
+            assert (buf[mask].float() == 7.0).all()
+        results.append((T.clone(), y.clone()))
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+    # dW accumulates deterministically: two identical accumulations give identical buffers
+    U = wsl.lora_bwd_prepass(dY, B, 2.0)
+    T = results[0][0].contiguous()
+    outs = []
+    for _ in range(2):
+        dW = torch.zeros(N, K, device="cuda")
+        dA = torch.zeros(r, K, device="cuda")
+        dB = torch.zeros(N, r, device="cuda")
+        wsl.lora_linear_bwd_dw(dY, U, x, T, dW, dA, dB)
+        outs.append((dW, dA, dB))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+
+
+def test_argument_errors_return_codes(wsl):
+    """Bad arguments come back as status codes before any launch."""
+    from weightshared_torchtitan_b200 import _lib
+    lib = _lib.lib()
+    x = torch.zeros(128, 72, device="cuda", dtype=torch.bfloat16)
+    W = torch.zeros(64, 72, device="cuda", dtype=torch.bfloat16)
+    y = torch.zeros(128, 64, device="cuda", dtype=torch.bfloat16)
+    s = torch.cuda.current_stream().cuda_stream
+    assert lib.wsl_linear_fwd(None, 72, W.data_ptr(), y.data_ptr(), 64, 128, 64, 72, 0, 0, s) == _lib.WSL_ERR_BAD_ARG
+    assert lib.wsl_linear_fwd(x.data_ptr(), 72, W.data_ptr(), y.data_ptr(), 64, 0, 64, 72, 0, 0, s) == _lib.WSL_ERR_BAD_ARG
+    assert lib.wsl_linear_fwd(x.data_ptr(), 72, W.data_ptr(), y.data_ptr(), 64, 128, 64, 72, 0, 5, s) == _lib.WSL_ERR_BAD_ARG
+    # pitch not a multiple of 8 elements / pointer not 16-byte aligned
+    assert lib.wsl_linear_fwd(x.data_ptr(), 73, W.data_ptr(), y.data_ptr(), 64, 128, 64, 72, 0, 0, s) == _lib.WSL_ERR_ALIGN
+    assert lib.wsl_linear_fwd(x.data_ptr() + 2, 72, W.data_ptr(), y.data_ptr(), 64, 127, 64, 72, 0, 0, s) == _lib.WSL_ERR_ALIGN
+    assert "alignment" in _lib.status_string(_lib.WSL_ERR_ALIGN)
+
+
+# ---------------------------------------------------------------- embedding
+def test_embedding_gather_is_bit_exact(wsl):
+    g = torch.Generator().manual_seed(3)
+    V, r_e = 151936, 256
+    E = torch.randn(V, r_e, generator=g).cuda().to(torch.bfloat16)
+    tok = torch.randint(0, V, (4, 1000), generator=g).cuda()
+    G = wsl.embed_gather(tok, E)
+    assert torch.equal(G, E[tok.reshape(-1)])
+    # repeated and boundary ids
+    tok2 = torch.tensor([0, V - 1, 5, 5, 5, V - 1], device="cuda")
+    assert torch.equal(wsl.embed_gather(tok2, E), E[tok2])
+
+
+@pytest.mark.parametrize("mode", ["f32", "bf16"])
+def test_factorized_embedding_fwd_bwd(wsl, mode):
+    from weightshared_torchtitan_b200.modules import factorized_embedding
+    g = torch.Generator().manual_seed(4)
+    V, r_e, d, M = 2048, 64, 192, 600
+    dt = torch.float32 if mode == "f32" else torch.bfloat16
+    tol = TOL_F32 if mode == "f32" else TOL_BF16
+    E = torch.randn(V, r_e, generator=g).to(dt)
+    P = (torch.randn(d, r_e, generator=g) * 0.05).to(dt)
+    tok = torch.randint(0, 300, (M,), generator=g)      # many collisions
+    dH = torch.randn(M, d, generator=g).to(dt)
+    Eo, Po = E.float().clone().requires_grad_(True), P.float().clone().requires_grad_(True)
+    ho = O.factorized_embedding(tok, Eo, Po)
+    ho.backward(dH.float())
+    Ec, Pc = E.detach().cuda().requires_grad_(True), P.detach().cuda().requires_grad_(True)
+    h = factorized_embedding(tok.cuda(), Ec, Pc)
+    h.backward(dH.cuda())
+    assert rel(h, ho) < tol
+    assert rel(Pc.grad, Po.grad) < tol
+    assert rel(Ec.grad, Eo.grad) < tol
+
+
+# ------------------------------------------------ baseline sizes, size-independent checks
+def test_headline_shape_sampled_rows_and_linearity(wsl):
+    """Configuration 4 MLP gate shape (M=16384, N=12288, K=4096, r=64): rows of y and dX and
+    columns of dW against the oracle on a sample, plus linearity of the in-place dW."""
+    M, N, K, r = 16384, 12288, 4096, 64
+    g = torch.Generator(device="cuda").manual_seed(1238)
+    bf = torch.bfloat16
+    x = torch.randn(M, K, device="cuda", generator=g).to(bf)
+    W = (torch.randn(N, K, device="cuda", generator=g) * 0.02).to(bf)
+    A = ((torch.rand(r, K, device="cuda", generator=g) * 2 - 1) / K ** 0.5).to(bf)
+    B = (torch.randn(N, r, device="cuda", generator=g) * 0.02).to(bf)
+    dY = torch.randn(M, N, device="cuda", generator=g).to(bf)
+    T = wsl.lora_prepass(x, A, 2.0)
+    y = wsl.lora_linear_fwd(x, W, T, B)
+    U = wsl.lora_bwd_prepass(dY, B, 2.0)
+    dX = wsl.lora_linear_bwd_dx([dY], [U], [W], [A])
+    rows = torch.arange(0, M, 257, device="cuda")[:48]
+    xr, dYr = x[rows].float().cpu(), dY[rows].float().cpu()
+    Wc, Ac, Bc = W.float().cpu(), A.float().cpu(), B.float().cpu()
+    y_o = O.lora_linear(xr, Wc, Ac, Bc)
+    assert rel(y[rows], y_o) < TOL_BF16
+    dX_o = dYr @ Wc + 2.0 * (dYr @ Bc) @ Ac
+    assert rel(dX[rows], dX_o) < TOL_BF16
+    dW = torch.zeros(N, K, device="cuda")
+    dA = torch.zeros(r, K, device="cuda")
+    dB = torch.zeros(N, r, device="cuda")
+    wsl.lora_linear_bwd_dw(dY, U, x, T, dW, dA, dB)
+    cols = torch.arange(0, N, 509, device="cuda")[:24]
+    dW_o = dY[:, cols].float().T @ x.float()            # fp32 on the device for the big contraction
+    assert rel(dW[cols], dW_o) < TOL_BF16
+    assert rel(dB[cols], dY[:, cols].float().T @ T.float()) < TOL_BF16
+    assert rel(dA, U.float().T @ x.float()) < TOL_BF16
+    # accumulating the same contribution twice doubles the buffer exactly (in-place +=)
+    before = dW.clone()
+    wsl.lora_linear_bwd_dw(dY, U, x, T, dW, None, None)
+    assert rel(dW, 2.0 * before) < 1e-6

@@ -1,0 +1,218 @@
+"""torch.autograd.Function wrappers of the fused shared-W + LoRA projection.
+
+Shaped like the reference's own kernel-backed Functions (GroupedGemmMg,
+torchtitan/experiments/kernels/triton_mg_group_gemm/torchao_pr/mg_grouped_gemm.py:1202-1300:
+``forward(ctx, tensors..., non-tensor args)``, ``ctx.save_for_backward``, ``backward`` returning
+one entry per forward argument, plus a functional wrapper that calls ``.apply``).
+
+The arithmetic replaces base(x) + LoRAModule.forward(x) and its autograd graph
+(torchtitan/models/llama3/model/model.py:111-145,189-192,392-398).
+
+Weight gradients can go two ways:
+  * returned to autograd as fresh tensors (default; drop-in for any optimizer setup), or
+  * accumulated IN PLACE into caller-owned fp32 buffers ("sinks"), which is how one shared
+    base weight collects the contributions of every layer that reuses it without a
+    temporary per use. Then ``None`` is returned for those inputs.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import ops
+
+Sinks = Optional[Tuple[Optional[torch.Tensor], Optional[torch.Tensor], Optional[torch.Tensor]]]
+
+
+def _flat(x: torch.Tensor) -> torch.Tensor:
+    return x.reshape(-1, x.shape[-1])
+
+
+class LoRALinearGroupFunction(torch.autograd.Function):
+    """P projections that read the same x: y_p = x W_p^T + s (x A_p^T) B_p^T, p < P <= 3.
+
+    forward(ctx, x, s, sinks, anchors, W_0, A_0, B_0, W_1, A_1, B_1, ...) -> (y_0, ..., y_{P-1})
+
+    ``sinks`` is None or a list of P triples (dW, dA, dB) of fp32 buffers to accumulate into.
+    ``anchors`` is a tuple of tensors that only tie the output to the autograd graph (the
+    fp32 master parameters when W/A/B are detached compute copies); they get no gradient.
+    """
+
+    @staticmethod
+    def forward(ctx, x, s, sinks, anchors, *wab):
+        P = len(wab) // 3
+        Ws, As, Bs = list(wab[0::3]), list(wab[1::3]), list(wab[2::3])
+        x2 = _flat(x)
+        if not x2.is_contiguous() and x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        A_cat = As[0] if P == 1 else torch.cat(As, dim=0)
+        T_cat = ops.lora_prepass(x2, A_cat, s)
+        ys, Ts = [], []
+        off = 0
+        for p in range(P):
+            r = As[p].shape[0]
+            T = T_cat[:, off:off + r]
+            off += r
+            Ts.append(T)
+            ys.append(ops.lora_linear_fwd(x2, Ws[p], T, Bs[p]).view(*x.shape[:-1], Ws[p].shape[0]))
+        ctx.save_for_backward(x2, T_cat, *wab)
+        ctx.s = float(s)
+        ctx.sinks = sinks
+        ctx.P = P
+        ctx.x_shape = x.shape
+        return tuple(ys)
+
+    @staticmethod
+    def backward(ctx, *dYs):
+        x2, T_cat, *wab = ctx.saved_tensors
+        P = ctx.P
+        Ws, As, Bs = list(wab[0::3]), list(wab[1::3]), list(wab[2::3])
+        dY2, Us = [], []
+        for p in range(P):
+            d = dYs[p]
+            if d is None:
+                d = torch.zeros(x2.shape[0], Ws[p].shape[0], device=x2.device, dtype=x2.dtype)
+            d = _flat(d)
+            if d.stride(-1) != 1:
+                d = d.contiguous()
+            dY2.append(d)
+            Us.append(ops.lora_bwd_prepass(d, Bs[p], ctx.s))
+        dX = None
+        if ctx.needs_input_grad[0]:
+            dX = ops.lora_linear_bwd_dx(dY2, Us, Ws, As).view(ctx.x_shape)
+        grads: List[Optional[torch.Tensor]] = []
+        off = 0
+        for p in range(P):
+            r = As[p].shape[0]
+            T = T_cat[:, off:off + r]
+            off += r
+            if ctx.sinks is not None:
+                dW, dA, dB = ctx.sinks[p]
+                if dW is not None or dA is not None or dB is not None:
+                    ops.lora_linear_bwd_dw(dY2[p], Us[p], x2, T, dW, dA, dB)
+                grads += [None, None, None]
+            else:
+                need = ctx.needs_input_grad[4 + 3 * p: 7 + 3 * p]
+                dev = x2.device
+                dW = torch.zeros(Ws[p].shape, device=dev, dtype=torch.float32) if need[0] else None
+                dA = torch.zeros(As[p].shape, device=dev, dtype=torch.float32) if need[1] else None
+                dB = torch.zeros(Bs[p].shape, device=dev, dtype=torch.float32) if need[2] else None
+                if any(need):
+                    ops.lora_linear_bwd_dw(dY2[p], Us[p], x2, T, dW, dA, dB)
+                grads += [g.to(w.dtype) if g is not None else None
+                          for g, w in ((dW, Ws[p]), (dA, As[p]), (dB, Bs[p]))]
+        return (dX, None, None, None, *grads)
+
+
+def lora_linear_group(x: torch.Tensor, Ws: Sequence[torch.Tensor], As: Sequence[torch.Tensor],
+                      Bs: Sequence[torch.Tensor], s: float, sinks=None,
+                      anchors: Tuple[torch.Tensor, ...] = ()) -> Tuple[torch.Tensor, ...]:
+    """Functional form of LoRALinearGroupFunction (q|k|v or gate|up sharing one input)."""
+    wab = []
+    for W, A, B in zip(Ws, As, Bs):
+        wab += [W, A, B]
+    return LoRALinearGroupFunction.apply(x, s, sinks, _Anchor(anchors, x), *wab)
+
+
+def lora_linear(x: torch.Tensor, W: torch.Tensor, A: torch.Tensor, B: torch.Tensor, s: float,
+                sinks: Sinks = None, anchors: Tuple[torch.Tensor, ...] = ()) -> torch.Tensor:
+    """y = x W^T + s (x A^T) B^T through the fused kernels; differentiable in x, W, A, B."""
+    return lora_linear_group(x, [W], [A], [B], s, None if sinks is None else [sinks], anchors)[0]
+
+
+class _AnchorFn(torch.autograd.Function):
+    """Zero-size tensor that requires grad iff one of the anchors does. It lets a Function
+    whose weights are detached compute copies still run its backward when x itself does not
+    require grad (first layer), so the in-place sinks get filled."""
+
+    @staticmethod
+    def forward(ctx, *anchors):
+        return anchors[0].new_empty(0)
+
+    @staticmethod
+    def backward(ctx, g):
+        return (None,) * len(ctx.needs_input_grad)
+
+
+def _Anchor(anchors: Tuple[torch.Tensor, ...], like: torch.Tensor):
+    live = tuple(a for a in anchors if a.requires_grad)
+    if not live:
+        return None
+    return _AnchorFn.apply(*live)
+
+
+class LoRADeltaFunction(torch.autograd.Function):
+    """The adapter alone: s (x A^T) B^T, i.e. LoRAModule.forward
+    (torchtitan/models/llama3/model/model.py:189-192) for callers that keep the base
+    projection separate (head-sharing modes of the reference)."""
+
+    @staticmethod
+    def forward(ctx, x, A, B, s):
+        x2 = _flat(x)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        T = ops.lora_prepass(x2, A, s)
+        y = ops.linear_fwd(T, B)
+        ctx.save_for_backward(x2, T, A, B)
+        ctx.s = float(s)
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], B.shape[0])
+
+    @staticmethod
+    def backward(ctx, dY):
+        x2, T, A, B = ctx.saved_tensors
+        d = _flat(dY)
+        if d.stride(-1) != 1:
+            d = d.contiguous()
+        U = ops.lora_bwd_prepass(d, B, ctx.s)
+        dX = None
+        if ctx.needs_input_grad[0]:
+            dX = ops.lora_linear_bwd_dx([U], [None], [A], [None]).view(ctx.x_shape)
+        dA = torch.zeros(A.shape, device=A.device, dtype=torch.float32) if ctx.needs_input_grad[1] else None
+        dB = torch.zeros(B.shape, device=B.device, dtype=torch.float32) if ctx.needs_input_grad[2] else None
+        if dA is not None or dB is not None:
+            ops.lora_linear_bwd_dw(d, U, x2, T, None, dA, dB)
+        return (dX, dA.to(A.dtype) if dA is not None else None,
+                dB.to(B.dtype) if dB is not None else None, None)
+
+
+def lora_delta(x: torch.Tensor, A: torch.Tensor, B: torch.Tensor, s: float) -> torch.Tensor:
+    return LoRADeltaFunction.apply(x, A, B, s)
+
+
+class LinearFunction(torch.autograd.Function):
+    """Plain y = x W^T on the same kernels (projection without an adapter)."""
+
+    @staticmethod
+    def forward(ctx, x, W, sink):
+        x2 = _flat(x)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        y = ops.linear_fwd(x2, W)
+        ctx.save_for_backward(x2, W)
+        ctx.sink = sink
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], W.shape[0])
+
+    @staticmethod
+    def backward(ctx, dY):
+        x2, W = ctx.saved_tensors
+        d = _flat(dY)
+        if d.stride(-1) != 1:
+            d = d.contiguous()
+        dX = None
+        if ctx.needs_input_grad[0]:
+            dX = ops.lora_linear_bwd_dx([d], [None], [W], [None]).view(ctx.x_shape)
+        gW = None
+        if ctx.sink is not None:
+            ops.lora_linear_bwd_dw(d, None, x2, None, ctx.sink, None, None)
+        elif ctx.needs_input_grad[1]:
+            dW = torch.zeros(W.shape, device=W.device, dtype=torch.float32)
+            ops.lora_linear_bwd_dw(d, None, x2, None, dW, None, None)
+            gW = dW.to(W.dtype)
+        return dX, gW, None
+
+
+def linear(x: torch.Tensor, W: torch.Tensor, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+    return LinearFunction.apply(x, W, sink)

@@ -15,6 +15,34 @@ from . import _lib
 from ._lib import WSL_BF16, WSL_F32
 
 
+# Optional per-launch device timing (bench.py): when a list is installed every wrapper
+# brackets its C-ABI call with CUDA events on the launching stream and appends
+# (kind, algorithmic_flops, algorithmic_bytes, start_event, end_event).
+_TIMING = None
+
+
+def set_timing(records) -> None:
+    """Install (a list) or remove (None) the per-launch timing sink."""
+    global _TIMING
+    _TIMING = records
+
+
+def _tic():
+    if _TIMING is None:
+        return None
+    e = torch.cuda.Event(enable_timing=True)
+    e.record()
+    return e
+
+
+def _toc(e0, kind: str, flops: float, nbytes: float) -> None:
+    if e0 is None:
+        return
+    e1 = torch.cuda.Event(enable_timing=True)
+    e1.record()
+    _TIMING.append((kind, flops, nbytes, e0, e1))
+
+
 def _dtype_code(t: torch.Tensor) -> int:
     if t.dtype == torch.bfloat16:
         return WSL_BF16
@@ -61,8 +89,10 @@ def linear_fwd(x: torch.Tensor, W: torch.Tensor, out_f32: bool = False) -> torch
         raise ValueError("W must be [N, K]")
     y = torch.empty((M, N), device=x.device,
                     dtype=torch.float32 if (out_f32 or code == WSL_F32) else torch.bfloat16)
+    _e = _tic()
     st = _lib.lib().wsl_linear_fwd(x.data_ptr(), _ld(x), W.data_ptr(), y.data_ptr(), N, M, N, K,
                                    int(bool(out_f32)), code, _stream())
+    _toc(_e, "linear_fwd", 2.0 * M * N * K, x.element_size() * (M * K + N * K) + y.element_size() * M * N)
     _lib.check(st, "wsl_linear_fwd")
     return y
 
@@ -77,8 +107,10 @@ def lora_prepass(x: torch.Tensor, A_cat: torch.Tensor, s: float) -> torch.Tensor
     if A_cat.shape[1] != K:
         raise ValueError("A_cat must be [r_tot, K]")
     T = torch.empty((M, r_tot), device=x.device, dtype=x.dtype)
+    _e = _tic()
     st = _lib.lib().wsl_lora_prepass(x.data_ptr(), _ld(x), A_cat.data_ptr(), T.data_ptr(), r_tot,
                                      M, K, r_tot, float(s), code, _stream())
+    _toc(_e, "prepass_T", 2.0 * M * K * r_tot, x.element_size() * (M * K + r_tot * K + M * r_tot))
     _lib.check(st, "wsl_lora_prepass")
     return T
 
@@ -102,8 +134,10 @@ def lora_linear_fwd(x: torch.Tensor, W: torch.Tensor, T: Optional[torch.Tensor],
             raise ValueError("T must be [M, r] and B [N, r]")
         tp, bp, ldt = T.data_ptr(), B.data_ptr(), _ld(T)
     y = torch.empty((M, N), device=x.device, dtype=x.dtype)
+    _e = _tic()
     st = _lib.lib().wsl_lora_linear_fwd(x.data_ptr(), _ld(x), W.data_ptr(), tp, ldt, bp,
                                         y.data_ptr(), N, M, N, K, r, code, _stream())
+    _toc(_e, "fwd", 2.0 * M * N * (K + r), x.element_size() * (M * K + N * K + M * r + N * r + M * N))
     _lib.check(st, "wsl_lora_linear_fwd")
     return y
 
@@ -118,8 +152,10 @@ def lora_bwd_prepass(dY: torch.Tensor, B: torch.Tensor, s: float) -> torch.Tenso
     if B.shape[0] != N:
         raise ValueError("B must be [N, r]")
     U = torch.empty((M, r), device=dY.device, dtype=dY.dtype)
+    _e = _tic()
     st = _lib.lib().wsl_lora_bwd_prepass(dY.data_ptr(), _ld(dY), B.data_ptr(), U.data_ptr(), r,
                                          M, N, r, float(s), code, _stream())
+    _toc(_e, "prepass_U", 2.0 * M * N * r, dY.element_size() * (M * N + N * r + M * r))
     _lib.check(st, "wsl_lora_bwd_prepass")
     return U
 
@@ -154,8 +190,10 @@ def lora_linear_bwd_dx(dYs: Sequence[torch.Tensor], Us: Sequence[Optional[torch.
         else:
             u_p[p], ldu[p], a_p[p], rs[p] = None, 0, None, 0
     dX = torch.empty((M, K), device=dYs[0].device, dtype=dYs[0].dtype)
+    _e = _tic()
     st = _lib.lib().wsl_lora_linear_bwd_dx(n, dy_p, lddy, u_p, ldu, w_p, a_p, Ns, rs, dX.data_ptr(),
                                            K, M, K, code, _stream())
+    _toc(_e, "dx", 2.0 * M * K * sum(int(Ns[p]) + int(rs[p]) for p in range(n)), dX.element_size() * (M * K + sum((M + K) * (int(Ns[p]) + int(rs[p])) for p in range(n))))
     _lib.check(st, "wsl_lora_linear_bwd_dx")
     return dX
 
@@ -186,12 +224,14 @@ def lora_linear_bwd_dw(dY: torch.Tensor, U: Optional[torch.Tensor], x: torch.Ten
         if g is not None:
             if g.dtype != torch.float32 or not g.is_contiguous() or tuple(g.shape) != shape:
                 raise ValueError(f"{nm} must be a contiguous float32 tensor of shape {shape}")
+    _e = _tic()
     st = _lib.lib().wsl_lora_linear_bwd_dw(
         dY.data_ptr(), _ld(dY), up, ldu, x.data_ptr(), _ld(x), tp, ldt,
         dW.data_ptr() if dW is not None else None,
         dA.data_ptr() if dA is not None else None,
         dB.data_ptr() if dB is not None else None,
         M, N, K, r, code, _stream())
+    _toc(_e, "dw", 2.0 * M * ((N * K if dW is not None else 0) + (r * K if dA is not None else 0) + (N * r if dB is not None else 0)), dY.element_size() * (M * N + M * K + 2 * M * r) + 8.0 * ((N * K if dW is not None else 0) + (r * K if dA is not None else 0) + (N * r if dB is not None else 0)))
     _lib.check(st, "wsl_lora_linear_bwd_dw")
 
 
@@ -204,8 +244,10 @@ def embed_gather(tokens: torch.Tensor, E_small: torch.Tensor) -> torch.Tensor:
     E = _mat(E_small, "E_small").contiguous()
     V, r_e = E.shape
     G = torch.empty((tok.numel(), r_e), device=E.device, dtype=E.dtype)
+    _e = _tic()
     st = _lib.lib().wsl_embed_gather(tok.data_ptr(), E.data_ptr(), G.data_ptr(), tok.numel(), V, r_e,
                                      _dtype_code(E), _stream())
+    _toc(_e, "embed_gather", 0.0, 8.0 * tok.numel() + 2.0 * E.element_size() * tok.numel() * r_e)
     _lib.check(st, "wsl_embed_gather")
     return G
 
@@ -217,6 +259,8 @@ def embed_scatter_add(tokens: torch.Tensor, dG: torch.Tensor, dE: torch.Tensor) 
     if dE.dtype != torch.float32 or not dE.is_contiguous():
         raise ValueError("dE must be contiguous float32")
     V, r_e = dE.shape
+    _e = _tic()
     st = _lib.lib().wsl_embed_scatter_add(tok.data_ptr(), dG.data_ptr(), dE.data_ptr(), tok.numel(),
                                           V, r_e, _dtype_code(dG), _stream())
+    _toc(_e, "embed_scatter", 0.0, 8.0 * tok.numel() + (dG.element_size() + 8.0) * tok.numel() * r_e)
     _lib.check(st, "wsl_embed_scatter_add")
