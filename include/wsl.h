@@ -125,6 +125,13 @@ int wsl_lora_linear_bwd_dx(int nproj, const void* const* dY, const long long* ld
  * U and T carry the scale s already. dW is the gradient buffer of the SHARED
  * base weight: every layer that reuses W adds into the same fp32 buffer. Any of
  * dW, dA, dB may be NULL to skip that product.
+ * workspace: optional fp32 scratch of workspace_bytes (16-byte aligned; NULL/0 allowed).
+ * When the [N,K] tile grid is too small to fill the GPU (short weight matrices, long
+ * token count) the token contraction is split across CTAs, partial sums go to the
+ * workspace and a second kernel adds them into dW/dA/dB in a fixed order, so results stay
+ * bit-reproducible. wsl_bwd_dw_workspace_bytes() gives the size that allows the best
+ * split; a smaller or absent workspace only costs speed. The workspace contents are
+ * garbage afterwards; calls that overlap on the GPU need separate workspaces.
  * Replaces the MmBackward weight gradients and AccumulateGrad of
  * torchtitan/models/llama3/model/model.py:191,392-394 (one dW per use, cast and
  * added into W.grad by autograd in the reference).
@@ -132,7 +139,13 @@ int wsl_lora_linear_bwd_dx(int nproj, const void* const* dY, const long long* ld
 int wsl_lora_linear_bwd_dw(const void* dY, long long lddy, const void* U, long long ldu,
                            const void* x, long long ldx, const void* T, long long ldt, float* dW,
                            float* dA, float* dB, long long M, long long N, long long K,
-                           long long r, int dtype, void* stream);
+                           long long r, void* workspace, unsigned long long workspace_bytes,
+                           int dtype, void* stream);
+
+/* Workspace size (bytes, possibly 0) wsl_lora_linear_bwd_dw wants for these sizes; the
+ * want_* flags say which of dW, dA, dB will be non-NULL. No reference counterpart. */
+unsigned long long wsl_bwd_dw_workspace_bytes(long long M, long long N, long long K, long long r,
+                                              int want_dW, int want_dA, int want_dB);
 
 /*
  * G[M,r_e] = E_small[tokens[m], :]          (bit-exact row gather)

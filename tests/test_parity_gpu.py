@@ -332,3 +332,35 @@ def test_headline_shape_sampled_rows_and_linearity(wsl):
     before = dW.clone()
     wsl.lora_linear_bwd_dw(dY, U, x, T, dW, None, None)
     assert rel(dW, 2.0 * before) < 1e-6
+
+
+def test_split_contraction_for_small_weight_grads(wsl):
+    """Long token count, small weight: the dW kernel splits the token contraction across CTAs
+    through a workspace and reduces in a fixed order. Result must match the oracle, must not
+    depend on the run, and must agree with the unsplit kernel to fp32 rounding."""
+    from weightshared_torchtitan_b200 import _lib
+    lib = _lib.lib()
+    M, N, K, r = 8192, 256, 512, 16
+    assert lib.wsl_bwd_dw_workspace_bytes(M, N, K, r, 1, 1, 1) > 0     # this shape does split
+    x, W, A, B, dY = [t.cuda().to(torch.bfloat16) for t in O.projection_inputs(31, M, N, K, r)]
+    T = wsl.lora_prepass(x, A, 2.0)
+    U = wsl.lora_bwd_prepass(dY, B, 2.0)
+    runs = []
+    for _ in range(2):
+        dW = torch.ones(N, K, device="cuda")
+        dA = torch.ones(r, K, device="cuda")
+        dB = torch.ones(N, r, device="cuda")
+        wsl.lora_linear_bwd_dw(dY, U, x, T, dW, dA, dB)
+        runs.append((dW, dA, dB))
+    for a, b in zip(*runs):
+        assert torch.equal(a, b)
+    s = torch.cuda.current_stream().cuda_stream
+    dW0 = torch.ones(N, K, device="cuda")
+    dA0 = torch.ones(r, K, device="cuda")
+    dB0 = torch.ones(N, r, device="cuda")
+    st = lib.wsl_lora_linear_bwd_dw(dY.data_ptr(), N, U.data_ptr(), r, x.data_ptr(), K, T.data_ptr(), r,
+                                    dW0.data_ptr(), dA0.data_ptr(), dB0.data_ptr(), M, N, K, r, None, 0, 0, s)
+    assert st == 0
+    want = (1 + dY.float().T @ x.float(), 1 + U.float().T @ x.float(), 1 + dY.float().T @ T.float())
+    for got, unsplit, w in zip(runs[0], (dW0, dA0, dB0), want):
+        assert rel(got, w) < 1e-4 and rel(unsplit, w) < 1e-4

@@ -29,6 +29,7 @@
 #include <cudaTypedefs.h>
 #include <cstdio>
 #include <cstdlib>
+#include <cmath>
 
 #include "../../include/wsl.h"
 
@@ -61,6 +62,7 @@ struct Region {
   long long ld;
   int mode;
   float alpha;
+  long long ws_off;   // split-K: float offset of this region's partials in the workspace
 };
 
 struct GemmParams {
@@ -70,6 +72,9 @@ struct GemmParams {
   int nseg;
   int nregion;
   int total_tiles;
+  int splits;         // split-K factor: work units = total_tiles * splits
+  int kb_total;       // k-blocks summed over the segments
+  float* workspace;   // [splits][rows x cols] fp32 partials per region when splits > 1
   int mn_lbo;   // descriptor offsets of MN-major operand tiles (bytes)
   int mn_sbo;
 };
@@ -93,6 +98,16 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int t) {
   const int mt = first_m + rem % gsz;
   const int nt = rem / gsz;
   return {r, mt * BM, nt * R.bn};
+}
+
+// Segment-local k-block range [lo, hi) that split `split` of `splits` owns, given that the
+// segment starts at flattened k-block index `base` and has `nkb` blocks.
+__device__ __forceinline__ void split_range(int kb_total, int splits, int split, int base, int nkb,
+                                            int& lo, int& hi) {
+  const int g_lo = static_cast<int>((static_cast<long long>(kb_total) * split) / splits);
+  const int g_hi = static_cast<int>((static_cast<long long>(kb_total) * (split + 1)) / splits);
+  lo = max(g_lo - base, 0);
+  hi = min(g_hi - base, nkb);
 }
 
 __device__ __forceinline__ void record_timeout(int role, int tile) {
@@ -197,16 +212,24 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x) {
+      const int units = p.total_tiles * p.splits;
+      for (int u = blockIdx.x; ok && u < units; u += gridDim.x) {
+        const int t = u % p.total_tiles;
+        const int split = u / p.total_tiles;
         const TileInfo ti = decode_tile(p, t);
         const Region& R = p.reg[ti.r];
         const int b_slabs = (R.bn + 63) >> 6;
         const uint32_t tx = A_STAGE_BYTES + (B_MN ? b_slabs * SLAB_BYTES : R.bn * BK * 2);
+        int kb_base = 0;
         for (int sg = 0; ok && sg < p.nseg; ++sg) {
           const CUtensorMap* ma = &p.maps[R.a_map[sg]];
           const CUtensorMap* mb = &p.maps[R.b_map[sg]];
           const int klen = p.seg_k[sg];
-          for (int kk = 0; kk < klen; kk += BK) {
+          const int nkb = (klen + BK - 1) / BK;
+          int lo, hi;
+          split_range(p.kb_total, p.splits, split, kb_base, nkb, lo, hi);
+          kb_base += nkb;
+          for (int kk = lo * BK; kk < hi * BK; kk += BK) {
             if (!mbar_wait(empty_bar(s), ph ^ 1u, abortp, WAIT_LIMIT_NS)) {
               record_timeout(1, t);
               ok = false;
@@ -243,7 +266,10 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t ph = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < p.total_tiles; t += gridDim.x, ++it) {
+      const int units = p.total_tiles * p.splits;
+      for (int u = blockIdx.x; ok && u < units; u += gridDim.x, ++it) {
+        const int t = u % p.total_tiles;
+        const int split = u / p.total_tiles;
         const TileInfo ti = decode_tile(p, t);
         const Region& R = p.reg[ti.r];
         const uint32_t idesc = umma_idesc_bf16(BM, R.bn, A_MN ? 1 : 0, B_MN ? 1 : 0);
@@ -256,9 +282,14 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN_MAX);
         uint32_t accumulate = 0;
+        int kb_base = 0;
         for (int sg = 0; ok && sg < p.nseg; ++sg) {
           const int klen = p.seg_k[sg];
-          for (int kk = 0; kk < klen; kk += BK) {
+          const int nkb = (klen + BK - 1) / BK;
+          int lo, hi;
+          split_range(p.kb_total, p.splits, split, kb_base, nkb, lo, hi);
+          kb_base += nkb;
+          for (int kk = lo * BK; kk < hi * BK; kk += BK) {
             if (!mbar_wait(full_bar(s), ph, abortp, WAIT_LIMIT_NS)) {
               record_timeout(2, t);
               ok = false;
@@ -294,9 +325,20 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
     // --------------------------------------------------------------- epilogue
     const int q = warp & 3;   // TMEM lane quarter this warp may read
     int it = 0;
-    for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++it) {
+    const int units = p.total_tiles * p.splits;
+    for (int u = blockIdx.x; u < units; u += gridDim.x, ++it) {
+      const int t = u % p.total_tiles;
+      const int split = u / p.total_tiles;
       const TileInfo ti = decode_tile(p, t);
-      const Region& R = p.reg[ti.r];
+      Region R = p.reg[ti.r];
+      if (p.splits > 1) {
+        // partial sums go to this split's slice of the workspace; wsl_splitk_reduce folds
+        // them into the real output in a fixed order afterwards
+        R.out = p.workspace + R.ws_off + static_cast<long long>(split) * R.rows * R.cols;
+        R.ld = R.cols;
+        R.mode = kEpiStoreF32;
+        R.alpha = 1.f;
+      }
       const int buf = it & 1;
       const uint32_t tph = (static_cast<uint32_t>(it) >> 1) & 1u;
       bool ok = mbar_wait(tfull_bar(buf), tph, abortp, WAIT_LIMIT_NS);
@@ -340,6 +382,48 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// Fold split-K partials into the output in a fixed order (deterministic):
+//   out[i,j] (op)= alpha * (ws[0][i,j] + ws[1][i,j] + ... + ws[S-1][i,j])
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float4* __restrict__ ws, void* out, long long ld, int rows, int cols4,
+                     int splits, int mode, float alpha) {
+  const long long per = static_cast<long long>(rows) * cols4;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < per; i += gridDim.x * 256ll) {
+    float4 a = ws[i];
+    for (int s = 1; s < splits; ++s) {
+      const float4 b = ws[s * per + i];
+      a.x += b.x;
+      a.y += b.y;
+      a.z += b.z;
+      a.w += b.w;
+    }
+    a.x *= alpha;
+    a.y *= alpha;
+    a.z *= alpha;
+    a.w *= alpha;
+    const long long r = i / cols4;
+    const int c = static_cast<int>(i - r * cols4) * 4;
+    if (mode == kEpiStoreBf16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(a.z, a.w);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + r * ld + c) = pk;
+    } else {
+      float4* dst = reinterpret_cast<float4*>(static_cast<float*>(out) + r * ld + c);
+      if (mode == kEpiAccumF32) {
+        const float4 o = *dst;
+        a.x += o.x;
+        a.y += o.y;
+        a.z += o.z;
+        a.w += o.w;
+      }
+      *dst = a;
+    }
   }
 }
 
@@ -408,6 +492,38 @@ static int make_map_bf16(CUtensorMap* m, const Mat& t, int box_cols, int box_row
   return r == CUDA_SUCCESS ? WSL_OK : WSL_ERR_DRIVER;
 }
 
+// Split-K factor for a launch of `tiles` output tiles with `kb_total` k-blocks each. Cost
+// model per S: waves * k-blocks-per-unit (one k-block of one tile ~ 0.27 us) plus the
+// workspace round trip (S partial copies written and read once at ~6.5 MB/us) and the
+// second launch. S = 1 when the tile grid already fills the SMs twice over.
+int choose_splits(double tiles, int kb_total, long long out_elems, size_t ws_limit_bytes,
+                  int num_sms) {
+  if (tiles >= 2.0 * num_sms) return 1;
+  double best = 1e30;
+  int best_s = 1;
+  for (int S = 1; S <= 16 && S * 8 <= kb_total; ++S) {
+    if (S > 1 && static_cast<size_t>(S) * out_elems * 4 > ws_limit_bytes) break;
+    const double waves = ceil(tiles * S / num_sms - 1e-9);
+    double t = waves * ((kb_total + S - 1) / S) * 0.27;
+    if (S > 1) t += 2.0 * S * out_elems * 4 / 6.5e6 + 3.0;
+    if (t < best) {
+      best = t;
+      best_s = S;
+    }
+  }
+  return best_s;
+}
+
+// Tile count of one output region (BM x up-to-256 tiles), weighted by the relative cost of
+// a tile: narrow tiles (bn < 256) are bound by their operand loads, not by the MMAs.
+double region_tiles(long long mo, long long no) {
+  const long long n_tiles = (no + BN_MAX - 1) / BN_MAX;
+  const double bn = static_cast<double>((no + n_tiles - 1) / n_tiles);
+  const double w = bn / BN_MAX < 0.35 ? 0.35 : bn / BN_MAX;
+  return static_cast<double>(((mo + BM - 1) / BM) * n_tiles) * w;
+}
+int kblocks(long long k) { return static_cast<int>((k + BK - 1) / BK); }
+
 template <bool A_MN, bool B_MN>
 static int launch_variant(const GemmParams& p, int grid, cudaStream_t stream) {
   static bool attr_set = false;   // per instantiation
@@ -467,6 +583,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     R.ld = rd.ld_out;
     R.mode = rd.mode;
     R.alpha = rd.alpha;
+    R.ws_off = 0;
     tiles += m_tiles * n_tiles;
     for (int s = 0; s < kMaxSeg; ++s) {
       R.a_map[s] = 0;
@@ -490,6 +607,27 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     }
   }
   p.total_tiles = static_cast<int>(tiles);
+  int kb_total = 0;
+  for (int sgi = 0; sgi < g.nseg; ++sgi) kb_total += (g.seg_k[sgi] + BK - 1) / BK;
+  p.kb_total = kb_total;
+  p.splits = 1;
+  p.workspace = nullptr;
+  if (g.workspace != nullptr) {
+    long long out_elems = 0;
+    for (int r = 0; r < g.nregion; ++r) out_elems += g.region[r].mo * g.region[r].no;
+    double eff_tiles = 0.0;
+    for (int r = 0; r < g.nregion; ++r) eff_tiles += region_tiles(g.region[r].mo, g.region[r].no);
+    const int S = choose_splits(eff_tiles, kb_total, out_elems, g.workspace_bytes, g_num_sms);
+    if (S > 1) {
+      p.splits = S;
+      p.workspace = g.workspace;
+      long long off = 0;
+      for (int r = 0; r < g.nregion; ++r) {
+        p.reg[r].ws_off = off;
+        off += static_cast<long long>(S) * g.region[r].mo * g.region[r].no;
+      }
+    }
+  }
   p.mn_lbo = SLAB_BYTES;
   p.mn_sbo = 1024;
   if (const char* e = getenv("WSL_DBG_MN_SWAP")) {
@@ -498,12 +636,26 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       p.mn_sbo = SLAB_BYTES;
     }
   }
-  const int grid = static_cast<int>(tiles < g_num_sms ? tiles : g_num_sms);
+  const long long units = tiles * p.splits;
+  const int grid = static_cast<int>(units < g_num_sms ? units : g_num_sms);
 
-  if (g.a_mn && g.b_mn) return launch_variant<true, true>(p, grid, stream);
-  if (!g.a_mn && g.b_mn) return launch_variant<false, true>(p, grid, stream);
-  if (!g.a_mn && !g.b_mn) return launch_variant<false, false>(p, grid, stream);
-  return launch_variant<true, false>(p, grid, stream);
+  if (g.a_mn && g.b_mn) st = launch_variant<true, true>(p, grid, stream);
+  else if (!g.a_mn && g.b_mn) st = launch_variant<false, true>(p, grid, stream);
+  else if (!g.a_mn && !g.b_mn) st = launch_variant<false, false>(p, grid, stream);
+  else st = launch_variant<true, false>(p, grid, stream);
+  if (st != WSL_OK || p.splits == 1) return st;
+  for (int r = 0; r < g.nregion; ++r) {
+    const RegionDesc& rd = g.region[r];
+    const long long per = rd.mo * (rd.no / 4);
+    long long blocks = (per + 255) / 256;
+    if (blocks > 8ll * g_num_sms) blocks = 8ll * g_num_sms;
+    splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        reinterpret_cast<const float4*>(p.workspace + p.reg[r].ws_off), rd.out, rd.ld_out,
+        static_cast<int>(rd.mo), static_cast<int>(rd.no / 4), p.splits, rd.mode, rd.alpha);
+    if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
+    ++g_launch_count;
+  }
+  return WSL_OK;
 }
 
 }  // namespace wsl

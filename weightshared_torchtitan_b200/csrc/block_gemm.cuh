@@ -47,7 +47,16 @@ struct GemmDesc {
   int seg_k[kMaxSeg];   // contraction length of each segment (same for all regions)
   int nregion;
   RegionDesc region[kMaxRegion];
+  // Optional scratch for split-K (fp32, 16-byte aligned). When the tile grid is too small
+  // to fill the GPU the contraction is split, partials land here and a second kernel folds
+  // them into the outputs in a fixed order. nullptr disables splitting.
+  float* workspace;
+  size_t workspace_bytes;
 };
+
+// Workspace that lets launch_block_gemm split any contraction of these output sizes up to
+// its maximum factor (16): 16 * 4 * sum(mo * no) bytes.
+inline size_t splitk_workspace_bytes(long long out_elems) { return static_cast<size_t>(out_elems) * 64u; }
 
 // Enqueues the GEMM on `stream`. Returns a WSL_* status code (include/wsl.h).
 int launch_block_gemm(const GemmDesc& g, cudaStream_t stream);

@@ -239,7 +239,8 @@ int wsl_lora_linear_bwd_dx(int nproj, const void* const* dY, const long long* ld
 int wsl_lora_linear_bwd_dw(const void* dY, long long lddy, const void* U, long long ldu,
                            const void* x, long long ldx, const void* T, long long ldt, float* dW,
                            float* dA, float* dB, long long M, long long N, long long K,
-                           long long r, int dtype, void* stream) {
+                           long long r, void* workspace, unsigned long long workspace_bytes,
+                           int dtype, void* stream) {
   if (bad_dtype(dtype) || M <= 0 || N <= 0 || K <= 0 || r < 0) return WSL_ERR_BAD_ARG;
   if (r == 0 && (dA || dB)) return WSL_ERR_BAD_ARG;
   if (!dW && !dA && !dB) return WSL_ERR_BAD_ARG;
@@ -298,7 +299,24 @@ int wsl_lora_linear_bwd_dw(const void* dY, long long lddy, const void* U, long l
     rd.alpha = 1.f;
   }
   g.nregion = nr;
+  if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return WSL_ERR_ALIGN;
+  g.workspace = static_cast<float*>(workspace);
+  g.workspace_bytes = static_cast<size_t>(workspace_bytes);
   return launch_block_gemm(g, s);
+}
+
+unsigned long long wsl_bwd_dw_workspace_bytes(long long M, long long N, long long K, long long r,
+                                              int want_dW, int want_dA, int want_dB) {
+  if (M <= 0 || N <= 0 || K <= 0 || r < 0) return 0;
+  double tiles = 0.0;
+  long long out_elems = 0;
+  if (want_dW) { tiles += region_tiles(N, K); out_elems += N * K; }
+  if (want_dB && r > 0) { tiles += region_tiles(N, r); out_elems += N * r; }
+  if (want_dA && r > 0) { tiles += region_tiles(r, K); out_elems += r * K; }
+  if (out_elems == 0) return 0;
+  const int sms = device_check() == WSL_OK ? device_sm_count() : 148;
+  const int S = choose_splits(tiles, kblocks(M), out_elems, ~static_cast<size_t>(0), sms);
+  return S > 1 ? static_cast<unsigned long long>(S) * out_elems * 4ull : 0ull;
 }
 
 int wsl_embed_gather(const long long* tokens, const void* E_small, void* G, long long M,

@@ -224,13 +224,20 @@ def lora_linear_bwd_dw(dY: torch.Tensor, U: Optional[torch.Tensor], x: torch.Ten
         if g is not None:
             if g.dtype != torch.float32 or not g.is_contiguous() or tuple(g.shape) != shape:
                 raise ValueError(f"{nm} must be a contiguous float32 tensor of shape {shape}")
+    ws_bytes = 0
+    ws = None
+    if code == WSL_BF16:
+        ws_bytes = int(_lib.lib().wsl_bwd_dw_workspace_bytes(M, N, K, r, int(dW is not None),
+                                                             int(dA is not None), int(dB is not None)))
+        if ws_bytes:
+            ws = torch.empty(ws_bytes // 4, device=dY.device, dtype=torch.float32)
     _e = _tic()
     st = _lib.lib().wsl_lora_linear_bwd_dw(
         dY.data_ptr(), _ld(dY), up, ldu, x.data_ptr(), _ld(x), tp, ldt,
         dW.data_ptr() if dW is not None else None,
         dA.data_ptr() if dA is not None else None,
         dB.data_ptr() if dB is not None else None,
-        M, N, K, r, code, _stream())
+        M, N, K, r, ws.data_ptr() if ws is not None else None, ws_bytes, code, _stream())
     _toc(_e, "dw", 2.0 * M * ((N * K if dW is not None else 0) + (r * K if dA is not None else 0) + (N * r if dB is not None else 0)), dY.element_size() * (M * N + M * K + 2 * M * r) + 8.0 * ((N * K if dW is not None else 0) + (r * K if dA is not None else 0) + (N * r if dB is not None else 0)))
     _lib.check(st, "wsl_lora_linear_bwd_dw")
 
