@@ -43,6 +43,8 @@ extern "C" {
 #define WSL_BF16 0
 #define WSL_F32 1
 
+#define WSL_NOALLOC_SCRATCH_BYTES (64ull << 20) /* fixed scratch of wsl_lora_linear_bwd_dw_noalloc */
+
 #define WSL_MAX_PROJ 3 /* projections that can share one input in wsl_lora_linear_bwd_dx */
 
 /* Library version, (major << 16) | minor. */
@@ -146,6 +148,33 @@ int wsl_lora_linear_bwd_dw(const void* dY, long long lddy, const void* U, long l
  * want_* flags say which of dW, dA, dB will be non-NULL. No reference counterpart. */
 unsigned long long wsl_bwd_dw_workspace_bytes(long long M, long long N, long long K, long long r,
                                               int want_dW, int want_dA, int want_dB);
+
+/*
+ * wsl_lora_linear_bwd_dw for callers that cannot allocate (bf16 mode only).
+ * No counterpart in the reference: it exists for hosts that may not call cudaMalloc (or
+ * any allocator) around this call -- a pipeline whose memory was all handed out at
+ * start-up, a callback, a foreign-language binding that only owns the tensors it was
+ * given -- and therefore cannot supply the split-K workspace of the entry point above.
+ * The partial sums live in a WSL_NOALLOC_SCRATCH_BYTES (64 MiB) array that is part of the
+ * library image; every GPU that loads the library holds it until the process exits. The
+ * call itself allocates and frees nothing.
+ *   - Limit: 2 * 4 bytes * (elements of the requested dW, dA, dB) must not exceed the
+ *     array, i.e. about 8.3 M output elements; larger requests return WSL_ERR_TOO_LARGE
+ *     (weight matrices that big fill the GPU without a split: use the entry point above
+ *     with a NULL workspace).
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call before any
+ *     stream capture begins.
+ *   - All calls share the one array and it keeps the previous call's partial sums. Every
+ *     element a call reads back it has written first, so nothing needs clearing between
+ *     calls, but two calls that overlap on the GPU (different streams, or graphs replayed
+ *     concurrently) race on it; serialise them.
+ * Same arithmetic and result as wsl_lora_linear_bwd_dw.
+ */
+int wsl_lora_linear_bwd_dw_noalloc(const void* dY, long long lddy, const void* U, long long ldu,
+                                   const void* x, long long ldx, const void* T, long long ldt,
+                                   float* dW, float* dA, float* dB, long long M, long long N,
+                                   long long K, long long r, void* stream);
 
 /*
  * G[M,r_e] = E_small[tokens[m], :]          (bit-exact row gather)

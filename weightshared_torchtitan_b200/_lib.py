@@ -43,6 +43,7 @@ SIGNATURES = {
     "wsl_lora_linear_bwd_dx": (_i, [_i, _vpp, _llp, _vpp, _llp, _vpp, _vpp, _llp, _llp, _vp, _ll, _ll, _ll, _i, _vp]),
     "wsl_lora_linear_bwd_dw": (_i, [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _ll, _ll, _ll,
                                     _vp, ctypes.c_ulonglong, _i, _vp]),
+    "wsl_lora_linear_bwd_dw_noalloc": (_i, [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _vp]),
     "wsl_bwd_dw_workspace_bytes": (ctypes.c_ulonglong, [_ll, _ll, _ll, _ll, _i, _i, _i]),
     "wsl_embed_gather": (_i, [_vp, _vp, _vp, _ll, _ll, _ll, _i, _vp]),
     "wsl_embed_scatter_add": (_i, [_vp, _vp, _vp, _ll, _ll, _ll, _i, _vp]),

@@ -4,6 +4,7 @@
 #include "block_gemm.cu"
 #include "simt_gemm.cu"
 #include "embed.cu"
+#include "static_scratch.cu"
 
 namespace wsl {
 int launch_simt_gemm_f32(const float* A, long long sai, long long sak, const float* B,
