@@ -110,7 +110,7 @@ def _build_tiny(dtype):
                       vocab_size=a.vocab_size, embed_rank=a.embed_rank, max_seq_len=a.max_seq_len,
                       loss_chunk=16)
     m = WeightSharedDecoder(c).cuda()
-    m.load_oracle_params({k: v.cuda() for k, v in p.items()})
+    m.load_named_params({k: v.cuda() for k, v in p.items()})
     m.compute_dtype = dtype
     return a, p, m
 

@@ -1,0 +1,205 @@
+"""CPU tests: the C-ABI library loads and exports every symbol include/wsl.h declares (no
+compute without a GPU), host-side logic (modules' structure, converter, arena, cache), and
+the product's refusal to run without its CUDA library or on CPU tensors."""
+import os
+import re
+import types
+
+import pytest
+import torch
+import torch.nn as nn
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _header_symbols():
+    text = open(os.path.join(ROOT, "include", "wsl.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(wsl_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from weightshared_torchtitan_b200 import _lib
+    lib = _lib.lib()
+    declared = _header_symbols()
+    assert len(declared) >= 14
+    for name in declared:
+        assert hasattr(lib, name), name
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert set(_lib.SIGNATURES) == set(declared)
+    assert lib.wsl_version() > 0
+    assert _lib.status_string(0) == "ok"
+    for code in range(-7, 0):
+        assert _lib.status_string(code) != "unknown status"
+
+
+def test_argument_validation_needs_no_device():
+    from weightshared_torchtitan_b200 import _lib
+    lib = _lib.lib()
+    assert lib.wsl_linear_fwd(None, 8, None, None, 8, 1, 8, 8, 0, 0, None) == _lib.WSL_ERR_BAD_ARG
+    assert lib.wsl_lora_prepass(None, 8, None, None, 8, 0, 8, 8, 2.0, 0, None) == _lib.WSL_ERR_BAD_ARG
+    assert lib.wsl_lora_linear_bwd_dw_noalloc(None, 0, None, 0, None, 0, None, 0, None, None, None,
+                                              1, 1, 1, 0, None) == _lib.WSL_ERR_BAD_ARG
+    assert lib.wsl_bwd_dw_workspace_bytes(32768, 1024, 1024, 16, 1, 1, 1) > 0
+    assert lib.wsl_bwd_dw_workspace_bytes(16384, 12288, 4096, 64, 1, 1, 1) == 0
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU behaviour")
+def test_no_cpu_fallback():
+    from weightshared_torchtitan_b200 import _lib, ops
+    from weightshared_torchtitan_b200.modules import LoRAModule
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        ops.linear_fwd(torch.zeros(8, 8), torch.zeros(8, 8))
+    with pytest.raises(RuntimeError):
+        LoRAModule(16, 16, rank=8)(torch.zeros(2, 16))
+    x = torch.zeros(1)
+    st = _lib.lib().wsl_linear_fwd(x.data_ptr(), 8, x.data_ptr(), x.data_ptr(), 8, 8, 8, 8, 0, 0, None)
+    assert st == _lib.WSL_ERR_DEVICE
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from weightshared_torchtitan_b200 import _lib
+    monkeypatch.setattr(_lib, "_LIB", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libwsl.so"))
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.lib()
+
+
+def test_product_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "weightshared_torchtitan_b200")
+    for root, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith(".py"):
+                src = open(os.path.join(root, f)).read()
+                assert not re.search(r"^\s*(from|import)\s+oracle\b", src, flags=re.M), f
+                assert "lora_oracle" not in src, f
+
+
+def test_lora_module_structure_matches_reference_naming():
+    from weightshared_torchtitan_b200.modules import LoRAModule, SharedLoRALinear
+    base = nn.Linear(32, 48, bias=False)
+    a, b = LoRAModule(32, 48, rank=8), LoRAModule(32, 48, rank=8)
+    m1, m2 = SharedLoRALinear(base, a), SharedLoRALinear(base, b)
+    assert m1.base is m2.base
+    assert sorted(n for n, _ in m1.named_parameters()) == ["base.weight", "offset.w_a.weight", "offset.w_b.weight"]
+    assert a.alpha / a.rank == 2.0
+    with pytest.raises(ValueError):
+        SharedLoRALinear(nn.Linear(32, 24, bias=False), a)      # head-sharing widths stay eager
+    holder = nn.ModuleList([m1, m2])
+    assert sum(p.numel() for p in holder.parameters()) == 32 * 48 + 2 * (8 * 32 + 48 * 8)   # W counted once
+
+
+def test_broadcast_add_product_equals_oracle_on_cpu():
+    from oracle import lora_oracle as O
+    from weightshared_torchtitan_b200.modules import broadcast_add
+    g = torch.Generator().manual_seed(2)
+    for gg, H, D in ((1, 4, 8), (2, 8, 4), (4, 4, 16), (2, 2, 8)):
+        base = torch.randn(2, 7, gg * D, generator=g)
+        delta = torch.randn(2, 7, H * D, generator=g)
+        assert torch.equal(broadcast_add(base, delta, dim=-1, g=gg), O.broadcast_add(base, delta, dim=-1, g=gg))
+
+
+def test_copy_cache_refreshes_on_update():
+    from weightshared_torchtitan_b200.modules import CopyCache
+    c = CopyCache()
+    p = nn.Parameter(torch.ones(4, 4))
+    a = c.get(torch.bfloat16, p)
+    assert c.get(torch.bfloat16, p) is a
+    with torch.no_grad():
+        p.add_(1.0)
+    b = c.get(torch.bfloat16, p)
+    assert b is not a and float(b[0, 0]) == 2.0
+    q = nn.Parameter(torch.zeros(2, 4))
+    cat = c.get(torch.bfloat16, p, q)
+    assert cat.shape == (6, 4)
+    assert c.get(torch.float32, p).data_ptr() == p.data_ptr()
+
+
+class _TinyAttn(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.wq, self.wk, self.wv, self.wo = (nn.Linear(16, 16, bias=False) for _ in range(4))
+
+
+class _TinyFfn(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.w1, self.w2, self.w3 = nn.Linear(16, 32, bias=False), nn.Linear(32, 16, bias=False), nn.Linear(16, 32, bias=False)
+
+
+class _TinyBlock(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.attention, self.feed_forward = _TinyAttn(), _TinyFfn()
+
+
+class _TinyModel(nn.Module):
+    def __init__(self, n):
+        super().__init__()
+        self.tok_embeddings = nn.Embedding(64, 16)
+        self.layers = nn.ModuleDict({str(i): _TinyBlock() for i in range(n)})
+
+
+def test_converter_shares_bases_cyclically():
+    from weightshared_torchtitan_b200 import converter as C
+    from weightshared_torchtitan_b200.modules import FactorizedEmbedding, SharedLoRALinear
+    job = types.SimpleNamespace(model=types.SimpleNamespace(converters=["shared_lora"]),
+                                shared_lora=types.SimpleNamespace(n_unique=2, rank=8, embed_rank=8))
+    model = _TinyModel(6)
+    conv = C.build_model_converters(job, None)
+    conv.convert(model)
+    L = [model.layers[str(i)] for i in range(6)]
+    for l in range(6):
+        for n in ("wq", "wk", "wv", "wo"):
+            m = getattr(L[l].attention, n)
+            assert isinstance(m, SharedLoRALinear)
+            assert m.base is getattr(L[l % 2].attention, n).base
+            assert m.offset is not getattr(L[(l + 2) % 6].attention, n).offset
+        assert L[l].feed_forward.w2.base is L[l % 2].feed_forward.w2.base
+    assert isinstance(model.tok_embeddings, FactorizedEmbedding)
+    names = [n for n, _ in model.named_parameters()]
+    assert "layers.0.attention.wq.base.weight" in names and "layers.3.attention.wq.offset.w_a.weight" in names
+    assert not any(n.startswith("layers.2.") and ".base." in n for n in names)      # shared: listed once
+    n_base = sum(1 for n in names if n.endswith(".base.weight"))
+    assert n_base == 2 * 7                                   # 6 layers, 2 unique blocks, 7 projections
+    conv.post_optimizer_hook(model)
+    with pytest.raises(AssertionError):
+        C.register_model_converter(C.SharedLoRAConverter, "shared_lora")
+
+
+def test_grad_arena_layout_and_clip():
+    from weightshared_torchtitan_b200.decoder import DecoderConfig, WeightSharedDecoder
+    from weightshared_torchtitan_b200.dp import GradArena, shard_tokens
+    m = WeightSharedDecoder(DecoderConfig(dim=32, hidden_dim=64, n_layers=4, n_unique=2, n_heads=2, n_kv_heads=1,
+                                          head_dim=16, rank=8, vocab_size=64, embed_rank=16, max_seq_len=8))
+    a = GradArena(m)
+    labels = [s[0] for s in a.section_bounds]
+    assert labels == ["shared", "adapters", "embedding", "other"]
+    assert a.section_bounds[0][1] == 0 and a.section_bounds[-1][2] == a.buffer.numel()
+    for (_, b0, e0), (_, b1, _) in zip(a.section_bounds, a.section_bounds[1:]):
+        assert e0 == b1
+    for p, off in zip(a.params, a.offsets):
+        assert off % 64 == 0 and p.grad.data_ptr() == a.buffer.data_ptr() + 4 * off
+    assert len(a.params) == len(list(m.parameters()))       # shared weights appear once
+    a.buffer.fill_(1.0)
+    n = a.clip_(1.0)
+    assert abs(n.item() - a.buffer.numel() ** 0.5) < 1e-2
+    assert abs(a.grad_norm().item() - 1.0) < 1e-3
+    a.zero()
+    a.check_attached()
+    m.zero_grad(set_to_none=True)
+    with pytest.raises(RuntimeError):
+        a.check_attached()
+    assert shard_tokens(16, 3, 4) == (12, 16)
+    with pytest.raises(ValueError):
+        shard_tokens(10, 0, 4)
+
+
+def test_flops_formula():
+    from weightshared_torchtitan_b200.decoder import CONFIGS, flops_per_token, proj_shapes
+    c = CONFIGS["qwen3-8b-ws"]
+    f = flops_per_token(c, 8192)
+    per_layer = sum(6 * o * i + 6 * c.rank * (o + i) for o, i in proj_shapes(c).values())
+    assert f["linear"] == per_layer * 36
+    # SURVEY table: 19.44 TF per layer at M = 16384
+    assert abs(per_layer * 16384 / 1e12 - 19.44) < 0.05

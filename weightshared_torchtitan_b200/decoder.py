@@ -181,8 +181,8 @@ class WeightSharedDecoder(nn.Module):
         self.output.weight.normal_(0.0, self.config.dim ** -0.5, generator=g)
 
     @torch.no_grad()
-    def load_oracle_params(self, p: Dict[str, torch.Tensor]) -> None:
-        """Copy a parameter dictionary in the naming of the oracle's decoder
+    def load_named_params(self, p: Dict[str, torch.Tensor]) -> None:
+        """Copy a parameter dictionary in the flat naming used by the parity tests
         (blocks.{u}.{proj}.weight, layers.{l}.{proj}.w_a / .w_b, norms, embed.*, output)."""
         for u, blk in enumerate(self.blocks):
             for name in PROJ_NAMES:
