@@ -75,8 +75,7 @@ struct GemmParams {
   int splits;         // split-K factor: work units = total_tiles * splits
   int kb_total;       // k-blocks summed over the segments
   float* workspace;   // [splits][rows x cols] fp32 partials per region when splits > 1
-  int mn_lbo;   // descriptor offsets of MN-major operand tiles (bytes)
-  int mn_sbo;
+  int dbg;            // debug bits: 1 skip epilogue stores, 2 skip TMA loads, 4 skip MMAs
 };
 
 struct TileInfo {
@@ -84,21 +83,6 @@ struct TileInfo {
   int m0;
   int n0;
 };
-
-__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int t) {
-  int r = 0;
-  while (r + 1 < p.nregion && t >= p.reg[r + 1].tile_begin) ++r;
-  const Region& R = p.reg[r];
-  const int lt = t - R.tile_begin;
-  const int per_group = RASTER_GROUP * R.n_tiles;
-  const int g = lt / per_group;
-  const int first_m = g * RASTER_GROUP;
-  const int gsz = min(R.m_tiles - first_m, RASTER_GROUP);
-  const int rem = lt - g * per_group;
-  const int mt = first_m + rem % gsz;
-  const int nt = rem / gsz;
-  return {r, mt * BM, nt * R.bn};
-}
 
 // Segment-local k-block range [lo, hi) that split `split` of `splits` owns, given that the
 // segment starts at flattened k-block index `base` and has `nkb` blocks.
@@ -165,118 +149,199 @@ __device__ __forceinline__ void epilogue_store(const Region& R, int row, int col
   }
 }
 
-template <bool A_MN, bool B_MN>
+// Per-variant constants. PAIR = two CTAs (a cluster of 2, tcgen05 cta_group::2) share one
+// 256 x bn tile: each CTA owns 128 rows of A and of the accumulator and loads HALF of the
+// B tile, so a stage is 32 KiB (6-deep ring) instead of 48 KiB (4-deep).
+template <bool PAIR>
+struct Cfg {
+  static constexpr int kStages = PAIR ? 6 : 4;
+  static constexpr int kBStageBytes = PAIR ? B_STAGE_BYTES / 2 : B_STAGE_BYTES;
+  static constexpr int kStageBytes = A_STAGE_BYTES + kBStageBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+  static constexpr int kTileM = PAIR ? 2 * BM : BM;
+  static constexpr int kRasterGroup = PAIR ? RASTER_GROUP / 2 : RASTER_GROUP;
+};
+
+template <bool PAIR>
+__device__ __forceinline__ TileInfo decode_tile_t(const GemmParams& p, int t) {
+  int r = 0;
+  while (r + 1 < p.nregion && t >= p.reg[r + 1].tile_begin) ++r;
+  const Region& R = p.reg[r];
+  const int lt = t - R.tile_begin;
+  constexpr int G = Cfg<PAIR>::kRasterGroup;
+  const int per_group = G * R.n_tiles;
+  const int g = lt / per_group;
+  const int first_m = g * G;
+  const int gsz = min(R.m_tiles - first_m, G);
+  const int rem = lt - g * per_group;
+  const int mt = first_m + rem % gsz;
+  const int nt = rem / gsz;
+  return {r, mt * Cfg<PAIR>::kTileM, nt * R.bn};
+}
+
+// Role loops are executed by ALL 32 lanes of their warp with warp-uniform control flow;
+// only the TMA / MMA / commit instructions themselves are issued by one elected lane.
+// (A loop run by a single lane of a diverged warp keeps its state in per-thread registers
+// and pays a vector-to-uniform register move in front of every tcgen05.mma operand; the
+// issuing thread then cannot keep the tensor pipe fed.)
+template <bool A_MN, bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 block_gemm_kernel(const __grid_constant__ GemmParams p) {
+  using C = Cfg<PAIR>;
+  constexpr int S = C::kStages;
   extern __shared__ __align__(1024) uint8_t smem_dyn[];
-  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ __align__(8) uint64_t bars[2 * S + 4];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
+  // Clusters of 2 are consecutive blocks of the 1-D grid: rank 0 is the leader.
+  const int rank = PAIR ? static_cast<int>(blockIdx.x & 1u) : 0;
+  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int nworkers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
-  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
-  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * S + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * S + 2 + b); };
   volatile int* abortp = &abort_flag;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < S; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 4);
+      mbar_init(tempty_bar(b), PAIR ? 8 : 4);   // one arrival per epilogue warp (of both CTAs)
     }
     fence_barrier_init();
     fence_proxy_async_smem();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_smem), TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(&tmem_base_smem), TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(&tmem_base_smem), TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_base_smem);
+  const int units = p.total_tiles * p.splits;
+  const int dbg = p.dbg;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (elect_one())
       for (int i = 0; i < p.nregion * p.nseg * 2 && i < kMaxMaps; ++i) tma_prefetch_desc(&p.maps[i]);
-      int s = 0;
-      uint32_t ph = 0;
-      bool ok = true;
-      const int units = p.total_tiles * p.splits;
-      for (int u = blockIdx.x; ok && u < units; u += gridDim.x) {
-        const int t = u % p.total_tiles;
-        const int split = u / p.total_tiles;
-        const TileInfo ti = decode_tile(p, t);
-        const Region& R = p.reg[ti.r];
-        const int b_slabs = (R.bn + 63) >> 6;
-        const uint32_t tx = A_STAGE_BYTES + (B_MN ? b_slabs * SLAB_BYTES : R.bn * BK * 2);
-        int kb_base = 0;
-        for (int sg = 0; ok && sg < p.nseg; ++sg) {
-          const CUtensorMap* ma = &p.maps[R.a_map[sg]];
-          const CUtensorMap* mb = &p.maps[R.b_map[sg]];
-          const int klen = p.seg_k[sg];
-          const int nkb = (klen + BK - 1) / BK;
-          int lo, hi;
-          split_range(p.kb_total, p.splits, split, kb_base, nkb, lo, hi);
-          kb_base += nkb;
-          for (int kk = lo * BK; kk < hi * BK; kk += BK) {
-            if (!mbar_wait(empty_bar(s), ph ^ 1u, abortp, WAIT_LIMIT_NS)) {
-              record_timeout(1, t);
-              ok = false;
-              break;
-            }
-            const uint32_t fb = full_bar(s);
-            mbar_arrive_expect_tx(fb, tx);
-            const uint32_t sa = smem_base + s * STAGE_BYTES;
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int u = worker; ok && u < units; u += nworkers) {
+      const int t = u % p.total_tiles;
+      const int split = u / p.total_tiles;
+      const TileInfo ti = decode_tile_t<PAIR>(p, t);
+      const Region& R = p.reg[ti.r];
+      const int b_rows = PAIR ? (R.bn >> 1) : R.bn;          // B rows this CTA loads
+      const int b_slabs = (b_rows + 63) >> 6;
+      const uint32_t tx_cta = A_STAGE_BYTES + (B_MN ? b_slabs * SLAB_BYTES : b_rows * BK * 2);
+      const int m0 = ti.m0 + BM * rank;
+      const int n0 = ti.n0 + b_rows * rank;
+      int kb_base = 0;
+      for (int sg = 0; ok && sg < p.nseg; ++sg) {
+        const CUtensorMap* ma = &p.maps[R.a_map[sg]];
+        const CUtensorMap* mb = &p.maps[R.b_map[sg]];
+        const int klen = p.seg_k[sg];
+        const int nkb = (klen + BK - 1) / BK;
+        int lo, hi;
+        split_range(p.kb_total, p.splits, split, kb_base, nkb, lo, hi);
+        kb_base += nkb;
+        for (int kk = lo * BK; kk < hi * BK; kk += BK) {
+          ok = __all_sync(0xffffffffu, (dbg & 16) ? mbar_wait<true>(empty_bar(s), ph ^ 1u, abortp, WAIT_LIMIT_NS)
+                                                   : mbar_wait<false>(empty_bar(s), ph ^ 1u, abortp, WAIT_LIMIT_NS));
+          if (!ok) {
+            if (lane == 0) record_timeout(1, t);
+            break;
+          }
+          if (elect_one()) {
+            const uint32_t sa = smem_base + s * C::kStageBytes;
             const uint32_t sb = sa + A_STAGE_BYTES;
-            if (A_MN) {
-              tma_load_2d(sa, ma, fb, ti.m0, kk);
-              tma_load_2d(sa + SLAB_BYTES, ma, fb, ti.m0 + 64, kk);
+            if (dbg & 2) {
+              if (rank == 0) mbar_arrive(full_bar(s));
+            } else if (PAIR) {
+              // both CTAs' bytes are counted on the leader's barrier
+              if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2u * tx_cta);
+              const uint32_t fb = map_to_cta(full_bar(s), 0);
+              if (A_MN) {
+                tma_load_2d_pair(sa, ma, fb, m0, kk);
+                tma_load_2d_pair(sa + SLAB_BYTES, ma, fb, m0 + 64, kk);
+              } else {
+                tma_load_2d_pair(sa, ma, fb, kk, m0);
+              }
+              if (B_MN) {
+                for (int j = 0; j < b_slabs; ++j)
+                  tma_load_2d_pair(sb + j * SLAB_BYTES, mb, fb, n0 + 64 * j, kk);
+              } else {
+                tma_load_2d_pair(sb, mb, fb, kk, n0);
+              }
             } else {
-              tma_load_2d(sa, ma, fb, kk, ti.m0);
+              const uint32_t fb = full_bar(s);
+              mbar_arrive_expect_tx(fb, tx_cta);
+              if (A_MN) {
+                tma_load_2d(sa, ma, fb, m0, kk);
+                tma_load_2d(sa + SLAB_BYTES, ma, fb, m0 + 64, kk);
+              } else {
+                tma_load_2d(sa, ma, fb, kk, m0);
+              }
+              if (B_MN) {
+                for (int j = 0; j < b_slabs; ++j)
+                  tma_load_2d(sb + j * SLAB_BYTES, mb, fb, n0 + 64 * j, kk);
+              } else {
+                tma_load_2d(sb, mb, fb, kk, n0);
+              }
             }
-            if (B_MN) {
-              for (int j = 0; j < b_slabs; ++j)
-                tma_load_2d(sb + j * SLAB_BYTES, mb, fb, ti.n0 + 64 * j, kk);
-            } else {
-              tma_load_2d(sb, mb, fb, kk, ti.n0);
-            }
-            if (++s == STAGES) {
-              s = 0;
-              ph ^= 1u;
-            }
+          }
+          __syncwarp();
+          if (++s == S) {
+            s = 0;
+            ph ^= 1u;
           }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // ------------------------------------- MMA issuer (leader CTA only in a pair)
+    if (!PAIR || rank == 0) {
       int s = 0;
       uint32_t ph = 0;
       int it = 0;
       bool ok = true;
-      const int units = p.total_tiles * p.splits;
-      for (int u = blockIdx.x; ok && u < units; u += gridDim.x, ++it) {
+      // Descriptor constants: K-major tiles step 32 B per MMA inside the swizzled row,
+      // MN-major tiles step 16 k-rows (2 KiB); slabs of 64 MN elements are SLAB_BYTES
+      // apart (leading offset), 8-row groups 1 KiB (stride offset).
+      const uint64_t a_hi = A_MN ? smem_desc_sw128(0, SLAB_BYTES, 1024) : smem_desc_sw128(0, 16, 1024);
+      const uint64_t b_hi = B_MN ? smem_desc_sw128(0, SLAB_BYTES, 1024) : smem_desc_sw128(0, 16, 1024);
+      constexpr uint32_t a_step = (A_MN ? 2048u : 32u) >> 4;
+      constexpr uint32_t b_step = (B_MN ? 2048u : 32u) >> 4;
+      for (int u = worker; ok && u < units; u += nworkers, ++it) {
         const int t = u % p.total_tiles;
         const int split = u / p.total_tiles;
-        const TileInfo ti = decode_tile(p, t);
+        const TileInfo ti = decode_tile_t<PAIR>(p, t);
         const Region& R = p.reg[ti.r];
-        const uint32_t idesc = umma_idesc_bf16(BM, R.bn, A_MN ? 1 : 0, B_MN ? 1 : 0);
+        const uint32_t idesc = umma_idesc_bf16(C::kTileM, R.bn, A_MN ? 1 : 0, B_MN ? 1 : 0);
         const int buf = it & 1;
         const uint32_t tph = (static_cast<uint32_t>(it) >> 1) & 1u;
-        if (!mbar_wait(tempty_bar(buf), tph ^ 1u, abortp, WAIT_LIMIT_NS)) {
-          record_timeout(2, t);
+        ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(buf), tph ^ 1u, abortp, WAIT_LIMIT_NS));
+        if (!ok) {
+          if (lane == 0) record_timeout(2, t);
           break;
         }
         tc_fence_after_sync();
@@ -290,55 +355,66 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
           split_range(p.kb_total, p.splits, split, kb_base, nkb, lo, hi);
           kb_base += nkb;
           for (int kk = lo * BK; kk < hi * BK; kk += BK) {
-            if (!mbar_wait(full_bar(s), ph, abortp, WAIT_LIMIT_NS)) {
-              record_timeout(2, t);
-              ok = false;
+            ok = __all_sync(0xffffffffu, (dbg & 16) ? mbar_wait<true>(full_bar(s), ph, abortp, WAIT_LIMIT_NS)
+                                                     : mbar_wait<false>(full_bar(s), ph, abortp, WAIT_LIMIT_NS));
+            if (!ok) {
+              if (lane == 0) record_timeout(2, t);
               break;
             }
             tc_fence_after_sync();
             const int kvalid = min(BK, klen - kk);
-            const int nk = (kvalid + 15) >> 4;
-            const uint32_t sa = smem_base + s * STAGE_BYTES;
+            const int nk = (dbg & 4) ? 0 : ((kvalid + 15) >> 4);
+            const uint32_t sa = smem_base + s * C::kStageBytes;
             const uint32_t sb = sa + A_STAGE_BYTES;
-            for (int k = 0; k < nk; ++k) {
-              // K-major: 16 bf16 = 32 B further along the 128-B swizzled row.
-              // MN-major: 16 k-rows of 128 B further; slabs of 64 MN elements are
-              // SLAB_BYTES apart (leading offset), 8-row groups 1024 B (stride offset).
-              const uint64_t adesc = A_MN ? smem_desc_sw128(sa + k * 2048, p.mn_lbo, p.mn_sbo)
-                                          : smem_desc_sw128(sa + k * 32, 16, 1024);
-              const uint64_t bdesc = B_MN ? smem_desc_sw128(sb + k * 2048, p.mn_lbo, p.mn_sbo)
-                                          : smem_desc_sw128(sb + k * 32, 16, 1024);
-              umma_bf16(d_tmem, adesc, bdesc, idesc, accumulate);
-              accumulate = 1;
+            const uint32_t a_lo = (sa & 0x3FFFFu) >> 4;
+            const uint32_t b_lo = (sb & 0x3FFFFu) >> 4;
+            if (elect_one()) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                if (k < nk) {
+                  const uint64_t adesc = a_hi | static_cast<uint64_t>(a_lo + k * a_step);
+                  const uint64_t bdesc = b_hi | static_cast<uint64_t>(b_lo + k * b_step);
+                  if (PAIR) umma_bf16_pair(d_tmem, adesc, bdesc, idesc, accumulate);
+                  else umma_bf16(d_tmem, adesc, bdesc, idesc, accumulate);
+                  accumulate = 1;
+                }
+              }
+              if (PAIR) umma_commit_pair(empty_bar(s), 3);
+              else umma_commit(empty_bar(s));
             }
-            umma_commit(empty_bar(s));
-            if (++s == STAGES) {
+            __syncwarp();
+            accumulate = nk > 0 ? 1u : accumulate;
+            if (++s == S) {
               s = 0;
               ph ^= 1u;
             }
           }
         }
-        if (ok) umma_commit(tfull_bar(buf));
+        if (ok && elect_one()) {
+          if (PAIR) umma_commit_pair(tfull_bar(buf), 3);
+          else umma_commit(tfull_bar(buf));
+        }
+        __syncwarp();
       }
     }
   } else {
     // --------------------------------------------------------------- epilogue
     const int q = warp & 3;   // TMEM lane quarter this warp may read
     int it = 0;
-    const int units = p.total_tiles * p.splits;
-    for (int u = blockIdx.x; u < units; u += gridDim.x, ++it) {
+    for (int u = worker; u < units; u += nworkers, ++it) {
       const int t = u % p.total_tiles;
       const int split = u / p.total_tiles;
-      const TileInfo ti = decode_tile(p, t);
+      const TileInfo ti = decode_tile_t<PAIR>(p, t);
       Region R = p.reg[ti.r];
       if (p.splits > 1) {
-        // partial sums go to this split's slice of the workspace; wsl_splitk_reduce folds
+        // partial sums go to this split's slice of the workspace; splitk_reduce_kernel folds
         // them into the real output in a fixed order afterwards
         R.out = p.workspace + R.ws_off + static_cast<long long>(split) * R.rows * R.cols;
         R.ld = R.cols;
         R.mode = kEpiStoreF32;
         R.alpha = 1.f;
       }
+      if (dbg & 1) R.rows = 0;   // debug: read TMEM, store nothing
       const int buf = it & 1;
       const uint32_t tph = (static_cast<uint32_t>(it) >> 1) & 1u;
       bool ok = mbar_wait(tfull_bar(buf), tph, abortp, WAIT_LIMIT_NS);
@@ -348,7 +424,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
         break;
       }
       tc_fence_after_sync();
-      const int row = ti.m0 + q * 32 + lane;
+      const int row = ti.m0 + BM * rank + q * 32 + lane;
       const uint32_t taddr =
           tmem_base + static_cast<uint32_t>(buf * BN_MAX) + (static_cast<uint32_t>(q * 32) << 16);
       for (int c = 0; c < R.bn; c += 32) {
@@ -366,7 +442,10 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(buf));
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));
+        else mbar_arrive(tempty_bar(buf));
+      }
     }
   }
 
@@ -374,14 +453,16 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
   if (*abortp != 0) {
     // Give TMA copies that are still in flight time to land before the CTA's
     // shared memory is released.
-    const uint64_t t0 = global_timer_ns();
-    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 400000ll) __nanosleep(1000);
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's shared memory and barriers stay valid until both are done
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -524,22 +605,63 @@ double region_tiles(long long mo, long long no) {
 }
 int kblocks(long long k) { return static_cast<int>((k + BK - 1) / BK); }
 
-template <bool A_MN, bool B_MN>
-static int launch_variant(const GemmParams& p, int grid, cudaStream_t stream) {
+static int g_max_clusters = 0;   // co-resident CTA pairs of the PAIR variant
+
+template <bool A_MN, bool B_MN, bool PAIR>
+static int launch_variant(const GemmParams& p, long long units, cudaStream_t stream) {
   static bool attr_set = false;   // per instantiation
-  auto kern = block_gemm_kernel<A_MN, B_MN>;
+  auto kern = block_gemm_kernel<A_MN, B_MN, PAIR>;
+  constexpr int smem = Cfg<PAIR>::kSmemBytes;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN_BYTES) !=
-        cudaSuccess) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
       cudaGetLastError();
       return WSL_ERR_CUDA;
     }
     attr_set = true;
   }
-  kern<<<grid, NUM_THREADS, SMEM_DYN_BYTES, stream>>>(p);
-  if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  long long workers;
+  if (PAIR) {
+    if (g_max_clusters == 0) {
+      cfg.gridDim = dim3(2 * (g_num_sms / 2));
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = g_num_sms / 2;
+      }
+      g_max_clusters = n < g_num_sms / 2 ? n : g_num_sms / 2;
+    }
+    workers = units < g_max_clusters ? units : g_max_clusters;
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * workers));
+  } else {
+    workers = units < g_num_sms ? units : g_num_sms;
+    cfg.gridDim = dim3(static_cast<unsigned>(workers));
+  }
+  if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) {
+    cudaGetLastError();
+    return WSL_ERR_CUDA;
+  }
   ++g_launch_count;
   return WSL_OK;
+}
+
+static bool pair_mode_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("WSL_PAIR");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
 }
 
 int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
@@ -558,6 +680,10 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   for (int s = 0; s < g.nseg; ++s)
     if (g.seg_k[s] <= 0) return WSL_ERR_BAD_ARG;
 
+  // CTA pairs (256-row tiles) for the large GEMMs; single CTAs for narrow/short ones.
+  const bool pair = pair_mode_enabled() && g.region[0].mo >= 512 && g.region[0].no >= 128;
+  const int bm_tile = pair ? 2 * BM : BM;
+  const int bn_round = pair ? 32 : 16;
   int nmaps = 0;
   long long tiles = 0;
   for (int r = 0; r < g.nregion; ++r) {
@@ -570,8 +696,8 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       return WSL_ERR_ALIGN;
     const long long n_tiles = (rd.no + BN_MAX - 1) / BN_MAX;
     long long bn = (rd.no + n_tiles - 1) / n_tiles;
-    bn = (bn + 15) / 16 * 16;
-    const long long m_tiles = (rd.mo + BM - 1) / BM;
+    bn = (bn + bn_round - 1) / bn_round * bn_round;
+    const long long m_tiles = (rd.mo + bm_tile - 1) / bm_tile;
     if (m_tiles * n_tiles + tiles > 0x7fffffffLL) return WSL_ERR_TOO_LARGE;
     R.m_tiles = static_cast<int>(m_tiles);
     R.n_tiles = static_cast<int>(n_tiles);
@@ -601,7 +727,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       if (st != WSL_OK) return st;
       R.a_map[s] = static_cast<signed char>(nmaps++);
       st = g.b_mn ? make_map_bf16(&p.maps[nmaps], b, 64, BK)
-                  : make_map_bf16(&p.maps[nmaps], b, BK, static_cast<int>(bn));
+                  : make_map_bf16(&p.maps[nmaps], b, BK, static_cast<int>(pair ? bn / 2 : bn));
       if (st != WSL_OK) return st;
       R.b_map[s] = static_cast<signed char>(nmaps++);
     }
@@ -628,21 +754,16 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       }
     }
   }
-  p.mn_lbo = SLAB_BYTES;
-  p.mn_sbo = 1024;
-  if (const char* e = getenv("WSL_DBG_MN_SWAP")) {
-    if (e[0] == '1') {
-      p.mn_lbo = 1024;
-      p.mn_sbo = SLAB_BYTES;
-    }
-  }
+  p.dbg = 0;
+  if (const char* e = getenv("WSL_DBG")) p.dbg = atoi(e);
   const long long units = tiles * p.splits;
-  const int grid = static_cast<int>(units < g_num_sms ? units : g_num_sms);
-
-  if (g.a_mn && g.b_mn) st = launch_variant<true, true>(p, grid, stream);
-  else if (!g.a_mn && g.b_mn) st = launch_variant<false, true>(p, grid, stream);
-  else if (!g.a_mn && !g.b_mn) st = launch_variant<false, false>(p, grid, stream);
-  else st = launch_variant<true, false>(p, grid, stream);
+#define WSL_LAUNCH(AM, BM_) (pair ? launch_variant<AM, BM_, true>(p, units, stream) \
+                                  : launch_variant<AM, BM_, false>(p, units, stream))
+  if (g.a_mn && g.b_mn) st = WSL_LAUNCH(true, true);
+  else if (!g.a_mn && g.b_mn) st = WSL_LAUNCH(false, true);
+  else if (!g.a_mn && !g.b_mn) st = WSL_LAUNCH(false, false);
+  else st = WSL_LAUNCH(true, false);
+#undef WSL_LAUNCH
   if (st != WSL_OK || p.splits == 1) return st;
   for (int r = 0; r < g.nregion; ++r) {
     const RegionDesc& rd = g.region[r];
