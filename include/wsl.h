@@ -192,6 +192,50 @@ int wsl_embed_gather(const long long* tokens, const void* E_small, void* G, long
 int wsl_embed_scatter_add(const long long* tokens, const void* dG, float* dE, long long M,
                           long long V, long long r_e, int dtype, void* stream);
 
+/* ---- rows either side of the projections (HBM-bound streaming kernels) ---- */
+
+/*
+ * Mean-token cross-entropy, forward and gradient in one pass over the logits, IN PLACE:
+ *   row_loss[i] = logsumexp(logits[i,:]) - logits[i, labels[i]]
+ *   logits[i,j] <- scale * (softmax(logits[i,:])[j] - [j == labels[i]])
+ * logits is [rows, V] (pitch ld) in the storage type; a label outside [0, V) marks an
+ * ignored row (zero loss, zero gradient). The caller sums row_loss and passes
+ * scale = 1 / (number of counted rows).
+ * Replaces F.cross_entropy(pred.flatten(0,1).float(), labels.flatten(0,1)) and its
+ * backward: torchtitan/components/loss.py:18-22.
+ */
+int wsl_ce_fwd_bwd(void* logits, long long ld, const long long* labels, float* row_loss,
+                   long long rows, long long V, float scale, int dtype, void* stream);
+
+/*
+ * out = silu(gate) * up over n contiguous elements (n % 8 == 0 for bf16, % 4 for fp32), and
+ * its backward (dgate, dup from dout, gate, up).
+ * Replaces F.silu(self.w1(x)) * self.w3(x): torchtitan/experiments/qwen3/model/model.py:251.
+ */
+int wsl_swiglu_fwd(const void* gate, const void* up, void* out, long long n, int dtype, void* stream);
+int wsl_swiglu_bwd(const void* dout, const void* gate, const void* up, void* dgate, void* dup,
+                   long long n, int dtype, void* stream);
+
+/*
+ * y[r,:] = x[r,:] * rstd[r] * w, rstd = 1/sqrt(mean(x[r,:]^2) + eps); rstd [rows] fp32 is
+ * written for the backward (may be NULL). With rope_cos / rope_sin ([seq, D] fp32, both or
+ * neither) the normalised row is rotated: y = n*cos + rotate_half(n)*sin at position
+ * (r / heads) % seq -- the q/k head norm followed by the rotary embedding in one pass.
+ * Supported widths: D/vec a power of two <= 32 or D a multiple of 32*vec up to 8*32*vec
+ * (vec = 8 for bf16, 4 for fp32), i.e. D <= 2048 in bf16; other widths return
+ * WSL_ERR_TOO_LARGE. Rotary needs D <= 32*vec. w and dw are fp32 [D]; dw is accumulated
+ * (+=, atomics) and may be NULL.
+ * Replaces nn.RMSNorm and apply_rotary_emb:
+ * torchtitan/experiments/qwen3/model/model.py:40-90,136-143,195-203,288-289,312-313.
+ */
+int wsl_rmsnorm_fwd(const void* x, long long ldx, const float* w, void* y, long long ldy, float* rstd,
+                    long long rows, long long D, float eps, const float* rope_cos,
+                    const float* rope_sin, long long heads, long long seq, int dtype, void* stream);
+int wsl_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long ldx, const float* w,
+                    const float* rstd, void* dx, long long lddx, float* dw, long long rows,
+                    long long D, const float* rope_cos, const float* rope_sin, long long heads,
+                    long long seq, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,123 @@
+"""GPU parity of the row kernels either side of the projections (softmax cross-entropy,
+SwiGLU, RMSNorm with fused rotary embedding) against the oracle's eager PyTorch
+formulas. Tolerances: 1e-5 max-relative in fp32, 1e-2 for bf16 storage."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import lora_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def rel(a, b):
+    return O.max_rel_err(a, b)
+
+
+def leaf(t, device="cpu", dtype=None):
+    """A fresh leaf tensor (never an alias of its source) that requires grad."""
+    t = t.detach().to(device=device, dtype=dtype if dtype is not None else t.dtype, copy=True)
+    return t.requires_grad_(True)
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _dev():
+    if not torch.cuda.is_available():
+        pytest.fail("gpu tests need a CUDA device")
+    yield
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("dtype,V,tol", [(torch.float32, 1003, 1e-5), (torch.float32, 4096, 1e-5),
+                                          (torch.bfloat16, 151936, 1e-2), (torch.bfloat16, 1003, 1e-2)])
+def test_cross_entropy_forward_and_gradient(dtype, V, tol):
+    from weightshared_torchtitan_b200 import ops
+    g = torch.Generator().manual_seed(V)
+    rows = 37
+    ld = (V + 7) // 8 * 8
+    buf = torch.zeros(rows, ld)
+    buf[:, :V] = torch.randn(rows, V, generator=g) * 3
+    labels = torch.randint(0, V, (rows,), generator=g)
+    labels[5] = -100                      # ignored row, as F.cross_entropy's ignore_index
+    logits = buf.to(dtype).cuda()
+    ref_in = leaf(logits[:, :V], "cpu", torch.float32)
+    ref = F.cross_entropy(ref_in, labels, reduction="none", ignore_index=-100)
+    scale = 1.0 / 36
+    (ref.sum() * scale).backward()
+    view = logits[:, :V]
+    row_loss = ops.ce_fwd_bwd(view, labels.cuda(), scale)
+    assert rel(row_loss, ref.detach()) < max(tol, 1e-5)
+    assert row_loss[5].item() == 0.0 and view[5].abs().max().item() == 0.0
+    assert rel(view, ref_in.grad) < tol
+    if ld > V:
+        assert logits[:, V:].abs().max().item() == 0.0     # pitch padding untouched
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
+def test_swiglu(dtype, tol):
+    from weightshared_torchtitan_b200.functional import swiglu
+    g = torch.Generator().manual_seed(1)
+    a = (torch.randn(300, 3072, generator=g) * 2).to(dtype)
+    b = torch.randn(300, 3072, generator=g).to(dtype)
+    d = torch.randn(300, 3072, generator=g).to(dtype)
+    ar, br = leaf(a, dtype=torch.float32), leaf(b, dtype=torch.float32)
+    (F.silu(ar) * br).backward(d.float())
+    ac, bc = leaf(a, "cuda"), leaf(b, "cuda")
+    out = swiglu(ac, bc)
+    out.backward(d.cuda())
+    assert rel(out, F.silu(ar) * br) < tol
+    assert rel(ac.grad, ar.grad) < tol and rel(bc.grad, br.grad) < tol
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("D", [16, 64, 128, 1024, 2048])
+def test_rmsnorm(dtype, tol, D):
+    from weightshared_torchtitan_b200 import ops
+    from weightshared_torchtitan_b200.functional import rmsnorm
+    if dtype == torch.float32 and D > 1024:
+        assert not ops.rmsnorm_supported(D, dtype)
+        return
+    assert ops.rmsnorm_supported(D, dtype)
+    g = torch.Generator().manual_seed(D)
+    rows = 333
+    x = torch.randn(rows, D, generator=g).to(dtype)
+    w = 1.0 + 0.2 * torch.randn(D, generator=g)
+    dy = torch.randn(rows, D, generator=g).to(dtype)
+    xr, wr = leaf(x, dtype=torch.float32), leaf(w)
+    yr = F.rms_norm(xr, (D,), wr, 1e-6)
+    yr.backward(dy.float())
+    xc, wc = leaf(x, "cuda"), leaf(w, "cuda")
+    y = rmsnorm(xc, wc, 1e-6)
+    y.backward(dy.cuda())
+    assert rel(y, yr) < tol and rel(xc.grad, xr.grad) < tol
+    assert rel(wc.grad, wr.grad) < max(tol, 2e-5)
+    # in-place sink: gradient of the scale accumulates into a caller buffer
+    sink = torch.ones(D, device="cuda")
+    xc2 = leaf(x, "cuda")
+    rmsnorm(xc2, wc.detach(), 1e-6, None, sink).backward(dy.cuda())
+    assert rel(sink - 1.0, wr.grad) < max(tol, 2e-5)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("D,heads", [(128, 16), (128, 8), (16, 4), (64, 2)])
+def test_head_norm_with_rotary(dtype, tol, D, heads):
+    """q/k head RMSNorm followed by the rotary embedding, against the oracle's formulas
+    (rms_norm, then apply_rope on [b, s, h, d])."""
+    from weightshared_torchtitan_b200.decoder import rope_tables
+    from weightshared_torchtitan_b200.functional import rmsnorm
+    g = torch.Generator().manual_seed(D + heads)
+    b, s = 2, 37
+    x = torch.randn(b, s, heads, D, generator=g).to(dtype)
+    w = 1.0 + 0.2 * torch.randn(D, generator=g)
+    dy = torch.randn(b, s, heads, D, generator=g).to(dtype)
+    cache = O.rope_cache(D, s, 1_000_000.0)
+    xr, wr = leaf(x, dtype=torch.float32), leaf(w)
+    n = F.rms_norm(xr, (D,), wr, 1e-6)
+    yr, _ = O.apply_rope(n, n, cache)
+    yr.backward(dy.float())
+    cos, sin = rope_tables(D, s, 1_000_000.0, "cuda")
+    xc, wc = leaf(x, "cuda"), leaf(w, "cuda")
+    y = rmsnorm(xc, wc, 1e-6, (cos.contiguous(), sin.contiguous(), heads, s))
+    y.backward(dy.cuda())
+    assert rel(y, yr) < tol and rel(xc.grad, xr.grad) < tol
+    assert rel(wc.grad, wr.grad) < max(tol, 2e-5)

@@ -45,6 +45,11 @@ SIGNATURES = {
                                     _vp, ctypes.c_ulonglong, _i, _vp]),
     "wsl_lora_linear_bwd_dw_noalloc": (_i, [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _vp]),
     "wsl_bwd_dw_workspace_bytes": (ctypes.c_ulonglong, [_ll, _ll, _ll, _ll, _i, _i, _i]),
+    "wsl_ce_fwd_bwd": (_i, [_vp, _ll, _vp, _vp, _ll, _ll, _f, _i, _vp]),
+    "wsl_swiglu_fwd": (_i, [_vp, _vp, _vp, _ll, _i, _vp]),
+    "wsl_swiglu_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _ll, _i, _vp]),
+    "wsl_rmsnorm_fwd": (_i, [_vp, _ll, _vp, _vp, _ll, _vp, _ll, _ll, _f, _vp, _vp, _ll, _ll, _i, _vp]),
+    "wsl_rmsnorm_bwd": (_i, [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _i, _vp]),
     "wsl_embed_gather": (_i, [_vp, _vp, _vp, _ll, _ll, _ll, _i, _vp]),
     "wsl_embed_scatter_add": (_i, [_vp, _vp, _vp, _ll, _ll, _ll, _i, _vp]),
 }

@@ -5,6 +5,7 @@
 #include "simt_gemm.cu"
 #include "embed.cu"
 #include "static_scratch.cu"
+#include "elementwise.cu"
 
 namespace wsl {
 int launch_simt_gemm_f32(const float* A, long long sai, long long sak, const float* B,
@@ -332,6 +333,43 @@ int wsl_embed_scatter_add(const long long* tokens, const void* dG, float* dE, lo
   if (bad_dtype(dtype)) return WSL_ERR_BAD_ARG;
   return launch_embed_scatter_add(tokens, dG, dE, M, V, r_e, dtype == WSL_F32 ? 1 : 0,
                                   static_cast<cudaStream_t>(stream));
+}
+
+int wsl_ce_fwd_bwd(void* logits, long long ld, const long long* labels, float* row_loss,
+                   long long rows, long long V, float scale, int dtype, void* stream) {
+  if (bad_dtype(dtype)) return WSL_ERR_BAD_ARG;
+  return launch_ce(logits, ld, labels, row_loss, rows, V, scale, dtype == WSL_F32,
+                   static_cast<cudaStream_t>(stream));
+}
+
+int wsl_swiglu_fwd(const void* gate, const void* up, void* out, long long n, int dtype, void* stream) {
+  if (bad_dtype(dtype)) return WSL_ERR_BAD_ARG;
+  return launch_swiglu(gate, up, out, nullptr, nullptr, nullptr, n, dtype == WSL_F32,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int wsl_swiglu_bwd(const void* dout, const void* gate, const void* up, void* dgate, void* dup,
+                   long long n, int dtype, void* stream) {
+  if (bad_dtype(dtype) || !dout) return WSL_ERR_BAD_ARG;
+  return launch_swiglu(gate, up, nullptr, dout, dgate, dup, n, dtype == WSL_F32,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int wsl_rmsnorm_fwd(const void* x, long long ldx, const float* w, void* y, long long ldy, float* rstd,
+                    long long rows, long long D, float eps, const float* rope_cos,
+                    const float* rope_sin, long long heads, long long seq, int dtype, void* stream) {
+  if (bad_dtype(dtype)) return WSL_ERR_BAD_ARG;
+  return launch_rmsnorm_fwd(x, ldx, w, y, ldy, rstd, rows, D, eps, rope_cos, rope_sin, heads, seq,
+                            dtype == WSL_F32, static_cast<cudaStream_t>(stream));
+}
+
+int wsl_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long ldx, const float* w,
+                    const float* rstd, void* dx, long long lddx, float* dw, long long rows,
+                    long long D, const float* rope_cos, const float* rope_sin, long long heads,
+                    long long seq, int dtype, void* stream) {
+  if (bad_dtype(dtype)) return WSL_ERR_BAD_ARG;
+  return launch_rmsnorm_bwd(dy, lddy, x, ldx, w, rstd, dx, lddx, dw, rows, D, rope_cos, rope_sin,
+                            heads, seq, dtype == WSL_F32, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -1,0 +1,554 @@
+// HBM-bound row kernels of the decoder step that sit either side of the projections:
+// softmax cross-entropy (forward + gradient in one go, in place), SwiGLU, RMSNorm with an
+// optional fused rotary embedding. Each is a plain streaming kernel: 16-byte vector
+// accesses, fp32 math, one rounding to the storage type. T is __nv_bfloat16 or float.
+#include "block_gemm.cuh"
+#include "status.cuh"
+#include "../../include/wsl.h"
+#include <cuda_bf16.h>
+
+namespace wsl {
+
+template <typename T>
+struct Vec;   // 16-byte vector of T
+template <>
+struct Vec<float> {
+  static constexpr int N = 4;
+  float v[4];
+  __device__ __forceinline__ float get(int i) const { return v[i]; }
+  __device__ __forceinline__ void set(int i, float x) { v[i] = x; }
+};
+template <>
+struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __nv_bfloat16 v[8];
+  __device__ __forceinline__ float get(int i) const { return __bfloat162float(v[i]); }
+  __device__ __forceinline__ void set(int i, float x) { v[i] = __float2bfloat16_rn(x); }
+};
+template <typename T>
+__device__ __forceinline__ Vec<T> ldv(const T* p) {
+  Vec<T> r;
+  *reinterpret_cast<uint4*>(&r) = *reinterpret_cast<const uint4*>(p);
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ void stv(T* p, const Vec<T>& r) {
+  *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(&r);
+}
+template <typename T>
+__device__ __forceinline__ float ld1(const T* p);
+template <>
+__device__ __forceinline__ float ld1<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float ld1<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T>
+__device__ __forceinline__ void st1(T* p, float x);
+template <>
+__device__ __forceinline__ void st1<float>(float* p, float x) { *p = x; }
+template <>
+__device__ __forceinline__ void st1<__nv_bfloat16>(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ------------------------------------------------------------ softmax cross-entropy
+// One CTA per row. Pass 1: running (max, sum of exp) per thread, merged across the block.
+// Pass 2: logits[row, j] <- scale * (softmax_j - [j == label]) written IN PLACE in the
+// storage type; row_loss[row] = logsumexp - logit[label]. A label outside [0, V) marks an
+// ignored row: zero loss, zero gradient.
+constexpr int CE_THREADS = 1024;
+
+template <typename T>
+__global__ void __launch_bounds__(CE_THREADS)
+ce_fwd_bwd_kernel(T* logits, long long ld, const long long* __restrict__ labels,
+                  float* __restrict__ row_loss, int V, float scale) {
+  __shared__ float red_m[32];
+  __shared__ float red_s[32];
+  __shared__ float bcast[2];
+  T* row = logits + static_cast<long long>(blockIdx.x) * ld;
+  const long long label = labels[blockIdx.x];
+  const bool ignored = label < 0 || label >= V;
+  constexpr int NV = Vec<T>::N;
+  const int nvec = V / NV;
+  float m = -INFINITY, s = 0.f;
+  if (!ignored) {
+    for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+      const Vec<T> x = ldv<T>(row + static_cast<long long>(i) * NV);
+      float lm = x.get(0);
+#pragma unroll
+      for (int e = 1; e < NV; ++e) lm = fmaxf(lm, x.get(e));
+      if (lm > m) {
+        s *= __expf(m - lm);
+        m = lm;
+      }
+#pragma unroll
+      for (int e = 0; e < NV; ++e) s += __expf(x.get(e) - m);
+    }
+    for (int j = nvec * NV + threadIdx.x; j < V; j += CE_THREADS) {
+      const float x = ld1<T>(row + j);
+      if (x > m) {
+        s *= __expf(m - x);
+        m = x;
+      }
+      s += __expf(x - m);
+    }
+    // merge (m, s) pairs: warp, then block
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+      const float s2 = __shfl_xor_sync(0xffffffffu, s, o);
+      const float mm = fmaxf(m, m2);
+      s = (m == -INFINITY ? 0.f : s * __expf(m - mm)) + (m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mm));
+      m = mm;
+    }
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) {
+      red_m[w] = m;
+      red_s[w] = s;
+    }
+    __syncthreads();
+    if (w == 0) {
+      m = red_m[l];
+      s = red_s[l];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+        const float s2 = __shfl_xor_sync(0xffffffffu, s, o);
+        const float mm = fmaxf(m, m2);
+        s = (m == -INFINITY ? 0.f : s * __expf(m - mm)) + (m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mm));
+        m = mm;
+      }
+      if (l == 0) {
+        bcast[0] = m;
+        bcast[1] = logf(s) + m;   // logsumexp
+        row_loss[blockIdx.x] = bcast[1] - ld1<T>(row + label);
+      }
+    }
+    __syncthreads();
+  } else if (threadIdx.x == 0) {
+    row_loss[blockIdx.x] = 0.f;
+  }
+  const float lse = ignored ? 0.f : bcast[1];
+  const int lab = static_cast<int>(label);
+  for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+    T* p = row + static_cast<long long>(i) * NV;
+    Vec<T> x = ldv<T>(p);
+#pragma unroll
+    for (int e = 0; e < NV; ++e) {
+      float g = 0.f;
+      if (!ignored) {
+        g = __expf(x.get(e) - lse);
+        if (i * NV + e == lab) g -= 1.f;
+        g *= scale;
+      }
+      x.set(e, g);
+    }
+    stv<T>(p, x);
+  }
+  for (int j = nvec * NV + threadIdx.x; j < V; j += CE_THREADS) {
+    float g = 0.f;
+    if (!ignored) {
+      g = __expf(ld1<T>(row + j) - lse);
+      if (j == lab) g -= 1.f;
+      g *= scale;
+    }
+    st1<T>(row + j, g);
+  }
+}
+
+// ------------------------------------------------------------------------- SwiGLU
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_fwd_kernel(const T* __restrict__ g, const T* __restrict__ u, T* __restrict__ out,
+                  long long nvec) {
+  constexpr int NV = Vec<T>::N;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < nvec; i += gridDim.x * 256ll) {
+    const Vec<T> a = ldv<T>(g + i * NV), b = ldv<T>(u + i * NV);
+    Vec<T> o;
+#pragma unroll
+    for (int e = 0; e < NV; ++e) {
+      const float x = a.get(e);
+      o.set(e, x / (1.f + __expf(-x)) * b.get(e));
+    }
+    stv<T>(out + i * NV, o);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const T* __restrict__ d, const T* __restrict__ g, const T* __restrict__ u,
+                  T* __restrict__ dg, T* __restrict__ du, long long nvec) {
+  constexpr int NV = Vec<T>::N;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < nvec; i += gridDim.x * 256ll) {
+    const Vec<T> dd = ldv<T>(d + i * NV), a = ldv<T>(g + i * NV), b = ldv<T>(u + i * NV);
+    Vec<T> og, ou;
+#pragma unroll
+    for (int e = 0; e < NV; ++e) {
+      const float x = a.get(e), dy = dd.get(e);
+      const float sg = 1.f / (1.f + __expf(-x));
+      og.set(e, dy * b.get(e) * sg * (1.f + x * (1.f - sg)));
+      ou.set(e, dy * x * sg);
+    }
+    stv<T>(dg + i * NV, og);
+    stv<T>(du + i * NV, ou);
+  }
+}
+
+// ------------------------------------------------- RMSNorm (+ rotary embedding)
+// A row of width D is handled by `lpr` lanes (a power of two <= 32, D = kv * lpr * NV with
+// kv <= RN_MAX_VEC), so a warp covers 32/lpr rows at once: hidden-size rows use a whole
+// warp, head-size rows (D = 128: 16 lanes in bf16) two per warp. Lane l of a row holds
+// elements [(k*lpr + l)*NV, +NV) for k < kv. With rotary (kv == 1, D = head_dim), row r
+// belongs to position (r / heads) % seq and
+//   y = n * cos + rotate_half(n) * sin,   n = x * rstd * w,   rstd = 1/sqrt(mean(x^2) + eps);
+// the rotate_half partner j +- D/2 lives in lane l ^ (lpr/2).
+constexpr int RN_MAX_VEC = 8;
+constexpr int RN_WARPS = 8;
+
+__device__ __forceinline__ float group_sum(float v, int lpr) {
+  for (int o = lpr >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Each lane group walks `iters` consecutive rows and keeps the scale w (and, with rotary,
+// the cos/sin of the current position: iters = heads, so all rows of a group belong to one
+// token) in registers, so per row only x is read and y written.
+template <typename T, bool ROPE, int KV>
+__global__ void __launch_bounds__(RN_WARPS * 32)
+rmsnorm_fwd_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ w,
+                   T* __restrict__ y, long long ldy, float* __restrict__ rstd_out, long long rows,
+                   int D, int lpr, float eps, const float* __restrict__ cs,
+                   const float* __restrict__ sn, int heads, int seq, int iters) {
+  constexpr int NV = Vec<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int rpw = 32 / lpr;
+  const int l = lane % lpr;
+  constexpr int kv = KV;
+  const long long group = (blockIdx.x * static_cast<long long>(RN_WARPS) + (threadIdx.x >> 5)) * rpw + lane / lpr;
+  const long long row0 = group * iters;
+  float wr[KV][NV];
+#pragma unroll
+  for (int k = 0; k < KV; ++k)
+    if (k < kv)
+#pragma unroll
+      for (int e = 0; e < NV; ++e) wr[k][e] = w[(k * lpr + l) * NV + e];
+  float cr[NV], sr[NV];
+  if (ROPE) {
+    const long long pos = (row0 < rows ? row0 / heads : 0) % seq;
+#pragma unroll
+    for (int e = 0; e < NV; ++e) {
+      cr[e] = cs[pos * D + l * NV + e];
+      sr[e] = sn[pos * D + l * NV + e];
+      if (l < (lpr >> 1)) sr[e] = -sr[e];   // rotate_half: first half takes -n[j + D/2]
+    }
+  }
+#pragma unroll 2
+  for (int rr = 0; rr < iters; ++rr) {
+    const long long row = row0 + rr;
+    const bool valid = row < rows;
+    Vec<T> xv[KV];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < KV; ++k)
+      if (k < kv) {
+        if (valid) xv[k] = ldv<T>(x + row * ldx + (k * lpr + l) * NV);
+        else
+#pragma unroll
+          for (int e = 0; e < NV; ++e) xv[k].set(e, 0.f);
+#pragma unroll
+        for (int e = 0; e < NV; ++e) ss += xv[k].get(e) * xv[k].get(e);
+      }
+    ss = group_sum(ss, lpr);
+    const float rstd = rsqrtf(ss / D + eps);
+    if (valid && l == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+    for (int k = 0; k < KV; ++k)
+      if (k < kv) {
+        Vec<T> o;
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+          float v = xv[k].get(e) * rstd * wr[k][e];
+          if (ROPE) {
+            const float partner = __shfl_xor_sync(0xffffffffu, v, lpr >> 1);
+            v = v * cr[e] + partner * sr[e];
+          }
+          o.set(e, v);
+        }
+        if (valid) stv<T>(y + row * ldy + (k * lpr + l) * NV, o);
+      }
+  }
+}
+
+// Backward: dx = rstd * (g - x * rstd^2 * mean(g * x)), g = dn * w, dn = un-rotated dy;
+// dw[j] += sum_rows dn[j] * x[j] * rstd (registers -> shared-memory partials -> atomics).
+template <typename T, bool ROPE, int KV>
+__global__ void __launch_bounds__(RN_WARPS * 32)
+rmsnorm_bwd_kernel(const T* __restrict__ dy, long long lddy, const T* __restrict__ x, long long ldx,
+                   const float* __restrict__ w, const float* __restrict__ rstd_in,
+                   T* __restrict__ dx, long long lddx, float* dw, long long rows, int D, int lpr,
+                   const float* __restrict__ cs, const float* __restrict__ sn, int heads, int seq,
+                   int iters) {
+  constexpr int NV = Vec<T>::N;
+  extern __shared__ float dw_part[];   // [D]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int rpw = 32 / lpr;
+  const int l = lane % lpr;
+  constexpr int kv = KV;
+  for (int j = threadIdx.x; j < D; j += RN_WARPS * 32) dw_part[j] = 0.f;
+  __syncthreads();
+  float dwacc[KV][NV], wr[KV][NV];
+#pragma unroll
+  for (int k = 0; k < KV; ++k)
+#pragma unroll
+    for (int e = 0; e < NV; ++e) {
+      dwacc[k][e] = 0.f;
+      wr[k][e] = w[(k * lpr + l) * NV + e];
+    }
+  const long long group = (blockIdx.x * static_cast<long long>(RN_WARPS) + warp) * rpw + lane / lpr;
+  const long long row0 = group * iters;
+  float cr[NV], sr[NV];
+  long long cur_pos = -1;
+  for (int rr = 0; rr < iters; ++rr) {
+    const long long row = row0 + rr;
+    const bool valid = row < rows;
+    const float rstd = valid ? rstd_in[row] : 0.f;
+    if (ROPE) {
+      const long long pos = (valid ? row / heads : 0) % seq;
+      if (pos != cur_pos) {
+        cur_pos = pos;
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+          cr[e] = cs[pos * D + l * NV + e];
+          sr[e] = sn[pos * D + l * NV + e];
+        }
+      }
+    }
+    float dn[KV][NV];
+    Vec<T> xv[KV];
+#pragma unroll
+    for (int k = 0; k < KV; ++k)
+      if (k < kv) {
+        if (valid) {
+          const Vec<T> d = ldv<T>(dy + row * lddy + (k * lpr + l) * NV);
+          xv[k] = ldv<T>(x + row * ldx + (k * lpr + l) * NV);
+#pragma unroll
+          for (int e = 0; e < NV; ++e) dn[k][e] = d.get(e);
+        } else {
+#pragma unroll
+          for (int e = 0; e < NV; ++e) {
+            dn[k][e] = 0.f;
+            xv[k].set(e, 0.f);
+          }
+        }
+      }
+    if (ROPE) {
+#pragma unroll
+      for (int e = 0; e < NV; ++e) {
+        // dn[j] = dy[j] cos[j] + (j < D/2 ? dy[j+D/2] sin[j+D/2] : -dy[j-D/2] sin[j-D/2])
+        const float other = __shfl_xor_sync(0xffffffffu, dn[0][e] * sr[e], lpr >> 1);
+        dn[0][e] = dn[0][e] * cr[e] + (l < (lpr >> 1) ? other : -other);
+      }
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < KV; ++k)
+      if (k < kv)
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+          const float xe = xv[k].get(e);
+          dot += dn[k][e] * wr[k][e] * xe;
+          dwacc[k][e] += dn[k][e] * xe * rstd;
+        }
+    dot = group_sum(dot, lpr);
+    const float c = dot * rstd * rstd / D;
+#pragma unroll
+    for (int k = 0; k < KV; ++k)
+      if (k < kv) {
+        Vec<T> o;
+#pragma unroll
+        for (int e = 0; e < NV; ++e) o.set(e, rstd * (dn[k][e] * wr[k][e] - xv[k].get(e) * c));
+        if (valid) stv<T>(dx + row * lddx + (k * lpr + l) * NV, o);
+      }
+  }
+  if (dw != nullptr) {
+#pragma unroll
+    for (int k = 0; k < KV; ++k)
+      if (k < kv)
+#pragma unroll
+        for (int e = 0; e < NV; ++e) atomicAdd(&dw_part[(k * lpr + l) * NV + e], dwacc[k][e]);
+    __syncthreads();
+    for (int j = threadIdx.x; j < D; j += RN_WARPS * 32) atomicAdd(dw + j, dw_part[j]);
+  }
+}
+
+// ------------------------------------------------------------------ host launchers
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename T>
+static int ce_launch(void* logits, long long ld, const long long* labels, float* row_loss,
+                     long long rows, long long V, float scale, cudaStream_t s) {
+  ce_fwd_bwd_kernel<T><<<static_cast<unsigned>(rows), CE_THREADS, 0, s>>>(
+      static_cast<T*>(logits), ld, labels, row_loss, static_cast<int>(V), scale);
+  return cudaGetLastError() == cudaSuccess ? WSL_OK : WSL_ERR_CUDA;
+}
+
+int launch_ce(void* logits, long long ld, const long long* labels, float* row_loss, long long rows,
+              long long V, float scale, int is_f32, cudaStream_t s) {
+  int st = device_check();
+  if (st != WSL_OK) return st;
+  if (!logits || !labels || !row_loss || rows <= 0 || V <= 0 || ld < V) return WSL_ERR_BAD_ARG;
+  if (rows > 0x7fffffffLL || V > 0x7fffffffLL) return WSL_ERR_TOO_LARGE;
+  const int nv = is_f32 ? 4 : 8;
+  if (!aligned16(logits) || (ld % nv) != 0) return WSL_ERR_ALIGN;
+  st = is_f32 ? ce_launch<float>(logits, ld, labels, row_loss, rows, V, scale, s)
+              : ce_launch<__nv_bfloat16>(logits, ld, labels, row_loss, rows, V, scale, s);
+  if (st == WSL_OK) ++g_launch_count;
+  return st;
+}
+
+int launch_swiglu(const void* g, const void* u, void* out, const void* d, void* dg, void* du,
+                  long long n, int is_f32, cudaStream_t s) {
+  int st = device_check();
+  if (st != WSL_OK) return st;
+  if (!g || !u || n <= 0) return WSL_ERR_BAD_ARG;
+  const int nv = is_f32 ? 4 : 8;
+  if ((n % nv) != 0 || !aligned16(g) || !aligned16(u)) return WSL_ERR_ALIGN;
+  const long long nvec = n / nv;
+  long long blocks = (nvec + 255) / 256;
+  const long long cap = 32ll * device_sm_count();
+  if (blocks > cap) blocks = cap;
+  const unsigned gb = static_cast<unsigned>(blocks);
+  if (d == nullptr) {
+    if (!out || !aligned16(out)) return WSL_ERR_BAD_ARG;
+    if (is_f32)
+      swiglu_fwd_kernel<float><<<gb, 256, 0, s>>>(static_cast<const float*>(g), static_cast<const float*>(u),
+                                                  static_cast<float*>(out), nvec);
+    else
+      swiglu_fwd_kernel<__nv_bfloat16><<<gb, 256, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(g), static_cast<const __nv_bfloat16*>(u),
+          static_cast<__nv_bfloat16*>(out), nvec);
+  } else {
+    if (!dg || !du || !aligned16(d) || !aligned16(dg) || !aligned16(du)) return WSL_ERR_BAD_ARG;
+    if (is_f32)
+      swiglu_bwd_kernel<float><<<gb, 256, 0, s>>>(static_cast<const float*>(d), static_cast<const float*>(g),
+                                                  static_cast<const float*>(u), static_cast<float*>(dg),
+                                                  static_cast<float*>(du), nvec);
+    else
+      swiglu_bwd_kernel<__nv_bfloat16><<<gb, 256, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(d), static_cast<const __nv_bfloat16*>(g),
+          static_cast<const __nv_bfloat16*>(u), static_cast<__nv_bfloat16*>(dg),
+          static_cast<__nv_bfloat16*>(du), nvec);
+  }
+  if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
+  ++g_launch_count;
+  return WSL_OK;
+}
+
+// lanes per row for a width-D row, or 0 when the kernels do not cover D.
+static int rms_lanes(long long D, int nv) {
+  if (D <= 0 || (D % nv) != 0) return 0;
+  long long lanes = D / nv;
+  if (lanes >= 32) {
+    const long long kv = D / (32 * nv);
+    return (D % (32 * nv)) == 0 && (kv == 1 || kv == 2 || kv == 4 || kv == 8) ? 32 : 0;
+  }
+  return (lanes & (lanes - 1)) == 0 ? static_cast<int>(lanes) : 0;
+}
+
+static int rms_check(const void* x, long long ldx, long long rows, long long D, int is_f32,
+                     const float* cs, const float* sn, long long heads, long long seq) {
+  if (!x || rows <= 0 || D <= 0 || ldx < D) return WSL_ERR_BAD_ARG;
+  const int nv = is_f32 ? 4 : 8;
+  const int lpr = rms_lanes(D, nv);
+  if (lpr == 0) return WSL_ERR_TOO_LARGE;
+  if ((ldx % nv) != 0 || !aligned16(x)) return WSL_ERR_ALIGN;
+  if ((cs == nullptr) != (sn == nullptr)) return WSL_ERR_BAD_ARG;
+  if (cs != nullptr && (heads <= 0 || seq <= 0 || lpr < 2 || D != static_cast<long long>(lpr) * nv))
+    return WSL_ERR_BAD_ARG;
+  return WSL_OK;
+}
+
+int launch_rmsnorm_fwd(const void* x, long long ldx, const float* w, void* y, long long ldy,
+                       float* rstd, long long rows, long long D, float eps, const float* cs,
+                       const float* sn, long long heads, long long seq, int is_f32, cudaStream_t s) {
+  int st = device_check();
+  if (st != WSL_OK) return st;
+  st = rms_check(x, ldx, rows, D, is_f32, cs, sn, heads, seq);
+  if (st != WSL_OK) return st;
+  if (!w || !y || !aligned16(y) || ldy < D) return WSL_ERR_BAD_ARG;
+  const int lpr = rms_lanes(D, is_f32 ? 4 : 8);
+  // rows per lane group: all heads of one token with rotary (one cos/sin fetch), else enough
+  // to amortise the register copy of w while still filling the GPU
+  long long iters = cs ? heads : 4;
+  if (!cs && rows < 4ll * RN_WARPS * (32 / lpr) * device_sm_count()) iters = 1;
+  const long long rows_per_block = static_cast<long long>(RN_WARPS) * (32 / lpr) * iters;
+  const unsigned gb = static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block);
+  const int d = static_cast<int>(D), h = static_cast<int>(heads), sq = static_cast<int>(seq);
+  const int kvn = static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
+#define WSL_RN(T, R, KVN)                                                                          \
+  rmsnorm_fwd_kernel<T, R, KVN><<<gb, RN_WARPS * 32, 0, s>>>(                                      \
+      static_cast<const T*>(x), ldx, w, static_cast<T*>(y), ldy, rstd, rows, d, lpr, eps, cs, sn, \
+      h, sq, static_cast<int>(iters))
+#define WSL_RN_KV(T)                                              \
+  do {                                                            \
+    if (cs) WSL_RN(T, true, 1);                                   \
+    else if (kvn == 1) WSL_RN(T, false, 1);                       \
+    else if (kvn == 2) WSL_RN(T, false, 2);                       \
+    else if (kvn == 4) WSL_RN(T, false, 4);                       \
+    else if (kvn == 8) WSL_RN(T, false, 8);                       \
+    else return WSL_ERR_TOO_LARGE;                                \
+  } while (0)
+  if (is_f32) WSL_RN_KV(float); else WSL_RN_KV(__nv_bfloat16);
+#undef WSL_RN_KV
+#undef WSL_RN
+  if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
+  ++g_launch_count;
+  return WSL_OK;
+}
+
+int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long ldx, const float* w,
+                       const float* rstd, void* dx, long long lddx, float* dw, long long rows,
+                       long long D, const float* cs, const float* sn, long long heads,
+                       long long seq, int is_f32, cudaStream_t s) {
+  int st = device_check();
+  if (st != WSL_OK) return st;
+  st = rms_check(x, ldx, rows, D, is_f32, cs, sn, heads, seq);
+  if (st != WSL_OK) return st;
+  if (!dy || !w || !rstd || !dx || !aligned16(dy) || !aligned16(dx) || lddy < D || lddx < D)
+    return WSL_ERR_BAD_ARG;
+  // enough rows per warp that the dw atomics stay a small fraction of the work
+  const int lpr = rms_lanes(D, is_f32 ? 4 : 8);
+  const long long rows_per_pass = static_cast<long long>(RN_WARPS) * (32 / lpr);
+  const long long target_blocks = 8ll * device_sm_count();
+  long long rpw = (rows + target_blocks * rows_per_pass - 1) / (target_blocks * rows_per_pass);
+  if (rpw < 1) rpw = 1;
+  const unsigned gb = static_cast<unsigned>((rows + rows_per_pass * rpw - 1) / (rows_per_pass * rpw));
+  const int d = static_cast<int>(D), h = static_cast<int>(heads), sq = static_cast<int>(seq);
+  const size_t smem = static_cast<size_t>(D) * sizeof(float);
+  const int kvn = static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
+#define WSL_RNB(T, R, KVN)                                                                         \
+  rmsnorm_bwd_kernel<T, R, KVN><<<gb, RN_WARPS * 32, smem, s>>>(                                   \
+      static_cast<const T*>(dy), lddy, static_cast<const T*>(x), ldx, w, rstd, static_cast<T*>(dx), \
+      lddx, dw, rows, d, lpr, cs, sn, h, sq, static_cast<int>(rpw))
+#define WSL_RNB_KV(T)                                             \
+  do {                                                            \
+    if (cs) WSL_RNB(T, true, 1);                                  \
+    else if (kvn == 1) WSL_RNB(T, false, 1);                      \
+    else if (kvn == 2) WSL_RNB(T, false, 2);                      \
+    else if (kvn == 4) WSL_RNB(T, false, 4);                      \
+    else if (kvn == 8) WSL_RNB(T, false, 8);                      \
+    else return WSL_ERR_TOO_LARGE;                                \
+  } while (0)
+  if (is_f32) WSL_RNB_KV(float); else WSL_RNB_KV(__nv_bfloat16);
+#undef WSL_RNB_KV
+#undef WSL_RNB
+  if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
+  ++g_launch_count;
+  return WSL_OK;
+}
+
+}  // namespace wsl

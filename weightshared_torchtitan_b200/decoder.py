@@ -98,9 +98,26 @@ def rope_tables(head_dim: int, seq_len: int, theta: float, device) -> Tuple[torc
     return ang.cos(), ang.sin()
 
 
-def _rms(norm: nn.RMSNorm, x: torch.Tensor) -> torch.Tensor:
-    """RMSNorm with the fp32 master scale cast to the activation dtype (library call)."""
-    return F.rms_norm(x, norm.normalized_shape, norm.weight.to(x.dtype), norm.eps)
+def _rms(norm: nn.RMSNorm, x: torch.Tensor, rope=None) -> torch.Tensor:
+    """RMSNorm (optionally + rotary embedding) through the fused row kernel; widths the
+    kernel does not cover use the PyTorch call with the scale cast to the activation dtype.
+    rope = (cos, sin, heads, seq) with fp32 [seq, head_dim] tables."""
+    D = x.shape[-1]
+    w = norm.weight
+    if w.dtype == torch.float32 and ops.rmsnorm_supported(D, x.dtype, rope is not None):
+        sink = None
+        if torch.is_grad_enabled() and w.requires_grad and x.requires_grad:
+            if w.grad is None:
+                w.grad = torch.zeros_like(w)
+            sink = w.grad
+        return WF.rmsnorm(x, w if sink is None else w.detach(), norm.eps, rope, sink)
+    y = F.rms_norm(x, norm.normalized_shape, w.to(x.dtype), norm.eps)
+    if rope is not None:
+        cos, sin, heads, seq = rope
+        c = cos[:seq].to(x.dtype).view(1, seq, 1, D)
+        s_ = sin[:seq].to(x.dtype).view(1, seq, 1, D)
+        y = _rope(y, c, s_)
+    return y
 
 
 def _rope(t: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
@@ -113,7 +130,7 @@ class _HeadLossFunction(torch.autograd.Function):
     """Output head + mean cross-entropy, sliced over tokens so that the fp32 logits of only
     `chunk` tokens exist at a time. Forward already computes d(loss)/d(h) and the head
     weight gradient (accumulated into `sink`); backward scales dH by the incoming gradient.
-    GEMMs are the library's kernels; log-softmax is a PyTorch call."""
+    GEMMs and the softmax-cross-entropy row kernel are the library's."""
 
     @staticmethod
     def forward(ctx, h, Wc, labels, sink, chunk, anchor):
@@ -122,17 +139,14 @@ class _HeadLossFunction(torch.autograd.Function):
         total = torch.zeros((), device=h.device, dtype=torch.float32)
         for m0 in range(0, M, chunk):
             hs = h[m0:m0 + chunk]
-            logits = ops.linear_fwd(hs, Wc, out_f32=True)
-            lse = torch.logsumexp(logits, dim=-1, keepdim=True)
-            lab = labels[m0:m0 + chunk].unsqueeze(1)
-            total += (lse - logits.gather(1, lab)).sum()
-            logits.sub_(lse).exp_()
-            logits.scatter_add_(1, lab, torch.full_like(lab, -1.0, dtype=torch.float32))
-            dl = (logits * (1.0 / M)).to(h.dtype)
-            del logits
-            dH[m0:m0 + chunk] = ops.lora_linear_bwd_dx([dl], [None], [Wc], [None])
+            # logits in the compute dtype (bf16 under the reference's autocast, cast up inside
+            # the loss kernel), overwritten in place by their gradient
+            logits = ops.linear_fwd(hs, Wc)
+            total += ops.ce_fwd_bwd(logits, labels[m0:m0 + chunk], 1.0 / M).sum()
+            dH[m0:m0 + chunk] = ops.lora_linear_bwd_dx([logits], [None], [Wc], [None])
             if sink is not None:
-                ops.lora_linear_bwd_dw(dl, None, hs, None, sink, None, None)
+                ops.lora_linear_bwd_dw(logits, None, hs, None, sink, None, None)
+            del logits
         ctx.save_for_backward(dH)
         return total / M
 
@@ -236,16 +250,15 @@ class WeightSharedDecoder(nn.Module):
                                      sinks=(self._sink(E), self._sink(P)), anchors=(E, P))
         else:
             h = factorized_embedding(tokens, self._cache.get(dt, E), self._cache.get(dt, P))
-        if self._rope is None or self._rope[0].shape[0] < s or self._rope[0].device != h.device:
-            cos, sin = rope_tables(c.head_dim, max(s, c.max_seq_len), c.rope_theta, h.device)
-            self._rope = (cos.to(dt), sin.to(dt))
-        cos = self._rope[0][:s].view(1, s, 1, c.head_dim)
-        sin = self._rope[1][:s].view(1, s, 1, c.head_dim)
+        if self._rope is None or self._rope[0].shape[0] != s or self._rope[0].device != h.device:
+            cos, sin = rope_tables(c.head_dim, s, c.rope_theta, h.device)
+            self._rope = (cos.contiguous(), sin.contiguous())       # fp32 [s, head_dim]
+        cos, sin = self._rope
         for lyr in self.layers:
             xn = _rms(lyr.attention_norm, h)
             q, k, v = self._group(lyr, ("wq", "wk", "wv"), xn)
-            q = _rope(_rms(lyr.q_norm, q.view(b, s, c.n_heads, c.head_dim)), cos, sin)
-            k = _rope(_rms(lyr.k_norm, k.view(b, s, c.n_kv_heads, c.head_dim)), cos, sin)
+            q = _rms(lyr.q_norm, q.view(b, s, c.n_heads, c.head_dim), (cos, sin, c.n_heads, s))
+            k = _rms(lyr.k_norm, k.view(b, s, c.n_kv_heads, c.head_dim), (cos, sin, c.n_kv_heads, s))
             v = v.view(b, s, c.n_kv_heads, c.head_dim)
             o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                                is_causal=True, enable_gqa=c.n_heads != c.n_kv_heads)
@@ -253,7 +266,7 @@ class WeightSharedDecoder(nn.Module):
             h = h + self._group(lyr, ("wo",), o)[0]
             xn = _rms(lyr.ffn_norm, h)
             gate, up = self._group(lyr, ("w1", "w3"), xn)
-            h = h + self._group(lyr, ("w2",), F.silu(gate) * up)[0]
+            h = h + self._group(lyr, ("w2",), WF.swiglu(gate, up))[0]
         return _rms(self.norm, h)
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:

@@ -216,3 +216,61 @@ class LinearFunction(torch.autograd.Function):
 
 def linear(x: torch.Tensor, W: torch.Tensor, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     return LinearFunction.apply(x, W, sink)
+
+
+class SwiGLUFunction(torch.autograd.Function):
+    """silu(gate) * up in one pass each way (torchtitan/experiments/qwen3/model/model.py:251)."""
+
+    @staticmethod
+    def forward(ctx, gate, up):
+        gate, up = gate.contiguous(), up.contiguous()
+        ctx.save_for_backward(gate, up)
+        return ops.swiglu_fwd(gate, up)
+
+    @staticmethod
+    def backward(ctx, dout):
+        gate, up = ctx.saved_tensors
+        return ops.swiglu_bwd(dout, gate, up)
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    return SwiGLUFunction.apply(gate, up)
+
+
+class RMSNormFunction(torch.autograd.Function):
+    """RMSNorm over the last dimension with an fp32 scale, optionally followed by the rotary
+    embedding of the normalised row (q/k head norm + RoPE of
+    torchtitan/experiments/qwen3/model/model.py:195-203 in one pass).
+
+    forward(ctx, x, w, eps, rope, sink): rope = None or (cos [seq, D] fp32, sin, heads, seq);
+    sink = fp32 [D] buffer to accumulate dw into in place (then no gradient is returned
+    for w), or None."""
+
+    @staticmethod
+    def forward(ctx, x, w, eps, rope, sink):
+        D = x.shape[-1]
+        x2 = x.reshape(-1, D)
+        y, rstd = ops.rmsnorm_fwd(x2, w, eps, rope)
+        ctx.save_for_backward(x2, w, rstd)
+        ctx.rope = rope
+        ctx.sink = sink
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, rstd = ctx.saved_tensors
+        D = x2.shape[-1]
+        dy2 = dy.reshape(-1, D)
+        if dy2.stride(-1) != 1:
+            dy2 = dy2.contiguous()
+        if ctx.sink is not None:
+            dx = ops.rmsnorm_bwd(dy2, x2, w, rstd, ctx.sink, ctx.rope)
+            return dx.view(ctx.shape), None, None, None, None
+        dw = torch.zeros(D, device=x2.device, dtype=torch.float32) if ctx.needs_input_grad[1] else None
+        dx = ops.rmsnorm_bwd(dy2, x2, w, rstd, dw, ctx.rope)
+        return dx.view(ctx.shape), (dw.to(w.dtype) if dw is not None else None), None, None, None
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, rope=None, sink=None) -> torch.Tensor:
+    return RMSNormFunction.apply(x, w, eps, rope, sink)

@@ -271,3 +271,96 @@ def embed_scatter_add(tokens: torch.Tensor, dG: torch.Tensor, dE: torch.Tensor) 
                                           V, r_e, _dtype_code(dG), _stream())
     _toc(_e, "embed_scatter", 0.0, 8.0 * tok.numel() + (dG.element_size() + 8.0) * tok.numel() * r_e)
     _lib.check(st, "wsl_embed_scatter_add")
+
+
+# ------------------------------------------------ rows either side of the projections
+def ce_fwd_bwd(logits: torch.Tensor, labels: torch.Tensor, scale: float) -> torch.Tensor:
+    """In place: logits <- scale * (softmax - onehot); returns per-row loss (fp32)."""
+    logits = _mat(logits, "logits")
+    lab = labels.reshape(-1)
+    if lab.dtype != torch.int64 or not lab.is_cuda or lab.numel() != logits.shape[0]:
+        raise TypeError("labels must be a CUDA int64 tensor with one entry per row")
+    lab = lab.contiguous()
+    rows, V = logits.shape
+    row_loss = torch.empty(rows, device=logits.device, dtype=torch.float32)
+    _e = _tic()
+    st = _lib.lib().wsl_ce_fwd_bwd(logits.data_ptr(), _ld(logits), lab.data_ptr(), row_loss.data_ptr(),
+                                   rows, V, float(scale), _dtype_code(logits), _stream())
+    _toc(_e, "ce", 0.0, 3.0 * logits.element_size() * rows * V)
+    _lib.check(st, "wsl_ce_fwd_bwd")
+    return row_loss
+
+
+def swiglu_fwd(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    gate, up = gate.contiguous(), up.contiguous()
+    out = torch.empty_like(gate)
+    _e = _tic()
+    st = _lib.lib().wsl_swiglu_fwd(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(),
+                                   _dtype_code(gate), _stream())
+    _toc(_e, "swiglu_fwd", 0.0, 3.0 * gate.element_size() * gate.numel())
+    _lib.check(st, "wsl_swiglu_fwd")
+    return out
+
+
+def swiglu_bwd(dout: torch.Tensor, gate: torch.Tensor, up: torch.Tensor):
+    dout = dout.contiguous()
+    dg, du = torch.empty_like(gate), torch.empty_like(up)
+    _e = _tic()
+    st = _lib.lib().wsl_swiglu_bwd(dout.data_ptr(), gate.data_ptr(), up.data_ptr(), dg.data_ptr(),
+                                   du.data_ptr(), gate.numel(), _dtype_code(gate), _stream())
+    _toc(_e, "swiglu_bwd", 0.0, 5.0 * gate.element_size() * gate.numel())
+    _lib.check(st, "wsl_swiglu_bwd")
+    return dg, du
+
+
+def rmsnorm_supported(D: int, dtype: torch.dtype, rope: bool = False) -> bool:
+    """Row widths the fused RMSNorm kernels cover (see wsl_rmsnorm_fwd in include/wsl.h)."""
+    nv = 8 if dtype == torch.bfloat16 else 4
+    if D % nv:
+        return False
+    lanes = D // nv
+    if rope:
+        return 2 <= lanes <= 32 and lanes & (lanes - 1) == 0
+    if lanes >= 32:
+        return D % (32 * nv) == 0 and D // (32 * nv) in (1, 2, 4, 8)
+    return lanes & (lanes - 1) == 0
+
+
+def rmsnorm_fwd(x2: torch.Tensor, w: torch.Tensor, eps: float, rope=None):
+    """x2 [rows, D]; w fp32 [D]; rope = (cos, sin, heads, seq) with fp32 [seq, D] tables.
+    Returns (y, rstd)."""
+    x2 = _mat(x2, "x")
+    rows, D = x2.shape
+    y = torch.empty((rows, D), device=x2.device, dtype=x2.dtype)
+    rstd = torch.empty(rows, device=x2.device, dtype=torch.float32)
+    cs = sn = None
+    heads = seq = 0
+    if rope is not None:
+        cos, sin, heads, seq = rope
+        cs, sn = cos.data_ptr(), sin.data_ptr()
+    _e = _tic()
+    st = _lib.lib().wsl_rmsnorm_fwd(x2.data_ptr(), _ld(x2), w.data_ptr(), y.data_ptr(), D, rstd.data_ptr(),
+                                    rows, D, float(eps), cs, sn, heads, seq, _dtype_code(x2), _stream())
+    _toc(_e, "rmsnorm_fwd", 0.0, 2.0 * x2.element_size() * rows * D)
+    _lib.check(st, "wsl_rmsnorm_fwd")
+    return y, rstd
+
+
+def rmsnorm_bwd(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, rstd: torch.Tensor,
+                dw: Optional[torch.Tensor], rope=None) -> torch.Tensor:
+    dy2, x2 = _mat(dy2, "dy"), _mat(x2, "x")
+    rows, D = x2.shape
+    dx = torch.empty((rows, D), device=x2.device, dtype=x2.dtype)
+    cs = sn = None
+    heads = seq = 0
+    if rope is not None:
+        cos, sin, heads, seq = rope
+        cs, sn = cos.data_ptr(), sin.data_ptr()
+    _e = _tic()
+    st = _lib.lib().wsl_rmsnorm_bwd(dy2.data_ptr(), _ld(dy2), x2.data_ptr(), _ld(x2), w.data_ptr(),
+                                    rstd.data_ptr(), dx.data_ptr(), D,
+                                    dw.data_ptr() if dw is not None else None, rows, D, cs, sn, heads, seq,
+                                    _dtype_code(x2), _stream())
+    _toc(_e, "rmsnorm_bwd", 0.0, 3.0 * x2.element_size() * rows * D)
+    _lib.check(st, "wsl_rmsnorm_bwd")
+    return dx
