@@ -43,7 +43,7 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;       // 16 KiB
 constexpr int B_STAGE_BYTES = BN_MAX * BK * 2;   // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int SLAB_BYTES = 64 * BK * 2;          // one MN-major slab: 64 k-rows of 128 B
-constexpr int SMEM_DYN_BYTES = STAGES * STAGE_BYTES + 1024;
+constexpr int EPI_STAGE_BYTES = 128 * 128;       // epilogue staging: 128 rows x 128 B, two of them
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int RASTER_GROUP = 16;
@@ -63,6 +63,8 @@ struct Region {
   int mode;
   float alpha;
   long long ws_off;   // split-K: float offset of this region's partials in the workspace
+  int transposed;     // fp32 output element (row, col) of the tile lives at out[col * ld + row]
+  int out_map;        // tensor map of the output for the TMA-store epilogue, or -1
 };
 
 struct GemmParams {
@@ -82,6 +84,7 @@ struct TileInfo {
   int r;
   int m0;
   int n0;
+  int split;
 };
 
 // Segment-local k-block range [lo, hi) that split `split` of `splits` owns, given that the
@@ -107,6 +110,20 @@ __device__ __forceinline__ void epilogue_store(const Region& R, int row, int col
                                                const uint32_t (&v)[NV]) {
   if (row >= R.rows) return;
   const float alpha = R.alpha;
+  if (R.transposed) {
+    // one fp32 per lane and column: lanes hold consecutive rows, i.e. consecutive addresses
+    float* o = static_cast<float*>(R.out) + row;
+    const bool acc = (R.mode == kEpiAccumF32);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      if (col0 + j < R.cols) {
+        float* dst = o + static_cast<long long>(col0 + j) * R.ld;
+        const float f = alpha * __uint_as_float(v[j]);
+        *dst = acc ? (*dst + f) : f;
+      }
+    }
+    return;
+  }
   if (R.mode == kEpiStoreBf16) {
     __nv_bfloat16* o = static_cast<__nv_bfloat16*>(R.out) + static_cast<long long>(row) * R.ld + col0;
 #pragma unroll
@@ -149,6 +166,32 @@ __device__ __forceinline__ void epilogue_store(const Region& R, int row, int col
   }
 }
 
+// Named barrier 1 joins the 128 epilogue threads (warps 2-5).
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// AND-vote over the 128 epilogue threads, so that they leave the tile loop together.
+__device__ __forceinline__ bool epi_vote_and(bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t"
+      "}\n"
+      : "=r"(r)
+      : "r"(static_cast<uint32_t>(ok))
+      : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h2 = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h2);
+}
+
 // Per-variant constants. PAIR = two CTAs (a cluster of 2, tcgen05 cta_group::2) share one
 // 256 x bn tile: each CTA owns 128 rows of A and of the accumulator and loads HALF of the
 // B tile, so a stage is 32 KiB (6-deep ring) instead of 48 KiB (4-deep).
@@ -157,17 +200,23 @@ struct Cfg {
   static constexpr int kStages = PAIR ? 6 : 4;
   static constexpr int kBStageBytes = PAIR ? B_STAGE_BYTES / 2 : B_STAGE_BYTES;
   static constexpr int kStageBytes = A_STAGE_BYTES + kBStageBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 2 * EPI_STAGE_BYTES + 1024;
   static constexpr int kTileM = PAIR ? 2 * BM : BM;
   static constexpr int kRasterGroup = PAIR ? RASTER_GROUP / 2 : RASTER_GROUP;
 };
 
+// Work unit u -> (region, tile, split). Units are ordered region by region (the large
+// region first), and inside a region split-major, so with round-robin assignment every
+// worker gets its share of the expensive units before the cheap narrow ones fill the gaps.
 template <bool PAIR>
-__device__ __forceinline__ TileInfo decode_tile_t(const GemmParams& p, int t) {
+__device__ __forceinline__ TileInfo decode_tile_t(const GemmParams& p, int u) {
   int r = 0;
-  while (r + 1 < p.nregion && t >= p.reg[r + 1].tile_begin) ++r;
+  while (r + 1 < p.nregion && u >= p.reg[r + 1].tile_begin * p.splits) ++r;
   const Region& R = p.reg[r];
-  const int lt = t - R.tile_begin;
+  const int ul = u - R.tile_begin * p.splits;
+  const int tiles_r = R.m_tiles * R.n_tiles;
+  const int split = ul / tiles_r;
+  const int lt = ul - split * tiles_r;
   constexpr int G = Cfg<PAIR>::kRasterGroup;
   const int per_group = G * R.n_tiles;
   const int g = lt / per_group;
@@ -176,7 +225,7 @@ __device__ __forceinline__ TileInfo decode_tile_t(const GemmParams& p, int t) {
   const int rem = lt - g * per_group;
   const int mt = first_m + rem % gsz;
   const int nt = rem / gsz;
-  return {r, mt * Cfg<PAIR>::kTileM, nt * R.bn};
+  return {r, mt * Cfg<PAIR>::kTileM, nt * R.bn, split};
 }
 
 // Role loops are executed by ALL 32 lanes of their warp with warp-uniform control flow;
@@ -246,9 +295,9 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
     uint32_t ph = 0;
     bool ok = true;
     for (int u = worker; ok && u < units; u += nworkers) {
-      const int t = u % p.total_tiles;
-      const int split = u / p.total_tiles;
-      const TileInfo ti = decode_tile_t<PAIR>(p, t);
+      const int t = u;
+      const TileInfo ti = decode_tile_t<PAIR>(p, u);
+      const int split = ti.split;
       const Region& R = p.reg[ti.r];
       const int b_rows = PAIR ? (R.bn >> 1) : R.bn;          // B rows this CTA loads
       const int b_slabs = (b_rows + 63) >> 6;
@@ -332,9 +381,9 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       constexpr uint32_t a_step = (A_MN ? 2048u : 32u) >> 4;
       constexpr uint32_t b_step = (B_MN ? 2048u : 32u) >> 4;
       for (int u = worker; ok && u < units; u += nworkers, ++it) {
-        const int t = u % p.total_tiles;
-        const int split = u / p.total_tiles;
-        const TileInfo ti = decode_tile_t<PAIR>(p, t);
+        const int t = u;
+        const TileInfo ti = decode_tile_t<PAIR>(p, u);
+        const int split = ti.split;
         const Region& R = p.reg[ti.r];
         const uint32_t idesc = umma_idesc_bf16(C::kTileM, R.bn, A_MN ? 1 : 0, B_MN ? 1 : 0);
         const int buf = it & 1;
@@ -400,44 +449,99 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
   } else {
     // --------------------------------------------------------------- epilogue
     const int q = warp & 3;   // TMEM lane quarter this warp may read
+    const int trow = q * 32 + lane;                       // row inside this CTA's 128-row tile
+    const bool issuer = (warp == 2 && lane == 0);         // issues the TMA stores
+    const uint32_t epi_base = smem_base + S * C::kStageBytes;
+    uint32_t chunk_ctr = 0;
     int it = 0;
     for (int u = worker; u < units; u += nworkers, ++it) {
-      const int t = u % p.total_tiles;
-      const int split = u / p.total_tiles;
-      const TileInfo ti = decode_tile_t<PAIR>(p, t);
+      const int t = u;
+      const TileInfo ti = decode_tile_t<PAIR>(p, u);
+      const int split = ti.split;
       Region R = p.reg[ti.r];
       if (p.splits > 1) {
         // partial sums go to this split's slice of the workspace; splitk_reduce_kernel folds
         // them into the real output in a fixed order afterwards
         R.out = p.workspace + R.ws_off + static_cast<long long>(split) * R.rows * R.cols;
-        R.ld = R.cols;
+        R.ld = R.transposed ? R.rows : R.cols;
         R.mode = kEpiStoreF32;
         R.alpha = 1.f;
+        R.out_map = -1;
       }
       if (dbg & 1) R.rows = 0;   // debug: read TMEM, store nothing
       const int buf = it & 1;
       const uint32_t tph = (static_cast<uint32_t>(it) >> 1) & 1u;
-      bool ok = mbar_wait(tfull_bar(buf), tph, abortp, WAIT_LIMIT_NS);
-      ok = __all_sync(0xffffffffu, ok);
+      const bool ok = epi_vote_and(mbar_wait(tfull_bar(buf), tph, abortp, WAIT_LIMIT_NS));
       if (!ok) {
-        if (lane == 0) record_timeout(3, t);
+        if (issuer) record_timeout(3, t);
         break;
       }
       tc_fence_after_sync();
-      const int row = ti.m0 + BM * rank + q * 32 + lane;
+      const int row0 = ti.m0 + BM * rank;
+      const int row = row0 + trow;
       const uint32_t taddr =
           tmem_base + static_cast<uint32_t>(buf * BN_MAX) + (static_cast<uint32_t>(q * 32) << 16);
-      for (int c = 0; c < R.bn; c += 32) {
-        if (R.bn - c >= 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c, v);
-          tmem_ld_wait();
-          epilogue_store<32>(R, row, ti.n0 + c, v);
-        } else {
-          uint32_t v[16];
-          tmem_ld_32x16(taddr + c, v);
-          tmem_ld_wait();
-          epilogue_store<16>(R, row, ti.n0 + c, v);
+      if (R.out_map >= 0) {
+        // ---- staged epilogue: TMEM -> registers -> swizzled shared memory -> TMA store (or
+        // TMA reduce-add for the in-place fp32 accumulation). 128-byte rows: 64 bf16 or 32 fp32
+        // columns per chunk; two staging buffers so a store drains while the next chunk fills.
+        const CUtensorMap* om = &p.maps[R.out_map];
+        const bool f32 = R.mode != kEpiStoreBf16;
+        const float alpha = R.alpha;
+        const int step = f32 ? 32 : 64;
+        const uint32_t swz = static_cast<uint32_t>(trow & 7);
+        for (int c = 0; c < R.bn; c += step, ++chunk_ctr) {
+          const uint32_t sbuf = epi_base + (chunk_ctr & 1u) * EPI_STAGE_BYTES;
+          const uint32_t srow = sbuf + static_cast<uint32_t>(trow) * 128u;
+          if (issuer) tma_wait_group_read<1>();   // the store that last used this buffer has read it
+          epi_bar_sync();
+          if (f32) {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              st_shared_v4(srow + ((static_cast<uint32_t>(j) ^ swz) << 4),
+                           __float_as_uint(alpha * __uint_as_float(v[4 * j])),
+                           __float_as_uint(alpha * __uint_as_float(v[4 * j + 1])),
+                           __float_as_uint(alpha * __uint_as_float(v[4 * j + 2])),
+                           __float_as_uint(alpha * __uint_as_float(v[4 * j + 3])));
+          } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t v[32];
+              tmem_ld_32x32(taddr + c + 32 * h, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                st_shared_v4(srow + ((static_cast<uint32_t>(4 * h + j) ^ swz) << 4),
+                             pack_bf16(alpha * __uint_as_float(v[8 * j]), alpha * __uint_as_float(v[8 * j + 1])),
+                             pack_bf16(alpha * __uint_as_float(v[8 * j + 2]), alpha * __uint_as_float(v[8 * j + 3])),
+                             pack_bf16(alpha * __uint_as_float(v[8 * j + 4]), alpha * __uint_as_float(v[8 * j + 5])),
+                             pack_bf16(alpha * __uint_as_float(v[8 * j + 6]), alpha * __uint_as_float(v[8 * j + 7])));
+            }
+          }
+          fence_proxy_async_smem();
+          epi_bar_sync();
+          if (issuer && R.rows > 0) {
+            if (R.mode == kEpiAccumF32) tma_reduce_add_2d(om, sbuf, ti.n0 + c, row0);
+            else tma_store_2d(om, sbuf, ti.n0 + c, row0);
+            tma_commit_group();
+          }
+        }
+      } else {
+        for (int c = 0; c < R.bn; c += 32) {
+          if (R.bn - c >= 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + c, v);
+            tmem_ld_wait();
+            epilogue_store<32>(R, row, ti.n0 + c, v);
+          } else {
+            uint32_t v[16];
+            tmem_ld_32x16(taddr + c, v);
+            tmem_ld_wait();
+            epilogue_store<16>(R, row, ti.n0 + c, v);
+          }
         }
       }
       tc_fence_before_sync();
@@ -447,6 +551,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
         else mbar_arrive(tempty_bar(buf));
       }
     }
+    if (issuer) tma_wait_group<0>();   // all stores of this CTA have completed
   }
 
   // ---------------------------------------------------------------- tear-down
@@ -466,37 +571,57 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
   }
 }
 
-// Fold split-K partials into the output in a fixed order (deterministic):
-//   out[i,j] (op)= alpha * (ws[0][i,j] + ws[1][i,j] + ... + ws[S-1][i,j])
+// Fold split-K partials into the outputs in a fixed order (deterministic), all regions of
+// the launch in one kernel:  out[i,j] (op)= alpha * (ws[0][i,j] + ... + ws[S-1][i,j]).
+struct ReduceRegion {
+  const float4* ws;
+  void* out;
+  long long ld;
+  long long begin;    // first float4 index of this region in the flattened index space
+  int rows;
+  int cols4;
+  int mode;
+  float alpha;
+};
+struct ReduceParams {
+  ReduceRegion reg[kMaxRegion];
+  long long total;    // float4 elements over all regions
+  int nregion;
+  int splits;
+};
+
 __global__ void __launch_bounds__(256)
-splitk_reduce_kernel(const float4* __restrict__ ws, void* out, long long ld, int rows, int cols4,
-                     int splits, int mode, float alpha) {
-  const long long per = static_cast<long long>(rows) * cols4;
-  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < per; i += gridDim.x * 256ll) {
-    float4 a = ws[i];
-    for (int s = 1; s < splits; ++s) {
-      const float4 b = ws[s * per + i];
+splitk_reduce_kernel(const __grid_constant__ ReduceParams rp) {
+  for (long long gi = blockIdx.x * 256ll + threadIdx.x; gi < rp.total; gi += gridDim.x * 256ll) {
+    int r = 0;
+    while (r + 1 < rp.nregion && gi >= rp.reg[r + 1].begin) ++r;
+    const ReduceRegion& R = rp.reg[r];
+    const long long i = gi - R.begin;
+    const long long per = static_cast<long long>(R.rows) * R.cols4;
+    float4 a = R.ws[i];
+    for (int s = 1; s < rp.splits; ++s) {
+      const float4 b = R.ws[s * per + i];
       a.x += b.x;
       a.y += b.y;
       a.z += b.z;
       a.w += b.w;
     }
-    a.x *= alpha;
-    a.y *= alpha;
-    a.z *= alpha;
-    a.w *= alpha;
-    const long long r = i / cols4;
-    const int c = static_cast<int>(i - r * cols4) * 4;
-    if (mode == kEpiStoreBf16) {
+    a.x *= R.alpha;
+    a.y *= R.alpha;
+    a.z *= R.alpha;
+    a.w *= R.alpha;
+    const long long row = i / R.cols4;
+    const int c = static_cast<int>(i - row * R.cols4) * 4;
+    if (R.mode == kEpiStoreBf16) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y);
       __nv_bfloat162 hi = __floats2bfloat162_rn(a.z, a.w);
       uint2 pk;
       pk.x = *reinterpret_cast<uint32_t*>(&lo);
       pk.y = *reinterpret_cast<uint32_t*>(&hi);
-      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + r * ld + c) = pk;
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(R.out) + row * R.ld + c) = pk;
     } else {
-      float4* dst = reinterpret_cast<float4*>(static_cast<float*>(out) + r * ld + c);
-      if (mode == kEpiAccumF32) {
+      float4* dst = reinterpret_cast<float4*>(static_cast<float*>(R.out) + row * R.ld + c);
+      if (R.mode == kEpiAccumF32) {
         const float4 o = *dst;
         a.x += o.x;
         a.y += o.y;
@@ -558,6 +683,22 @@ static int ensure_encode() {
 
 // Tensor map over a row-major bf16 matrix [rows, cols] (pitch ld elements) with a
 // box of box_cols (<= 64) x box_rows, 128-byte swizzle, zero fill outside.
+// Tensor map over a row-major output matrix (bf16 or fp32) for the staged epilogue: box of
+// 128 bytes x 128 rows, 128-byte swizzle.
+static int make_map_out(CUtensorMap* m, void* ptr, long long rows, long long cols, long long ld,
+                        bool f32) {
+  const int es = f32 ? 4 : 2;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * es};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / es), 128u};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                        ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? WSL_OK : WSL_ERR_DRIVER;
+}
+
 static int make_map_bf16(CUtensorMap* m, const Mat& t, int box_cols, int box_rows) {
   if (t.ptr == nullptr || t.rows <= 0 || t.cols <= 0) return WSL_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(t.ptr) & 15u) != 0 || (t.ld % 8) != 0 || t.ld < t.cols)
@@ -573,20 +714,40 @@ static int make_map_bf16(CUtensorMap* m, const Mat& t, int box_cols, int box_row
   return r == CUDA_SUCCESS ? WSL_OK : WSL_ERR_DRIVER;
 }
 
-// Split-K factor for a launch of `tiles` output tiles with `kb_total` k-blocks each. Cost
-// model per S: waves * k-blocks-per-unit (one k-block of one tile ~ 0.27 us) plus the
-// workspace round trip (S partial copies written and read once at ~6.5 MB/us) and the
-// second launch. S = 1 when the tile grid already fills the SMs twice over.
-int choose_splits(double tiles, int kb_total, long long out_elems, size_t ws_limit_bytes,
-                  int num_sms) {
-  if (tiles >= 2.0 * num_sms) return 1;
+// Relative cost of one k-block of a tile with MMA N = bn: wide tiles are bound by the
+// MMAs, narrow ones by their operand loads.
+double tile_weight(long long no) {
+  const long long n_tiles = (no + BN_MAX - 1) / BN_MAX;
+  const double bn = static_cast<double>((no + n_tiles - 1) / n_tiles);
+  return bn / BN_MAX < 0.4 ? 0.4 : bn / BN_MAX;
+}
+
+// Split-K factor for a launch. `tiles[i]`, `weight[i]`: number of 128-row-equivalent tiles
+// and per-k-block weight of region i (regions in launch order). The work units (tiles x S,
+// region by region) are dealt round-robin to `num_sms` workers exactly as the kernel does;
+// the S with the smallest simulated makespan wins, charging the workspace round trip
+// (S partial copies written and read once at ~6.5 MB/us) and the reduce launch.
+// One k-block of a full tile ~ 0.27 us.
+int choose_splits(int nregion, const long long* tiles, const double* weight, int kb_total,
+                  long long out_elems, size_t ws_limit_bytes, int num_sms) {
+  long long total = 0;
+  for (int i = 0; i < nregion; ++i) total += tiles[i];
+  if (total >= 6ll * num_sms) return 1;
   double best = 1e30;
   int best_s = 1;
+  double load[256];
+  const int W = num_sms < 256 ? num_sms : 256;
   for (int S = 1; S <= 16 && S * 8 <= kb_total; ++S) {
     if (S > 1 && static_cast<size_t>(S) * out_elems * 4 > ws_limit_bytes) break;
-    const double waves = ceil(tiles * S / num_sms - 1e-9);
-    double t = waves * ((kb_total + S - 1) / S) * 0.27;
-    if (S > 1) t += 2.0 * S * out_elems * 4 / 6.5e6 + 3.0;
+    for (int w = 0; w < W; ++w) load[w] = 0.0;
+    const double kb = static_cast<double>((kb_total + S - 1) / S);
+    long long u = 0;
+    for (int i = 0; i < nregion; ++i)
+      for (long long j = 0; j < tiles[i] * S; ++j, ++u) load[u % W] += kb * weight[i] + 6.0;
+    double mk = 0.0;
+    for (int w = 0; w < W; ++w) mk = load[w] > mk ? load[w] : mk;
+    double t = mk * 0.27;
+    if (S > 1) t += 2.0 * S * out_elems * 4 / 6.5e6 + 4.0;
     if (t < best) {
       best = t;
       best_s = S;
@@ -595,14 +756,14 @@ int choose_splits(double tiles, int kb_total, long long out_elems, size_t ws_lim
   return best_s;
 }
 
-// Tile count of one output region (BM x up-to-256 tiles), weighted by the relative cost of
-// a tile: narrow tiles (bn < 256) are bound by their operand loads, not by the MMAs.
-double region_tiles(long long mo, long long no) {
-  const long long n_tiles = (no + BN_MAX - 1) / BN_MAX;
-  const double bn = static_cast<double>((no + n_tiles - 1) / n_tiles);
-  const double w = bn / BN_MAX < 0.35 ? 0.35 : bn / BN_MAX;
-  return static_cast<double>(((mo + BM - 1) / BM) * n_tiles) * w;
+// The launch uses CTA pairs (256-row tiles) when its first region is large enough.
+bool use_pair_tiles(long long mo0, long long no0);
+
+long long region_tiles(bool pair, long long mo, long long no) {
+  const long long tm = pair ? 2 * BM : BM;
+  return ((mo + tm - 1) / tm) * ((no + BN_MAX - 1) / BN_MAX);
 }
+int split_workers(bool pair, int num_sms) { return pair ? num_sms / 2 : num_sms; }
 int kblocks(long long k) { return static_cast<int>((k + BK - 1) / BK); }
 
 static int g_max_clusters = 0;   // co-resident CTA pairs of the PAIR variant
@@ -664,6 +825,10 @@ static bool pair_mode_enabled() {
   return v == 1;
 }
 
+bool use_pair_tiles(long long mo0, long long no0) {
+  return pair_mode_enabled() && mo0 >= 512 && no0 >= 128;
+}
+
 int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   int st = ensure_device();
   if (st != WSL_OK) return st;
@@ -671,7 +836,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   if (st != WSL_OK) return st;
   if (g.nseg < 1 || g.nseg > kMaxSeg || g.nregion < 1 || g.nregion > kMaxRegion)
     return WSL_ERR_BAD_ARG;
-  if (g.nseg * g.nregion * 2 > kMaxMaps) return WSL_ERR_BAD_ARG;
+  if (g.nseg * g.nregion * 2 + g.nregion > kMaxMaps) return WSL_ERR_BAD_ARG;
 
   GemmParams p;
   p.nseg = g.nseg;
@@ -681,7 +846,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     if (g.seg_k[s] <= 0) return WSL_ERR_BAD_ARG;
 
   // CTA pairs (256-row tiles) for the large GEMMs; single CTAs for narrow/short ones.
-  const bool pair = pair_mode_enabled() && g.region[0].mo >= 512 && g.region[0].no >= 128;
+  const bool pair = use_pair_tiles(g.region[0].mo, g.region[0].no);
   const int bm_tile = pair ? 2 * BM : BM;
   const int bn_round = pair ? 32 : 16;
   int nmaps = 0;
@@ -691,9 +856,15 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     Region& R = p.reg[r];
     if (rd.mo <= 0 || rd.no <= 0 || rd.out == nullptr) return WSL_ERR_BAD_ARG;
     const int vec = rd.mode == kEpiStoreBf16 ? 8 : 4;
-    if ((rd.no % vec) != 0 || (rd.ld_out % vec) != 0 || rd.ld_out < rd.no ||
-        (reinterpret_cast<uintptr_t>(rd.out) & 15u) != 0)
+    if (rd.transposed) {
+      if (rd.mode == kEpiStoreBf16) return WSL_ERR_BAD_ARG;
+      if ((rd.mo % 4) != 0 || (rd.ld_out % 4) != 0 || rd.ld_out < rd.mo ||
+          (reinterpret_cast<uintptr_t>(rd.out) & 15u) != 0)
+        return WSL_ERR_ALIGN;
+    } else if ((rd.no % vec) != 0 || (rd.ld_out % vec) != 0 || rd.ld_out < rd.no ||
+               (reinterpret_cast<uintptr_t>(rd.out) & 15u) != 0) {
       return WSL_ERR_ALIGN;
+    }
     const long long n_tiles = (rd.no + BN_MAX - 1) / BN_MAX;
     long long bn = (rd.no + n_tiles - 1) / n_tiles;
     bn = (bn + bn_round - 1) / bn_round * bn_round;
@@ -710,6 +881,8 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     R.mode = rd.mode;
     R.alpha = rd.alpha;
     R.ws_off = 0;
+    R.transposed = rd.transposed ? 1 : 0;
+    R.out_map = -1;
     tiles += m_tiles * n_tiles;
     for (int s = 0; s < kMaxSeg; ++s) {
       R.a_map[s] = 0;
@@ -741,9 +914,14 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   if (g.workspace != nullptr) {
     long long out_elems = 0;
     for (int r = 0; r < g.nregion; ++r) out_elems += g.region[r].mo * g.region[r].no;
-    double eff_tiles = 0.0;
-    for (int r = 0; r < g.nregion; ++r) eff_tiles += region_tiles(g.region[r].mo, g.region[r].no);
-    const int S = choose_splits(eff_tiles, kb_total, out_elems, g.workspace_bytes, g_num_sms);
+    long long rt[kMaxRegion];
+    double rw[kMaxRegion];
+    for (int r = 0; r < g.nregion; ++r) {
+      rt[r] = region_tiles(pair, g.region[r].mo, g.region[r].no);
+      rw[r] = tile_weight(g.region[r].no);
+    }
+    const int S = choose_splits(g.nregion, rt, rw, kb_total, out_elems, g.workspace_bytes,
+                                split_workers(pair, g_num_sms));
     if (S > 1) {
       p.splits = S;
       p.workspace = g.workspace;
@@ -756,6 +934,17 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   }
   p.dbg = 0;
   if (const char* e = getenv("WSL_DBG")) p.dbg = atoi(e);
+  if (p.splits == 1 && !(p.dbg & 32)) {
+    // staged TMA-store epilogue where the tile width is a whole number of 128-byte chunks
+    for (int r = 0; r < g.nregion; ++r) {
+      const RegionDesc& rd = g.region[r];
+      const bool f32 = rd.mode != kEpiStoreBf16;
+      if (rd.transposed || (p.reg[r].bn % (f32 ? 32 : 64)) != 0) continue;
+      st = make_map_out(&p.maps[nmaps], rd.out, rd.mo, rd.no, rd.ld_out, f32);
+      if (st != WSL_OK) return st;
+      p.reg[r].out_map = nmaps++;
+    }
+  }
   const long long units = tiles * p.splits;
 #define WSL_LAUNCH(AM, BM_) (pair ? launch_variant<AM, BM_, true>(p, units, stream) \
                                   : launch_variant<AM, BM_, false>(p, units, stream))
@@ -765,17 +954,32 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   else st = WSL_LAUNCH(true, false);
 #undef WSL_LAUNCH
   if (st != WSL_OK || p.splits == 1) return st;
+  ReduceParams rp;
+  rp.nregion = g.nregion;
+  rp.splits = p.splits;
+  long long total = 0;
   for (int r = 0; r < g.nregion; ++r) {
     const RegionDesc& rd = g.region[r];
-    const long long per = rd.mo * (rd.no / 4);
-    long long blocks = (per + 255) / 256;
-    if (blocks > 8ll * g_num_sms) blocks = 8ll * g_num_sms;
-    splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-        reinterpret_cast<const float4*>(p.workspace + p.reg[r].ws_off), rd.out, rd.ld_out,
-        static_cast<int>(rd.mo), static_cast<int>(rd.no / 4), p.splits, rd.mode, rd.alpha);
-    if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
-    ++g_launch_count;
+    // output orientation: a transposed region's result matrix is [no, mo]
+    const long long orows = rd.transposed ? rd.no : rd.mo;
+    const long long ocols = rd.transposed ? rd.mo : rd.no;
+    ReduceRegion& R = rp.reg[r];
+    R.ws = reinterpret_cast<const float4*>(p.workspace + p.reg[r].ws_off);
+    R.out = rd.out;
+    R.ld = rd.ld_out;
+    R.begin = total;
+    R.rows = static_cast<int>(orows);
+    R.cols4 = static_cast<int>(ocols / 4);
+    R.mode = rd.mode;
+    R.alpha = rd.alpha;
+    total += orows * (ocols / 4);
   }
+  rp.total = total;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 8ll * g_num_sms) blocks = 8ll * g_num_sms;
+  splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(rp);
+  if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
+  ++g_launch_count;
   return WSL_OK;
 }
 

@@ -38,6 +38,11 @@ struct RegionDesc {
   long long ld_out;
   int mode;
   float alpha;
+  // fp32 modes only: write the tile transposed, i.e. the result matrix is [no, mo] with
+  // pitch ld_out and tile element (i, j) goes to out[j * ld_out + i]. Lets a product whose
+  // natural output is short and wide (dA = U^T x, [r, K]) run as its tall-and-narrow
+  // transpose (x^T U, [K, r]) with a narrow, cheap MMA N.
+  bool transposed;
 };
 
 struct GemmDesc {

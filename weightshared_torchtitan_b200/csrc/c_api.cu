@@ -21,6 +21,43 @@ static inline Mat mat(const void* p, long long rows, long long cols, long long l
   m.ld = ld;
   return m;
 }
+// The three regions of the weight-gradient launch (token contraction, MN-major operands):
+//   dW[N,K] += dY^T x ;  dB[N,r] += dY^T T ;  dA[r,K] += U^T x, run as its transpose
+//   x^T U -> [K, r] so that the narrow dimension r is the MMA N (cheap) instead of a
+//   mostly-empty 128-row M tile.
+void build_bwd_dw_desc(GemmDesc& g, const void* dY, long long lddy, const void* U, long long ldu,
+                       const void* x, long long ldx, const void* T, long long ldt, float* dW,
+                       float* dA, float* dB, long long M, long long N, long long K, long long r) {
+  g.a_mn = true;
+  g.b_mn = true;
+  g.nseg = 1;
+  g.seg_k[0] = static_cast<int>(M);
+  int nr = 0;
+  auto add = [&](const void* a, long long a_cols, long long lda, const void* b, long long b_cols,
+                 long long ldb, float* out, long long ld_out, bool transposed) {
+    RegionDesc& rd = g.region[nr++];
+    rd.a[0].ptr = a;
+    rd.a[0].rows = M;
+    rd.a[0].cols = a_cols;
+    rd.a[0].ld = lda;
+    rd.b[0].ptr = b;
+    rd.b[0].rows = M;
+    rd.b[0].cols = b_cols;
+    rd.b[0].ld = ldb;
+    rd.mo = a_cols;
+    rd.no = b_cols;
+    rd.out = out;
+    rd.ld_out = ld_out;
+    rd.mode = kEpiAccumF32;
+    rd.alpha = 1.f;
+    rd.transposed = transposed;
+  };
+  if (dW) add(dY, N, lddy, x, K, ldx, dW, K, false);
+  if (dB) add(dY, N, lddy, T, r, ldt, dB, r, false);
+  if (dA) add(x, K, ldx, U, r, ldu, dA, K, true);
+  g.nregion = nr;
+}
+
 static inline bool bad_dtype(int dtype) { return dtype != WSL_BF16 && dtype != WSL_F32; }
 static inline const float* f32(const void* p) { return static_cast<const float*>(p); }
 }  // namespace wsl
@@ -262,45 +299,7 @@ int wsl_lora_linear_bwd_dw(const void* dY, long long lddy, const void* U, long l
     return st;
   }
   GemmDesc g = {};
-  g.a_mn = true;
-  g.b_mn = true;
-  g.nseg = 1;
-  g.seg_k[0] = static_cast<int>(M);
-  int nr = 0;
-  if (dW) {
-    RegionDesc& rd = g.region[nr++];
-    rd.a[0] = mat(dY, M, N, lddy);
-    rd.b[0] = mat(x, M, K, ldx);
-    rd.mo = N;
-    rd.no = K;
-    rd.out = dW;
-    rd.ld_out = K;
-    rd.mode = kEpiAccumF32;
-    rd.alpha = 1.f;
-  }
-  if (dB) {
-    RegionDesc& rd = g.region[nr++];
-    rd.a[0] = mat(dY, M, N, lddy);
-    rd.b[0] = mat(T, M, r, ldt);
-    rd.mo = N;
-    rd.no = r;
-    rd.out = dB;
-    rd.ld_out = r;
-    rd.mode = kEpiAccumF32;
-    rd.alpha = 1.f;
-  }
-  if (dA) {
-    RegionDesc& rd = g.region[nr++];
-    rd.a[0] = mat(U, M, r, ldu);
-    rd.b[0] = mat(x, M, K, ldx);
-    rd.mo = r;
-    rd.no = K;
-    rd.out = dA;
-    rd.ld_out = K;
-    rd.mode = kEpiAccumF32;
-    rd.alpha = 1.f;
-  }
-  g.nregion = nr;
+  build_bwd_dw_desc(g, dY, lddy, U, ldu, x, ldx, T, ldt, dW, dA, dB, M, N, K, r);
   if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return WSL_ERR_ALIGN;
   g.workspace = static_cast<float*>(workspace);
   g.workspace_bytes = static_cast<size_t>(workspace_bytes);
@@ -310,14 +309,20 @@ int wsl_lora_linear_bwd_dw(const void* dY, long long lddy, const void* U, long l
 unsigned long long wsl_bwd_dw_workspace_bytes(long long M, long long N, long long K, long long r,
                                               int want_dW, int want_dA, int want_dB) {
   if (M <= 0 || N <= 0 || K <= 0 || r < 0) return 0;
-  double tiles = 0.0;
+  long long rt[3];
+  double rw[3];
+  int nr = 0;
   long long out_elems = 0;
-  if (want_dW) { tiles += region_tiles(N, K); out_elems += N * K; }
-  if (want_dB && r > 0) { tiles += region_tiles(N, r); out_elems += N * r; }
-  if (want_dA && r > 0) { tiles += region_tiles(r, K); out_elems += r * K; }
+  // same region order and tiling rule as the launch itself
+  const bool pair = want_dW ? use_pair_tiles(N, K)
+                            : (want_dB && r > 0 ? use_pair_tiles(N, r) : use_pair_tiles(K, r));
+  if (want_dW) { rt[nr] = region_tiles(pair, N, K); rw[nr++] = tile_weight(K); out_elems += N * K; }
+  if (want_dB && r > 0) { rt[nr] = region_tiles(pair, N, r); rw[nr++] = tile_weight(r); out_elems += N * r; }
+  if (want_dA && r > 0) { rt[nr] = region_tiles(pair, K, r); rw[nr++] = tile_weight(r); out_elems += r * K; }
   if (out_elems == 0) return 0;
   const int sms = device_check() == WSL_OK ? device_sm_count() : 148;
-  const int S = choose_splits(tiles, kblocks(M), out_elems, ~static_cast<size_t>(0), sms);
+  const int S = choose_splits(nr, rt, rw, kblocks(M), out_elems, ~static_cast<size_t>(0),
+                              split_workers(pair, sms));
   return S > 1 ? static_cast<unsigned long long>(S) * out_elems * 4ull : 0ull;
 }
 

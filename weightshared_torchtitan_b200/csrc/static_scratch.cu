@@ -20,6 +20,10 @@
 
 namespace wsl {
 
+void build_bwd_dw_desc(GemmDesc& g, const void* dY, long long lddy, const void* U, long long ldu,
+                       const void* x, long long ldx, const void* T, long long ldt, float* dW,
+                       float* dA, float* dB, long long M, long long N, long long K, long long r);
+
 constexpr unsigned long long kStaticScratchBytes = WSL_NOALLOC_SCRATCH_BYTES;
 constexpr int kMaxDevices = 64;
 
@@ -78,33 +82,7 @@ extern "C" int wsl_lora_linear_bwd_dw_noalloc(const void* dY, long long lddy, co
   if (st != WSL_OK) return st;
 
   GemmDesc g = {};
-  g.a_mn = true;
-  g.b_mn = true;
-  g.nseg = 1;
-  g.seg_k[0] = static_cast<int>(M);
-  int nr = 0;
-  auto add = [&](const void* a, long long a_cols, long long lda, const void* b, long long b_cols,
-                 long long ldb, float* out) {
-    RegionDesc& rd = g.region[nr++];
-    rd.a[0].ptr = a;
-    rd.a[0].rows = M;
-    rd.a[0].cols = a_cols;
-    rd.a[0].ld = lda;
-    rd.b[0].ptr = b;
-    rd.b[0].rows = M;
-    rd.b[0].cols = b_cols;
-    rd.b[0].ld = ldb;
-    rd.mo = a_cols;
-    rd.no = b_cols;
-    rd.out = out;
-    rd.ld_out = b_cols;
-    rd.mode = kEpiAccumF32;
-    rd.alpha = 1.f;
-  };
-  if (dW) add(dY, N, lddy, x, K, ldx, dW);
-  if (dB) add(dY, N, lddy, T, r, ldt, dB);
-  if (dA) add(U, r, ldu, x, K, ldx, dA);
-  g.nregion = nr;
+  build_bwd_dw_desc(g, dY, lddy, U, ldu, x, ldx, T, ldt, dW, dA, dB, M, N, K, r);
   g.workspace = scratch;
   g.workspace_bytes = static_cast<size_t>(kStaticScratchBytes);
   return launch_block_gemm(g, static_cast<cudaStream_t>(stream));
