@@ -46,7 +46,6 @@ constexpr int SLAB_BYTES = 64 * BK * 2;          // one MN-major slab: 64 k-rows
 constexpr int EPI_STAGE_BYTES = 128 * 128;       // epilogue staging: 128 rows x 128 B, two of them
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int RASTER_GROUP = 16;
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s
 
 struct Region {
@@ -65,6 +64,7 @@ struct Region {
   long long ws_off;   // split-K: float offset of this region's partials in the workspace
   int transposed;     // fp32 output element (row, col) of the tile lives at out[col * ld + row]
   int out_map;        // tensor map of the output for the TMA-store epilogue, or -1
+  int group;          // rasterisation: M-tiles per group (their A rows stay L2-resident)
 };
 
 struct GemmParams {
@@ -202,7 +202,6 @@ struct Cfg {
   static constexpr int kStageBytes = A_STAGE_BYTES + kBStageBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + 2 * EPI_STAGE_BYTES + 1024;
   static constexpr int kTileM = PAIR ? 2 * BM : BM;
-  static constexpr int kRasterGroup = PAIR ? RASTER_GROUP / 2 : RASTER_GROUP;
 };
 
 // Work unit u -> (region, tile, split). Units are ordered region by region (the large
@@ -217,7 +216,7 @@ __device__ __forceinline__ TileInfo decode_tile_t(const GemmParams& p, int u) {
   const int tiles_r = R.m_tiles * R.n_tiles;
   const int split = ul / tiles_r;
   const int lt = ul - split * tiles_r;
-  constexpr int G = Cfg<PAIR>::kRasterGroup;
+  const int G = R.group;
   const int per_group = G * R.n_tiles;
   const int g = lt / per_group;
   const int first_m = g * G;
@@ -883,6 +882,17 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     R.ws_off = 0;
     R.transposed = rd.transposed ? 1 : 0;
     R.out_map = -1;
+    {
+      // A rows of one group (all contraction segments) should sit in about a third of the
+      // 126 MB L2 while the B tiles stream past them; at least one wave of workers wide.
+      long long ktot = 0;
+      for (int sgi = 0; sgi < g.nseg; ++sgi) ktot += g.seg_k[sgi];
+      long long grp = (40ll << 20) / (2 * ktot * bm_tile);
+      if (grp < 4) grp = 4;
+      if (grp > (pair ? 16 : 32)) grp = pair ? 16 : 32;   // keep a wave a 2-D patch of tiles
+      if (grp > m_tiles) grp = m_tiles;
+      R.group = static_cast<int>(grp);
+    }
     tiles += m_tiles * n_tiles;
     for (int s = 0; s < kMaxSeg; ++s) {
       R.a_map[s] = 0;
