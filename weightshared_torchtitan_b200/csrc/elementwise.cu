@@ -245,22 +245,36 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, long long ldx, const float* __restri
       if (l < (lpr >> 1)) sr[e] = -sr[e];   // rotate_half: first half takes -n[j + D/2]
     }
   }
-#pragma unroll 2
+  // software pipeline: the loads of row rr+1 are in flight while row rr is reduced and stored
+  Vec<T> nxt[KV];
+#pragma unroll
+  for (int k = 0; k < KV; ++k) {
+    if (row0 < rows) nxt[k] = ldv<T>(x + row0 * ldx + (k * lpr + l) * NV);
+    else
+#pragma unroll
+      for (int e = 0; e < NV; ++e) nxt[k].set(e, 0.f);
+  }
   for (int rr = 0; rr < iters; ++rr) {
     const long long row = row0 + rr;
     const bool valid = row < rows;
     Vec<T> xv[KV];
     float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < KV; ++k)
-      if (k < kv) {
-        if (valid) xv[k] = ldv<T>(x + row * ldx + (k * lpr + l) * NV);
+    for (int k = 0; k < KV; ++k) xv[k] = nxt[k];
+    if (rr + 1 < iters) {
+      const bool nvalid = row + 1 < rows;
+#pragma unroll
+      for (int k = 0; k < KV; ++k) {
+        if (nvalid) nxt[k] = ldv<T>(x + (row + 1) * ldx + (k * lpr + l) * NV);
         else
 #pragma unroll
-          for (int e = 0; e < NV; ++e) xv[k].set(e, 0.f);
-#pragma unroll
-        for (int e = 0; e < NV; ++e) ss += xv[k].get(e) * xv[k].get(e);
+          for (int e = 0; e < NV; ++e) nxt[k].set(e, 0.f);
       }
+    }
+#pragma unroll
+    for (int k = 0; k < KV; ++k)
+#pragma unroll
+      for (int e = 0; e < NV; ++e) ss += xv[k].get(e) * xv[k].get(e);
     ss = group_sum(ss, lpr);
     const float rstd = rsqrtf(ss / D + eps);
     if (valid && l == 0 && rstd_out) rstd_out[row] = rstd;
@@ -284,8 +298,10 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, long long ldx, const float* __restri
 
 // Backward: dx = rstd * (g - x * rstd^2 * mean(g * x)), g = dn * w, dn = un-rotated dy;
 // dw[j] += sum_rows dn[j] * x[j] * rstd (registers -> shared-memory partials -> atomics).
+// Two CTAs per SM (register cap 128): the row loop is latency-bound, so resident warps
+// matter more than registers; the scale w is re-read from L1 per row instead of cached.
 template <typename T, bool ROPE, int KV>
-__global__ void __launch_bounds__(RN_WARPS * 32)
+__global__ void __launch_bounds__(RN_WARPS * 32, 2)
 rmsnorm_bwd_kernel(const T* __restrict__ dy, long long lddy, const T* __restrict__ x, long long ldx,
                    const float* __restrict__ w, const float* __restrict__ rstd_in,
                    T* __restrict__ dx, long long lddx, float* dw, long long rows, int D, int lpr,
@@ -297,17 +313,13 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, long long lddy, const T* __restrict
   const int warp = threadIdx.x >> 5;
   const int rpw = 32 / lpr;
   const int l = lane % lpr;
-  constexpr int kv = KV;
   for (int j = threadIdx.x; j < D; j += RN_WARPS * 32) dw_part[j] = 0.f;
   __syncthreads();
-  float dwacc[KV][NV], wr[KV][NV];
+  float dwacc[KV][NV];
 #pragma unroll
   for (int k = 0; k < KV; ++k)
 #pragma unroll
-    for (int e = 0; e < NV; ++e) {
-      dwacc[k][e] = 0.f;
-      wr[k][e] = w[(k * lpr + l) * NV + e];
-    }
+    for (int e = 0; e < NV; ++e) dwacc[k][e] = 0.f;
   const long long group = (blockIdx.x * static_cast<long long>(RN_WARPS) + warp) * rpw + lane / lpr;
   const long long row0 = group * iters;
   float cr[NV], sr[NV];
@@ -327,59 +339,58 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, long long lddy, const T* __restrict
         }
       }
     }
-    float dn[KV][NV];
-    Vec<T> xv[KV];
+    Vec<T> dv[KV], xv[KV];
 #pragma unroll
-    for (int k = 0; k < KV; ++k)
-      if (k < kv) {
-        if (valid) {
-          const Vec<T> d = ldv<T>(dy + row * lddy + (k * lpr + l) * NV);
-          xv[k] = ldv<T>(x + row * ldx + (k * lpr + l) * NV);
+    for (int k = 0; k < KV; ++k) {
+      if (valid) {
+        dv[k] = ldv<T>(dy + row * lddy + (k * lpr + l) * NV);
+        xv[k] = ldv<T>(x + row * ldx + (k * lpr + l) * NV);
+      } else {
 #pragma unroll
-          for (int e = 0; e < NV; ++e) dn[k][e] = d.get(e);
-        } else {
-#pragma unroll
-          for (int e = 0; e < NV; ++e) {
-            dn[k][e] = 0.f;
-            xv[k].set(e, 0.f);
-          }
+        for (int e = 0; e < NV; ++e) {
+          dv[k].set(e, 0.f);
+          xv[k].set(e, 0.f);
         }
       }
+    }
+    float dn0[NV];   // un-rotated gradient of the (single) vector when ROPE
     if (ROPE) {
 #pragma unroll
       for (int e = 0; e < NV; ++e) {
         // dn[j] = dy[j] cos[j] + (j < D/2 ? dy[j+D/2] sin[j+D/2] : -dy[j-D/2] sin[j-D/2])
-        const float other = __shfl_xor_sync(0xffffffffu, dn[0][e] * sr[e], lpr >> 1);
-        dn[0][e] = dn[0][e] * cr[e] + (l < (lpr >> 1) ? other : -other);
+        const float d = dv[0].get(e);
+        const float other = __shfl_xor_sync(0xffffffffu, d * sr[e], lpr >> 1);
+        dn0[e] = d * cr[e] + (l < (lpr >> 1) ? other : -other);
       }
     }
     float dot = 0.f;
 #pragma unroll
     for (int k = 0; k < KV; ++k)
-      if (k < kv)
 #pragma unroll
-        for (int e = 0; e < NV; ++e) {
-          const float xe = xv[k].get(e);
-          dot += dn[k][e] * wr[k][e] * xe;
-          dwacc[k][e] += dn[k][e] * xe * rstd;
-        }
+      for (int e = 0; e < NV; ++e) {
+        const float xe = xv[k].get(e);
+        const float dne = ROPE ? dn0[e] : dv[k].get(e);
+        dot += dne * __ldg(w + (k * lpr + l) * NV + e) * xe;
+        dwacc[k][e] += dne * xe * rstd;
+      }
     dot = group_sum(dot, lpr);
     const float c = dot * rstd * rstd / D;
 #pragma unroll
-    for (int k = 0; k < KV; ++k)
-      if (k < kv) {
-        Vec<T> o;
+    for (int k = 0; k < KV; ++k) {
+      Vec<T> o;
 #pragma unroll
-        for (int e = 0; e < NV; ++e) o.set(e, rstd * (dn[k][e] * wr[k][e] - xv[k].get(e) * c));
-        if (valid) stv<T>(dx + row * lddx + (k * lpr + l) * NV, o);
+      for (int e = 0; e < NV; ++e) {
+        const float dne = ROPE ? dn0[e] : dv[k].get(e);
+        o.set(e, rstd * (dne * __ldg(w + (k * lpr + l) * NV + e) - xv[k].get(e) * c));
       }
+      if (valid) stv<T>(dx + row * lddx + (k * lpr + l) * NV, o);
+    }
   }
   if (dw != nullptr) {
 #pragma unroll
     for (int k = 0; k < KV; ++k)
-      if (k < kv)
 #pragma unroll
-        for (int e = 0; e < NV; ++e) atomicAdd(&dw_part[(k * lpr + l) * NV + e], dwacc[k][e]);
+      for (int e = 0; e < NV; ++e) atomicAdd(&dw_part[(k * lpr + l) * NV + e], dwacc[k][e]);
     __syncthreads();
     for (int j = threadIdx.x; j < D; j += RN_WARPS * 32) atomicAdd(dw + j, dw_part[j]);
   }
