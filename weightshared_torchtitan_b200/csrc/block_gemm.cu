@@ -77,7 +77,9 @@ struct GemmParams {
   int splits;         // split-K factor: work units = total_tiles * splits
   int kb_total;       // k-blocks summed over the segments
   float* workspace;   // [splits][rows x cols] fp32 partials per region when splits > 1
-  int dbg;            // debug bits: 1 skip epilogue stores, 2 skip TMA loads, 4 skip MMAs
+  int dbg;            // debug bits: 1 skip epilogue stores, 2 skip TMA loads, 4 skip MMAs,
+                      // 64 the producer never fills the ring (exercises the bounded waits)
+  unsigned long long wait_limit_ns;   // bound of every mbarrier wait
 };
 
 struct TileInfo {
@@ -313,13 +315,13 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
         split_range(p.kb_total, p.splits, split, kb_base, nkb, lo, hi);
         kb_base += nkb;
         for (int kk = lo * BK; kk < hi * BK; kk += BK) {
-          ok = __all_sync(0xffffffffu, (dbg & 16) ? mbar_wait<true>(empty_bar(s), ph ^ 1u, abortp, WAIT_LIMIT_NS)
-                                                   : mbar_wait<false>(empty_bar(s), ph ^ 1u, abortp, WAIT_LIMIT_NS));
+          ok = __all_sync(0xffffffffu, (dbg & 16) ? mbar_wait<true>(empty_bar(s), ph ^ 1u, abortp, p.wait_limit_ns)
+                                                   : mbar_wait<false>(empty_bar(s), ph ^ 1u, abortp, p.wait_limit_ns));
           if (!ok) {
             if (lane == 0) record_timeout(1, t);
             break;
           }
-          if (elect_one()) {
+          if (elect_one() && !(dbg & 64)) {
             const uint32_t sa = smem_base + s * C::kStageBytes;
             const uint32_t sb = sa + A_STAGE_BYTES;
             if (dbg & 2) {
@@ -387,7 +389,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t idesc = umma_idesc_bf16(C::kTileM, R.bn, A_MN ? 1 : 0, B_MN ? 1 : 0);
         const int buf = it & 1;
         const uint32_t tph = (static_cast<uint32_t>(it) >> 1) & 1u;
-        ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(buf), tph ^ 1u, abortp, WAIT_LIMIT_NS));
+        ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(buf), tph ^ 1u, abortp, p.wait_limit_ns));
         if (!ok) {
           if (lane == 0) record_timeout(2, t);
           break;
@@ -403,8 +405,8 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
           split_range(p.kb_total, p.splits, split, kb_base, nkb, lo, hi);
           kb_base += nkb;
           for (int kk = lo * BK; kk < hi * BK; kk += BK) {
-            ok = __all_sync(0xffffffffu, (dbg & 16) ? mbar_wait<true>(full_bar(s), ph, abortp, WAIT_LIMIT_NS)
-                                                     : mbar_wait<false>(full_bar(s), ph, abortp, WAIT_LIMIT_NS));
+            ok = __all_sync(0xffffffffu, (dbg & 16) ? mbar_wait<true>(full_bar(s), ph, abortp, p.wait_limit_ns)
+                                                     : mbar_wait<false>(full_bar(s), ph, abortp, p.wait_limit_ns));
             if (!ok) {
               if (lane == 0) record_timeout(2, t);
               break;
@@ -470,7 +472,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       if (dbg & 1) R.rows = 0;   // debug: read TMEM, store nothing
       const int buf = it & 1;
       const uint32_t tph = (static_cast<uint32_t>(it) >> 1) & 1u;
-      const bool ok = epi_vote_and(mbar_wait(tfull_bar(buf), tph, abortp, WAIT_LIMIT_NS));
+      const bool ok = epi_vote_and(mbar_wait(tfull_bar(buf), tph, abortp, p.wait_limit_ns));
       if (!ok) {
         if (issuer) record_timeout(3, t);
         break;
@@ -944,6 +946,11 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   }
   p.dbg = 0;
   if (const char* e = getenv("WSL_DBG")) p.dbg = atoi(e);
+  p.wait_limit_ns = WAIT_LIMIT_NS;
+  if (const char* e = getenv("WSL_WAIT_LIMIT_MS")) {
+    const long ms = atol(e);
+    if (ms > 0 && ms <= 10000) p.wait_limit_ns = static_cast<unsigned long long>(ms) * 1000000ull;
+  }
   if (p.splits == 1 && !(p.dbg & 32)) {
     // staged TMA-store epilogue where the tile width is a whole number of 128-byte chunks
     for (int r = 0; r < g.nregion; ++r) {
