@@ -185,6 +185,30 @@ int wsl_embed_gather(const long long* tokens, const void* E_small, void* G, long
                      long long V, long long r_e, int dtype, void* stream);
 
 /*
+ * h[M,d] = E_small[tokens, :] * P[d,r_e]^T        (bf16)
+ * The factorized embedding in one kernel: the TMA producer of the tcgen05 GEMM fetches the
+ * rows E_small[tokens[m]] with tile::gather4 straight into the swizzled operand tile, so the
+ * gathered matrix is never written to memory. A token id outside [0, V) contributes a zero
+ * row.
+ * Replaces nn.Embedding (torchtitan/experiments/qwen3/model/model.py:350,441); the
+ * factorization itself (E_small, P) is not in the reference.
+ */
+int wsl_embed_fwd(const long long* tokens, const void* E_small, const void* P, void* h,
+                  long long ldh, long long M, long long V, long long r_e, long long d,
+                  void* stream);
+
+/*
+ * dP[d,r_e] += dH[M,d]^T * E_small[tokens, :]     (fp32 in place; operands bf16)
+ * The projection gradient of the factorized embedding, again gathering E_small's rows in
+ * the TMA producer. workspace: optional split-K scratch as in wsl_lora_linear_bwd_dw
+ * (4 * 16 * d * r_e bytes always suffices).
+ */
+int wsl_embed_bwd_dproj(const long long* tokens, const void* dH, long long lddh,
+                        const void* E_small, float* dP, long long M, long long V, long long r_e,
+                        long long d, void* workspace, unsigned long long workspace_bytes,
+                        void* stream);
+
+/*
  * dE[tokens[m], :] += dG[m, :]              (fp32 scatter-add, atomics)
  * dG is bf16 (WSL_BF16) or fp32 (WSL_F32); dE is fp32 [V, r_e].
  * Replaces embedding_dense_backward behind nn.Embedding (same lines).

@@ -364,3 +364,27 @@ def test_split_contraction_for_small_weight_grads(wsl):
     want = (1 + dY.float().T @ x.float(), 1 + U.float().T @ x.float(), 1 + dY.float().T @ T.float())
     for got, unsplit, w in zip(runs[0], (dW0, dA0, dB0), want):
         assert rel(got, w) < 1e-4 and rel(unsplit, w) < 1e-4
+
+
+def test_fused_embedding_gathers_exact_rows(wsl):
+    """The TMA-gather GEMM (wsl_embed_fwd) with P = [I ; 0]: h[:, :r_e] must be E_small[tokens]
+    bit for bit (indices exact), ragged token count, repeated ids, full vocabulary size."""
+    g = torch.Generator().manual_seed(8)
+    V, r_e, d, M = 151936, 256, 512, 1000
+    E = torch.randn(V, r_e, generator=g).cuda().to(torch.bfloat16)
+    tok = torch.randint(0, V, (M,), generator=g).cuda()
+    tok[:6] = torch.tensor([0, V - 1, 7, 7, 7, V - 1], device="cuda")
+    P = torch.zeros(d, r_e, device="cuda", dtype=torch.bfloat16)
+    P[:r_e] = torch.eye(r_e, device="cuda", dtype=torch.bfloat16)
+    h = wsl.embed_fwd(tok, E, P)
+    assert torch.equal(h[:, :r_e], E[tok])
+    assert h[:, r_e:].abs().max().item() == 0.0
+    # same product through the stand-alone gather + GEMM
+    P2 = (torch.randn(d, r_e, generator=g) * 0.05).cuda().to(torch.bfloat16)
+    ref = wsl.linear_fwd(wsl.embed_gather(tok, E), P2)
+    assert rel(wsl.embed_fwd(tok, E, P2), ref) < 1e-6
+    # projection gradient with the gather in the contraction
+    dH = torch.randn(M, d, generator=g).cuda().to(torch.bfloat16)
+    dP = torch.zeros(d, r_e, device="cuda")
+    wsl.embed_bwd_dproj(tok, dH, E, dP)
+    assert rel(dP, dH.float().T @ E[tok].float()) < 1e-4

@@ -80,6 +80,13 @@ struct GemmParams {
   int dbg;            // debug bits: 1 skip epilogue stores, 2 skip TMA loads, 4 skip MMAs,
                       // 64 the producer never fills the ring (exercises the bounded waits)
   unsigned long long wait_limit_ns;   // bound of every mbarrier wait
+  // Row gather (factorized embedding): when set, the rows of region 0 / segment 0's A operand
+  // (gather_a, K-major) or the k-rows of its B operand (gather_b, MN-major) are the rows
+  // tokens[i] of the mapped matrix, fetched by TMA tile::gather4 (1-CTA variant only).
+  const long long* gather_tokens;
+  long long gather_count;
+  int gather_a;
+  int gather_b;
 };
 
 struct TileInfo {
@@ -307,6 +314,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       const int n0 = ti.n0 + b_rows * rank;
       int kb_base = 0;
       for (int sg = 0; ok && sg < p.nseg; ++sg) {
+        const bool gather = p.gather_tokens != nullptr && ti.r == 0 && sg == 0;
         const CUtensorMap* ma = &p.maps[R.a_map[sg]];
         const CUtensorMap* mb = &p.maps[R.b_map[sg]];
         const int klen = p.seg_k[sg];
@@ -348,14 +356,44 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
               if (A_MN) {
                 tma_load_2d(sa, ma, fb, m0, kk);
                 tma_load_2d(sa + SLAB_BYTES, ma, fb, m0 + 64, kk);
-              } else {
+              } else if (!(gather && p.gather_a)) {
                 tma_load_2d(sa, ma, fb, kk, m0);
               }
               if (B_MN) {
-                for (int j = 0; j < b_slabs; ++j)
-                  tma_load_2d(sb + j * SLAB_BYTES, mb, fb, n0 + 64 * j, kk);
+                if (!(gather && p.gather_b))
+                  for (int j = 0; j < b_slabs; ++j)
+                    tma_load_2d(sb + j * SLAB_BYTES, mb, fb, n0 + 64 * j, kk);
               } else {
                 tma_load_2d(sb, mb, fb, kk, n0);
+              }
+            }
+          }
+          if (!PAIR && gather && !(dbg & (2 | 64))) {
+            // Gathered operand: every lane fetches 4 rows (512 B) per tile::gather4; a row
+            // id outside the matrix reads as zeros.
+            const uint32_t fb = full_bar(s);
+            const uint32_t sa = smem_base + s * C::kStageBytes;
+            const uint32_t sb = sa + A_STAGE_BYTES;
+            if (!A_MN && p.gather_a) {
+              int r4[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const long long row = static_cast<long long>(m0) + 4 * lane + e;
+                r4[e] = row < p.gather_count ? static_cast<int>(p.gather_tokens[row]) : -1;
+              }
+              tma_gather4_2d(sa + lane * 512, ma, fb, kk, r4[0], r4[1], r4[2], r4[3]);
+            }
+            if (B_MN && p.gather_b) {
+              for (int q4 = lane; q4 < 16 * b_slabs; q4 += 32) {
+                const int j = q4 >> 4;            // slab
+                const int g4 = q4 & 15;           // group of 4 k-rows inside the slab
+                int r4[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const long long row = static_cast<long long>(kk) + 4 * g4 + e;
+                  r4[e] = row < p.gather_count ? static_cast<int>(p.gather_tokens[row]) : -1;
+                }
+                tma_gather4_2d(sb + j * SLAB_BYTES + g4 * 512, mb, fb, n0 + 64 * j, r4[0], r4[1], r4[2], r4[3]);
               }
             }
           }
@@ -847,7 +885,12 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     if (g.seg_k[s] <= 0) return WSL_ERR_BAD_ARG;
 
   // CTA pairs (256-row tiles) for the large GEMMs; single CTAs for narrow/short ones.
-  const bool pair = use_pair_tiles(g.region[0].mo, g.region[0].no);
+  if (g.gather_tokens != nullptr) {
+    if ((g.gather_a && g.a_mn) || (g.gather_b && !g.b_mn) || (g.gather_a && g.gather_b) ||
+        g.gather_count <= 0)
+      return WSL_ERR_BAD_ARG;
+  }
+  const bool pair = g.gather_tokens == nullptr && use_pair_tiles(g.region[0].mo, g.region[0].no);
   const int bm_tile = pair ? 2 * BM : BM;
   const int bn_round = pair ? 32 : 16;
   int nmaps = 0;
@@ -904,15 +947,24 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       const Mat& a = rd.a[s];
       const Mat& b = rd.b[s];
       // Shape checks: K-major operand is [mo|no, k]; MN-major operand is [k, mo|no].
-      if (g.a_mn ? (a.rows != g.seg_k[s] || a.cols != rd.mo) : (a.rows != rd.mo || a.cols != g.seg_k[s]))
+      // (a gathered operand is the source matrix [V, cols]; its row count is free)
+      const bool ga0 = g.gather_tokens != nullptr && g.gather_a && r == 0 && s == 0;
+      const bool gb0 = g.gather_tokens != nullptr && g.gather_b && r == 0 && s == 0;
+      if (g.a_mn ? (a.rows != g.seg_k[s] || a.cols != rd.mo)
+                 : ((!ga0 && a.rows != rd.mo) || a.cols != g.seg_k[s]))
         return WSL_ERR_BAD_ARG;
-      if (g.b_mn ? (b.rows != g.seg_k[s] || b.cols != rd.no) : (b.rows != rd.no || b.cols != g.seg_k[s]))
+      if (g.b_mn ? ((!gb0 && b.rows != g.seg_k[s]) || b.cols != rd.no)
+                 : (b.rows != rd.no || b.cols != g.seg_k[s]))
         return WSL_ERR_BAD_ARG;
-      st = g.a_mn ? make_map_bf16(&p.maps[nmaps], a, 64, BK) : make_map_bf16(&p.maps[nmaps], a, BK, BM);
+      const bool ga = g.gather_tokens != nullptr && g.gather_a && r == 0 && s == 0;
+      const bool gb = g.gather_tokens != nullptr && g.gather_b && r == 0 && s == 0;
+      if (ga) st = make_map_bf16(&p.maps[nmaps], a, BK, 1);          // gather4: box of one row
+      else st = g.a_mn ? make_map_bf16(&p.maps[nmaps], a, 64, BK) : make_map_bf16(&p.maps[nmaps], a, BK, BM);
       if (st != WSL_OK) return st;
       R.a_map[s] = static_cast<signed char>(nmaps++);
-      st = g.b_mn ? make_map_bf16(&p.maps[nmaps], b, 64, BK)
-                  : make_map_bf16(&p.maps[nmaps], b, BK, static_cast<int>(pair ? bn / 2 : bn));
+      if (gb) st = make_map_bf16(&p.maps[nmaps], b, 64, 1);
+      else st = g.b_mn ? make_map_bf16(&p.maps[nmaps], b, 64, BK)
+                       : make_map_bf16(&p.maps[nmaps], b, BK, static_cast<int>(pair ? bn / 2 : bn));
       if (st != WSL_OK) return st;
       R.b_map[s] = static_cast<signed char>(nmaps++);
     }
@@ -944,6 +996,10 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       }
     }
   }
+  p.gather_tokens = g.gather_tokens;
+  p.gather_count = g.gather_count;
+  p.gather_a = g.gather_a ? 1 : 0;
+  p.gather_b = g.gather_b ? 1 : 0;
   p.dbg = 0;
   if (const char* e = getenv("WSL_DBG")) p.dbg = atoi(e);
   p.wait_limit_ns = WAIT_LIMIT_NS;

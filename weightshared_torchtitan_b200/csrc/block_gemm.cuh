@@ -57,6 +57,14 @@ struct GemmDesc {
   // them into the outputs in a fixed order. nullptr disables splitting.
   float* workspace;
   size_t workspace_bytes;
+  // Row gather for region 0 / segment 0 (factorized embedding). With gather_a the A operand
+  // (K-major) is described by its SOURCE matrix [V, k] and tile row i reads source row
+  // tokens[i]; with gather_b the B operand (MN-major) is the source [V, no] and contraction
+  // row k reads source row tokens[k]. gather_count = number of token ids.
+  const long long* gather_tokens;
+  long long gather_count;
+  bool gather_a;
+  bool gather_b;
 };
 
 // Workspace that lets launch_block_gemm split any contraction of these output sizes up to

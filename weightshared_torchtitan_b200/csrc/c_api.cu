@@ -333,6 +333,60 @@ int wsl_embed_gather(const long long* tokens, const void* E_small, void* G, long
                              static_cast<cudaStream_t>(stream));
 }
 
+int wsl_embed_fwd(const long long* tokens, const void* E_small, const void* P, void* h,
+                  long long ldh, long long M, long long V, long long r_e, long long d,
+                  void* stream) {
+  if (!tokens || !E_small || !P || !h || M <= 0 || V <= 0 || r_e <= 0 || d <= 0)
+    return WSL_ERR_BAD_ARG;
+  GemmDesc g = {};
+  g.nseg = 1;
+  g.seg_k[0] = static_cast<int>(r_e);
+  g.nregion = 1;
+  RegionDesc& r0 = g.region[0];
+  r0.a[0] = mat(E_small, V, r_e, r_e);     // source matrix; rows are picked by token id
+  r0.b[0] = mat(P, d, r_e, r_e);
+  r0.mo = M;
+  r0.no = d;
+  r0.out = h;
+  r0.ld_out = ldh;
+  r0.mode = kEpiStoreBf16;
+  r0.alpha = 1.f;
+  g.gather_tokens = tokens;
+  g.gather_count = M;
+  g.gather_a = true;
+  return launch_block_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+int wsl_embed_bwd_dproj(const long long* tokens, const void* dH, long long lddh,
+                        const void* E_small, float* dP, long long M, long long V, long long r_e,
+                        long long d, void* workspace, unsigned long long workspace_bytes,
+                        void* stream) {
+  if (!tokens || !dH || !E_small || !dP || M <= 0 || V <= 0 || r_e <= 0 || d <= 0)
+    return WSL_ERR_BAD_ARG;
+  if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return WSL_ERR_ALIGN;
+  GemmDesc g = {};
+  g.a_mn = true;
+  g.b_mn = true;
+  g.nseg = 1;
+  g.seg_k[0] = static_cast<int>(M);
+  g.nregion = 1;
+  RegionDesc& r0 = g.region[0];
+  r0.a[0] = mat(dH, M, d, lddh);
+  r0.b[0] = mat(E_small, V, r_e, r_e);     // source matrix; contraction rows picked by token id
+  r0.mo = d;
+  r0.no = r_e;
+  r0.out = dP;
+  r0.ld_out = r_e;
+  r0.mode = kEpiAccumF32;
+  r0.alpha = 1.f;
+  g.gather_tokens = tokens;
+  g.gather_count = M;
+  g.gather_b = true;
+  g.workspace = static_cast<float*>(workspace);
+  g.workspace_bytes = static_cast<size_t>(workspace_bytes);
+  return launch_block_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
 int wsl_embed_scatter_add(const long long* tokens, const void* dG, float* dE, long long M,
                           long long V, long long r_e, int dtype, void* stream) {
   if (bad_dtype(dtype)) return WSL_ERR_BAD_ARG;

@@ -194,9 +194,16 @@ class FactorizedEmbeddingFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, tokens, E, P, sinks, anchor):
-        G = ops.embed_gather(tokens, E)
-        h = ops.linear_fwd(G, P)
-        ctx.save_for_backward(tokens, G, P)
+        fused = E.dtype == torch.bfloat16
+        if fused:
+            # TMA gather inside the tcgen05 GEMM: the gathered rows never touch memory
+            h = ops.embed_fwd(tokens, E, P)
+            ctx.save_for_backward(tokens, E, P)
+        else:
+            G = ops.embed_gather(tokens, E)
+            h = ops.linear_fwd(G, P)
+            ctx.save_for_backward(tokens, G, P)
+        ctx.fused = fused
         ctx.e_shape = E.shape
         ctx.e_dtype = E.dtype
         ctx.sinks = sinks
@@ -204,20 +211,23 @@ class FactorizedEmbeddingFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dH):
-        tokens, G, P = ctx.saved_tensors
+        tokens, GE, P = ctx.saved_tensors       # GE: E_small (fused) or the gathered rows
         d = dH.reshape(-1, dH.shape[-1])
         if d.stride(-1) != 1:
             d = d.contiguous()
         dG = ops.lora_linear_bwd_dx([d], [None], [P], [None])
         if ctx.sinks is not None:
             dE, dP = ctx.sinks
-            ops.lora_linear_bwd_dw(d, None, G, None, dP, None, None)
-            ops.embed_scatter_add(tokens, dG, dE)
-            return None, None, None, None, None
-        dP = torch.zeros(P.shape, device=P.device, dtype=torch.float32)
-        ops.lora_linear_bwd_dw(d, None, G, None, dP, None, None)
-        dE = torch.zeros(ctx.e_shape, device=P.device, dtype=torch.float32)
+        else:
+            dP = torch.zeros(P.shape, device=P.device, dtype=torch.float32)
+            dE = torch.zeros(ctx.e_shape, device=P.device, dtype=torch.float32)
+        if ctx.fused:
+            ops.embed_bwd_dproj(tokens, d, GE, dP)
+        else:
+            ops.lora_linear_bwd_dw(d, None, GE, None, dP, None, None)
         ops.embed_scatter_add(tokens, dG, dE)
+        if ctx.sinks is not None:
+            return None, None, None, None, None
         return None, dE.to(ctx.e_dtype), dP.to(P.dtype), None, None
 
 

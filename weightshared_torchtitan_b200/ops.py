@@ -259,6 +259,44 @@ def embed_gather(tokens: torch.Tensor, E_small: torch.Tensor) -> torch.Tensor:
     return G
 
 
+def embed_fwd(tokens: torch.Tensor, E_small: torch.Tensor, P: torch.Tensor) -> torch.Tensor:
+    """h = E_small[tokens] @ P.T with the row gather inside the GEMM's TMA producer (bf16)."""
+    tok = tokens.reshape(-1)
+    if tok.dtype != torch.int64 or not tok.is_cuda:
+        raise TypeError("tokens must be a CUDA int64 tensor")
+    tok = tok.contiguous()
+    E, P = _mat(E_small, "E_small").contiguous(), _mat(P, "P").contiguous()
+    if E.dtype != torch.bfloat16 or P.dtype != torch.bfloat16:
+        raise TypeError("embed_fwd is the bf16 path; fp32 uses embed_gather + linear_fwd")
+    V, r_e = E.shape
+    d = P.shape[0]
+    M = tok.numel()
+    h = torch.empty((M, d), device=E.device, dtype=E.dtype)
+    _e = _tic()
+    st = _lib.lib().wsl_embed_fwd(tok.data_ptr(), E.data_ptr(), P.data_ptr(), h.data_ptr(), d, M, V, r_e, d,
+                                  _stream())
+    _toc(_e, "embed_fwd", 2.0 * M * r_e * d, 8.0 * M + 2.0 * (M * r_e + r_e * d + M * d))
+    _lib.check(st, "wsl_embed_fwd")
+    return h
+
+
+def embed_bwd_dproj(tokens: torch.Tensor, dH: torch.Tensor, E_small: torch.Tensor, dP: torch.Tensor) -> None:
+    """dP += dH.T @ E_small[tokens] (fp32 in place), gathering inside the GEMM."""
+    tok = tokens.reshape(-1).contiguous()
+    dH = _mat(dH, "dH")
+    E = _mat(E_small, "E_small").contiguous()
+    V, r_e = E.shape
+    M, d = dH.shape
+    if dP.dtype != torch.float32 or not dP.is_contiguous() or tuple(dP.shape) != (d, r_e):
+        raise ValueError("dP must be contiguous float32 [d, r_e]")
+    ws = torch.empty(16 * d * r_e, device=dH.device, dtype=torch.float32)
+    _e = _tic()
+    st = _lib.lib().wsl_embed_bwd_dproj(tok.data_ptr(), dH.data_ptr(), _ld(dH), E.data_ptr(), dP.data_ptr(),
+                                        M, V, r_e, d, ws.data_ptr(), ws.numel() * 4, _stream())
+    _toc(_e, "embed_dproj", 2.0 * M * r_e * d, 8.0 * M + 2.0 * (M * r_e + M * d) + 8.0 * r_e * d)
+    _lib.check(st, "wsl_embed_bwd_dproj")
+
+
 def embed_scatter_add(tokens: torch.Tensor, dG: torch.Tensor, dE: torch.Tensor) -> None:
     """dE[tokens[m]] += dG[m] into a contiguous fp32 [V, r_e] buffer."""
     tok = tokens.reshape(-1).contiguous()
