@@ -40,6 +40,9 @@ if ROOT not in sys.path:
 WORKLOAD = "qwen3-0.6b-ws"
 SEQ_LEN = 4096
 MICRO_BATCH = 8
+# (sequence length, micro-batch per GPU) of the other baseline configurations, for --workload
+WORKLOAD_SHAPES = {"qwen3-0.6b-ws": (4096, 8), "qwen3-1.7b-ws": (4096, 8), "qwen3-4b-ws": (8192, 4),
+                   "qwen3-8b-ws": (8192, 2)}
 METRIC = "step_tokens_per_s"
 UNIT = "tokens/s"
 
@@ -326,7 +329,9 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{WORKLOAD} decoder training step (baseline config 1)", "seq_len": SEQ_LEN,
+            "config": {"workload": f"{WORKLOAD} decoder training step (baseline config "
+                                   f"{list(WORKLOAD_SHAPES).index(WORKLOAD) + 1})",
+                       "seq_len": SEQ_LEN,
                        "micro_batch_per_gpu": MICRO_BATCH, "global_batch": MICRO_BATCH * world,
                        "parallelism": f"dp{world}",
                        "l2": "per-step activations and weights (tens of GB) exceed the 126 MB L2; no flush needed"},
@@ -357,13 +362,18 @@ def run_ours(args):
 
 
 def main():
+    global WORKLOAD, SEQ_LEN, MICRO_BATCH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip op_headline and cpu_baseline (N=1)")
+    ap.add_argument("--workload", default=WORKLOAD, choices=sorted(WORKLOAD_SHAPES),
+                    help="baseline configuration to step (default: configuration 1, the contract workload)")
     args = ap.parse_args()
+    WORKLOAD = args.workload
+    SEQ_LEN, MICRO_BATCH = WORKLOAD_SHAPES[WORKLOAD]
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
