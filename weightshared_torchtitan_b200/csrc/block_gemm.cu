@@ -65,6 +65,8 @@ struct Region {
   int transposed;     // fp32 output element (row, col) of the tile lives at out[col * ld + row]
   int out_map;        // tensor map of the output for the TMA-store epilogue, or -1
   int group;          // rasterisation: M-tiles per group (their A rows stay L2-resident)
+  int splits;         // split-K factor of this region (1 = none)
+  int unit_begin;     // first work unit of this region (units = tiles * splits)
 };
 
 struct GemmParams {
@@ -74,7 +76,7 @@ struct GemmParams {
   int nseg;
   int nregion;
   int total_tiles;
-  int splits;         // split-K factor: work units = total_tiles * splits
+  int total_units;    // work units over all regions (tiles x the region's split factor)
   int kb_total;       // k-blocks summed over the segments
   float* workspace;   // [splits][rows x cols] fp32 partials per region when splits > 1
   int dbg;            // debug bits: 1 skip epilogue stores, 2 skip TMA loads, 4 skip MMAs,
@@ -219,9 +221,9 @@ struct Cfg {
 template <bool PAIR>
 __device__ __forceinline__ TileInfo decode_tile_t(const GemmParams& p, int u) {
   int r = 0;
-  while (r + 1 < p.nregion && u >= p.reg[r + 1].tile_begin * p.splits) ++r;
+  while (r + 1 < p.nregion && u >= p.reg[r + 1].unit_begin) ++r;
   const Region& R = p.reg[r];
-  const int ul = u - R.tile_begin * p.splits;
+  const int ul = u - R.unit_begin;
   const int tiles_r = R.m_tiles * R.n_tiles;
   const int split = ul / tiles_r;
   const int lt = ul - split * tiles_r;
@@ -292,7 +294,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
   if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_base_smem);
-  const int units = p.total_tiles * p.splits;
+  const int units = p.total_units;
   const int dbg = p.dbg;
 
   if (warp == 0) {
@@ -320,7 +322,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
         const int klen = p.seg_k[sg];
         const int nkb = (klen + BK - 1) / BK;
         int lo, hi;
-        split_range(p.kb_total, p.splits, split, kb_base, nkb, lo, hi);
+        split_range(p.kb_total, R.splits, split, kb_base, nkb, lo, hi);
         kb_base += nkb;
         for (int kk = lo * BK; kk < hi * BK; kk += BK) {
           ok = __all_sync(0xffffffffu, (dbg & 16) ? mbar_wait<true>(empty_bar(s), ph ^ 1u, abortp, p.wait_limit_ns)
@@ -440,7 +442,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
           const int klen = p.seg_k[sg];
           const int nkb = (klen + BK - 1) / BK;
           int lo, hi;
-          split_range(p.kb_total, p.splits, split, kb_base, nkb, lo, hi);
+          split_range(p.kb_total, R.splits, split, kb_base, nkb, lo, hi);
           kb_base += nkb;
           for (int kk = lo * BK; kk < hi * BK; kk += BK) {
             ok = __all_sync(0xffffffffu, (dbg & 16) ? mbar_wait<true>(full_bar(s), ph, abortp, p.wait_limit_ns)
@@ -498,7 +500,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       const TileInfo ti = decode_tile_t<PAIR>(p, u);
       const int split = ti.split;
       Region R = p.reg[ti.r];
-      if (p.splits > 1) {
+      if (R.splits > 1) {
         // partial sums go to this split's slice of the workspace; splitk_reduce_kernel folds
         // them into the real output in a fixed order afterwards
         R.out = p.workspace + R.ws_off + static_cast<long long>(split) * R.rows * R.cols;
@@ -621,12 +623,12 @@ struct ReduceRegion {
   int cols4;
   int mode;
   float alpha;
+  int splits;
 };
 struct ReduceParams {
   ReduceRegion reg[kMaxRegion];
   long long total;    // float4 elements over all regions
   int nregion;
-  int splits;
 };
 
 __global__ void __launch_bounds__(256)
@@ -638,7 +640,7 @@ splitk_reduce_kernel(const __grid_constant__ ReduceParams rp) {
     const long long i = gi - R.begin;
     const long long per = static_cast<long long>(R.rows) * R.cols4;
     float4 a = R.ws[i];
-    for (int s = 1; s < rp.splits; ++s) {
+    for (int s = 1; s < R.splits; ++s) {
       const float4 b = R.ws[s * per + i];
       a.x += b.x;
       a.y += b.y;
@@ -761,38 +763,70 @@ double tile_weight(long long no) {
   return bn / BN_MAX < 0.4 ? 0.4 : bn / BN_MAX;
 }
 
-// Split-K factor for a launch. `tiles[i]`, `weight[i]`: number of 128-row-equivalent tiles
-// and per-k-block weight of region i (regions in launch order). The work units (tiles x S,
-// region by region) are dealt round-robin to `num_sms` workers exactly as the kernel does;
-// the S with the smallest simulated makespan wins, charging the workspace round trip
-// (S partial copies written and read once at ~6.5 MB/us) and the reduce launch.
-// One k-block of a full tile ~ 0.27 us.
-int choose_splits(int nregion, const long long* tiles, const double* weight, int kb_total,
-                  long long out_elems, size_t ws_limit_bytes, int num_sms) {
+// Split-K plan of a launch. `tiles[i]`, `weight[i]`, `elems[i]`: tile count (in the kernel's
+// own tiling), per-k-block cost weight and output elements of region i, in launch order.
+// The first region gets S, narrow regions (weight < 1: bound by operand loads, cheap per
+// unit) are split at least into one unit per worker so they spread over the whole GPU. The
+// work units are dealt round-robin to `workers` exactly as the kernel does; the S with the
+// smallest simulated makespan wins, charging the workspace round trip (partials written and
+// read once at ~6.5 MB/us) and the reduce launch. One k-block of a full tile ~ 0.27 us.
+// Returns the workspace bytes the plan needs (0 = no split anywhere).
+size_t plan_splits(int nregion, const long long* tiles, const double* weight, const long long* elems,
+                   int kb_total, size_t ws_limit_bytes, int workers, int* splits_out) {
+  for (int i = 0; i < nregion; ++i) splits_out[i] = 1;
   long long total = 0;
   for (int i = 0; i < nregion; ++i) total += tiles[i];
-  if (total >= 6ll * num_sms) return 1;
+  if (total >= 6ll * workers || nregion > kMaxRegion) return 0;
+  const int s_cap = kb_total / 8 < 16 ? (kb_total / 8 < 1 ? 1 : kb_total / 8) : 16;
   double best = 1e30;
-  int best_s = 1;
+  int best_s[kMaxRegion];
+  size_t best_bytes = 0;
+  for (int i = 0; i < nregion; ++i) best_s[i] = 1;
   double load[256];
-  const int W = num_sms < 256 ? num_sms : 256;
-  for (int S = 1; S <= 16 && S * 8 <= kb_total; ++S) {
-    if (S > 1 && static_cast<size_t>(S) * out_elems * 4 > ws_limit_bytes) break;
+  const int W = workers < 256 ? workers : 256;
+  for (int S = 1; S <= s_cap; ++S) {
+    int sr[kMaxRegion];
+    size_t bytes = 0;
+    bool any = false;
+    for (int i = 0; i < nregion; ++i) {
+      sr[i] = S;
+      if (S > 1 && i > 0 && weight[i] < 1.0) {
+        long long fine = (W + tiles[i] - 1) / tiles[i];
+        if (fine > s_cap) fine = s_cap;
+        if (fine > sr[i]) sr[i] = static_cast<int>(fine);
+      }
+      if (sr[i] > 1) {
+        bytes += static_cast<size_t>(sr[i]) * elems[i] * 4;
+        any = true;
+      }
+    }
+    if (any) {
+      // either every region goes through the workspace or none (one reduce launch)
+      bytes = 0;
+      for (int i = 0; i < nregion; ++i) {
+        if (sr[i] < 2) sr[i] = 2 <= s_cap ? 2 : 1;
+        bytes += static_cast<size_t>(sr[i]) * elems[i] * 4;
+      }
+      if (bytes > ws_limit_bytes) break;
+    }
     for (int w = 0; w < W; ++w) load[w] = 0.0;
-    const double kb = static_cast<double>((kb_total + S - 1) / S);
     long long u = 0;
-    for (int i = 0; i < nregion; ++i)
-      for (long long j = 0; j < tiles[i] * S; ++j, ++u) load[u % W] += kb * weight[i] + 6.0;
+    for (int i = 0; i < nregion; ++i) {
+      const double kb = static_cast<double>((kb_total + sr[i] - 1) / sr[i]);
+      for (long long j = 0; j < tiles[i] * sr[i]; ++j, ++u) load[u % W] += kb * weight[i] + 6.0;
+    }
     double mk = 0.0;
     for (int w = 0; w < W; ++w) mk = load[w] > mk ? load[w] : mk;
     double t = mk * 0.27;
-    if (S > 1) t += 2.0 * S * out_elems * 4 / 6.5e6 + 4.0;
+    if (any) t += 2.0 * static_cast<double>(bytes) / 6.5e6 + 4.0;
     if (t < best) {
       best = t;
-      best_s = S;
+      best_bytes = any ? bytes : 0;
+      for (int i = 0; i < nregion; ++i) best_s[i] = sr[i];
     }
   }
-  return best_s;
+  for (int i = 0; i < nregion; ++i) splits_out[i] = best_s[i];
+  return best_bytes;
 }
 
 // The launch uses CTA pairs (256-row tiles) when its first region is large enough.
@@ -973,28 +1007,35 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   int kb_total = 0;
   for (int sgi = 0; sgi < g.nseg; ++sgi) kb_total += (g.seg_k[sgi] + BK - 1) / BK;
   p.kb_total = kb_total;
-  p.splits = 1;
   p.workspace = nullptr;
+  int plan[kMaxRegion];
+  for (int r = 0; r < kMaxRegion; ++r) plan[r] = 1;
   if (g.workspace != nullptr) {
-    long long out_elems = 0;
-    for (int r = 0; r < g.nregion; ++r) out_elems += g.region[r].mo * g.region[r].no;
-    long long rt[kMaxRegion];
+    long long rt[kMaxRegion], re[kMaxRegion];
     double rw[kMaxRegion];
     for (int r = 0; r < g.nregion; ++r) {
-      rt[r] = region_tiles(pair, g.region[r].mo, g.region[r].no);
+      rt[r] = static_cast<long long>(p.reg[r].m_tiles) * p.reg[r].n_tiles;
       rw[r] = tile_weight(g.region[r].no);
+      re[r] = g.region[r].mo * g.region[r].no;
     }
-    const int S = choose_splits(g.nregion, rt, rw, kb_total, out_elems, g.workspace_bytes,
-                                split_workers(pair, g_num_sms));
-    if (S > 1) {
-      p.splits = S;
+    if (plan_splits(g.nregion, rt, rw, re, kb_total, g.workspace_bytes, split_workers(pair, g_num_sms),
+                    plan) > 0)
       p.workspace = g.workspace;
-      long long off = 0;
-      for (int r = 0; r < g.nregion; ++r) {
-        p.reg[r].ws_off = off;
-        off += static_cast<long long>(S) * g.region[r].mo * g.region[r].no;
-      }
+  }
+  bool any_split = false;
+  {
+    long long off = 0, ub = 0;
+    for (int r = 0; r < g.nregion; ++r) {
+      Region& R = p.reg[r];
+      R.splits = plan[r];
+      R.unit_begin = static_cast<int>(ub);
+      R.ws_off = off;
+      any_split = any_split || plan[r] > 1;
+      off += static_cast<long long>(plan[r]) * g.region[r].mo * g.region[r].no;
+      ub += static_cast<long long>(R.m_tiles) * R.n_tiles * plan[r];
     }
+    if (ub > 0x7fffffffLL) return WSL_ERR_TOO_LARGE;
+    p.total_units = static_cast<int>(ub);
   }
   p.gather_tokens = g.gather_tokens;
   p.gather_count = g.gather_count;
@@ -1007,7 +1048,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     const long ms = atol(e);
     if (ms > 0 && ms <= 10000) p.wait_limit_ns = static_cast<unsigned long long>(ms) * 1000000ull;
   }
-  if (p.splits == 1 && !(p.dbg & 32)) {
+  if (!any_split && !(p.dbg & 32)) {
     // staged TMA-store epilogue where the tile width is a whole number of 128-byte chunks
     for (int r = 0; r < g.nregion; ++r) {
       const RegionDesc& rd = g.region[r];
@@ -1018,7 +1059,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       p.reg[r].out_map = nmaps++;
     }
   }
-  const long long units = tiles * p.splits;
+  const long long units = p.total_units;
 #define WSL_LAUNCH(AM, BM_) (pair ? launch_variant<AM, BM_, true>(p, units, stream) \
                                   : launch_variant<AM, BM_, false>(p, units, stream))
   if (g.a_mn && g.b_mn) st = WSL_LAUNCH(true, true);
@@ -1026,10 +1067,9 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   else if (!g.a_mn && !g.b_mn) st = WSL_LAUNCH(false, false);
   else st = WSL_LAUNCH(true, false);
 #undef WSL_LAUNCH
-  if (st != WSL_OK || p.splits == 1) return st;
+  if (st != WSL_OK || !any_split) return st;
   ReduceParams rp;
   rp.nregion = g.nregion;
-  rp.splits = p.splits;
   long long total = 0;
   for (int r = 0; r < g.nregion; ++r) {
     const RegionDesc& rd = g.region[r];
@@ -1045,6 +1085,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     R.cols4 = static_cast<int>(ocols / 4);
     R.mode = rd.mode;
     R.alpha = rd.alpha;
+    R.splits = p.reg[r].splits;
     total += orows * (ocols / 4);
   }
   rp.total = total;

@@ -309,21 +309,19 @@ int wsl_lora_linear_bwd_dw(const void* dY, long long lddy, const void* U, long l
 unsigned long long wsl_bwd_dw_workspace_bytes(long long M, long long N, long long K, long long r,
                                               int want_dW, int want_dA, int want_dB) {
   if (M <= 0 || N <= 0 || K <= 0 || r < 0) return 0;
-  long long rt[3];
+  long long rt[3], re[3];
   double rw[3];
   int nr = 0;
-  long long out_elems = 0;
   // same region order and tiling rule as the launch itself
   const bool pair = want_dW ? use_pair_tiles(N, K)
                             : (want_dB && r > 0 ? use_pair_tiles(N, r) : use_pair_tiles(K, r));
-  if (want_dW) { rt[nr] = region_tiles(pair, N, K); rw[nr++] = tile_weight(K); out_elems += N * K; }
-  if (want_dB && r > 0) { rt[nr] = region_tiles(pair, N, r); rw[nr++] = tile_weight(r); out_elems += N * r; }
-  if (want_dA && r > 0) { rt[nr] = region_tiles(pair, K, r); rw[nr++] = tile_weight(r); out_elems += r * K; }
-  if (out_elems == 0) return 0;
+  if (want_dW) { rt[nr] = region_tiles(pair, N, K); rw[nr] = tile_weight(K); re[nr++] = N * K; }
+  if (want_dB && r > 0) { rt[nr] = region_tiles(pair, N, r); rw[nr] = tile_weight(r); re[nr++] = N * r; }
+  if (want_dA && r > 0) { rt[nr] = region_tiles(pair, K, r); rw[nr] = tile_weight(r); re[nr++] = r * K; }
+  if (nr == 0) return 0;
   const int sms = device_check() == WSL_OK ? device_sm_count() : 148;
-  const int S = choose_splits(nr, rt, rw, kblocks(M), out_elems, ~static_cast<size_t>(0),
-                              split_workers(pair, sms));
-  return S > 1 ? static_cast<unsigned long long>(S) * out_elems * 4ull : 0ull;
+  int plan[3];
+  return plan_splits(nr, rt, rw, re, kblocks(M), ~static_cast<size_t>(0), split_workers(pair, sms), plan);
 }
 
 int wsl_embed_gather(const long long* tokens, const void* E_small, void* G, long long M,
