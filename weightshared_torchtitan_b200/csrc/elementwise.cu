@@ -298,16 +298,18 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, long long ldx, const float* __restri
 
 // Backward: dx = rstd * (g - x * rstd^2 * mean(g * x)), g = dn * w, dn = un-rotated dy;
 // dw[j] += sum_rows dn[j] * x[j] * rstd (registers -> shared-memory partials -> atomics).
-// Two CTAs per SM (register cap 128): the row loop is latency-bound, so resident warps
-// matter more than registers; the scale w is re-read from L1 per row instead of cached.
+// The row loop is latency-bound, so each lane group loads U rows (dy and x) before it
+// computes any of them (U = 4 for one-vector rows, 2 for hidden-size rows); the scale w is
+// re-read from L1 per row instead of cached in registers.
 template <typename T, bool ROPE, int KV>
-__global__ void __launch_bounds__(RN_WARPS * 32, 2)
+__global__ void __launch_bounds__(RN_WARPS * 32, KV <= 2 ? 2 : 1)
 rmsnorm_bwd_kernel(const T* __restrict__ dy, long long lddy, const T* __restrict__ x, long long ldx,
                    const float* __restrict__ w, const float* __restrict__ rstd_in,
                    T* __restrict__ dx, long long lddx, float* dw, long long rows, int D, int lpr,
                    const float* __restrict__ cs, const float* __restrict__ sn, int heads, int seq,
                    int iters) {
   constexpr int NV = Vec<T>::N;
+  constexpr int U = KV == 1 ? 4 : (KV <= 4 ? 2 : 1);
   extern __shared__ float dw_part[];   // [D]
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -324,66 +326,76 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, long long lddy, const T* __restrict
   const long long row0 = group * iters;
   float cr[NV], sr[NV];
   long long cur_pos = -1;
-  for (int rr = 0; rr < iters; ++rr) {
-    const long long row = row0 + rr;
-    const bool valid = row < rows;
-    const float rstd = valid ? rstd_in[row] : 0.f;
-    if (ROPE) {
-      const long long pos = (valid ? row / heads : 0) % seq;
-      if (pos != cur_pos) {
-        cur_pos = pos;
+  for (int rr = 0; rr < iters; rr += U) {
+    Vec<T> dv[U][KV], xv[U][KV];
+    float rs[U];
 #pragma unroll
-        for (int e = 0; e < NV; ++e) {
-          cr[e] = cs[pos * D + l * NV + e];
-          sr[e] = sn[pos * D + l * NV + e];
+    for (int u = 0; u < U; ++u) {
+      const long long row = row0 + rr + u;
+      const bool valid = rr + u < iters && row < rows;
+      rs[u] = valid ? rstd_in[row] : 0.f;
+#pragma unroll
+      for (int k = 0; k < KV; ++k) {
+        if (valid) {
+          dv[u][k] = ldv<T>(dy + row * lddy + (k * lpr + l) * NV);
+          xv[u][k] = ldv<T>(x + row * ldx + (k * lpr + l) * NV);
+        } else {
+#pragma unroll
+          for (int e = 0; e < NV; ++e) {
+            dv[u][k].set(e, 0.f);
+            xv[u][k].set(e, 0.f);
+          }
         }
       }
     }
-    Vec<T> dv[KV], xv[KV];
 #pragma unroll
-    for (int k = 0; k < KV; ++k) {
-      if (valid) {
-        dv[k] = ldv<T>(dy + row * lddy + (k * lpr + l) * NV);
-        xv[k] = ldv<T>(x + row * ldx + (k * lpr + l) * NV);
-      } else {
+    for (int u = 0; u < U; ++u) {
+      const long long row = row0 + rr + u;
+      const bool valid = rr + u < iters && row < rows;
+      const float rstd = rs[u];
+      if (ROPE) {
+        const long long pos = (valid ? row / heads : 0) % seq;
+        if (pos != cur_pos) {
+          cur_pos = pos;
 #pragma unroll
-        for (int e = 0; e < NV; ++e) {
-          dv[k].set(e, 0.f);
-          xv[k].set(e, 0.f);
+          for (int e = 0; e < NV; ++e) {
+            cr[e] = cs[pos * D + l * NV + e];
+            sr[e] = sn[pos * D + l * NV + e];
+          }
         }
       }
-    }
-    float dn0[NV];   // un-rotated gradient of the (single) vector when ROPE
-    if (ROPE) {
+      float dn0[NV];   // un-rotated gradient of the (single) vector when ROPE
+      if (ROPE) {
 #pragma unroll
-      for (int e = 0; e < NV; ++e) {
-        // dn[j] = dy[j] cos[j] + (j < D/2 ? dy[j+D/2] sin[j+D/2] : -dy[j-D/2] sin[j-D/2])
-        const float d = dv[0].get(e);
-        const float other = __shfl_xor_sync(0xffffffffu, d * sr[e], lpr >> 1);
-        dn0[e] = d * cr[e] + (l < (lpr >> 1) ? other : -other);
+        for (int e = 0; e < NV; ++e) {
+          // dn[j] = dy[j] cos[j] + (j < D/2 ? dy[j+D/2] sin[j+D/2] : -dy[j-D/2] sin[j-D/2])
+          const float d = dv[u][0].get(e);
+          const float other = __shfl_xor_sync(0xffffffffu, d * sr[e], lpr >> 1);
+          dn0[e] = d * cr[e] + (l < (lpr >> 1) ? other : -other);
+        }
       }
-    }
-    float dot = 0.f;
+      float dot = 0.f;
 #pragma unroll
-    for (int k = 0; k < KV; ++k)
+      for (int k = 0; k < KV; ++k)
 #pragma unroll
-      for (int e = 0; e < NV; ++e) {
-        const float xe = xv[k].get(e);
-        const float dne = ROPE ? dn0[e] : dv[k].get(e);
-        dot += dne * __ldg(w + (k * lpr + l) * NV + e) * xe;
-        dwacc[k][e] += dne * xe * rstd;
+        for (int e = 0; e < NV; ++e) {
+          const float xe = xv[u][k].get(e);
+          const float dne = ROPE ? dn0[e] : dv[u][k].get(e);
+          dot += dne * __ldg(w + (k * lpr + l) * NV + e) * xe;
+          dwacc[k][e] += dne * xe * rstd;
+        }
+      dot = group_sum(dot, lpr);
+      const float c = dot * rstd * rstd / D;
+#pragma unroll
+      for (int k = 0; k < KV; ++k) {
+        Vec<T> o;
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+          const float dne = ROPE ? dn0[e] : dv[u][k].get(e);
+          o.set(e, rstd * (dne * __ldg(w + (k * lpr + l) * NV + e) - xv[u][k].get(e) * c));
+        }
+        if (valid) stv<T>(dx + row * lddx + (k * lpr + l) * NV, o);
       }
-    dot = group_sum(dot, lpr);
-    const float c = dot * rstd * rstd / D;
-#pragma unroll
-    for (int k = 0; k < KV; ++k) {
-      Vec<T> o;
-#pragma unroll
-      for (int e = 0; e < NV; ++e) {
-        const float dne = ROPE ? dn0[e] : dv[k].get(e);
-        o.set(e, rstd * (dne * __ldg(w + (k * lpr + l) * NV + e) - xv[k].get(e) * c));
-      }
-      if (valid) stv<T>(dx + row * lddx + (k * lpr + l) * NV, o);
     }
   }
   if (dw != nullptr) {
@@ -534,7 +546,10 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
   // enough rows per warp that the dw atomics stay a small fraction of the work
   const int lpr = rms_lanes(D, is_f32 ? 4 : 8);
   const long long rows_per_pass = static_cast<long long>(RN_WARPS) * (32 / lpr);
-  const long long target_blocks = 8ll * device_sm_count();
+  // wide rows run one CTA per SM (register-heavy): few, long-lived CTAs keep the number of
+  // contended dw atomics small; narrow rows fit several CTAs per SM
+  const long long kv_host = D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8));
+  const long long target_blocks = (kv_host >= 4 ? 2ll : 8ll) * device_sm_count();
   long long rpw = (rows + target_blocks * rows_per_pass - 1) / (target_blocks * rows_per_pass);
   if (rpw < 1) rpw = 1;
   const unsigned gb = static_cast<unsigned>((rows + rows_per_pass * rpw - 1) / (rows_per_pass * rpw));
