@@ -227,6 +227,9 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
+        # NCCL's own log lines (e.g. its version banner) go to stderr: stdout carries only the
+        # one JSON line
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     _lib.lib()
     peaks = load_peaks()
