@@ -79,8 +79,11 @@ struct GemmParams {
   int total_units;    // work units over all regions (tiles x the region's split factor)
   int kb_total;       // k-blocks summed over the segments
   float* workspace;   // [splits][rows x cols] fp32 partials per region when splits > 1
-  int dbg;            // debug bits: 1 skip epilogue stores, 2 skip TMA loads, 4 skip MMAs,
-                      // 64 the producer never fills the ring (exercises the bounded waits)
+  // Diagnostic switches (environment variable WSL_DBG, a bit mask; 0 in normal use):
+  // 1 skip epilogue stores, 2 skip TMA loads, 4 skip MMAs (time the other parts alone),
+  // 32 direct-store epilogue instead of the staged TMA store, 64 the producer never fills
+  // the ring (exercises the bounded waits).
+  int dbg;
   unsigned long long wait_limit_ns;   // bound of every mbarrier wait
   // Row gather (factorized embedding): when set, the rows of region 0 / segment 0's A operand
   // (gather_a, K-major) or the k-rows of its B operand (gather_b, MN-major) are the rows
@@ -325,8 +328,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
         split_range(p.kb_total, R.splits, split, kb_base, nkb, lo, hi);
         kb_base += nkb;
         for (int kk = lo * BK; kk < hi * BK; kk += BK) {
-          ok = __all_sync(0xffffffffu, (dbg & 16) ? mbar_wait<true>(empty_bar(s), ph ^ 1u, abortp, p.wait_limit_ns)
-                                                   : mbar_wait<false>(empty_bar(s), ph ^ 1u, abortp, p.wait_limit_ns));
+          ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1u, abortp, p.wait_limit_ns));
           if (!ok) {
             if (lane == 0) record_timeout(1, t);
             break;
@@ -445,8 +447,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
           split_range(p.kb_total, R.splits, split, kb_base, nkb, lo, hi);
           kb_base += nkb;
           for (int kk = lo * BK; kk < hi * BK; kk += BK) {
-            ok = __all_sync(0xffffffffu, (dbg & 16) ? mbar_wait<true>(full_bar(s), ph, abortp, p.wait_limit_ns)
-                                                     : mbar_wait<false>(full_bar(s), ph, abortp, p.wait_limit_ns));
+            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, abortp, p.wait_limit_ns));
             if (!ok) {
               if (lane == 0) record_timeout(2, t);
               break;

@@ -63,21 +63,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Non-blocking probe of a phase (never suspends the thread).
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
 // Bounded wait. `abort_flag` is a word in shared memory that any role sets when
 // it gives up; every other role then leaves its own waits too.
 // Returns true when the phase completed, false on time-out / abort.
@@ -85,14 +70,11 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 // when the phase is not complete); the clock and the abort flag are looked at only
 // every 256 failed polls, and the limit is measured with the SM cycle counter
 // (reading %globaltimer costs far more than a poll).
-template <bool SPIN = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile int* abort_flag, uint64_t limit_ns) {
   uint32_t spins = 0;
   long long t0 = 0;
-  // SPIN: poll with test_wait (the thread is never suspended, so it reacts to the phase
-  // flip within a few cycles); otherwise try_wait, which parks the thread in hardware.
-  while (!(SPIN ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity))) {
+  while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 255u) == 0u) {
       if (*abort_flag != 0) return false;
       const long long now = clock64();
