@@ -203,3 +203,30 @@ def test_flops_formula():
     assert f["linear"] == per_layer * 36
     # SURVEY table: 19.44 TF per layer at M = 16384
     assert abs(per_layer * 16384 / 1e12 - 19.44) < 0.05
+
+
+def test_row_kernel_entry_points_validate_arguments():
+    """Null pointers and impossible sizes come back as status codes from every entry point
+    added around the projections (no device needed: validation precedes any CUDA call or
+    reports the missing device)."""
+    from weightshared_torchtitan_b200 import _lib
+    lib = _lib.lib()
+    bad = {_lib.WSL_ERR_BAD_ARG, _lib.WSL_ERR_DEVICE}
+    assert lib.wsl_ce_fwd_bwd(None, 8, None, None, 1, 8, 1.0, 0, None) in bad
+    assert lib.wsl_ce_fwd_bwd(None, 8, None, None, 1, 8, 1.0, 9, None) == _lib.WSL_ERR_BAD_ARG
+    assert lib.wsl_swiglu_fwd(None, None, None, 8, 0, None) in bad
+    assert lib.wsl_swiglu_bwd(None, None, None, None, None, 8, 0, None) == _lib.WSL_ERR_BAD_ARG
+    assert lib.wsl_rmsnorm_fwd(None, 8, None, None, 8, None, 1, 8, 1e-6, None, None, 0, 0, 0, None) in bad
+    assert lib.wsl_rmsnorm_bwd(None, 8, None, 8, None, None, None, 8, None, 1, 8, None, None, 0, 0, 3, None) \
+        == _lib.WSL_ERR_BAD_ARG
+    assert lib.wsl_embed_fwd(None, None, None, None, 8, 1, 8, 8, 8, None) == _lib.WSL_ERR_BAD_ARG
+    assert lib.wsl_embed_bwd_dproj(None, None, 8, None, None, 1, 8, 8, 8, None, 0, None) == _lib.WSL_ERR_BAD_ARG
+
+
+def test_rmsnorm_supported_widths():
+    from weightshared_torchtitan_b200 import ops
+    bf, f32 = torch.bfloat16, torch.float32
+    assert all(ops.rmsnorm_supported(d, bf) for d in (16, 64, 128, 256, 512, 1024, 2048))
+    assert not ops.rmsnorm_supported(2560, bf) and not ops.rmsnorm_supported(4096, bf)
+    assert ops.rmsnorm_supported(128, bf, rope=True) and not ops.rmsnorm_supported(512, bf, rope=True)
+    assert ops.rmsnorm_supported(1024, f32) and not ops.rmsnorm_supported(2048, f32)

@@ -388,3 +388,37 @@ def test_fused_embedding_gathers_exact_rows(wsl):
     dP = torch.zeros(d, r_e, device="cuda")
     wsl.embed_bwd_dproj(tok, dH, E, dP)
     assert rel(dP, dH.float().T @ E[tok].float()) < 1e-4
+
+
+def test_random_shapes_against_oracle(wsl):
+    """Seeded random shapes (multiples of 8, ragged against every tile size) for the whole
+    projection fwd+bwd in bf16; covers both the 1-CTA and the CTA-pair variants."""
+    import random
+    rnd = random.Random(20260101)
+    for case in range(10):
+        M = rnd.choice([8, 72, 136, 520, 776, 1288, 2056])
+        N = 8 * rnd.randint(2, 160)
+        K = 8 * rnd.randint(2, 160)
+        r = rnd.choice([8, 16, 24, 32, 64])
+        ins = [t.cuda().to(torch.bfloat16) for t in O.projection_inputs(500 + case, M, N, K, r)]
+        outs = run_projection(wsl, *ins)
+        want = oracle_projection(*ins)
+        for got, w, name in zip(outs, want, ("y", "dX", "dW", "dA", "dB")):
+            assert rel(got, w) < TOL_BF16, (case, (M, N, K, r), name, rel(got, w))
+
+
+def test_dx_mixed_segments(wsl):
+    """dX over projections with and without an adapter (r = 0 for one of them) and different
+    widths: the segment list is built per projection."""
+    g = torch.Generator().manual_seed(77)
+    bf = torch.bfloat16
+    M, K = 640, 512
+    Ns, rs = (768, 256, 1024), (16, 0, 32)
+    dYs = [torch.randn(M, n, generator=g).cuda().to(bf) for n in Ns]
+    Ws = [(torch.randn(n, K, generator=g) * 0.03).cuda().to(bf) for n in Ns]
+    Us = [torch.randn(M, r, generator=g).cuda().to(bf) if r else None for r in rs]
+    As = [(torch.randn(r, K, generator=g) * 0.05).cuda().to(bf) if r else None for r in rs]
+    dX = wsl.lora_linear_bwd_dx(dYs, Us, Ws, As)
+    want = sum(d.float().cpu() @ w.float().cpu() for d, w in zip(dYs, Ws))
+    want = want + sum(u.float().cpu() @ a.float().cpu() for u, a in zip(Us, As) if u is not None)
+    assert rel(dX, want) < TOL_BF16
