@@ -144,6 +144,24 @@ int wsl_lora_linear_bwd_dw(const void* dY, long long lddy, const void* U, long l
                            long long r, void* workspace, unsigned long long workspace_bytes,
                            int dtype, void* stream);
 
+/*
+ * wsl_lora_linear_bwd_dw for nproj <= WSL_MAX_PROJ projections that read the same x (q|k|v,
+ * gate|up) in ONE launch: dW_p += dY_p^T x, dA_p += U_p^T x, dB_p += dY_p^T T_p. All
+ * projections must want all three products when r_p > 0 (dA_p/dB_p NULL only with r_p = 0);
+ * dW_p is required. More tiles per launch fill the GPU better than one launch per
+ * projection. Workspace as above; wsl_bwd_dw_group_workspace_bytes gives its size.
+ * Replaces the same autograd nodes as wsl_lora_linear_bwd_dw, for the q/k/v and gate/up
+ * call sites that share an input (torchtitan/experiments/qwen3/model/model.py:184,251).
+ */
+int wsl_lora_linear_bwd_dw_group(int nproj, const void* const* dY, const long long* lddy,
+                                 const void* const* U, const long long* ldu, const void* x,
+                                 long long ldx, const void* const* T, const long long* ldt,
+                                 float* const* dW, float* const* dA, float* const* dB,
+                                 const long long* N, const long long* r, long long M, long long K,
+                                 void* workspace, unsigned long long workspace_bytes, void* stream);
+unsigned long long wsl_bwd_dw_group_workspace_bytes(int nproj, const long long* N, const long long* r,
+                                                    long long M, long long K);
+
 /* Workspace size (bytes, possibly 0) wsl_lora_linear_bwd_dw wants for these sizes; the
  * want_* flags say which of dW, dA, dB will be non-NULL. No reference counterpart. */
 unsigned long long wsl_bwd_dw_workspace_bytes(long long M, long long N, long long K, long long r,

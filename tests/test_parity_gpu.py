@@ -422,3 +422,25 @@ def test_dx_mixed_segments(wsl):
     want = sum(d.float().cpu() @ w.float().cpu() for d, w in zip(dYs, Ws))
     want = want + sum(u.float().cpu() @ a.float().cpu() for u, a in zip(Us, As) if u is not None)
     assert rel(dX, want) < TOL_BF16
+
+
+def test_grouped_weight_gradients_match_single_launches(wsl):
+    """q|k|v in one dW launch (9 regions) against three single-projection launches."""
+    g = torch.Generator().manual_seed(91)
+    bf = torch.bfloat16
+    M, K, r = 4096, 512, 16
+    Ns = (1024, 256, 256)
+    x = torch.randn(M, K, generator=g).cuda().to(bf)
+    dYs = [torch.randn(M, n, generator=g).cuda().to(bf) for n in Ns]
+    Us = [torch.randn(M, r, generator=g).cuda().to(bf) for _ in Ns]
+    T_cat = torch.randn(M, 3 * r, generator=g).cuda().to(bf)
+    Ts = [T_cat[:, i * r:(i + 1) * r] for i in range(3)]
+    one = [[torch.ones(n, K, device="cuda"), torch.ones(r, K, device="cuda"), torch.ones(n, r, device="cuda")] for n in Ns]
+    grp = [[torch.ones(n, K, device="cuda"), torch.ones(r, K, device="cuda"), torch.ones(n, r, device="cuda")] for n in Ns]
+    for p in range(3):
+        wsl.lora_linear_bwd_dw(dYs[p], Us[p], x, Ts[p], *one[p])
+    wsl.lora_linear_bwd_dw_group(dYs, Us, x, Ts, [t[0] for t in grp], [t[1] for t in grp], [t[2] for t in grp])
+    for p in range(3):
+        want = (1 + dYs[p].float().T @ x.float(), 1 + Us[p].float().T @ x.float(), 1 + dYs[p].float().T @ Ts[p].float())
+        for a, b, w in zip(one[p], grp[p], want):
+            assert rel(b, w) < 1e-4 and rel(a, b) < 1e-5

@@ -8,9 +8,9 @@
 
 namespace wsl {
 
-constexpr int kMaxMaps = 16;    // tensor maps carried in the kernel parameters
+constexpr int kMaxMaps = 32;    // tensor maps carried in the kernel parameters
 constexpr int kMaxSeg = 6;      // contraction segments (K-concatenation)
-constexpr int kMaxRegion = 3;   // output regions sharing one launch
+constexpr int kMaxRegion = 9;   // output regions sharing one launch (3 projections x dW, dB, dA)
 
 enum EpilogueMode : int {
   kEpiStoreBf16 = 0,   // out(bf16)  = alpha * acc

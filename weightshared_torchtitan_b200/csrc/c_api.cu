@@ -21,13 +21,23 @@ static inline Mat mat(const void* p, long long rows, long long cols, long long l
   m.ld = ld;
   return m;
 }
-// The three regions of the weight-gradient launch (token contraction, MN-major operands):
-//   dW[N,K] += dY^T x ;  dB[N,r] += dY^T T ;  dA[r,K] += U^T x, run as its transpose
-//   x^T U -> [K, r] so that the narrow dimension r is the MMA N (cheap) instead of a
-//   mostly-empty 128-row M tile.
-void build_bwd_dw_desc(GemmDesc& g, const void* dY, long long lddy, const void* U, long long ldu,
-                       const void* x, long long ldx, const void* T, long long ldt, float* dW,
-                       float* dA, float* dB, long long M, long long N, long long K, long long r) {
+// The regions of a weight-gradient launch (token contraction, MN-major operands), for P
+// projections that read the same x:
+//   dW_p[N_p,K] += dY_p^T x ;  dB_p[N_p,r_p] += dY_p^T T_p ;  dA_p[r_p,K] += U_p^T x, run as its
+//   transpose x^T U_p -> [K, r_p] so that the narrow dimension r is the MMA N (cheap) instead
+//   of a mostly-empty 128-row M tile.
+// All wide (dW) regions come first, then the narrow ones, so the round-robin deal hands out
+// the expensive units before the cheap ones.
+struct BwdDwProj {
+  const void* dY; long long lddy;
+  const void* U; long long ldu;
+  const void* T; long long ldt;
+  float* dW; float* dA; float* dB;
+  long long N; long long r;
+};
+
+int build_bwd_dw_group(GemmDesc& g, int nproj, const BwdDwProj* pj, const void* x, long long ldx,
+                       long long M, long long K) {
   g.a_mn = true;
   g.b_mn = true;
   g.nseg = 1;
@@ -52,10 +62,24 @@ void build_bwd_dw_desc(GemmDesc& g, const void* dY, long long lddy, const void* 
     rd.alpha = 1.f;
     rd.transposed = transposed;
   };
-  if (dW) add(dY, N, lddy, x, K, ldx, dW, K, false);
-  if (dB) add(dY, N, lddy, T, r, ldt, dB, r, false);
-  if (dA) add(x, K, ldx, U, r, ldu, dA, K, true);
+  int want = 0;
+  for (int p = 0; p < nproj; ++p) want += (pj[p].dW ? 1 : 0) + (pj[p].dB ? 1 : 0) + (pj[p].dA ? 1 : 0);
+  if (want == 0 || want > kMaxRegion) return WSL_ERR_BAD_ARG;
+  for (int p = 0; p < nproj; ++p)
+    if (pj[p].dW) add(pj[p].dY, pj[p].N, pj[p].lddy, x, K, ldx, pj[p].dW, K, false);
+  for (int p = 0; p < nproj; ++p)
+    if (pj[p].dB) add(pj[p].dY, pj[p].N, pj[p].lddy, pj[p].T, pj[p].r, pj[p].ldt, pj[p].dB, pj[p].r, false);
+  for (int p = 0; p < nproj; ++p)
+    if (pj[p].dA) add(x, K, ldx, pj[p].U, pj[p].r, pj[p].ldu, pj[p].dA, K, true);
   g.nregion = nr;
+  return WSL_OK;
+}
+
+void build_bwd_dw_desc(GemmDesc& g, const void* dY, long long lddy, const void* U, long long ldu,
+                       const void* x, long long ldx, const void* T, long long ldt, float* dW,
+                       float* dA, float* dB, long long M, long long N, long long K, long long r) {
+  BwdDwProj pj = {dY, lddy, U, ldu, T, ldt, dW, dA, dB, N, r};
+  build_bwd_dw_group(g, 1, &pj, x, ldx, M, K);
 }
 
 static inline bool bad_dtype(int dtype) { return dtype != WSL_BF16 && dtype != WSL_F32; }
@@ -304,6 +328,50 @@ int wsl_lora_linear_bwd_dw(const void* dY, long long lddy, const void* U, long l
   g.workspace = static_cast<float*>(workspace);
   g.workspace_bytes = static_cast<size_t>(workspace_bytes);
   return launch_block_gemm(g, s);
+}
+
+int wsl_lora_linear_bwd_dw_group(int nproj, const void* const* dY, const long long* lddy,
+                                 const void* const* U, const long long* ldu, const void* x,
+                                 long long ldx, const void* const* T, const long long* ldt,
+                                 float* const* dW, float* const* dA, float* const* dB,
+                                 const long long* N, const long long* r, long long M, long long K,
+                                 void* workspace, unsigned long long workspace_bytes, void* stream) {
+  if (nproj < 1 || nproj > WSL_MAX_PROJ || !dY || !lddy || !x || !N || !r || !dW || !dA || !dB ||
+      M <= 0 || K <= 0)
+    return WSL_ERR_BAD_ARG;
+  BwdDwProj pj[WSL_MAX_PROJ];
+  for (int p = 0; p < nproj; ++p) {
+    if (N[p] <= 0 || r[p] < 0 || !dY[p]) return WSL_ERR_BAD_ARG;
+    if (r[p] == 0 && (dA[p] || dB[p])) return WSL_ERR_BAD_ARG;
+    if (dA[p] && (!U || !ldu || !U[p])) return WSL_ERR_BAD_ARG;
+    if (dB[p] && (!T || !ldt || !T[p])) return WSL_ERR_BAD_ARG;
+    pj[p] = {dY[p], lddy[p], U ? U[p] : nullptr, ldu ? ldu[p] : 0, T ? T[p] : nullptr, ldt ? ldt[p] : 0,
+             dW[p], dA[p], dB[p], N[p], r[p]};
+  }
+  if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return WSL_ERR_ALIGN;
+  GemmDesc g = {};
+  int st = build_bwd_dw_group(g, nproj, pj, x, ldx, M, K);
+  if (st != WSL_OK) return st;
+  g.workspace = static_cast<float*>(workspace);
+  g.workspace_bytes = static_cast<size_t>(workspace_bytes);
+  return launch_block_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+unsigned long long wsl_bwd_dw_group_workspace_bytes(int nproj, const long long* N, const long long* r,
+                                                    long long M, long long K) {
+  if (nproj < 1 || nproj > WSL_MAX_PROJ || !N || !r || M <= 0 || K <= 0) return 0;
+  long long rt[kMaxRegion], re[kMaxRegion];
+  double rw[kMaxRegion];
+  int nr = 0;
+  const bool pair = use_pair_tiles(N[0], K);
+  for (int p = 0; p < nproj; ++p) { rt[nr] = region_tiles(pair, N[p], K); rw[nr] = tile_weight(K); re[nr++] = N[p] * K; }
+  for (int p = 0; p < nproj; ++p)
+    if (r[p] > 0) { rt[nr] = region_tiles(pair, N[p], r[p]); rw[nr] = tile_weight(r[p]); re[nr++] = N[p] * r[p]; }
+  for (int p = 0; p < nproj; ++p)
+    if (r[p] > 0) { rt[nr] = region_tiles(pair, K, r[p]); rw[nr] = tile_weight(r[p]); re[nr++] = r[p] * K; }
+  const int sms = device_check() == WSL_OK ? device_sm_count() : 148;
+  int plan[kMaxRegion];
+  return plan_splits(nr, rt, rw, re, kblocks(M), ~static_cast<size_t>(0), split_workers(pair, sms), plan);
 }
 
 unsigned long long wsl_bwd_dw_workspace_bytes(long long M, long long N, long long K, long long r,

@@ -83,6 +83,17 @@ class LoRALinearGroupFunction(torch.autograd.Function):
             dX = ops.lora_linear_bwd_dx(dY2, Us, Ws, As).view(ctx.x_shape)
         grads: List[Optional[torch.Tensor]] = []
         off = 0
+        if (ctx.sinks is not None and P > 1 and x2.dtype == torch.bfloat16
+                and all(s[0] is not None and s[1] is not None and s[2] is not None for s in ctx.sinks)):
+            # all projections of the group in one weight-gradient launch
+            Ts = []
+            for p in range(P):
+                r = As[p].shape[0]
+                Ts.append(T_cat[:, off:off + r])
+                off += r
+            ops.lora_linear_bwd_dw_group(dY2, Us, x2, Ts, [s[0] for s in ctx.sinks],
+                                         [s[1] for s in ctx.sinks], [s[2] for s in ctx.sinks])
+            return (dX, None, None, None, *([None] * (3 * P)))
         for p in range(P):
             r = As[p].shape[0]
             T = T_cat[:, off:off + r]

@@ -242,6 +242,54 @@ def lora_linear_bwd_dw(dY: torch.Tensor, U: Optional[torch.Tensor], x: torch.Ten
     _lib.check(st, "wsl_lora_linear_bwd_dw")
 
 
+def lora_linear_bwd_dw_group(dYs, Us, x, Ts, dWs, dAs, dBs) -> None:
+    """One launch for the weight gradients of projections that read the same x (bf16):
+    dW_p += dY_p.T @ x, dA_p += U_p.T @ x, dB_p += dY_p.T @ T_p, all fp32 in place."""
+    n = len(dYs)
+    dYs = [_mat(t, "dY") for t in dYs]
+    x = _mat(x, "x")
+    code = _dtype_code(x)
+    if code != WSL_BF16:
+        raise TypeError("the grouped weight-gradient launch is the bf16 path")
+    M, K = x.shape
+    vp, ll = ctypes.c_void_p * n, ctypes.c_longlong * n
+    dy_p, u_p, t_p, dw_p, da_p, db_p = vp(), vp(), vp(), vp(), vp(), vp()
+    lddy, ldu, ldt, Ns, rs = ll(), ll(), ll(), ll(), ll()
+    keep = []
+    flops = 0.0
+    nbytes = 2.0 * M * K
+    for p in range(n):
+        _same(code, dYs[p])
+        N = dYs[p].shape[1]
+        r = 0
+        dy_p[p], lddy[p], Ns[p] = dYs[p].data_ptr(), _ld(dYs[p]), N
+        if Us[p] is not None:
+            U, T = _mat(Us[p], "U"), _mat(Ts[p], "T")
+            keep += [U, T]
+            r = U.shape[1]
+            u_p[p], ldu[p], t_p[p], ldt[p] = U.data_ptr(), _ld(U), T.data_ptr(), _ld(T)
+        else:
+            u_p[p], ldu[p], t_p[p], ldt[p] = None, 0, None, 0
+        rs[p] = r
+        for gbuf, shape, nm in ((dWs[p], (N, K), "dW"), (dAs[p], (r, K), "dA"), (dBs[p], (N, r), "dB")):
+            if gbuf is not None and (gbuf.dtype != torch.float32 or not gbuf.is_contiguous()
+                                     or tuple(gbuf.shape) != shape):
+                raise ValueError(f"{nm} must be a contiguous float32 tensor of shape {shape}")
+        dw_p[p] = dWs[p].data_ptr()
+        da_p[p] = dAs[p].data_ptr() if dAs[p] is not None else None
+        db_p[p] = dBs[p].data_ptr() if dBs[p] is not None else None
+        flops += 2.0 * M * (N * K + r * K + N * r)
+        nbytes += 2.0 * (M * N + 2 * M * r) + 8.0 * (N * K + r * K + N * r)
+    ws_bytes = int(_lib.lib().wsl_bwd_dw_group_workspace_bytes(n, Ns, rs, M, K))
+    ws = torch.empty(ws_bytes // 4, device=x.device, dtype=torch.float32) if ws_bytes else None
+    _e = _tic()
+    st = _lib.lib().wsl_lora_linear_bwd_dw_group(
+        n, dy_p, lddy, u_p, ldu, x.data_ptr(), _ld(x), t_p, ldt, dw_p, da_p, db_p, Ns, rs, M, K,
+        ws.data_ptr() if ws is not None else None, ws_bytes, _stream())
+    _toc(_e, "dw", flops, nbytes)
+    _lib.check(st, "wsl_lora_linear_bwd_dw_group")
+
+
 def embed_gather(tokens: torch.Tensor, E_small: torch.Tensor) -> torch.Tensor:
     """G[m] = E_small[tokens[m]] (bit-exact row copy)."""
     tok = tokens.reshape(-1)
