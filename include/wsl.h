@@ -103,6 +103,17 @@ int wsl_lora_linear_fwd(const void* x, long long ldx, const void* W, const void*
                         long long N, long long K, long long r, int dtype, void* stream);
 
 /*
+ * wsl_lora_linear_fwd for nproj <= WSL_MAX_PROJ projections that read the same x and have the
+ * same rank (q|k|v, gate|up) in ONE launch (bf16): y_p = x W_p^T + T_p B_p^T.
+ * Replaces the same lines as wsl_lora_linear_fwd at the call sites that share an input:
+ * torchtitan/experiments/qwen3/model/model.py:184,251.
+ */
+int wsl_lora_linear_fwd_group(int nproj, const void* x, long long ldx, const void* const* W,
+                              const void* const* T, const long long* ldt, const void* const* B,
+                              void* const* y, const long long* ldy, const long long* N,
+                              const long long* r, long long M, long long K, void* stream);
+
+/*
  * U[M,r] = s * dY[M,N] * B[N,r]
  * Backward pre-pass (the autograd MmBackward of w_b together with the
  * MulBackward of the scale): torchtitan/models/llama3/model/model.py:191.

@@ -444,3 +444,23 @@ def test_grouped_weight_gradients_match_single_launches(wsl):
         want = (1 + dYs[p].float().T @ x.float(), 1 + Us[p].float().T @ x.float(), 1 + dYs[p].float().T @ Ts[p].float())
         for a, b, w in zip(one[p], grp[p], want):
             assert rel(b, w) < 1e-4 and rel(a, b) < 1e-5
+
+
+def test_grouped_forward_matches_single_launches(wsl):
+    """q|k|v forward in one launch (3 regions x 2 segments) is bit-identical to three
+    single-projection launches."""
+    g = torch.Generator().manual_seed(92)
+    bf = torch.bfloat16
+    M, K, r = 1000, 512, 16
+    Ns = (1024, 256, 264)
+    x = torch.randn(M, K, generator=g).cuda().to(bf)
+    Ws = [(torch.randn(n, K, generator=g) * 0.03).cuda().to(bf) for n in Ns]
+    Bs = [(torch.randn(n, r, generator=g) * 0.1).cuda().to(bf) for n in Ns]
+    A_cat = (torch.randn(3 * r, K, generator=g) * 0.05).cuda().to(bf)
+    T_cat = wsl.lora_prepass(x, A_cat, 2.0)
+    Ts = [T_cat[:, i * r:(i + 1) * r] for i in range(3)]
+    ys = wsl.lora_linear_fwd_group(x, Ws, Ts, Bs)
+    for p in range(3):
+        assert torch.equal(ys[p], wsl.lora_linear_fwd(x, Ws[p], Ts[p], Bs[p]))
+        ref = x.float() @ Ws[p].float().T + Ts[p].float() @ Bs[p].float().T
+        assert rel(ys[p], ref) < TOL_BF16

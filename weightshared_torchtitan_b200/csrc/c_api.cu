@@ -217,6 +217,41 @@ int wsl_lora_linear_fwd(const void* x, long long ldx, const void* W, const void*
   return launch_block_gemm(g, s);
 }
 
+int wsl_lora_linear_fwd_group(int nproj, const void* x, long long ldx, const void* const* W,
+                              const void* const* T, const long long* ldt, const void* const* B,
+                              void* const* y, const long long* ldy, const long long* N,
+                              const long long* r, long long M, long long K, void* stream) {
+  if (nproj < 1 || nproj > WSL_MAX_PROJ || !x || !W || !y || !ldy || !N || !r || M <= 0 || K <= 0)
+    return WSL_ERR_BAD_ARG;
+  // one contraction layout for all regions: [x | T_p], so the ranks must agree
+  const long long r0v = r[0];
+  for (int p = 0; p < nproj; ++p) {
+    if (!W[p] || !y[p] || N[p] <= 0 || r[p] != r0v || r[p] < 0) return WSL_ERR_BAD_ARG;
+    if (r0v > 0 && (!T || !ldt || !B || !T[p] || !B[p])) return WSL_ERR_BAD_ARG;
+  }
+  GemmDesc g = {};
+  g.nseg = r0v > 0 ? 2 : 1;
+  g.seg_k[0] = static_cast<int>(K);
+  g.seg_k[1] = static_cast<int>(r0v);
+  g.nregion = nproj;
+  for (int p = 0; p < nproj; ++p) {
+    RegionDesc& rd = g.region[p];
+    rd.a[0] = mat(x, M, K, ldx);
+    rd.b[0] = mat(W[p], N[p], K, K);
+    if (r0v > 0) {
+      rd.a[1] = mat(T[p], M, r0v, ldt[p]);
+      rd.b[1] = mat(B[p], N[p], r0v, r0v);
+    }
+    rd.mo = M;
+    rd.no = N[p];
+    rd.out = y[p];
+    rd.ld_out = ldy[p];
+    rd.mode = kEpiStoreBf16;
+    rd.alpha = 1.f;
+  }
+  return launch_block_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
 int wsl_lora_bwd_prepass(const void* dY, long long lddy, const void* B, void* U, long long ldu,
                          long long M, long long N, long long r, float sc, int dtype,
                          void* stream) {

@@ -52,10 +52,13 @@ class LoRALinearGroupFunction(torch.autograd.Function):
         off = 0
         for p in range(P):
             r = As[p].shape[0]
-            T = T_cat[:, off:off + r]
+            Ts.append(T_cat[:, off:off + r])
             off += r
-            Ts.append(T)
-            ys.append(ops.lora_linear_fwd(x2, Ws[p], T, Bs[p]).view(*x.shape[:-1], Ws[p].shape[0]))
+        if P > 1 and x2.dtype == torch.bfloat16 and len({A.shape[0] for A in As}) == 1:
+            ys = [y.view(*x.shape[:-1], y.shape[1]) for y in ops.lora_linear_fwd_group(x2, Ws, Ts, Bs)]
+        else:
+            for p in range(P):
+                ys.append(ops.lora_linear_fwd(x2, Ws[p], Ts[p], Bs[p]).view(*x.shape[:-1], Ws[p].shape[0]))
         ctx.save_for_backward(x2, T_cat, *wab)
         ctx.s = float(s)
         ctx.sinks = sinks

@@ -142,6 +142,42 @@ def lora_linear_fwd(x: torch.Tensor, W: torch.Tensor, T: Optional[torch.Tensor],
     return y
 
 
+def lora_linear_fwd_group(x: torch.Tensor, Ws, Ts, Bs):
+    """y_p = x @ W_p.T + T_p @ B_p.T for projections sharing x and rank, in one launch (bf16)."""
+    x = _mat(x, "x")
+    code = _dtype_code(x)
+    if code != WSL_BF16:
+        raise TypeError("the grouped forward launch is the bf16 path")
+    n = len(Ws)
+    M, K = x.shape
+    Ws = [_mat(w, "W").contiguous() for w in Ws]
+    Bs = [_mat(b, "B").contiguous() for b in Bs]
+    Ts = [_mat(t, "T") for t in Ts]
+    vp, ll = ctypes.c_void_p * n, ctypes.c_longlong * n
+    w_p, t_p, b_p, y_p = vp(), vp(), vp(), vp()
+    ldt, ldy, Ns, rs = ll(), ll(), ll(), ll()
+    ys = []
+    flops = 0.0
+    nbytes = 2.0 * M * K
+    for p in range(n):
+        _same(code, Ws[p], Bs[p], Ts[p])
+        N, r = Ws[p].shape[0], Bs[p].shape[1]
+        if Ws[p].shape[1] != K or Ts[p].shape != (M, r) or Bs[p].shape[0] != N:
+            raise ValueError("W_p must be [N_p, K], T_p [M, r], B_p [N_p, r]")
+        y = torch.empty((M, N), device=x.device, dtype=x.dtype)
+        ys.append(y)
+        w_p[p], t_p[p], b_p[p], y_p[p] = Ws[p].data_ptr(), Ts[p].data_ptr(), Bs[p].data_ptr(), y.data_ptr()
+        ldt[p], ldy[p], Ns[p], rs[p] = _ld(Ts[p]), N, N, r
+        flops += 2.0 * M * N * (K + r)
+        nbytes += 2.0 * (N * K + M * r + N * r + M * N)
+    _e = _tic()
+    st = _lib.lib().wsl_lora_linear_fwd_group(n, x.data_ptr(), _ld(x), w_p, t_p, ldt, b_p, y_p, ldy, Ns, rs,
+                                              M, K, _stream())
+    _toc(_e, "fwd", flops, nbytes)
+    _lib.check(st, "wsl_lora_linear_fwd_group")
+    return ys
+
+
 def lora_bwd_prepass(dY: torch.Tensor, B: torch.Tensor, s: float) -> torch.Tensor:
     """U = s * dY @ B (wsl_lora_bwd_prepass)."""
     dY, B = _mat(dY, "dY"), _mat(B, "B").contiguous()
