@@ -276,7 +276,7 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, long long ldx, const float* __restri
 #pragma unroll
       for (int e = 0; e < NV; ++e) ss += xv[k].get(e) * xv[k].get(e);
     ss = group_sum(ss, lpr);
-    const float rstd = rsqrtf(ss / D + eps);
+    const float rstd = 1.0f / sqrtf(ss / D + eps);
     if (valid && l == 0 && rstd_out) rstd_out[row] = rstd;
 #pragma unroll
     for (int k = 0; k < KV; ++k)

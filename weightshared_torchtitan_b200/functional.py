@@ -72,6 +72,11 @@ class LoRALinearGroupFunction(torch.autograd.Function):
         P = ctx.P
         Ws, As, Bs = list(wab[0::3]), list(wab[1::3]), list(wab[2::3])
         dY2, Us = [], []
+        # the U of all projections side by side, so that dX contracts [U_0 | U_1 | ...] with
+        # the stacked A matrices in ONE rank-sum segment instead of one tiny segment each
+        r_tot = sum(A.shape[0] for A in As)
+        U_cat = torch.empty(x2.shape[0], r_tot, device=x2.device, dtype=x2.dtype)
+        off = 0
         for p in range(P):
             d = dYs[p]
             if d is None:
@@ -80,10 +85,17 @@ class LoRALinearGroupFunction(torch.autograd.Function):
             if d.stride(-1) != 1:
                 d = d.contiguous()
             dY2.append(d)
-            Us.append(ops.lora_bwd_prepass(d, Bs[p], ctx.s))
+            r = As[p].shape[0]
+            Us.append(ops.lora_bwd_prepass(d, Bs[p], ctx.s, out=U_cat[:, off:off + r]))
+            off += r
         dX = None
         if ctx.needs_input_grad[0]:
-            dX = ops.lora_linear_bwd_dx(dY2, Us, Ws, As).view(ctx.x_shape)
+            if P == 1:
+                dX = ops.lora_linear_bwd_dx(dY2, Us, Ws, As)
+            else:
+                A_cat = torch.cat(As, dim=0)
+                dX = ops.lora_linear_bwd_dx(dY2, [U_cat] + [None] * (P - 1), Ws, [A_cat] + [None] * (P - 1))
+            dX = dX.view(ctx.x_shape)
         grads: List[Optional[torch.Tensor]] = []
         off = 0
         if (ctx.sinks is not None and P > 1 and x2.dtype == torch.bfloat16

@@ -178,8 +178,10 @@ def lora_linear_fwd_group(x: torch.Tensor, Ws, Ts, Bs):
     return ys
 
 
-def lora_bwd_prepass(dY: torch.Tensor, B: torch.Tensor, s: float) -> torch.Tensor:
-    """U = s * dY @ B (wsl_lora_bwd_prepass)."""
+def lora_bwd_prepass(dY: torch.Tensor, B: torch.Tensor, s: float,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """U = s * dY @ B (wsl_lora_bwd_prepass). `out` may be a column slice [M, r] of a wider
+    buffer (the U of several projections side by side)."""
     dY, B = _mat(dY, "dY"), _mat(B, "B").contiguous()
     code = _dtype_code(dY)
     _same(code, B)
@@ -187,9 +189,14 @@ def lora_bwd_prepass(dY: torch.Tensor, B: torch.Tensor, s: float) -> torch.Tenso
     r = B.shape[1]
     if B.shape[0] != N:
         raise ValueError("B must be [N, r]")
-    U = torch.empty((M, r), device=dY.device, dtype=dY.dtype)
+    if out is None:
+        U = torch.empty((M, r), device=dY.device, dtype=dY.dtype)
+    else:
+        U = out
+        if tuple(U.shape) != (M, r) or U.dtype != dY.dtype or U.stride(1) != 1:
+            raise ValueError("out must be an [M, r] view with contiguous rows")
     _e = _tic()
-    st = _lib.lib().wsl_lora_bwd_prepass(dY.data_ptr(), _ld(dY), B.data_ptr(), U.data_ptr(), r,
+    st = _lib.lib().wsl_lora_bwd_prepass(dY.data_ptr(), _ld(dY), B.data_ptr(), U.data_ptr(), _ld(U),
                                          M, N, r, float(s), code, _stream())
     _toc(_e, "prepass_U", 2.0 * M * N * r, dY.element_size() * (M * N + N * r + M * r))
     _lib.check(st, "wsl_lora_bwd_prepass")
