@@ -123,3 +123,53 @@ def test_head_norm_with_rotary(dtype, tol, D, heads):
     y.backward(dy.cuda())
     assert rel(y, yr) < tol and rel(xc.grad, xr.grad) < tol
     assert rel(wc.grad, wr.grad) < tol
+
+
+@pytest.mark.parametrize("D,rows,heads", [(128, 100_003, 0), (128, 80_000, 16), (1024, 9_477, 0),
+                                          (2048, 5_000, 0), (256, 40_001, 0)])
+def test_rmsnorm_backward_over_many_tiles(D, rows, heads):
+    """Row counts at which every CTA of the staged backward walks its ring of shared-memory
+    stages several times (so the barrier phases flip) and the last tile is ragged."""
+    from weightshared_torchtitan_b200.decoder import rope_tables
+    from weightshared_torchtitan_b200.functional import rmsnorm
+    g = torch.Generator().manual_seed(rows)
+    x = torch.randn(rows, D, generator=g).to(torch.bfloat16)
+    w = 1.0 + 0.2 * torch.randn(D, generator=g)
+    dy = torch.randn(rows, D, generator=g).to(torch.bfloat16)
+    xr, wr = leaf(x, "cuda", dtype=torch.float32), leaf(w, "cuda")
+    n = F.rms_norm(xr, (D,), wr, 1e-6)
+    rope = None
+    if heads:
+        s = rows // heads // 2
+        cache = O.rope_cache(D, s, 1_000_000.0).cuda()
+        n, _ = O.apply_rope(n.view(2, s, heads, D), n.view(2, s, heads, D), cache)
+        n = n.reshape(rows, D)
+        cos, sin = rope_tables(D, s, 1_000_000.0, "cuda")
+        rope = (cos.contiguous(), sin.contiguous(), heads, s)
+    n.backward(dy.cuda().float())
+    xc, wc = leaf(x, "cuda"), leaf(w, "cuda")
+    y = rmsnorm(xc, wc, 1e-6, rope)
+    y.backward(dy.cuda())
+    assert rel(y, n) < 1e-2 and rel(xc.grad, xr.grad) < 1e-2
+    assert rel(wc.grad, wr.grad) < 1e-2
+
+
+def test_rmsnorm_strided_rows_take_the_direct_kernel():
+    """Rows with a pitch larger than their width cannot be bulk-copied as dense tiles; the
+    entry points accept them and must give the same result as dense rows."""
+    from weightshared_torchtitan_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    rows, D = 777, 1024
+    xw = torch.randn(rows, D + 64, generator=g).to(torch.bfloat16).cuda()
+    dyw = torch.randn(rows, D + 64, generator=g).to(torch.bfloat16).cuda()
+    w = (1.0 + 0.2 * torch.randn(D, generator=g)).cuda()
+    x_s, dy_s = xw[:, :D], dyw[:, :D]
+    y_s, rstd_s = ops.rmsnorm_fwd(x_s, w, 1e-6)
+    y_d, rstd_d = ops.rmsnorm_fwd(x_s.contiguous(), w, 1e-6)
+    assert rel(y_s, y_d) < 1e-2 and rel(rstd_s, rstd_d) < 1e-6
+    dw_s, dw_d = torch.zeros(D, device="cuda"), torch.zeros(D, device="cuda")
+    dx_s = ops.rmsnorm_bwd(dy_s, x_s, w, rstd_s, dw_s)
+    dx_d = ops.rmsnorm_bwd(dy_s.contiguous(), x_s.contiguous(), w, rstd_d, dw_d)
+    # two kernels, two summation orders: equal up to the bf16 rounding of y and dx
+    assert rel(dx_s, dx_d) < 1e-2
+    assert rel(dw_s, dw_d) < 1e-4

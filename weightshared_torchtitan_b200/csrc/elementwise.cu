@@ -408,7 +408,21 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, long long lddy, const T* __restrict
   }
 }
 
+}  // namespace wsl
+#include "rownorm_staged.cuh"
+namespace wsl {
+
 // ------------------------------------------------------------------ host launchers
+// Diagnostic switch: WSL_ROW_STAGED=0 sends every row-kernel call to the direct (register
+// pipelined) kernels, for A/B timing of the staged ones.
+static bool row_staged_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("WSL_ROW_STAGED");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <typename T>
@@ -512,6 +526,44 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const float* w, void* y, lo
   const unsigned gb = static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block);
   const int d = static_cast<int>(D), h = static_cast<int>(heads), sq = static_cast<int>(seq);
   const int kvn = static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
+  if (row_staged_enabled() && ldx == D && (!cs || (heads % 4 == 0 && aligned16(cs) && aligned16(sn)))) {
+    // rotary rows: two half-row vectors per lane (the staged kernels' layout), else as above
+    const int kvn = cs ? 2 : static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
+    const int lpr = cs ? static_cast<int>(D / (2 * (is_f32 ? 4 : 8))) : rms_lanes(D, is_f32 ? 4 : 8);
+    const long long tile_rows = static_cast<long long>(RN_WARPS) * (32 / lpr) * (8 / kvn);
+    const long long n_tiles = (rows + tile_rows - 1) / tile_rows;
+    const unsigned sgb = static_cast<unsigned>(n_tiles < device_sm_count() ? n_tiles : device_sm_count());
+    const size_t ssmem = rn_fwd_staged_smem(d);
+#define WSL_RNFS(T, R, KVN)                                                                        \
+  do {                                                                                             \
+    static bool attr_set = false;                                                                  \
+    if (!attr_set) {                                                                               \
+      if (cudaFuncSetAttribute(rmsnorm_fwd_staged_kernel<T, R, KVN>,                               \
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,                        \
+                               static_cast<int>(rn_fwd_staged_smem(2048))) != cudaSuccess)         \
+        return WSL_ERR_CUDA;                                                                       \
+      attr_set = true;                                                                             \
+    }                                                                                              \
+    rmsnorm_fwd_staged_kernel<T, R, KVN><<<sgb, (RN_WARPS + 1) * 32, ssmem, s>>>(                  \
+        static_cast<const T*>(x), w, static_cast<T*>(y), ldy, rstd, rows, d, lpr, eps, cs, sn, h,  \
+        sq, n_tiles);                                                                              \
+  } while (0)
+#define WSL_RNFS_KV(T)                                            \
+  do {                                                            \
+    if (cs) WSL_RNFS(T, true, 2);                                 \
+    else if (kvn == 1) WSL_RNFS(T, false, 1);                     \
+    else if (kvn == 2) WSL_RNFS(T, false, 2);                     \
+    else if (kvn == 4) WSL_RNFS(T, false, 4);                     \
+    else if (kvn == 8) WSL_RNFS(T, false, 8);                     \
+    else return WSL_ERR_TOO_LARGE;                                \
+  } while (0)
+    if (is_f32) WSL_RNFS_KV(float); else WSL_RNFS_KV(__nv_bfloat16);
+#undef WSL_RNFS_KV
+#undef WSL_RNFS
+    if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
+    ++g_launch_count;
+    return WSL_OK;
+  }
 #define WSL_RN(T, R, KVN)                                                                          \
   rmsnorm_fwd_kernel<T, R, KVN><<<gb, RN_WARPS * 32, 0, s>>>(                                      \
       static_cast<const T*>(x), ldx, w, static_cast<T*>(y), ldy, rstd, rows, d, lpr, eps, cs, sn, \
@@ -556,6 +608,48 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
   const int d = static_cast<int>(D), h = static_cast<int>(heads), sq = static_cast<int>(seq);
   const size_t smem = static_cast<size_t>(D) * sizeof(float);
   const int kvn = static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
+  // contiguous rows take the staged kernel (bulk copies need 16-byte aligned, dense tiles)
+  if (row_staged_enabled() && lddy == D && ldx == D &&
+      (!cs || (heads % 4 == 0 && aligned16(cs) && aligned16(sn)))) {
+    // rotary rows: two half-row vectors per lane (the staged kernels' layout), else as above
+    const int kvn = cs ? 2 : static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
+    const int lpr = cs ? static_cast<int>(D / (2 * (is_f32 ? 4 : 8))) : rms_lanes(D, is_f32 ? 4 : 8);
+    const int rpg = 8 / kvn;
+    const int cw = rn_compute_warps(kvn * (is_f32 ? 4 : 8), cs != nullptr);
+    const long long tile_rows = static_cast<long long>(cw) * (32 / lpr) * rpg;
+    const long long n_tiles = (rows + tile_rows - 1) / tile_rows;
+    const unsigned sgb = static_cast<unsigned>(n_tiles < device_sm_count() ? n_tiles : device_sm_count());
+    const size_t ssmem = rn_staged_smem(d);
+#define WSL_RNS(T, R, KVN)                                                                         \
+  do {                                                                                             \
+    static bool attr_set = false;                                                                  \
+    if (!attr_set) {                                                                               \
+      if (cudaFuncSetAttribute(rmsnorm_bwd_staged_kernel<T, R, KVN>,                               \
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,                        \
+                               static_cast<int>(rn_staged_smem(2048))) != cudaSuccess)             \
+        return WSL_ERR_CUDA;                                                                       \
+      attr_set = true;                                                                             \
+    }                                                                                              \
+    rmsnorm_bwd_staged_kernel<T, R, KVN><<<sgb, (cw + 1) * 32, ssmem, s>>>(                           \
+        static_cast<const T*>(dy), static_cast<const T*>(x), w, rstd, static_cast<T*>(dx), lddx,   \
+        dw, rows, d, lpr, cs, sn, h, sq, n_tiles);                                                 \
+  } while (0)
+#define WSL_RNS_KV(T)                                             \
+  do {                                                            \
+    if (cs) WSL_RNS(T, true, 2);                                  \
+    else if (kvn == 1) WSL_RNS(T, false, 1);                      \
+    else if (kvn == 2) WSL_RNS(T, false, 2);                      \
+    else if (kvn == 4) WSL_RNS(T, false, 4);                      \
+    else if (kvn == 8) WSL_RNS(T, false, 8);                      \
+    else return WSL_ERR_TOO_LARGE;                                \
+  } while (0)
+    if (is_f32) WSL_RNS_KV(float); else WSL_RNS_KV(__nv_bfloat16);
+#undef WSL_RNS_KV
+#undef WSL_RNS
+    if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
+    ++g_launch_count;
+    return WSL_OK;
+  }
 #define WSL_RNB(T, R, KVN)                                                                         \
   rmsnorm_bwd_kernel<T, R, KVN><<<gb, RN_WARPS * 32, smem, s>>>(                                   \
       static_cast<const T*>(dy), lddy, static_cast<const T*>(x), ldx, w, rstd, static_cast<T*>(dx), \

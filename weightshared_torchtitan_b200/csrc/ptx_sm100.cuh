@@ -104,6 +104,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
       : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
 }
+// Untiled bulk copy global -> shared of `bytes` contiguous bytes, completion on an mbarrier.
+// Both addresses must be 16-byte aligned and `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes,
+                                             uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      :
+      : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
 // Row gather: four rows (r0..r3) x one box of columns starting at c0.
 __device__ __forceinline__ void tma_gather4_2d(uint32_t dst_smem, const CUtensorMap* m,
                                                uint32_t bar, int c0, int r0, int r1, int r2,
