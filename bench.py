@@ -20,7 +20,7 @@ configuration-4 MLP shapes (M = 16384), the figure the baseline's target is quot
 host cores for a bounded sample.
 
 `--impl reference` times that CPU eager path alone (the reference has no other
-implementation of this path that runs without a GPU-side rewrite; see DESIGN.md).
+implementation of this path that runs without a GPU-side rewrite).
 """
 from __future__ import annotations
 

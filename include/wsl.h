@@ -173,6 +173,45 @@ int wsl_lora_linear_bwd_dw_group(int nproj, const void* const* dY, const long lo
 unsigned long long wsl_bwd_dw_group_workspace_bytes(int nproj, const long long* N, const long long* r,
                                                     long long M, long long K);
 
+/*
+ * Backward through the layer's own weight gradient (bf16 mode), for callers that need dW
+ * anyway (the shared base weight is trained). With G_l = dY^T x of THIS layer,
+ *     dB = s * G_l * A^T      and      dA = s * B^T * G_l
+ * are the same rank-r products as dY^T T and U^T x, but read the [N,K] matrix G_l instead of
+ * streaming the M-row activations again, and dX = dY * (W + s B A) needs no pre-pass over dY.
+ * Three entry points:
+ *
+ * wsl_lora_merge_weight:  Weff_p[N_p,K] = bf16( W_p[N_p,K] + s * B_p[N_p,r] * A_p[r,K] ) for
+ *   nproj projections with the same K and rank (r = 8, 16, 32 or 64) in one launch: one
+ *   streaming pass over W, r FMAs per element; dense row-major matrices. Give Weff_p to
+ *   wsl_lora_linear_bwd_dx as W_p with U_p = A_p = NULL.
+ * wsl_bwd_dw_layer_group: dW_p[N_p,K] += dY_p^T x (fp32, in place, shared across layers) and
+ *   dWl_p[N_p,K] = bf16(dY_p^T x) (this launch's addend alone, dense) for nproj projections
+ *   that read the same x, one launch. Workspace: wsl_bwd_dw_group_workspace_bytes with r = 0.
+ * wsl_lora_adapter_grads_from_dw: dA_p[r_p,K] += s * B_p^T dWl_p, dB_p[N_p,r_p] += s * dWl_p
+ *   A_p^T (fp32, in place; A_p, B_p, dWl_p dense bf16), two launches for the whole group. The
+ *   optional workspace (wsl_adapter_grads_workspace_bytes) lets the short contractions be split
+ *   over the GPU, folded in a fixed order.
+ *
+ * The bf16 rounding of G_l and of Weff is of the same order as the bf16 rounding of U and T
+ * in the direct formulation. Replaces the same autograd nodes as wsl_lora_linear_bwd_dx/_dw:
+ * torchtitan/models/llama3/model/model.py:191,392-398.
+ */
+int wsl_lora_merge_weight(int nproj, const void* const* W, const void* const* A, const void* const* B,
+                          void* const* Weff, const long long* N, long long K, long long r, float s,
+                          void* stream);
+int wsl_bwd_dw_layer_group(int nproj, const void* const* dY, const long long* lddy, const void* x,
+                           long long ldx, float* const* dW, void* const* dWl, const long long* N,
+                           long long M, long long K, void* workspace,
+                           unsigned long long workspace_bytes, void* stream);
+int wsl_lora_adapter_grads_from_dw(int nproj, const void* const* dWl, const void* const* A,
+                                   const void* const* B, float* const* dA, float* const* dB,
+                                   const long long* N, const long long* r, long long K, float s,
+                                   void* workspace, unsigned long long workspace_bytes,
+                                   void* stream);
+unsigned long long wsl_adapter_grads_workspace_bytes(int nproj, const long long* N, const long long* r,
+                                                     long long K);
+
 /* Workspace size (bytes, possibly 0) wsl_lora_linear_bwd_dw wants for these sizes; the
  * want_* flags say which of dW, dA, dB will be non-NULL. No reference counterpart. */
 unsigned long long wsl_bwd_dw_workspace_bytes(long long M, long long N, long long K, long long r,

@@ -72,7 +72,7 @@ def lora_linear(x: torch.Tensor, W: torch.Tensor, A: torch.Tensor, B: torch.Tens
 
 
 def lora_linear_fwd_bwd(x, W, A, B, dY):
-    """Forward and all gradients by autograd (the graph of SURVEY call stack 3.3):
+    """Forward and all gradients by autograd (base F.linear plus LoRAModule.forward, added):
     returns y, dX, dW, dA, dB."""
     x = x.detach().clone().requires_grad_(True)
     W = W.detach().clone().requires_grad_(True)

@@ -32,7 +32,7 @@ import torch.nn as nn
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("WSL_REFERENCE_CHECKOUT", "reference")
 sys.path.insert(0, REF)
 sys.path.insert(1, ROOT)
 

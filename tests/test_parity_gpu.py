@@ -464,3 +464,114 @@ def test_grouped_forward_matches_single_launches(wsl):
         assert torch.equal(ys[p], wsl.lora_linear_fwd(x, Ws[p], Ts[p], Bs[p]))
         ref = x.float() @ Ws[p].float().T + Ts[p].float() @ Bs[p].float().T
         assert rel(ys[p], ref) < TOL_BF16
+
+
+# ------------------------------------------- backward through the layer's own weight gradient
+def test_merge_weight(wsl):
+    """W_eff = bf16(W + s B A) against the same sum in fp32 (one rounding either way: at most
+    one bf16 ulp apart)."""
+    g = torch.Generator().manual_seed(101)
+    bf = torch.bfloat16
+    for N, K, r in [(1024, 1024, 16), (264, 520, 8), (3072, 1024, 64)]:
+        W = (torch.randn(N, K, generator=g) * 0.03).cuda().to(bf)
+        A = (torch.randn(r, K, generator=g) * 0.05).cuda().to(bf)
+        B = (torch.randn(N, r, generator=g) * 0.1).cuda().to(bf)
+        got = wsl.lora_merge_weight([W], [A], [B], 2.0)[0]
+        want = W.float() + 2.0 * (B.float() @ A.float())
+        assert got.dtype == bf and got.shape == W.shape
+        # 1e-6: elements where W and s B A nearly cancel see the fp32 summation order
+        assert bool(((got.float() - want).abs() <= want.abs() * 2.0 ** -7 + 1e-6).all())
+    # q|k|v in one launch, different widths and ranks
+    Ns, rs, K = (1024, 256, 262), (8, 8, 8), 512
+    Ws = [(torch.randn(n, K, generator=g) * 0.03).cuda().to(bf) for n in Ns]
+    As = [(torch.randn(r, K, generator=g) * 0.05).cuda().to(bf) for r in rs]
+    Bs = [(torch.randn(n, r, generator=g) * 0.1).cuda().to(bf) for n, r in zip(Ns, rs)]
+    outs = wsl.lora_merge_weight(Ws, As, Bs, 2.0)
+    for p in range(3):
+        assert torch.equal(outs[p], wsl.lora_merge_weight([Ws[p]], [As[p]], [Bs[p]], 2.0)[0])
+        want = Ws[p].float() + 2.0 * (Bs[p].float() @ As[p].float())
+        assert rel(outs[p], want) < 4e-3
+
+
+@pytest.mark.parametrize("M,K,Ns", [(8192, 512, (1024, 256, 256)),      # split contraction
+                                    (1024, 2048, (2048, 2048)),         # whole tiles, staged epilogue
+                                    (1000, 520, (264,))])               # ragged edges
+def test_layer_weight_gradient_with_copy(wsl, M, K, Ns):
+    """dW += dY^T x in place and, from the same launch, the bf16 matrix dY^T x of this call
+    alone."""
+    g = torch.Generator().manual_seed(M + K)
+    bf = torch.bfloat16
+    x = torch.randn(M, K, generator=g).cuda().to(bf)
+    dYs = [torch.randn(M, n, generator=g).cuda().to(bf) for n in Ns]
+    dWs = [torch.full((n, K), 3.0, device="cuda") for n in Ns]
+    dWls = wsl.bwd_dw_layer_group(dYs, x, dWs)
+    for p, n in enumerate(Ns):
+        want = dYs[p].float().T @ x.float()
+        assert rel(dWs[p] - 3.0, want) < 1e-4
+        assert dWls[p].dtype == bf and dWls[p].shape == (n, K)
+        assert rel(dWls[p], want) < TOL_BF16
+        # the copy is the fp32 addend rounded once
+        assert rel(dWls[p].float(), (dWs[p] - 3.0).to(bf).float()) < 1e-2
+
+
+@pytest.mark.parametrize("Ns", [(1024, 256, 256), (512, 512), (264,)])
+def test_adapter_gradients_from_layer_gradient(wsl, Ns):
+    """dA = s B^T G and dB = s G A^T with G = dY^T x against the oracle's autograd."""
+    g = torch.Generator().manual_seed(sum(Ns))
+    bf = torch.bfloat16
+    M, K, r, s = 2048, 520, 16, 2.0
+    x = (torch.randn(M, K, generator=g)).to(bf)
+    dWs, dAs, dBs, want = [], [], [], []
+    dYs, As, Bs = [], [], []
+    for n in Ns:
+        W = (torch.randn(n, K, generator=g) * 0.03).to(bf)
+        A = (torch.randn(r, K, generator=g) * 0.05).to(bf)
+        B = (torch.randn(n, r, generator=g) * 0.1).to(bf)
+        dY = (torch.randn(M, n, generator=g) * 0.1).to(bf)
+        want.append(oracle_projection(x, W, A, B, dY))
+        dYs.append(dY.cuda()); As.append(A.cuda()); Bs.append(B.cuda())
+        dWs.append(torch.zeros(n, K, device="cuda"))
+        dAs.append(torch.full((r, K), 1.0, device="cuda"))
+        dBs.append(torch.full((n, r), 1.0, device="cuda"))
+    dWls = wsl.bwd_dw_layer_group(dYs, x.cuda(), dWs)
+    wsl.lora_adapter_grads_from_dw(dWls, As, Bs, dAs, dBs, s)
+    for p in range(len(Ns)):
+        _, _, dW_o, dA_o, dB_o = want[p]
+        assert rel(dWs[p], dW_o) < TOL_BF16
+        assert rel(dAs[p] - 1.0, dA_o) < TOL_BF16
+        assert rel(dBs[p] - 1.0, dB_o) < TOL_BF16
+
+
+@pytest.mark.parametrize("P", [1, 3])
+def test_autograd_function_both_backward_formulations(wsl, P):
+    """LoRALinearGroupFunction with in-place sinks: the backward through the layer's weight
+    gradient and the direct one (U = s dY B) both match the oracle."""
+    from weightshared_torchtitan_b200 import functional as Fn
+    g = torch.Generator().manual_seed(7 + P)
+    bf = torch.bfloat16
+    M, K, r, s = 1536, 512, 16, 2.0
+    Ns = (1024, 256, 256)[:P]
+    x = torch.randn(M, K, generator=g).to(bf)
+    Ws = [(torch.randn(n, K, generator=g) * 0.03).to(bf) for n in Ns]
+    As = [(torch.randn(r, K, generator=g) * 0.05).to(bf) for n in Ns]
+    Bs = [(torch.randn(n, r, generator=g) * 0.1).to(bf) for n in Ns]
+    dYs = [(torch.randn(M, n, generator=g) * 0.1).to(bf) for n in Ns]
+    want = [oracle_projection(x, Ws[p], As[p], Bs[p], dYs[p]) for p in range(P)]
+    dX_want = sum(w[1] for w in want)
+    saved = Fn.DERIVED_ADAPTER_GRADS
+    try:
+        for derived in (True, False):
+            Fn.DERIVED_ADAPTER_GRADS = derived
+            xc = x.cuda().requires_grad_(True)
+            sinks = [(torch.zeros(n, K, device="cuda"), torch.zeros(r, K, device="cuda"),
+                      torch.zeros(n, r, device="cuda")) for n in Ns]
+            ys = Fn.lora_linear_group(xc, [w.cuda() for w in Ws], [a.cuda() for a in As],
+                                      [b.cuda() for b in Bs], s, sinks)
+            torch.autograd.backward(list(ys), [d.cuda() for d in dYs])
+            assert rel(xc.grad, dX_want) < TOL_BF16
+            for p in range(P):
+                assert rel(ys[p], want[p][0]) < TOL_BF16
+                for got, ref in zip(sinks[p], want[p][2:]):
+                    assert rel(got, ref) < TOL_BF16
+    finally:
+        Fn.DERIVED_ADAPTER_GRADS = saved

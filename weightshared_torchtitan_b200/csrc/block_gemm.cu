@@ -67,6 +67,8 @@ struct Region {
   int group;          // rasterisation: M-tiles per group (their A rows stay L2-resident)
   int splits;         // split-K factor of this region (1 = none)
   int unit_begin;     // first work unit of this region (units = tiles * splits)
+  void* copy;         // bf16 copy of alpha * acc (RegionDesc::copy), or nullptr
+  long long ld_copy;
 };
 
 struct GemmParams {
@@ -509,8 +511,14 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
         R.mode = kEpiStoreF32;
         R.alpha = 1.f;
         R.out_map = -1;
+        R.copy = nullptr;   // the reduce kernel writes the copy from the folded sum
       }
       if (dbg & 1) R.rows = 0;   // debug: read TMEM, store nothing
+      Region RC = R;             // the bf16 copy of the tile, written with direct stores
+      RC.out = R.copy;
+      RC.ld = R.ld_copy;
+      RC.mode = kEpiStoreBf16;
+      RC.transposed = 0;
       const int buf = it & 1;
       const uint32_t tph = (static_cast<uint32_t>(it) >> 1) & 1u;
       const bool ok = epi_vote_and(mbar_wait(tfull_bar(buf), tph, abortp, p.wait_limit_ns));
@@ -541,6 +549,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
             uint32_t v[32];
             tmem_ld_32x32(taddr + c, v);
             tmem_ld_wait();
+            if (RC.out != nullptr) epilogue_store<32>(RC, row, ti.n0 + c, v);
 #pragma unroll
             for (int j = 0; j < 8; ++j)
               st_shared_v4(srow + ((static_cast<uint32_t>(j) ^ swz) << 4),
@@ -578,11 +587,13 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
             tmem_ld_32x32(taddr + c, v);
             tmem_ld_wait();
             epilogue_store<32>(R, row, ti.n0 + c, v);
+            if (RC.out != nullptr) epilogue_store<32>(RC, row, ti.n0 + c, v);
           } else {
             uint32_t v[16];
             tmem_ld_32x16(taddr + c, v);
             tmem_ld_wait();
             epilogue_store<16>(R, row, ti.n0 + c, v);
+            if (RC.out != nullptr) epilogue_store<16>(RC, row, ti.n0 + c, v);
           }
         }
       }
@@ -625,6 +636,8 @@ struct ReduceRegion {
   int mode;
   float alpha;
   int splits;
+  __nv_bfloat16* copy;   // RegionDesc::copy, or nullptr
+  long long ld_copy;
 };
 struct ReduceParams {
   ReduceRegion reg[kMaxRegion];
@@ -654,6 +667,14 @@ splitk_reduce_kernel(const __grid_constant__ ReduceParams rp) {
     a.w *= R.alpha;
     const long long row = i / R.cols4;
     const int c = static_cast<int>(i - row * R.cols4) * 4;
+    if (R.copy != nullptr) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(a.z, a.w);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(R.copy + row * R.ld_copy + c) = pk;
+    }
     if (R.mode == kEpiStoreBf16) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y);
       __nv_bfloat162 hi = __floats2bfloat162_rn(a.z, a.w);
@@ -962,6 +983,14 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     R.ws_off = 0;
     R.transposed = rd.transposed ? 1 : 0;
     R.out_map = -1;
+    if (rd.copy != nullptr) {
+      if (rd.transposed || rd.mode == kEpiStoreBf16) return WSL_ERR_BAD_ARG;
+      if ((rd.no % 8) != 0 || (rd.ld_copy % 8) != 0 || rd.ld_copy < rd.no ||
+          (reinterpret_cast<uintptr_t>(rd.copy) & 15u) != 0)
+        return WSL_ERR_ALIGN;
+    }
+    R.copy = rd.copy;
+    R.ld_copy = rd.ld_copy;
     {
       // A rows of one group (all contraction segments) should sit in about a third of the
       // 126 MB L2 while the B tiles stream past them; at least one wave of workers wide.
@@ -985,12 +1014,13 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       // (a gathered operand is the source matrix [V, cols]; its row count is free)
       const bool ga0 = g.gather_tokens != nullptr && g.gather_a && r == 0 && s == 0;
       const bool gb0 = g.gather_tokens != nullptr && g.gather_b && r == 0 && s == 0;
-      if (g.a_mn ? (a.rows != g.seg_k[s] || a.cols != rd.mo)
-                 : ((!ga0 && a.rows != rd.mo) || a.cols != g.seg_k[s]))
-        return WSL_ERR_BAD_ARG;
-      if (g.b_mn ? ((!gb0 && b.rows != g.seg_k[s]) || b.cols != rd.no)
-                 : (b.rows != rd.no || b.cols != g.seg_k[s]))
-        return WSL_ERR_BAD_ARG;
+      const long long ak = g.a_mn ? a.rows : a.cols, bk = g.b_mn ? b.rows : b.cols;
+      const bool a_k_ok = g.a_mn ? (ga0 ? true : ak == g.seg_k[s]) : ak == g.seg_k[s];
+      const bool b_k_ok = g.b_mn ? (gb0 ? true : bk == g.seg_k[s]) : bk == g.seg_k[s];
+      const bool ragged_ok = g.ragged_k && ak == bk && ak > 0 && ak <= g.seg_k[s];
+      if (!((a_k_ok && b_k_ok) || ragged_ok)) return WSL_ERR_BAD_ARG;
+      if (g.a_mn ? a.cols != rd.mo : (!ga0 && a.rows != rd.mo)) return WSL_ERR_BAD_ARG;
+      if (g.b_mn ? b.cols != rd.no : b.rows != rd.no) return WSL_ERR_BAD_ARG;
       const bool ga = g.gather_tokens != nullptr && g.gather_a && r == 0 && s == 0;
       const bool gb = g.gather_tokens != nullptr && g.gather_b && r == 0 && s == 0;
       if (ga) st = make_map_bf16(&p.maps[nmaps], a, BK, 1);          // gather4: box of one row
@@ -1087,6 +1117,8 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     R.mode = rd.mode;
     R.alpha = rd.alpha;
     R.splits = p.reg[r].splits;
+    R.copy = static_cast<__nv_bfloat16*>(rd.copy);
+    R.ld_copy = rd.ld_copy;
     total += orows * (ocols / 4);
   }
   rp.total = total;

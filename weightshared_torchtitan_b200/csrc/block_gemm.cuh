@@ -43,6 +43,12 @@ struct RegionDesc {
   // natural output is short and wide (dA = U^T x, [r, K]) run as its tall-and-narrow
   // transpose (x^T U, [K, r]) with a narrow, cheap MMA N.
   bool transposed;
+  // Optional second output of an fp32, non-transposed region: copy[mo, no] (bf16, pitch
+  // ld_copy) = alpha * product of THIS launch, whatever `mode` does to `out`. Gives a caller
+  // that accumulates in place (dW += dY^T x) the addend itself, rounded to bf16, as the
+  // operand of a follow-up GEMM. nullptr = none.
+  void* copy;
+  long long ld_copy;
 };
 
 struct GemmDesc {
@@ -65,6 +71,10 @@ struct GemmDesc {
   long long gather_count;
   bool gather_a;
   bool gather_b;
+  // Operands may have fewer rows/columns along the contraction than seg_k says; what is
+  // missing counts as zeros (the TMA out-of-bounds fill). Lets regions with different
+  // contraction lengths share one launch (seg_k = the longest).
+  bool ragged_k;
 };
 
 // Workspace that lets launch_block_gemm split any contraction of these output sizes up to

@@ -6,6 +6,7 @@
 #include "embed.cu"
 #include "static_scratch.cu"
 #include "elementwise.cu"
+#include "lora_merge.cu"
 
 namespace wsl {
 int launch_simt_gemm_f32(const float* A, long long sai, long long sak, const float* B,
@@ -34,6 +35,7 @@ struct BwdDwProj {
   const void* T; long long ldt;
   float* dW; float* dA; float* dB;
   long long N; long long r;
+  void* dWl;   // optional bf16 copy [N, K] of this call's dY^T x (see RegionDesc::copy)
 };
 
 int build_bwd_dw_group(GemmDesc& g, int nproj, const BwdDwProj* pj, const void* x, long long ldx,
@@ -44,8 +46,10 @@ int build_bwd_dw_group(GemmDesc& g, int nproj, const BwdDwProj* pj, const void* 
   g.seg_k[0] = static_cast<int>(M);
   int nr = 0;
   auto add = [&](const void* a, long long a_cols, long long lda, const void* b, long long b_cols,
-                 long long ldb, float* out, long long ld_out, bool transposed) {
+                 long long ldb, float* out, long long ld_out, bool transposed, void* copy = nullptr) {
     RegionDesc& rd = g.region[nr++];
+    rd.copy = copy;
+    rd.ld_copy = copy ? ld_out : 0;
     rd.a[0].ptr = a;
     rd.a[0].rows = M;
     rd.a[0].cols = a_cols;
@@ -66,7 +70,7 @@ int build_bwd_dw_group(GemmDesc& g, int nproj, const BwdDwProj* pj, const void* 
   for (int p = 0; p < nproj; ++p) want += (pj[p].dW ? 1 : 0) + (pj[p].dB ? 1 : 0) + (pj[p].dA ? 1 : 0);
   if (want == 0 || want > kMaxRegion) return WSL_ERR_BAD_ARG;
   for (int p = 0; p < nproj; ++p)
-    if (pj[p].dW) add(pj[p].dY, pj[p].N, pj[p].lddy, x, K, ldx, pj[p].dW, K, false);
+    if (pj[p].dW) add(pj[p].dY, pj[p].N, pj[p].lddy, x, K, ldx, pj[p].dW, K, false, pj[p].dWl);
   for (int p = 0; p < nproj; ++p)
     if (pj[p].dB) add(pj[p].dY, pj[p].N, pj[p].lddy, pj[p].T, pj[p].r, pj[p].ldt, pj[p].dB, pj[p].r, false);
   for (int p = 0; p < nproj; ++p)
@@ -78,7 +82,7 @@ int build_bwd_dw_group(GemmDesc& g, int nproj, const BwdDwProj* pj, const void* 
 void build_bwd_dw_desc(GemmDesc& g, const void* dY, long long lddy, const void* U, long long ldu,
                        const void* x, long long ldx, const void* T, long long ldt, float* dW,
                        float* dA, float* dB, long long M, long long N, long long K, long long r) {
-  BwdDwProj pj = {dY, lddy, U, ldu, T, ldt, dW, dA, dB, N, r};
+  BwdDwProj pj = {dY, lddy, U, ldu, T, ldt, dW, dA, dB, N, r, nullptr};
   build_bwd_dw_group(g, 1, &pj, x, ldx, M, K);
 }
 
@@ -381,7 +385,7 @@ int wsl_lora_linear_bwd_dw_group(int nproj, const void* const* dY, const long lo
     if (dA[p] && (!U || !ldu || !U[p])) return WSL_ERR_BAD_ARG;
     if (dB[p] && (!T || !ldt || !T[p])) return WSL_ERR_BAD_ARG;
     pj[p] = {dY[p], lddy[p], U ? U[p] : nullptr, ldu ? ldu[p] : 0, T ? T[p] : nullptr, ldt ? ldt[p] : 0,
-             dW[p], dA[p], dB[p], N[p], r[p]};
+             dW[p], dA[p], dB[p], N[p], r[p], nullptr};
   }
   if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return WSL_ERR_ALIGN;
   GemmDesc g = {};
@@ -390,6 +394,106 @@ int wsl_lora_linear_bwd_dw_group(int nproj, const void* const* dY, const long lo
   g.workspace = static_cast<float*>(workspace);
   g.workspace_bytes = static_cast<size_t>(workspace_bytes);
   return launch_block_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+int wsl_bwd_dw_layer_group(int nproj, const void* const* dY, const long long* lddy, const void* x,
+                           long long ldx, float* const* dW, void* const* dWl, const long long* N,
+                           long long M, long long K, void* workspace,
+                           unsigned long long workspace_bytes, void* stream) {
+  if (nproj < 1 || nproj > WSL_MAX_PROJ || !dY || !lddy || !x || !N || !dW || !dWl || M <= 0 || K <= 0)
+    return WSL_ERR_BAD_ARG;
+  BwdDwProj pj[WSL_MAX_PROJ];
+  for (int p = 0; p < nproj; ++p) {
+    if (N[p] <= 0 || !dY[p] || !dW[p] || !dWl[p]) return WSL_ERR_BAD_ARG;
+    pj[p] = {dY[p], lddy[p], nullptr, 0, nullptr, 0, dW[p], nullptr, nullptr, N[p], 0, dWl[p]};
+  }
+  if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return WSL_ERR_ALIGN;
+  GemmDesc g = {};
+  int st = build_bwd_dw_group(g, nproj, pj, x, ldx, M, K);
+  if (st != WSL_OK) return st;
+  g.workspace = static_cast<float*>(workspace);
+  g.workspace_bytes = static_cast<size_t>(workspace_bytes);
+  return launch_block_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+int wsl_lora_adapter_grads_from_dw(int nproj, const void* const* dWl, const void* const* A,
+                                   const void* const* B, float* const* dA, float* const* dB,
+                                   const long long* N, const long long* r, long long K, float s,
+                                   void* workspace, unsigned long long workspace_bytes,
+                                   void* stream) {
+  if (nproj < 1 || nproj > WSL_MAX_PROJ || !dWl || !A || !B || !dA || !dB || !N || !r || K <= 0)
+    return WSL_ERR_BAD_ARG;
+  long long n_max = 0;
+  for (int p = 0; p < nproj; ++p) {
+    if (!dWl[p] || !A[p] || !B[p] || !dA[p] || !dB[p] || N[p] <= 0 || r[p] <= 0) return WSL_ERR_BAD_ARG;
+    n_max = N[p] > n_max ? N[p] : n_max;
+  }
+  if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return WSL_ERR_ALIGN;
+  // dB_p[N, r] += s * dWl_p[N, K] * A_p[r, K]^T: both operands K-major, one region per projection
+  GemmDesc gb = {};
+  gb.a_mn = false;
+  gb.b_mn = false;
+  gb.nseg = 1;
+  gb.seg_k[0] = static_cast<int>(K);
+  gb.nregion = nproj;
+  gb.workspace = static_cast<float*>(workspace);
+  gb.workspace_bytes = static_cast<size_t>(workspace_bytes);
+  for (int p = 0; p < nproj; ++p) {
+    RegionDesc& rd = gb.region[p];
+    rd.a[0] = mat(dWl[p], N[p], K, K);
+    rd.b[0] = mat(A[p], r[p], K, K);
+    rd.mo = N[p];
+    rd.no = r[p];
+    rd.out = dB[p];
+    rd.ld_out = r[p];
+    rd.mode = kEpiAccumF32;
+    rd.alpha = s;
+  }
+  int st = launch_block_gemm(gb, static_cast<cudaStream_t>(stream));
+  if (st != WSL_OK) return st;
+  // dA_p[r, K] += s * B_p[N, r]^T * dWl_p[N, K], run as its transpose (dWl_p^T B_p, [K, r]) with
+  // the contraction over N: both operands MN-major, results written transposed. Projections of
+  // different widths share the launch: the contraction runs to the largest N and the shorter
+  // operands read as zeros beyond their end.
+  GemmDesc ga = {};
+  ga.a_mn = true;
+  ga.b_mn = true;
+  ga.nseg = 1;
+  ga.seg_k[0] = static_cast<int>(n_max);
+  ga.ragged_k = true;
+  ga.nregion = nproj;
+  ga.workspace = static_cast<float*>(workspace);
+  ga.workspace_bytes = static_cast<size_t>(workspace_bytes);
+  for (int p = 0; p < nproj; ++p) {
+    RegionDesc& rd = ga.region[p];
+    rd.a[0] = mat(dWl[p], N[p], K, K);
+    rd.b[0] = mat(B[p], N[p], r[p], r[p]);
+    rd.mo = K;
+    rd.no = r[p];
+    rd.out = dA[p];
+    rd.ld_out = K;
+    rd.mode = kEpiAccumF32;
+    rd.alpha = s;
+    rd.transposed = true;
+  }
+  return launch_block_gemm(ga, static_cast<cudaStream_t>(stream));
+}
+
+unsigned long long wsl_adapter_grads_workspace_bytes(int nproj, const long long* N, const long long* r,
+                                                     long long K) {
+  if (nproj < 1 || nproj > WSL_MAX_PROJ || !N || !r || K <= 0) return 0;
+  long long eb = 0, ea = 0;
+  for (int p = 0; p < nproj; ++p) {
+    eb += N[p] * r[p];
+    ea += r[p] * K;
+  }
+  return splitk_workspace_bytes(eb > ea ? eb : ea);
+}
+
+int wsl_lora_merge_weight(int nproj, const void* const* W, const void* const* A, const void* const* B,
+                          void* const* Weff, const long long* N, long long K, long long r, float s,
+                          void* stream) {
+  return launch_lora_merge(nproj, W, A, B, Weff, N, K, r, s, static_cast<cudaStream_t>(stream));
 }
 
 unsigned long long wsl_bwd_dw_group_workspace_bytes(int nproj, const long long* N, const long long* r,

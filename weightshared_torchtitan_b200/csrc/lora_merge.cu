@@ -1,0 +1,141 @@
+// W_eff = W + s * B * A rounded once to bf16: a layer's effective weight, [N, K], from the
+// shared W[N, K] and the adapter factors B[N, r], A[r, K]. Used by the backward pass, where
+// dX = dY * W_eff replaces a rank-r detour through dY * B. The product has contraction length
+// r only, so the kernel is a streaming pass over W (read) and W_eff (write) with r FMAs per
+// element on the CUDA cores; A and B are a few hundred KB and stay in L1/L2. Up to
+// WSL_MAX_PROJ projections of one input width go in one launch.
+#include "block_gemm.cuh"
+#include "status.cuh"
+#include "../../include/wsl.h"
+#include <cuda_bf16.h>
+#include <cstdint>
+
+namespace wsl {
+
+constexpr int MERGE_ROWS = 4;   // rows of W per thread (the unpacked A values are shared by them)
+
+struct MergeProj {
+  const __nv_bfloat16* W;
+  const __nv_bfloat16* A;
+  const __nv_bfloat16* B;
+  __nv_bfloat16* out;
+  long long N;
+  long long begin;   // first work item of this projection (item = MERGE_ROWS rows x 8 columns)
+};
+struct MergeParams {
+  MergeProj proj[WSL_MAX_PROJ];
+  int nproj;
+  int K8;            // K / 8
+  long long total;   // work items over all projections
+  float s;
+};
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const uint32_t* u = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    f[2 * e] = __uint_as_float(u[e] << 16);
+    f[2 * e + 1] = __uint_as_float(u[e] & 0xffff0000u);
+  }
+}
+
+// R = rank (multiple of 8). Work item i of a projection: rows [4 * (i / K8), +4), columns
+// [8 * (i % K8), +8); consecutive threads take consecutive column groups of the same rows.
+template <int R>
+__global__ void __launch_bounds__(256)
+lora_merge_kernel(const __grid_constant__ MergeParams mp) {
+  for (long long gi = blockIdx.x * 256ll + threadIdx.x; gi < mp.total; gi += gridDim.x * 256ll) {
+    int p = 0;
+    while (p + 1 < mp.nproj && gi >= mp.proj[p + 1].begin) ++p;
+    const MergeProj& P = mp.proj[p];
+    const long long i = gi - P.begin;
+    const long long n0 = (i / mp.K8) * MERGE_ROWS;
+    const int k8 = static_cast<int>(i % mp.K8);
+    const int K = mp.K8 * 8;
+    float d[MERGE_ROWS][8];
+#pragma unroll
+    for (int q = 0; q < MERGE_ROWS; ++q)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) d[q][e] = 0.f;
+#pragma unroll
+    for (int j0 = 0; j0 < R; j0 += 8) {
+      float b[MERGE_ROWS][8];
+#pragma unroll
+      for (int q = 0; q < MERGE_ROWS; ++q) {
+        const long long n = n0 + q < P.N ? n0 + q : P.N - 1;
+        unpack8(*reinterpret_cast<const uint4*>(P.B + n * R + j0), b[q]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float a[8];
+        unpack8(*reinterpret_cast<const uint4*>(P.A + static_cast<long long>(j0 + j) * K + k8 * 8), a);
+#pragma unroll
+        for (int q = 0; q < MERGE_ROWS; ++q)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) d[q][e] = fmaf(b[q][j], a[e], d[q][e]);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < MERGE_ROWS; ++q) {
+      if (n0 + q < P.N) {
+        float w[8];
+        unpack8(*reinterpret_cast<const uint4*>(P.W + (n0 + q) * K + k8 * 8), w);
+        uint4 ov;
+        uint32_t* ou = reinterpret_cast<uint32_t*>(&ov);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(fmaf(mp.s, d[q][2 * e], w[2 * e]),
+                                                   fmaf(mp.s, d[q][2 * e + 1], w[2 * e + 1]));
+          ou[e] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(P.out + (n0 + q) * K + k8 * 8) = ov;
+      }
+    }
+  }
+}
+
+int launch_lora_merge(int nproj, const void* const* W, const void* const* A, const void* const* B,
+                      void* const* out, const long long* N, long long K, long long r, float s,
+                      cudaStream_t stream) {
+  int st = device_check();
+  if (st != WSL_OK) return st;
+  if (nproj < 1 || nproj > WSL_MAX_PROJ || !W || !A || !B || !out || !N || K <= 0 || r <= 0)
+    return WSL_ERR_BAD_ARG;
+  if ((K % 8) != 0) return WSL_ERR_ALIGN;
+  if (K > 0x7fffffffLL) return WSL_ERR_TOO_LARGE;
+  if (r != 8 && r != 16 && r != 32 && r != 64) return WSL_ERR_TOO_LARGE;
+  MergeParams mp;
+  mp.nproj = nproj;
+  mp.K8 = static_cast<int>(K / 8);
+  mp.s = s;
+  long long total = 0;
+  for (int p = 0; p < nproj; ++p) {
+    if (!W[p] || !A[p] || !B[p] || !out[p] || N[p] <= 0) return WSL_ERR_BAD_ARG;
+    if (((reinterpret_cast<uintptr_t>(W[p]) | reinterpret_cast<uintptr_t>(A[p]) |
+          reinterpret_cast<uintptr_t>(B[p]) | reinterpret_cast<uintptr_t>(out[p])) & 15u) != 0)
+      return WSL_ERR_ALIGN;
+    mp.proj[p].W = static_cast<const __nv_bfloat16*>(W[p]);
+    mp.proj[p].A = static_cast<const __nv_bfloat16*>(A[p]);
+    mp.proj[p].B = static_cast<const __nv_bfloat16*>(B[p]);
+    mp.proj[p].out = static_cast<__nv_bfloat16*>(out[p]);
+    mp.proj[p].N = N[p];
+    mp.proj[p].begin = total;
+    total += ((N[p] + MERGE_ROWS - 1) / MERGE_ROWS) * mp.K8;
+  }
+  mp.total = total;
+  long long blocks = (total + 255) / 256;
+  const long long cap = 8ll * device_sm_count();
+  if (blocks > cap) blocks = cap;
+  const unsigned gb = static_cast<unsigned>(blocks);
+  switch (r) {
+    case 8: lora_merge_kernel<8><<<gb, 256, 0, stream>>>(mp); break;
+    case 16: lora_merge_kernel<16><<<gb, 256, 0, stream>>>(mp); break;
+    case 32: lora_merge_kernel<32><<<gb, 256, 0, stream>>>(mp); break;
+    default: lora_merge_kernel<64><<<gb, 256, 0, stream>>>(mp); break;
+  }
+  if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
+  ++g_launch_count;
+  return WSL_OK;
+}
+
+}  // namespace wsl

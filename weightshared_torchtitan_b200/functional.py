@@ -16,6 +16,7 @@ Weight gradients can go two ways:
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional, Sequence, Tuple
 
 import torch
@@ -27,6 +28,14 @@ Sinks = Optional[Tuple[Optional[torch.Tensor], Optional[torch.Tensor], Optional[
 
 def _flat(x: torch.Tensor) -> torch.Tensor:
     return x.reshape(-1, x.shape[-1])
+
+
+# When the shared weight is trained (dW wanted together with dA and dB, bf16), the backward
+# goes through the layer's own weight gradient G = dY^T x: dB = s G A^T, dA = s B^T G and
+# dX = dY (W + s B A). That reads the [N, K] matrix G instead of streaming the token rows
+# again for the two rank-r products, and needs no pre-pass over dY. False (or the environment
+# variable WSL_DERIVED_ADAPTER_GRADS=0) keeps the direct formulation with U = s dY B.
+DERIVED_ADAPTER_GRADS = os.environ.get("WSL_DERIVED_ADAPTER_GRADS", "1") != "0"
 
 
 class LoRALinearGroupFunction(torch.autograd.Function):
@@ -59,7 +68,9 @@ class LoRALinearGroupFunction(torch.autograd.Function):
         else:
             for p in range(P):
                 ys.append(ops.lora_linear_fwd(x2, Ws[p], Ts[p], Bs[p]).view(*x.shape[:-1], Ws[p].shape[0]))
-        ctx.save_for_backward(x2, T_cat, *wab)
+        ctx.derived = (DERIVED_ADAPTER_GRADS and sinks is not None and x2.dtype == torch.bfloat16
+                       and all(t[0] is not None and t[1] is not None and t[2] is not None for t in sinks))
+        ctx.save_for_backward(x2, None if ctx.derived else T_cat, *wab)
         ctx.s = float(s)
         ctx.sinks = sinks
         ctx.P = P
@@ -71,6 +82,27 @@ class LoRALinearGroupFunction(torch.autograd.Function):
         x2, T_cat, *wab = ctx.saved_tensors
         P = ctx.P
         Ws, As, Bs = list(wab[0::3]), list(wab[1::3]), list(wab[2::3])
+        if ctx.derived:
+            dY2 = []
+            for p in range(P):
+                d = dYs[p]
+                if d is None:
+                    d = torch.zeros(x2.shape[0], Ws[p].shape[0], device=x2.device, dtype=x2.dtype)
+                d = _flat(d)
+                if d.stride(-1) != 1:
+                    d = d.contiguous()
+                dY2.append(d)
+            dX = None
+            if ctx.needs_input_grad[0]:
+                if len({A.shape[0] for A in As}) == 1:
+                    Weffs = ops.lora_merge_weight(Ws, As, Bs, ctx.s)
+                else:
+                    Weffs = [ops.lora_merge_weight([Ws[p]], [As[p]], [Bs[p]], ctx.s)[0] for p in range(P)]
+                dX = ops.lora_linear_bwd_dx(dY2, [None] * P, Weffs, [None] * P).view(ctx.x_shape)
+            dWls = ops.bwd_dw_layer_group(dY2, x2, [t[0] for t in ctx.sinks])
+            ops.lora_adapter_grads_from_dw(dWls, As, Bs, [t[1] for t in ctx.sinks],
+                                           [t[2] for t in ctx.sinks], ctx.s)
+            return (dX, None, None, None, *([None] * (3 * P)))
         dY2, Us = [], []
         # the U of all projections side by side, so that dX contracts [U_0 | U_1 | ...] with
         # the stacked A matrices in ONE rank-sum segment instead of one tiny segment each

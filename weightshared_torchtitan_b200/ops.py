@@ -333,6 +333,114 @@ def lora_linear_bwd_dw_group(dYs, Us, x, Ts, dWs, dAs, dBs) -> None:
     _lib.check(st, "wsl_lora_linear_bwd_dw_group")
 
 
+def lora_merge_weight(Ws, As, Bs, s: float) -> list:
+    """W_eff_p = bf16(W_p + s B_p A_p) for projections with the same input width and rank, one
+    launch."""
+    n = len(Ws)
+    Ws = [_mat(t, "W").contiguous() for t in Ws]
+    As = [_mat(t, "A").contiguous() for t in As]
+    Bs = [_mat(t, "B").contiguous() for t in Bs]
+    K = Ws[0].shape[1]
+    vp, ll = ctypes.c_void_p * n, ctypes.c_longlong * n
+    w_p, a_p, b_p, o_p, Ns = vp(), vp(), vp(), vp(), ll()
+    r0 = As[0].shape[0]
+    outs = []
+    flops = nbytes = 0.0
+    for p in range(n):
+        if _dtype_code(Ws[p]) != WSL_BF16:
+            raise TypeError("lora_merge_weight is a bf16 operation")
+        _same(WSL_BF16, As[p], Bs[p])
+        N = Ws[p].shape[0]
+        r = As[p].shape[0]
+        if Ws[p].shape != (N, K) or As[p].shape != (r, K) or Bs[p].shape != (N, r):
+            raise ValueError(f"shapes W{tuple(Ws[p].shape)} A{tuple(As[p].shape)} B{tuple(Bs[p].shape)} "
+                             "do not fit W + s B A")
+        out = torch.empty_like(Ws[p])
+        outs.append(out)
+        if r != r0:
+            raise ValueError("projections merged in one launch must share the rank")
+        w_p[p], a_p[p], b_p[p], o_p[p], Ns[p] = (Ws[p].data_ptr(), As[p].data_ptr(), Bs[p].data_ptr(),
+                                                out.data_ptr(), N)
+        flops += 2.0 * N * K * r
+        nbytes += 4.0 * N * K
+    _e = _tic()
+    st = _lib.lib().wsl_lora_merge_weight(n, w_p, a_p, b_p, o_p, Ns, K, r0, float(s), _stream())
+    _toc(_e, "merge_weight", flops, nbytes)
+    _lib.check(st, "wsl_lora_merge_weight")
+    return outs
+
+
+def bwd_dw_layer_group(dYs, x, dWs) -> list:
+    """dW_p += dY_p.T @ x (fp32, in place) for projections that read the same x, one launch;
+    returns the bf16 matrices dWl_p = dY_p.T @ x of this call alone."""
+    n = len(dYs)
+    dYs = [_mat(t, "dY") for t in dYs]
+    x = _mat(x, "x")
+    if _dtype_code(x) != WSL_BF16:
+        raise TypeError("bwd_dw_layer_group is the bf16 path")
+    M, K = x.shape
+    vp, ll = ctypes.c_void_p * n, ctypes.c_longlong * n
+    dy_p, dw_p, dwl_p, lddy, Ns, rs = vp(), vp(), vp(), ll(), ll(), ll()
+    dWls = []
+    flops = 0.0
+    nbytes = 2.0 * M * K
+    for p in range(n):
+        _same(WSL_BF16, dYs[p])
+        N = dYs[p].shape[1]
+        g = dWs[p]
+        if g.dtype != torch.float32 or not g.is_contiguous() or tuple(g.shape) != (N, K):
+            raise ValueError(f"dW must be a contiguous float32 tensor of shape {(N, K)}")
+        dWl = torch.empty((N, K), device=x.device, dtype=torch.bfloat16)
+        dWls.append(dWl)
+        dy_p[p], lddy[p], Ns[p], rs[p] = dYs[p].data_ptr(), _ld(dYs[p]), N, 0
+        dw_p[p], dwl_p[p] = g.data_ptr(), dWl.data_ptr()
+        flops += 2.0 * M * N * K
+        nbytes += 2.0 * M * N + 10.0 * N * K
+    ws_bytes = int(_lib.lib().wsl_bwd_dw_group_workspace_bytes(n, Ns, rs, M, K))
+    ws = torch.empty(ws_bytes // 4, device=x.device, dtype=torch.float32) if ws_bytes else None
+    _e = _tic()
+    st = _lib.lib().wsl_bwd_dw_layer_group(n, dy_p, lddy, x.data_ptr(), _ld(x), dw_p, dwl_p, Ns, M, K,
+                                           ws.data_ptr() if ws is not None else None, ws_bytes, _stream())
+    _toc(_e, "dw", flops, nbytes)
+    _lib.check(st, "wsl_bwd_dw_layer_group")
+    return dWls
+
+
+def lora_adapter_grads_from_dw(dWls, As, Bs, dAs, dBs, s: float) -> None:
+    """dA_p += s B_p.T @ dWl_p, dB_p += s dWl_p @ A_p.T (fp32, in place)."""
+    n = len(dWls)
+    vp, ll = ctypes.c_void_p * n, ctypes.c_longlong * n
+    g_p, a_p, b_p, da_p, db_p, Ns, rs = vp(), vp(), vp(), vp(), vp(), ll(), ll()
+    keep = []
+    K = dWls[0].shape[1]
+    flops = 0.0
+    nbytes = 0.0
+    for p in range(n):
+        G, A, B = _mat(dWls[p], "dWl"), _mat(As[p], "A").contiguous(), _mat(Bs[p], "B").contiguous()
+        _same(WSL_BF16, G, A, B)
+        if not G.is_contiguous():
+            raise ValueError("dWl must be dense")
+        N, r = B.shape
+        if G.shape != (N, K) or A.shape != (r, K):
+            raise ValueError("shapes of dWl, A, B do not fit")
+        for gbuf, shape, nm in ((dAs[p], (r, K), "dA"), (dBs[p], (N, r), "dB")):
+            if gbuf.dtype != torch.float32 or not gbuf.is_contiguous() or tuple(gbuf.shape) != shape:
+                raise ValueError(f"{nm} must be a contiguous float32 tensor of shape {shape}")
+        keep += [G, A, B]
+        g_p[p], a_p[p], b_p[p] = G.data_ptr(), A.data_ptr(), B.data_ptr()
+        da_p[p], db_p[p], Ns[p], rs[p] = dAs[p].data_ptr(), dBs[p].data_ptr(), N, r
+        flops += 4.0 * N * K * r
+        nbytes += 4.0 * N * K
+    ws_bytes = int(_lib.lib().wsl_adapter_grads_workspace_bytes(n, Ns, rs, K))
+    ws = torch.empty(ws_bytes // 4, device=dWls[0].device, dtype=torch.float32) if ws_bytes else None
+    _e = _tic()
+    st = _lib.lib().wsl_lora_adapter_grads_from_dw(n, g_p, a_p, b_p, da_p, db_p, Ns, rs, K, float(s),
+                                                   ws.data_ptr() if ws is not None else None, ws_bytes,
+                                                   _stream())
+    _toc(_e, "adapter_grads", flops, nbytes)
+    _lib.check(st, "wsl_lora_adapter_grads_from_dw")
+
+
 def embed_gather(tokens: torch.Tensor, E_small: torch.Tensor) -> torch.Tensor:
     """G[m] = E_small[tokens[m]] (bit-exact row copy)."""
     tok = tokens.reshape(-1)
