@@ -170,8 +170,10 @@ def run_reference(args):
 
 # ------------------------------------------------------------------------ our arm
 def headline_op(ops, torch, peaks):
-    """Isolated fused projection fwd+bwd (prepass, fwd, bwd prepass, dX, dW/dA/dB) at the
-    configuration-4 MLP shapes, M = 16384, r = 64; inputs (>= 670 MB) exceed the 126 MB L2."""
+    """Isolated fused projection fwd+bwd through the autograd Function (pre-pass T, forward;
+    merged weight, dX, dW, dA, dB) at the configuration-4 MLP shapes, M = 16384, r = 64; inputs
+    (>= 670 MB) exceed the 126 MB L2."""
+    from weightshared_torchtitan_b200 import functional as Fn
     out = {}
     for name, (M, N, K, r) in {"gate_up_12288x4096": (16384, 12288, 4096, 64),
                                "down_4096x12288": (16384, 4096, 12288, 64)}.items():
@@ -186,12 +188,13 @@ def headline_op(ops, torch, peaks):
         dA = torch.zeros(r, K, device="cuda")
         dB = torch.zeros(N, r, device="cuda")
 
+        x.requires_grad_(True)
+
         def run():
-            T = ops.lora_prepass(x, A, 2.0)
-            ops.lora_linear_fwd(x, W, T, B)
-            U = ops.lora_bwd_prepass(dY, B, 2.0)
-            ops.lora_linear_bwd_dx([dY], [U], [W], [A])
-            ops.lora_linear_bwd_dw(dY, U, x, T, dW, dA, dB)
+            # the product's own call: the autograd Function with in-place fp32 gradient buffers
+            y = Fn.lora_linear(x, W, A, B, 2.0, (dW, dA, dB))
+            y.backward(dY)
+            x.grad = None
 
         for _ in range(3):
             run()

@@ -46,6 +46,7 @@ extern "C" {
 #define WSL_NOALLOC_SCRATCH_BYTES (64ull << 20) /* fixed scratch of wsl_lora_linear_bwd_dw_noalloc */
 
 #define WSL_MAX_PROJ 3 /* projections that can share one input in wsl_lora_linear_bwd_dx */
+#define WSL_MAX_ADAPTER_PROJ 9   /* projections per wsl_lora_adapter_grads_from_dw call */
 
 /* Library version, (major << 16) | minor. */
 int wsl_version(void);
@@ -182,16 +183,17 @@ unsigned long long wsl_bwd_dw_group_workspace_bytes(int nproj, const long long* 
  * Three entry points:
  *
  * wsl_lora_merge_weight:  Weff_p[N_p,K] = bf16( W_p[N_p,K] + s * B_p[N_p,r] * A_p[r,K] ) for
- *   nproj projections with the same K and rank (r = 8, 16, 32 or 64) in one launch: one
+ *   nproj projections with the same K and rank (r = 8, 16, 32, 64 or 128) in one launch: one
  *   streaming pass over W, r FMAs per element; dense row-major matrices. Give Weff_p to
  *   wsl_lora_linear_bwd_dx as W_p with U_p = A_p = NULL.
  * wsl_bwd_dw_layer_group: dW_p[N_p,K] += dY_p^T x (fp32, in place, shared across layers) and
  *   dWl_p[N_p,K] = bf16(dY_p^T x) (this launch's addend alone, dense) for nproj projections
  *   that read the same x, one launch. Workspace: wsl_bwd_dw_group_workspace_bytes with r = 0.
- * wsl_lora_adapter_grads_from_dw: dA_p[r_p,K] += s * B_p^T dWl_p, dB_p[N_p,r_p] += s * dWl_p
- *   A_p^T (fp32, in place; A_p, B_p, dWl_p dense bf16), two launches for the whole group. The
- *   optional workspace (wsl_adapter_grads_workspace_bytes) lets the short contractions be split
- *   over the GPU, folded in a fixed order.
+ * wsl_lora_adapter_grads_from_dw: dA_p[r_p,K_p] += s * B_p^T dWl_p, dB_p[N_p,r_p] += s * dWl_p
+ *   A_p^T (fp32, in place; A_p, B_p, dWl_p dense bf16) for up to WSL_MAX_ADAPTER_PROJ
+ *   projections of any sizes (all seven of a decoder layer) in two launches. The optional
+ *   workspace (wsl_adapter_grads_workspace_bytes) lets the short contractions be split over
+ *   the GPU, folded in a fixed order.
  *
  * The bf16 rounding of G_l and of Weff is of the same order as the bf16 rounding of U and T
  * in the direct formulation. Replaces the same autograd nodes as wsl_lora_linear_bwd_dx/_dw:
@@ -206,11 +208,11 @@ int wsl_bwd_dw_layer_group(int nproj, const void* const* dY, const long long* ld
                            unsigned long long workspace_bytes, void* stream);
 int wsl_lora_adapter_grads_from_dw(int nproj, const void* const* dWl, const void* const* A,
                                    const void* const* B, float* const* dA, float* const* dB,
-                                   const long long* N, const long long* r, long long K, float s,
+                                   const long long* N, const long long* K, const long long* r, float s,
                                    void* workspace, unsigned long long workspace_bytes,
                                    void* stream);
-unsigned long long wsl_adapter_grads_workspace_bytes(int nproj, const long long* N, const long long* r,
-                                                     long long K);
+unsigned long long wsl_adapter_grads_workspace_bytes(int nproj, const long long* N, const long long* K,
+                                                     const long long* r);
 
 /* Workspace size (bytes, possibly 0) wsl_lora_linear_bwd_dw wants for these sizes; the
  * want_* flags say which of dW, dA, dB will be non-NULL. No reference counterpart. */

@@ -575,3 +575,57 @@ def test_autograd_function_both_backward_formulations(wsl, P):
                     assert rel(got, ref) < TOL_BF16
     finally:
         Fn.DERIVED_ADAPTER_GRADS = saved
+
+
+def test_adapter_gradients_of_a_whole_layer_in_one_call(wsl):
+    """The seven projections of a decoder layer (three different input widths, four output
+    widths) in ONE adapter-gradient call: regions with shorter contractions than the launch's
+    read as zeros beyond their end."""
+    g = torch.Generator().manual_seed(2024)
+    bf = torch.bfloat16
+    r, s = 16, 2.0
+    shapes = [(512, 256), (256, 256), (256, 256), (256, 512), (768, 256), (768, 256), (256, 768)]   # (N, K)
+    Gs = [torch.randn(n, k, generator=g).cuda().to(bf) for n, k in shapes]
+    As = [(torch.randn(r, k, generator=g) * 0.05).cuda().to(bf) for n, k in shapes]
+    Bs = [(torch.randn(n, r, generator=g) * 0.1).cuda().to(bf) for n, k in shapes]
+    dAs = [torch.full((r, k), 0.5, device="cuda") for n, k in shapes]
+    dBs = [torch.full((n, r), 0.5, device="cuda") for n, k in shapes]
+    wsl.lora_adapter_grads_from_dw(Gs, As, Bs, dAs, dBs, s)
+    for p in range(len(shapes)):
+        assert rel(dAs[p] - 0.5, s * Bs[p].float().T @ Gs[p].float()) < 1e-4
+        assert rel(dBs[p] - 0.5, s * Gs[p].float() @ As[p].float().T) < 1e-4
+
+
+@pytest.mark.parametrize("expected", [2, 3])
+def test_adapter_gradient_batch_across_groups(wsl, expected):
+    """Two projection groups share an AdapterGradBatch: with expected = 2 it runs when the
+    second group reports, with expected = 3 (one group never reports) at the end of the
+    backward pass. Either way the gradients match the oracle."""
+    from weightshared_torchtitan_b200 import functional as Fn
+    g = torch.Generator().manual_seed(55 + expected)
+    bf = torch.bfloat16
+    M, K, r, s = 1024, 512, 16, 2.0
+    groups = [(1024, 256), (768,)]
+    x = torch.randn(M, K, generator=g).to(bf)
+    batch = Fn.AdapterGradBatch(expected)
+    xc = x.cuda().requires_grad_(True)
+    outs, all_sinks, want, dYs_all = [], [], [], []
+    for Ns in groups:
+        Ws = [(torch.randn(n, K, generator=g) * 0.03).to(bf) for n in Ns]
+        As = [(torch.randn(r, K, generator=g) * 0.05).to(bf) for n in Ns]
+        Bs = [(torch.randn(n, r, generator=g) * 0.1).to(bf) for n in Ns]
+        dYs = [(torch.randn(M, n, generator=g) * 0.1).to(bf) for n in Ns]
+        want += [oracle_projection(x, Ws[p], As[p], Bs[p], dYs[p]) for p in range(len(Ns))]
+        sinks = [(torch.zeros(n, K, device="cuda"), torch.zeros(r, K, device="cuda"),
+                  torch.zeros(n, r, device="cuda")) for n in Ns]
+        ys = Fn.lora_linear_group(xc, [w.cuda() for w in Ws], [a.cuda() for a in As],
+                                  [b.cuda() for b in Bs], s, sinks, (), batch)
+        outs += list(ys)
+        dYs_all += [d.cuda() for d in dYs]
+        all_sinks += sinks
+    torch.autograd.backward(outs, dYs_all)
+    assert not batch.pending
+    assert rel(xc.grad, sum(w[1] for w in want)) < TOL_BF16
+    for sk, w in zip(all_sinks, want):
+        for got, ref in zip(sk, w[2:]):
+            assert rel(got, ref) < TOL_BF16

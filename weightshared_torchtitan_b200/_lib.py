@@ -49,10 +49,10 @@ SIGNATURES = {
                                           _llp, _llp, _ll, _ll, _vp, ctypes.c_ulonglong, _vp]),
     "wsl_bwd_dw_group_workspace_bytes": (ctypes.c_ulonglong, [_i, _llp, _llp, _ll, _ll]),
     "wsl_lora_merge_weight": (_i, [_i, _vpp, _vpp, _vpp, _vpp, _llp, _ll, _ll, _f, _vp]),
-    "wsl_adapter_grads_workspace_bytes": (ctypes.c_ulonglong, [_i, _llp, _llp, _ll]),
+    "wsl_adapter_grads_workspace_bytes": (ctypes.c_ulonglong, [_i, _llp, _llp, _llp]),
     "wsl_bwd_dw_layer_group": (_i, [_i, _vpp, _llp, _vp, _ll, _vpp, _vpp, _llp, _ll, _ll, _vp,
                                     ctypes.c_ulonglong, _vp]),
-    "wsl_lora_adapter_grads_from_dw": (_i, [_i, _vpp, _vpp, _vpp, _vpp, _vpp, _llp, _llp, _ll, _f, _vp,
+    "wsl_lora_adapter_grads_from_dw": (_i, [_i, _vpp, _vpp, _vpp, _vpp, _vpp, _llp, _llp, _llp, _f, _vp,
                                             ctypes.c_ulonglong, _vp]),
     "wsl_bwd_dw_workspace_bytes": (ctypes.c_ulonglong, [_ll, _ll, _ll, _ll, _i, _i, _i]),
     "wsl_ce_fwd_bwd": (_i, [_vp, _ll, _vp, _vp, _ll, _ll, _f, _i, _vp]),

@@ -418,30 +418,35 @@ int wsl_bwd_dw_layer_group(int nproj, const void* const* dY, const long long* ld
 
 int wsl_lora_adapter_grads_from_dw(int nproj, const void* const* dWl, const void* const* A,
                                    const void* const* B, float* const* dA, float* const* dB,
-                                   const long long* N, const long long* r, long long K, float s,
+                                   const long long* N, const long long* K, const long long* r, float s,
                                    void* workspace, unsigned long long workspace_bytes,
                                    void* stream) {
-  if (nproj < 1 || nproj > WSL_MAX_PROJ || !dWl || !A || !B || !dA || !dB || !N || !r || K <= 0)
+  if (nproj < 1 || nproj > WSL_MAX_ADAPTER_PROJ || !dWl || !A || !B || !dA || !dB || !N || !K || !r)
     return WSL_ERR_BAD_ARG;
-  long long n_max = 0;
+  long long n_max = 0, k_max = 0;
   for (int p = 0; p < nproj; ++p) {
-    if (!dWl[p] || !A[p] || !B[p] || !dA[p] || !dB[p] || N[p] <= 0 || r[p] <= 0) return WSL_ERR_BAD_ARG;
+    if (!dWl[p] || !A[p] || !B[p] || !dA[p] || !dB[p] || N[p] <= 0 || K[p] <= 0 || r[p] <= 0)
+      return WSL_ERR_BAD_ARG;
     n_max = N[p] > n_max ? N[p] : n_max;
+    k_max = K[p] > k_max ? K[p] : k_max;
   }
   if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return WSL_ERR_ALIGN;
-  // dB_p[N, r] += s * dWl_p[N, K] * A_p[r, K]^T: both operands K-major, one region per projection
+  // dB_p[N, r] += s * dWl_p[N, K] * A_p[r, K]^T: both operands K-major, one region per projection.
+  // Projections of different sizes share the launch: the contraction runs to the longest and
+  // the shorter operands read as zeros beyond their end.
   GemmDesc gb = {};
   gb.a_mn = false;
   gb.b_mn = false;
   gb.nseg = 1;
-  gb.seg_k[0] = static_cast<int>(K);
+  gb.seg_k[0] = static_cast<int>(k_max);
+  gb.ragged_k = true;
   gb.nregion = nproj;
   gb.workspace = static_cast<float*>(workspace);
   gb.workspace_bytes = static_cast<size_t>(workspace_bytes);
   for (int p = 0; p < nproj; ++p) {
     RegionDesc& rd = gb.region[p];
-    rd.a[0] = mat(dWl[p], N[p], K, K);
-    rd.b[0] = mat(A[p], r[p], K, K);
+    rd.a[0] = mat(dWl[p], N[p], K[p], K[p]);
+    rd.b[0] = mat(A[p], r[p], K[p], K[p]);
     rd.mo = N[p];
     rd.no = r[p];
     rd.out = dB[p];
@@ -452,9 +457,7 @@ int wsl_lora_adapter_grads_from_dw(int nproj, const void* const* dWl, const void
   int st = launch_block_gemm(gb, static_cast<cudaStream_t>(stream));
   if (st != WSL_OK) return st;
   // dA_p[r, K] += s * B_p[N, r]^T * dWl_p[N, K], run as its transpose (dWl_p^T B_p, [K, r]) with
-  // the contraction over N: both operands MN-major, results written transposed. Projections of
-  // different widths share the launch: the contraction runs to the largest N and the shorter
-  // operands read as zeros beyond their end.
+  // the contraction over N: both operands MN-major, results written transposed.
   GemmDesc ga = {};
   ga.a_mn = true;
   ga.b_mn = true;
@@ -466,12 +469,12 @@ int wsl_lora_adapter_grads_from_dw(int nproj, const void* const* dWl, const void
   ga.workspace_bytes = static_cast<size_t>(workspace_bytes);
   for (int p = 0; p < nproj; ++p) {
     RegionDesc& rd = ga.region[p];
-    rd.a[0] = mat(dWl[p], N[p], K, K);
+    rd.a[0] = mat(dWl[p], N[p], K[p], K[p]);
     rd.b[0] = mat(B[p], N[p], r[p], r[p]);
-    rd.mo = K;
+    rd.mo = K[p];
     rd.no = r[p];
     rd.out = dA[p];
-    rd.ld_out = K;
+    rd.ld_out = K[p];
     rd.mode = kEpiAccumF32;
     rd.alpha = s;
     rd.transposed = true;
@@ -479,13 +482,13 @@ int wsl_lora_adapter_grads_from_dw(int nproj, const void* const* dWl, const void
   return launch_block_gemm(ga, static_cast<cudaStream_t>(stream));
 }
 
-unsigned long long wsl_adapter_grads_workspace_bytes(int nproj, const long long* N, const long long* r,
-                                                     long long K) {
-  if (nproj < 1 || nproj > WSL_MAX_PROJ || !N || !r || K <= 0) return 0;
+unsigned long long wsl_adapter_grads_workspace_bytes(int nproj, const long long* N, const long long* K,
+                                                     const long long* r) {
+  if (nproj < 1 || nproj > WSL_MAX_ADAPTER_PROJ || !N || !K || !r) return 0;
   long long eb = 0, ea = 0;
   for (int p = 0; p < nproj; ++p) {
     eb += N[p] * r[p];
-    ea += r[p] * K;
+    ea += r[p] * K[p];
   }
   return splitk_workspace_bytes(eb > ea ? eb : ea);
 }

@@ -103,7 +103,7 @@ int launch_lora_merge(int nproj, const void* const* W, const void* const* A, con
     return WSL_ERR_BAD_ARG;
   if ((K % 8) != 0) return WSL_ERR_ALIGN;
   if (K > 0x7fffffffLL) return WSL_ERR_TOO_LARGE;
-  if (r != 8 && r != 16 && r != 32 && r != 64) return WSL_ERR_TOO_LARGE;
+  if (r != 8 && r != 16 && r != 32 && r != 64 && r != 128) return WSL_ERR_TOO_LARGE;
   MergeParams mp;
   mp.nproj = nproj;
   mp.K8 = static_cast<int>(K / 8);
@@ -131,7 +131,8 @@ int launch_lora_merge(int nproj, const void* const* W, const void* const* A, con
     case 8: lora_merge_kernel<8><<<gb, 256, 0, stream>>>(mp); break;
     case 16: lora_merge_kernel<16><<<gb, 256, 0, stream>>>(mp); break;
     case 32: lora_merge_kernel<32><<<gb, 256, 0, stream>>>(mp); break;
-    default: lora_merge_kernel<64><<<gb, 256, 0, stream>>>(mp); break;
+    case 64: lora_merge_kernel<64><<<gb, 256, 0, stream>>>(mp); break;
+    default: lora_merge_kernel<128><<<gb, 256, 0, stream>>>(mp); break;
   }
   if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
   ++g_launch_count;

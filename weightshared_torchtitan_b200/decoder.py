@@ -220,7 +220,7 @@ class WeightSharedDecoder(nn.Module):
             p.grad = torch.zeros(p.shape, device=p.device, dtype=torch.float32)
         return p.grad
 
-    def _group(self, lyr: DecoderLayer, names, x):
+    def _group(self, lyr: DecoderLayer, names, x, batch=None):
         dt = self.compute_dtype
         Ws, As, Bs, sinks, anchors = [], [], [], [], []
         train = torch.is_grad_enabled()
@@ -235,7 +235,7 @@ class WeightSharedDecoder(nn.Module):
                 sinks.append((self._sink(W), self._sink(A), self._sink(B)))
                 anchors += [W, A, B]
         s = getattr(lyr, f"{names[0]}_offset").scale
-        return WF.lora_linear_group(x, Ws, As, Bs, s, sinks if train else None, tuple(anchors))
+        return WF.lora_linear_group(x, Ws, As, Bs, s, sinks if train else None, tuple(anchors), batch)
 
     # ------------------------------------------------------------------------ forward
     def hidden(self, tokens: torch.Tensor) -> torch.Tensor:
@@ -255,18 +255,20 @@ class WeightSharedDecoder(nn.Module):
             self._rope = (cos.contiguous(), sin.contiguous())       # fp32 [s, head_dim]
         cos, sin = self._rope
         for lyr in self.layers:
+            # the layer's four projection groups hand their adapter-gradient work to one batch
+            ab = WF.AdapterGradBatch(4) if torch.is_grad_enabled() else None
             xn = _rms(lyr.attention_norm, h)
-            q, k, v = self._group(lyr, ("wq", "wk", "wv"), xn)
+            q, k, v = self._group(lyr, ("wq", "wk", "wv"), xn, ab)
             q = _rms(lyr.q_norm, q.view(b, s, c.n_heads, c.head_dim), (cos, sin, c.n_heads, s))
             k = _rms(lyr.k_norm, k.view(b, s, c.n_kv_heads, c.head_dim), (cos, sin, c.n_kv_heads, s))
             v = v.view(b, s, c.n_kv_heads, c.head_dim)
             o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                                is_causal=True, enable_gqa=c.n_heads != c.n_kv_heads)
             o = o.transpose(1, 2).reshape(b, s, c.n_heads * c.head_dim)
-            h = h + self._group(lyr, ("wo",), o)[0]
+            h = h + self._group(lyr, ("wo",), o, ab)[0]
             xn = _rms(lyr.ffn_norm, h)
-            gate, up = self._group(lyr, ("w1", "w3"), xn)
-            h = h + self._group(lyr, ("w2",), WF.swiglu(gate, up))[0]
+            gate, up = self._group(lyr, ("w1", "w3"), xn, ab)
+            h = h + self._group(lyr, ("w2",), WF.swiglu(gate, up), ab)[0]
         return _rms(self.norm, h)
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:

@@ -38,10 +38,47 @@ def _flat(x: torch.Tensor) -> torch.Tensor:
 DERIVED_ADAPTER_GRADS = os.environ.get("WSL_DERIVED_ADAPTER_GRADS", "1") != "0"
 
 
+class AdapterGradBatch:
+    """Collects the adapter-gradient work (dA += s B^T G, dB += s G A^T) of several projection
+    groups and runs it in ONE call of two launches instead of one call per group; the products
+    are tiny and launch-bound, so a decoder layer hands the same batch to its four groups.
+
+    ``expected`` = number of groups that will report; the batch runs when the last one has.
+    If fewer report (a group got no gradient), what is pending runs when the backward pass
+    ends (an autograd engine callback), or when ``flush()`` is called.
+    """
+
+    def __init__(self, expected: int):
+        self.expected = int(expected)
+        self.count = 0
+        self.s: Optional[float] = None
+        self.pending: List[tuple] = []
+
+    def add(self, dWls, As, Bs, dAs, dBs, s: float) -> None:
+        if self.s is not None and self.s != s:
+            self.flush()
+        self.s = s
+        if not self.pending:
+            # safety net: whatever is still pending when this backward pass ends runs then
+            torch.autograd.Variable._execution_engine.queue_callback(self.flush)
+        self.pending += list(zip(dWls, As, Bs, dAs, dBs))
+        self.count += 1
+        if self.count >= self.expected:
+            self.flush()
+
+    def flush(self) -> None:
+        todo, self.pending, self.count = self.pending, [], 0
+        for i in range(0, len(todo), ops.MAX_ADAPTER_PROJ):
+            g, a, b, da, db = zip(*todo[i:i + ops.MAX_ADAPTER_PROJ])
+            ops.lora_adapter_grads_from_dw(g, a, b, da, db, self.s)
+
+
 class LoRALinearGroupFunction(torch.autograd.Function):
     """P projections that read the same x: y_p = x W_p^T + s (x A_p^T) B_p^T, p < P <= 3.
 
-    forward(ctx, x, s, sinks, anchors, W_0, A_0, B_0, W_1, A_1, B_1, ...) -> (y_0, ..., y_{P-1})
+    forward(ctx, x, s, sinks, anchors, batch, W_0, A_0, B_0, W_1, A_1, B_1, ...) -> (y_0, ..., y_{P-1})
+
+    ``batch`` is None or an AdapterGradBatch shared with other groups (see there).
 
     ``sinks`` is None or a list of P triples (dW, dA, dB) of fp32 buffers to accumulate into.
     ``anchors`` is a tuple of tensors that only tie the output to the autograd graph (the
@@ -49,8 +86,9 @@ class LoRALinearGroupFunction(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, s, sinks, anchors, *wab):
+    def forward(ctx, x, s, sinks, anchors, batch, *wab):
         P = len(wab) // 3
+        ctx.batch = batch
         Ws, As, Bs = list(wab[0::3]), list(wab[1::3]), list(wab[2::3])
         x2 = _flat(x)
         if not x2.is_contiguous() and x2.stride(-1) != 1:
@@ -69,7 +107,8 @@ class LoRALinearGroupFunction(torch.autograd.Function):
             for p in range(P):
                 ys.append(ops.lora_linear_fwd(x2, Ws[p], Ts[p], Bs[p]).view(*x.shape[:-1], Ws[p].shape[0]))
         ctx.derived = (DERIVED_ADAPTER_GRADS and sinks is not None and x2.dtype == torch.bfloat16
-                       and all(t[0] is not None and t[1] is not None and t[2] is not None for t in sinks))
+                       and all(t[0] is not None and t[1] is not None and t[2] is not None for t in sinks)
+                       and all(A.shape[0] in ops.MERGE_RANKS for A in As))
         ctx.save_for_backward(x2, None if ctx.derived else T_cat, *wab)
         ctx.s = float(s)
         ctx.sinks = sinks
@@ -100,9 +139,12 @@ class LoRALinearGroupFunction(torch.autograd.Function):
                     Weffs = [ops.lora_merge_weight([Ws[p]], [As[p]], [Bs[p]], ctx.s)[0] for p in range(P)]
                 dX = ops.lora_linear_bwd_dx(dY2, [None] * P, Weffs, [None] * P).view(ctx.x_shape)
             dWls = ops.bwd_dw_layer_group(dY2, x2, [t[0] for t in ctx.sinks])
-            ops.lora_adapter_grads_from_dw(dWls, As, Bs, [t[1] for t in ctx.sinks],
-                                           [t[2] for t in ctx.sinks], ctx.s)
-            return (dX, None, None, None, *([None] * (3 * P)))
+            if ctx.batch is not None:
+                ctx.batch.add(dWls, As, Bs, [t[1] for t in ctx.sinks], [t[2] for t in ctx.sinks], ctx.s)
+            else:
+                ops.lora_adapter_grads_from_dw(dWls, As, Bs, [t[1] for t in ctx.sinks],
+                                               [t[2] for t in ctx.sinks], ctx.s)
+            return (dX, None, None, None, None, *([None] * (3 * P)))
         dY2, Us = [], []
         # the U of all projections side by side, so that dX contracts [U_0 | U_1 | ...] with
         # the stacked A matrices in ONE rank-sum segment instead of one tiny segment each
@@ -140,7 +182,7 @@ class LoRALinearGroupFunction(torch.autograd.Function):
                 off += r
             ops.lora_linear_bwd_dw_group(dY2, Us, x2, Ts, [s[0] for s in ctx.sinks],
                                          [s[1] for s in ctx.sinks], [s[2] for s in ctx.sinks])
-            return (dX, None, None, None, *([None] * (3 * P)))
+            return (dX, None, None, None, None, *([None] * (3 * P)))
         for p in range(P):
             r = As[p].shape[0]
             T = T_cat[:, off:off + r]
@@ -151,7 +193,7 @@ class LoRALinearGroupFunction(torch.autograd.Function):
                     ops.lora_linear_bwd_dw(dY2[p], Us[p], x2, T, dW, dA, dB)
                 grads += [None, None, None]
             else:
-                need = ctx.needs_input_grad[4 + 3 * p: 7 + 3 * p]
+                need = ctx.needs_input_grad[5 + 3 * p: 8 + 3 * p]
                 dev = x2.device
                 dW = torch.zeros(Ws[p].shape, device=dev, dtype=torch.float32) if need[0] else None
                 dA = torch.zeros(As[p].shape, device=dev, dtype=torch.float32) if need[1] else None
@@ -160,17 +202,18 @@ class LoRALinearGroupFunction(torch.autograd.Function):
                     ops.lora_linear_bwd_dw(dY2[p], Us[p], x2, T, dW, dA, dB)
                 grads += [g.to(w.dtype) if g is not None else None
                           for g, w in ((dW, Ws[p]), (dA, As[p]), (dB, Bs[p]))]
-        return (dX, None, None, None, *grads)
+        return (dX, None, None, None, None, *grads)
 
 
 def lora_linear_group(x: torch.Tensor, Ws: Sequence[torch.Tensor], As: Sequence[torch.Tensor],
                       Bs: Sequence[torch.Tensor], s: float, sinks=None,
-                      anchors: Tuple[torch.Tensor, ...] = ()) -> Tuple[torch.Tensor, ...]:
+                      anchors: Tuple[torch.Tensor, ...] = (),
+                      batch: Optional[AdapterGradBatch] = None) -> Tuple[torch.Tensor, ...]:
     """Functional form of LoRALinearGroupFunction (q|k|v or gate|up sharing one input)."""
     wab = []
     for W, A, B in zip(Ws, As, Bs):
         wab += [W, A, B]
-    return LoRALinearGroupFunction.apply(x, s, sinks, _Anchor(anchors, x), *wab)
+    return LoRALinearGroupFunction.apply(x, s, sinks, _Anchor(anchors, x), batch, *wab)
 
 
 def lora_linear(x: torch.Tensor, W: torch.Tensor, A: torch.Tensor, B: torch.Tensor, s: float,

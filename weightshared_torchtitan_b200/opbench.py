@@ -55,21 +55,41 @@ def bench_shape(M, N, K, r, iters, what="all", warmup=3):
         "dx": lambda: ops.lora_linear_bwd_dx([dY], [U], [W], [A]),
         "dw": lambda: ops.lora_linear_bwd_dw(dY, U, x, T, dW, dA, dB),
     }
+    # the backward through the layer's own weight gradient (what the autograd Function runs when
+    # the shared weight is trained): merged weight -> dX, dW with a bf16 copy, adapters from it
+    Weff = ops.lora_merge_weight([W], [A], [B], 2.0)[0]
+    G = ops.bwd_dw_layer_group([dY], x, [dW])
+    via_dw = {
+        "merge": lambda: ops.lora_merge_weight([W], [A], [B], 2.0),
+        "dx_merged": lambda: ops.lora_linear_bwd_dx([dY], [None], [Weff], [None]),
+        "dw_copy": lambda: ops.bwd_dw_layer_group([dY], x, [dW]),
+        "adapter_grads": lambda: ops.lora_adapter_grads_from_dw(G, [A], [B], [dA], [dB], 2.0),
+    }
     res = {"M": M, "N": N, "K": K, "r": r}
     if what != "all":
-        res[what + "_ms"] = time_ms(parts[what], iters, warmup)
+        res[what + "_ms"] = time_ms({**parts, **via_dw}[what], iters, warmup)
         return res
 
     def whole():
         for f in parts.values():
             f()
 
-    ms = {k: time_ms(f, iters, warmup) for k, f in parts.items()}
-    total = time_ms(whole, iters, warmup)
+    def whole_via_dw():
+        parts["prepass_T"]()
+        parts["fwd"]()
+        for f in via_dw.values():
+            f()
+
+    ms = {k: time_ms(f, iters, warmup) for k, f in {**parts, **via_dw}.items()}
+    total_direct = time_ms(whole, iters, warmup)
+    total = time_ms(whole_via_dw, iters, warmup)
     flops = 6.0 * M * N * K + 6.0 * M * r * (K + N)
     res.update({
         "total_ms": total, "tflops": flops / total / 1e9, "frac_of_2.25PF": flops / total / 1e9 / 2250.0,
+        "total_ms_direct": total_direct, "tflops_direct": flops / total_direct / 1e9,
         "ms": ms,
+        "dx_merged_tflops": 2.0 * M * K * N / ms["dx_merged"] / 1e9,
+        "dw_copy_tflops": 2.0 * M * N * K / ms["dw_copy"] / 1e9,
         "fwd_tflops": 2.0 * M * N * (K + r) / ms["fwd"] / 1e9,
         "dx_tflops": 2.0 * M * K * (N + r) / ms["dx"] / 1e9,
         "dw_tflops": 2.0 * M * (N * K + r * K + N * r) / ms["dw"] / 1e9,
@@ -88,7 +108,8 @@ def main():
     ap.add_argument("--r", type=int, default=64)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--what", default="all", choices=["all", "prepass_T", "fwd", "prepass_U", "dx", "dw"])
+    ap.add_argument("--what", default="all", choices=["all", "prepass_T", "fwd", "prepass_U", "dx", "dw", "merge",
+                                                      "dx_merged", "dw_copy", "adapter_grads"])
     ap.add_argument("--sweep-r", action="store_true", help="baseline config 3 sweep: r in {8,16,32,64,128}, M=32768")
     args = ap.parse_args()
     if args.sweep_r:

@@ -333,6 +333,9 @@ def lora_linear_bwd_dw_group(dYs, Us, x, Ts, dWs, dAs, dBs) -> None:
     _lib.check(st, "wsl_lora_linear_bwd_dw_group")
 
 
+MERGE_RANKS = (8, 16, 32, 64, 128)   # ranks wsl_lora_merge_weight is built for
+
+
 def lora_merge_weight(Ws, As, Bs, s: float) -> list:
     """W_eff_p = bf16(W_p + s B_p A_p) for projections with the same input width and rank, one
     launch."""
@@ -406,13 +409,16 @@ def bwd_dw_layer_group(dYs, x, dWs) -> list:
     return dWls
 
 
+MAX_ADAPTER_PROJ = 9   # WSL_MAX_ADAPTER_PROJ
+
+
 def lora_adapter_grads_from_dw(dWls, As, Bs, dAs, dBs, s: float) -> None:
-    """dA_p += s B_p.T @ dWl_p, dB_p += s dWl_p @ A_p.T (fp32, in place)."""
+    """dA_p += s B_p.T @ dWl_p, dB_p += s dWl_p @ A_p.T (fp32, in place) for up to
+    MAX_ADAPTER_PROJ projections of any sizes in two launches."""
     n = len(dWls)
     vp, ll = ctypes.c_void_p * n, ctypes.c_longlong * n
-    g_p, a_p, b_p, da_p, db_p, Ns, rs = vp(), vp(), vp(), vp(), vp(), ll(), ll()
+    g_p, a_p, b_p, da_p, db_p, Ns, Ks, rs = vp(), vp(), vp(), vp(), vp(), ll(), ll(), ll()
     keep = []
-    K = dWls[0].shape[1]
     flops = 0.0
     nbytes = 0.0
     for p in range(n):
@@ -421,6 +427,7 @@ def lora_adapter_grads_from_dw(dWls, As, Bs, dAs, dBs, s: float) -> None:
         if not G.is_contiguous():
             raise ValueError("dWl must be dense")
         N, r = B.shape
+        K = G.shape[1]
         if G.shape != (N, K) or A.shape != (r, K):
             raise ValueError("shapes of dWl, A, B do not fit")
         for gbuf, shape, nm in ((dAs[p], (r, K), "dA"), (dBs[p], (N, r), "dB")):
@@ -428,13 +435,13 @@ def lora_adapter_grads_from_dw(dWls, As, Bs, dAs, dBs, s: float) -> None:
                 raise ValueError(f"{nm} must be a contiguous float32 tensor of shape {shape}")
         keep += [G, A, B]
         g_p[p], a_p[p], b_p[p] = G.data_ptr(), A.data_ptr(), B.data_ptr()
-        da_p[p], db_p[p], Ns[p], rs[p] = dAs[p].data_ptr(), dBs[p].data_ptr(), N, r
+        da_p[p], db_p[p], Ns[p], Ks[p], rs[p] = dAs[p].data_ptr(), dBs[p].data_ptr(), N, K, r
         flops += 4.0 * N * K * r
         nbytes += 4.0 * N * K
-    ws_bytes = int(_lib.lib().wsl_adapter_grads_workspace_bytes(n, Ns, rs, K))
+    ws_bytes = int(_lib.lib().wsl_adapter_grads_workspace_bytes(n, Ns, Ks, rs))
     ws = torch.empty(ws_bytes // 4, device=dWls[0].device, dtype=torch.float32) if ws_bytes else None
     _e = _tic()
-    st = _lib.lib().wsl_lora_adapter_grads_from_dw(n, g_p, a_p, b_p, da_p, db_p, Ns, rs, K, float(s),
+    st = _lib.lib().wsl_lora_adapter_grads_from_dw(n, g_p, a_p, b_p, da_p, db_p, Ns, Ks, rs, float(s),
                                                    ws.data_ptr() if ws is not None else None, ws_bytes,
                                                    _stream())
     _toc(_e, "adapter_grads", flops, nbytes)
