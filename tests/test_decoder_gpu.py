@@ -155,13 +155,23 @@ def test_tiny_decoder_fp32_matches_reference_golden(golden_dir):
         assert rel(got, _t(g[key])) < 2e-4, (key, rel(got, _t(g[key])))
 
 
-def test_tiny_decoder_bf16_close_to_reference_golden(golden_dir):
+@pytest.mark.parametrize("through_layer_gradient", [False, True])
+def test_tiny_decoder_bf16_close_to_reference_golden(golden_dir, through_layer_gradient):
+    """bf16 decoder against the reference's fp32 gradients, with the backward of the projections
+    in its direct form (U = s dY B) and through the layer's own weight gradient (merged weight,
+    adapter gradients batched per layer)."""
+    from weightshared_torchtitan_b200 import functional as Fn
     g = np.load(os.path.join(golden_dir, "decoder_tiny.npz"))
     a, p, m = _build_tiny(torch.bfloat16)
     tokens, labels = _t(g["tokens"]).cuda(), _t(g["labels"]).cuda()
-    loss = m.loss(tokens, labels)
-    assert abs(loss.item() - float(g["loss"])) < 1e-2 * float(g["loss"])
-    loss.backward()
+    saved = Fn.DERIVED_ADAPTER_GRADS
+    Fn.DERIVED_ADAPTER_GRADS = through_layer_gradient
+    try:
+        loss = m.loss(tokens, labels)
+        assert abs(loss.item() - float(g["loss"])) < 1e-2 * float(g["loss"])
+        loss.backward()
+    finally:
+        Fn.DERIVED_ADAPTER_GRADS = saved
     for key in ("g.blocks.0.wq.weight", "g.blocks.1.w2.weight", "g.layers.0.wq.w_a", "g.layers.3.w2.w_b", "g.embed.P"):
         assert rel(_grad_of(m, key[2:]), _t(g[key])) < 6e-2, (key, rel(_grad_of(m, key[2:]), _t(g[key])))
 

@@ -610,6 +610,10 @@ def test_adapter_gradient_batch_across_groups(wsl, expected):
     batch = Fn.AdapterGradBatch(expected)
     xc = x.cuda().requires_grad_(True)
     outs, all_sinks, want, dYs_all = [], [], [], []
+    saved = Fn.DERIVED_ADAPTER_GRADS
+    Fn.DERIVED_ADAPTER_GRADS = True   # small shapes: force the formulation under test
+    launches = []
+    real = wsl.lora_adapter_grads_from_dw
     for Ns in groups:
         Ws = [(torch.randn(n, K, generator=g) * 0.03).to(bf) for n in Ns]
         As = [(torch.randn(r, K, generator=g) * 0.05).to(bf) for n in Ns]
@@ -623,7 +627,18 @@ def test_adapter_gradient_batch_across_groups(wsl, expected):
         outs += list(ys)
         dYs_all += [d.cuda() for d in dYs]
         all_sinks += sinks
-    torch.autograd.backward(outs, dYs_all)
+    Fn.DERIVED_ADAPTER_GRADS = saved
+
+    def counting(dWls, *a, **k):
+        launches.append(len(dWls))
+        return real(dWls, *a, **k)
+
+    wsl.lora_adapter_grads_from_dw = counting
+    try:
+        torch.autograd.backward(outs, dYs_all)
+    finally:
+        wsl.lora_adapter_grads_from_dw = real
+    assert launches == [3]          # all three projections of the two groups in ONE call
     assert not batch.pending
     assert rel(xc.grad, sum(w[1] for w in want)) < TOL_BF16
     for sk, w in zip(all_sinks, want):

@@ -31,11 +31,25 @@ def _flat(x: torch.Tensor) -> torch.Tensor:
 
 
 # When the shared weight is trained (dW wanted together with dA and dB, bf16), the backward
-# goes through the layer's own weight gradient G = dY^T x: dB = s G A^T, dA = s B^T G and
-# dX = dY (W + s B A). That reads the [N, K] matrix G instead of streaming the token rows
-# again for the two rank-r products, and needs no pre-pass over dY. False (or the environment
-# variable WSL_DERIVED_ADAPTER_GRADS=0) keeps the direct formulation with U = s dY B.
-DERIVED_ADAPTER_GRADS = os.environ.get("WSL_DERIVED_ADAPTER_GRADS", "1") != "0"
+# can go through the layer's own weight gradient G = dY^T x: dB = s G A^T, dA = s B^T G and
+# dX = dY (W + s B A). That reads [N, K] matrices (merge W, copy G) instead of streaming the
+# M token rows again (pre-pass over dY, rank-r regions of the weight-gradient launch), so it
+# pays when M is large against N K / (N + K): yes for decoder layers at 32 k tokens per step
+# (M = 32768, N K <= 3 M), no for an 8B-shape MLP projection at M = 16384 (N K = 50 M).
+# "auto" decides per projection group with the measured per-element costs below; True / False
+# (environment variable WSL_DERIVED_ADAPTER_GRADS=1 / 0) force one formulation where eligible.
+_env = os.environ.get("WSL_DERIVED_ADAPTER_GRADS", "auto")
+DERIVED_ADAPTER_GRADS = {"0": False, "1": True}.get(_env, "auto")
+# picoseconds per element, from CUDA-event timings on B200: merging W and copying G cost about
+# 7.5 ps per weight element (+ ~15 us of launches per group); the pre-pass U costs about 0.4 ps
+# per dY element and the rank-r regions about 0.37 ps per (dY + x) element.
+_PS_PER_WEIGHT, _PS_FIXED, _PS_PER_DY, _PS_PER_ROWSTREAM = 7.5, 15e6, 0.4, 0.37
+
+
+def _derived_pays(M: int, K: int, Ns) -> bool:
+    derived = _PS_FIXED + sum(_PS_PER_WEIGHT * n * K for n in Ns)
+    direct = sum(_PS_PER_DY * M * n + _PS_PER_ROWSTREAM * M * (n + K) for n in Ns)
+    return derived < direct
 
 
 class AdapterGradBatch:
@@ -106,9 +120,11 @@ class LoRALinearGroupFunction(torch.autograd.Function):
         else:
             for p in range(P):
                 ys.append(ops.lora_linear_fwd(x2, Ws[p], Ts[p], Bs[p]).view(*x.shape[:-1], Ws[p].shape[0]))
-        ctx.derived = (DERIVED_ADAPTER_GRADS and sinks is not None and x2.dtype == torch.bfloat16
+        ctx.derived = (DERIVED_ADAPTER_GRADS is not False and sinks is not None and x2.dtype == torch.bfloat16
                        and all(t[0] is not None and t[1] is not None and t[2] is not None for t in sinks)
-                       and all(A.shape[0] in ops.MERGE_RANKS for A in As))
+                       and all(A.shape[0] in ops.MERGE_RANKS for A in As)
+                       and (DERIVED_ADAPTER_GRADS is True
+                            or _derived_pays(x2.shape[0], x2.shape[1], [W.shape[0] for W in Ws])))
         ctx.save_for_backward(x2, None if ctx.derived else T_cat, *wab)
         ctx.s = float(s)
         ctx.sinks = sinks
