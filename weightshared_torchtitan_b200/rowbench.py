@@ -1,0 +1,85 @@
+"""Isolated benchmark of the row kernels either side of the projections (CUDA-event timing,
+L2 flushed by a read of a 256 MB buffer between iterations).
+
+    python -m weightshared_torchtitan_b200.rowbench                 # all kernels, 32768 tokens
+    python -m weightshared_torchtitan_b200.rowbench --what rmsnorm --iters 1 --tokens 8192
+
+Prints one JSON line per kernel and shape: microseconds and GB/s over the algorithmic bytes
+(RMSNorm forward 2 passes, backward 3; SwiGLU 3 / 5; cross-entropy 3). `--what` / `--iters`
+give the small single-launch runs that ncu captures are taken from.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import ops
+from .decoder import rope_tables
+
+
+def time_us(fn, iters, warmup=2):
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    total = 0.0
+    for _ in range(iters):
+        flush.sum()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters * 1e3
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=32768)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--what", default="all", choices=["all", "rmsnorm", "swiglu", "ce"])
+    args = ap.parse_args()
+    M, S = args.tokens, args.seq
+    bf = torch.bfloat16
+    if args.what in ("all", "rmsnorm"):
+        # hidden rows (configurations 1 and 2) and head rows with the rotary embedding (16 and 8 heads)
+        for rows, D, heads in [(M, 1024, 0), (M, 2048, 0), (M * 16, 128, 16), (M * 8, 128, 8)]:
+            x = torch.randn(rows, D, device="cuda").to(bf)
+            dy = torch.randn(rows, D, device="cuda").to(bf)
+            w = torch.ones(D, device="cuda")
+            dw = torch.zeros(D, device="cuda")
+            rope = None
+            if heads:
+                cos, sin = rope_tables(D, S, 1e6, "cuda")
+                rope = (cos.contiguous(), sin.contiguous(), heads, S)
+            _, rstd = ops.rmsnorm_fwd(x, w, 1e-6, rope)
+            tf = time_us(lambda: ops.rmsnorm_fwd(x, w, 1e-6, rope), args.iters, args.warmup)
+            tb = time_us(lambda: ops.rmsnorm_bwd(dy, x, w, rstd, dw, rope), args.iters, args.warmup)
+            nb = rows * D * 2
+            print(json.dumps({"kernel": "rmsnorm", "rows": rows, "D": D, "heads": heads,
+                              "fwd_us": tf, "fwd_gbs": 2 * nb / tf / 1e3,
+                              "bwd_us": tb, "bwd_gbs": 3 * nb / tb / 1e3}), flush=True)
+    if args.what in ("all", "swiglu"):
+        g = torch.randn(M, 3072, device="cuda").to(bf)
+        u = torch.randn(M, 3072, device="cuda").to(bf)
+        d = torch.randn(M, 3072, device="cuda").to(bf)
+        nb = g.numel() * 2
+        tf = time_us(lambda: ops.swiglu_fwd(g, u), args.iters, args.warmup)
+        tb = time_us(lambda: ops.swiglu_bwd(d, g, u), args.iters, args.warmup)
+        print(json.dumps({"kernel": "swiglu", "rows": M, "D": 3072, "fwd_us": tf, "fwd_gbs": 3 * nb / tf / 1e3,
+                          "bwd_us": tb, "bwd_gbs": 5 * nb / tb / 1e3}), flush=True)
+    if args.what in ("all", "ce"):
+        rows, V = min(M, 8192), 151936
+        logits = torch.randn(rows, V, device="cuda").to(bf)
+        labels = torch.randint(0, V, (rows,), device="cuda")
+        nb = logits.numel() * 2
+        t = time_us(lambda: ops.ce_fwd_bwd(logits, labels, 1.0 / rows), args.iters, args.warmup)
+        print(json.dumps({"kernel": "ce_fwd_bwd", "rows": rows, "V": V, "us": t, "gbs": 3 * nb / t / 1e3}), flush=True)
+
+
+if __name__ == "__main__":
+    main()
