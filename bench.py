@@ -165,7 +165,7 @@ def run_reference(args):
         "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ------------------------------------------------------------------------ our arm
@@ -230,9 +230,6 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
-        # NCCL's own log lines (e.g. its version banner) go to stderr: stdout carries only the
-        # one JSON line
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     _lib.lib()
     peaks = load_peaks()
@@ -361,10 +358,26 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
                                     "sample": "1 sequence x 256 tokens, all 28 layers + head, fwd+loss+bwd, "
                                               "fp32 eager oracle", "s_per_step": sec}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+_OUT_FD = 1
+
+
+def claim_stdout() -> None:
+    """File descriptor 1 carries the one JSON line and nothing else: whatever a library prints
+    to stdout from here on (NCCL's version banner, for one) is sent to stderr instead."""
+    global _OUT_FD
+    sys.stdout.flush()
+    _OUT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    os.write(_OUT_FD, (json.dumps(line) + "\n").encode())
 
 
 def main():
@@ -388,6 +401,7 @@ def main():
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.abspath(__file__)] + sys.argv[1:]
         raise SystemExit(subprocess.call(cmd))
+    claim_stdout()
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -644,3 +644,33 @@ def test_adapter_gradient_batch_across_groups(wsl, expected):
     for sk, w in zip(all_sinks, want):
         for got, ref in zip(sk, w[2:]):
             assert rel(got, ref) < TOL_BF16
+
+
+def test_empty_batch_launches_nothing(wsl):
+    """Zero tokens: outputs of the right shape, zero gradients, no kernel launch, sinks untouched."""
+    from weightshared_torchtitan_b200 import _lib
+    from weightshared_torchtitan_b200 import functional as Fn
+    bf = torch.bfloat16
+    K, r = 64, 8
+    Ns = (128, 64)
+    x = torch.zeros(0, K, device="cuda", dtype=bf, requires_grad=True)
+    Ws = [torch.randn(n, K, device="cuda").to(bf) for n in Ns]
+    As = [torch.randn(r, K, device="cuda").to(bf) for n in Ns]
+    Bs = [torch.randn(n, r, device="cuda").to(bf) for n in Ns]
+    sinks = [(torch.ones(n, K, device="cuda"), torch.ones(r, K, device="cuda"), torch.ones(n, r, device="cuda"))
+             for n in Ns]
+    before = _lib.launch_count()
+    ys = Fn.lora_linear_group(x, Ws, As, Bs, 2.0, sinks)
+    assert [tuple(y.shape) for y in ys] == [(0, n) for n in Ns]
+    torch.autograd.backward(list(ys), [torch.zeros_like(y) for y in ys])
+    assert x.grad.shape == (0, K)
+    w = torch.ones(K, device="cuda", requires_grad=True)
+    n = Fn.rmsnorm(x.detach().requires_grad_(True), w, 1e-6)
+    n.sum().backward()
+    assert n.shape == (0, K) and float(w.grad.abs().sum()) == 0.0
+    g = Fn.swiglu(x.detach().requires_grad_(True), x.detach())
+    g.sum().backward()
+    assert _lib.launch_count() == before
+    for t in sinks:
+        for buf in t:
+            assert float((buf - 1.0).abs().sum()) == 0.0

@@ -104,6 +104,12 @@ class LoRALinearGroupFunction(torch.autograd.Function):
         P = len(wab) // 3
         ctx.batch = batch
         Ws, As, Bs = list(wab[0::3]), list(wab[1::3]), list(wab[2::3])
+        ctx.empty = x.numel() == 0
+        if ctx.empty:
+            # no tokens: nothing to launch, every gradient contribution is zero
+            ctx.P, ctx.x_shape, ctx.sinks = P, x.shape, sinks
+            ctx.save_for_backward(*wab)
+            return tuple(x.new_zeros(*x.shape[:-1], W.shape[0]) for W in Ws)
         x2 = _flat(x)
         if not x2.is_contiguous() and x2.stride(-1) != 1:
             x2 = x2.contiguous()
@@ -134,6 +140,14 @@ class LoRALinearGroupFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *dYs):
+        if ctx.empty:
+            wab = ctx.saved_tensors
+            dX = wab[0].new_zeros(ctx.x_shape) if ctx.needs_input_grad[0] else None
+            grads = [None] * (3 * ctx.P)
+            if ctx.sinks is None:
+                grads = [torch.zeros_like(w) if need else None
+                         for w, need in zip(wab, ctx.needs_input_grad[5:])]
+            return (dX, None, None, None, None, *grads)
         x2, T_cat, *wab = ctx.saved_tensors
         P = ctx.P
         Ws, As, Bs = list(wab[0::3]), list(wab[1::3]), list(wab[2::3])
@@ -342,11 +356,15 @@ class SwiGLUFunction(torch.autograd.Function):
     def forward(ctx, gate, up):
         gate, up = gate.contiguous(), up.contiguous()
         ctx.save_for_backward(gate, up)
+        if gate.numel() == 0:
+            return torch.empty_like(gate)
         return ops.swiglu_fwd(gate, up)
 
     @staticmethod
     def backward(ctx, dout):
         gate, up = ctx.saved_tensors
+        if gate.numel() == 0:
+            return torch.empty_like(gate), torch.empty_like(up)
         return ops.swiglu_bwd(dout, gate, up)
 
 
@@ -367,7 +385,10 @@ class RMSNormFunction(torch.autograd.Function):
     def forward(ctx, x, w, eps, rope, sink):
         D = x.shape[-1]
         x2 = x.reshape(-1, D)
-        y, rstd = ops.rmsnorm_fwd(x2, w, eps, rope)
+        if x2.shape[0] == 0:
+            y, rstd = torch.empty_like(x2), x2.new_empty(0, dtype=torch.float32)
+        else:
+            y, rstd = ops.rmsnorm_fwd(x2, w, eps, rope)
         ctx.save_for_backward(x2, w, rstd)
         ctx.rope = rope
         ctx.sink = sink
@@ -378,6 +399,9 @@ class RMSNormFunction(torch.autograd.Function):
     def backward(ctx, dy):
         x2, w, rstd = ctx.saved_tensors
         D = x2.shape[-1]
+        if x2.shape[0] == 0:
+            dw0 = torch.zeros_like(w) if ctx.sink is None and ctx.needs_input_grad[1] else None
+            return torch.empty_like(x2).view(ctx.shape), dw0, None, None, None
         dy2 = dy.reshape(-1, D)
         if dy2.stride(-1) != 1:
             dy2 = dy2.contiguous()
