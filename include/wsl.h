@@ -330,6 +330,23 @@ int wsl_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long ldx
                     long long D, const float* rope_cos, const float* rope_sin, long long heads,
                     long long seq, int dtype, void* stream);
 
+/*
+ * The residual add that precedes a hidden-size RMSNorm, and its mirror image in the backward,
+ * folded into the norm kernels (dense rows, no rotary):
+ *   forward : h = x + res (rounded to the storage type and written out), y = RMSNorm(h) * w
+ *   backward: dx = dRMSNorm(dy; h, w, rstd) + dres, dw += ...   (dres = the gradient that
+ *             reaches h through the residual stream; dx is the gradient of both x and res)
+ * One pass over memory less each way than an add kernel followed by the norm kernel.
+ * Replaces `h = h + self.attention(...)`, `out = h + self.feed_forward(self.ffn_norm(h))` and
+ * the norm that reads the sum: torchtitan/experiments/qwen3/model/model.py:310-313.
+ * Widths as wsl_rmsnorm_fwd; rows dense with pitch D.
+ */
+int wsl_add_rmsnorm_fwd(const void* x, const void* res, const float* w, void* h, void* y, float* rstd,
+                        long long rows, long long D, float eps, int dtype, void* stream);
+int wsl_add_rmsnorm_bwd(const void* dy, const void* h, const void* dres, const float* w,
+                        const float* rstd, void* dx, float* dw, long long rows, long long D,
+                        int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -173,3 +173,41 @@ def test_rmsnorm_strided_rows_take_the_direct_kernel():
     # two kernels, two summation orders: equal up to the bf16 rounding of y and dx
     assert rel(dx_s, dx_d) < 1e-2
     assert rel(dw_s, dw_d) < 1e-4
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-5), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("D,rows", [(1024, 333), (2048, 5_003), (256, 40_001), (64, 77)])
+def test_residual_add_folded_into_the_norm(dtype, tol, D, rows):
+    """h = x + res and y = RMSNorm(h) in one kernel; the backward adds the gradient of the
+    residual stream to the norm's dx. Against the same three steps in fp32 PyTorch; h must be
+    exactly the sum rounded once."""
+    from weightshared_torchtitan_b200 import ops
+    from weightshared_torchtitan_b200.functional import add_rmsnorm
+    if not ops.rmsnorm_supported(D, dtype):
+        pytest.skip("width not covered in this dtype")
+    g = torch.Generator().manual_seed(D + rows)
+    x = torch.randn(rows, D, generator=g).to(dtype)
+    res = torch.randn(rows, D, generator=g).to(dtype)
+    w = 1.0 + 0.2 * torch.randn(D, generator=g)
+    dh = torch.randn(rows, D, generator=g).to(dtype)
+    dy = torch.randn(rows, D, generator=g).to(dtype)
+    xr, rr, wr = leaf(x, "cuda", dtype=torch.float32), leaf(res, "cuda", dtype=torch.float32), leaf(w, "cuda")
+    hr = (xr + rr).to(dtype).float()          # the rounding an add kernel applies
+    hr_exact = xr + rr
+    yr = F.rms_norm(hr_exact, (D,), wr, 1e-6)
+    torch.autograd.backward([hr_exact, yr], [dh.cuda().float(), dy.cuda().float()])
+    xc, rc, wc = leaf(x, "cuda"), leaf(res, "cuda"), leaf(w, "cuda")
+    h, y = add_rmsnorm(xc, rc, wc, 1e-6)
+    torch.autograd.backward([h, y], [dh.cuda(), dy.cuda()])
+    assert torch.equal(h.float(), hr)
+    assert rel(y, yr) < tol
+    assert rel(xc.grad, xr.grad) < tol and torch.equal(xc.grad, rc.grad)
+    assert rel(wc.grad, wr.grad) < tol
+    # only y used downstream: the residual-stream gradient is absent
+    xc2, rc2 = leaf(x, "cuda"), leaf(res, "cuda")
+    sink = torch.zeros(D, device="cuda")
+    _, y2 = add_rmsnorm(xc2, rc2, wc.detach(), 1e-6, sink)
+    y2.backward(dy.cuda())
+    xr2, rr2 = leaf(x, "cuda", dtype=torch.float32), leaf(res, "cuda", dtype=torch.float32)
+    F.rms_norm(xr2 + rr2, (D,), wr.detach(), 1e-6).backward(dy.cuda().float())
+    assert rel(xc2.grad, xr2.grad) < tol

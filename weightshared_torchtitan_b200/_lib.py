@@ -60,6 +60,8 @@ SIGNATURES = {
     "wsl_swiglu_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _ll, _i, _vp]),
     "wsl_rmsnorm_fwd": (_i, [_vp, _ll, _vp, _vp, _ll, _vp, _ll, _ll, _f, _vp, _vp, _ll, _ll, _i, _vp]),
     "wsl_rmsnorm_bwd": (_i, [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _i, _vp]),
+    "wsl_add_rmsnorm_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _f, _i, _vp]),
+    "wsl_add_rmsnorm_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _vp]),
     "wsl_embed_fwd": (_i, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _vp]),
     "wsl_embed_bwd_dproj": (_i, [_vp, _vp, _ll, _vp, _vp, _ll, _ll, _ll, _ll, _vp, ctypes.c_ulonglong, _vp]),
     "wsl_embed_gather": (_i, [_vp, _vp, _vp, _ll, _ll, _ll, _i, _vp]),

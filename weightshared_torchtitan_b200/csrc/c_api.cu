@@ -626,7 +626,22 @@ int wsl_rmsnorm_fwd(const void* x, long long ldx, const float* w, void* y, long 
                     long long rows, long long D, float eps, const float* rope_cos,
                     const float* rope_sin, long long heads, long long seq, int dtype, void* stream) {
   if (bad_dtype(dtype)) return WSL_ERR_BAD_ARG;
-  return launch_rmsnorm_fwd(x, ldx, w, y, ldy, rstd, rows, D, eps, rope_cos, rope_sin, heads, seq,
+  return launch_rmsnorm_fwd(x, ldx, nullptr, nullptr, w, y, ldy, rstd, rows, D, eps, rope_cos, rope_sin,
+                            heads, seq, dtype == WSL_F32, static_cast<cudaStream_t>(stream));
+}
+
+int wsl_add_rmsnorm_fwd(const void* x, const void* res, const float* w, void* h, void* y, float* rstd,
+                        long long rows, long long D, float eps, int dtype, void* stream) {
+  if (bad_dtype(dtype) || !res || !h) return WSL_ERR_BAD_ARG;
+  return launch_rmsnorm_fwd(x, D, res, h, w, y, D, rstd, rows, D, eps, nullptr, nullptr, 0, 0,
+                            dtype == WSL_F32, static_cast<cudaStream_t>(stream));
+}
+
+int wsl_add_rmsnorm_bwd(const void* dy, const void* h, const void* dres, const float* w,
+                        const float* rstd, void* dx, float* dw, long long rows, long long D,
+                        int dtype, void* stream) {
+  if (bad_dtype(dtype) || !dres) return WSL_ERR_BAD_ARG;
+  return launch_rmsnorm_bwd(dy, D, h, D, dres, w, rstd, dx, D, dw, rows, D, nullptr, nullptr, 0, 0,
                             dtype == WSL_F32, static_cast<cudaStream_t>(stream));
 }
 
@@ -635,7 +650,7 @@ int wsl_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long ldx
                     long long D, const float* rope_cos, const float* rope_sin, long long heads,
                     long long seq, int dtype, void* stream) {
   if (bad_dtype(dtype)) return WSL_ERR_BAD_ARG;
-  return launch_rmsnorm_bwd(dy, lddy, x, ldx, w, rstd, dx, lddx, dw, rows, D, rope_cos, rope_sin,
+  return launch_rmsnorm_bwd(dy, lddy, x, ldx, nullptr, w, rstd, dx, lddx, dw, rows, D, rope_cos, rope_sin,
                             heads, seq, dtype == WSL_F32, static_cast<cudaStream_t>(stream));
 }
 

@@ -509,9 +509,12 @@ static int rms_check(const void* x, long long ldx, long long rows, long long D, 
   return WSL_OK;
 }
 
-int launch_rmsnorm_fwd(const void* x, long long ldx, const float* w, void* y, long long ldy,
-                       float* rstd, long long rows, long long D, float eps, const float* cs,
-                       const float* sn, long long heads, long long seq, int is_f32, cudaStream_t s) {
+// res / h_out: optional residual addend and sum output (dense [rows, D]); then the rows that
+// are normalised are h = x + res. Only the staged kernel does that: rows must be dense.
+int launch_rmsnorm_fwd(const void* x, long long ldx, const void* res, void* h_out, const float* w,
+                       void* y, long long ldy, float* rstd, long long rows, long long D, float eps,
+                       const float* cs, const float* sn, long long heads, long long seq, int is_f32,
+                       cudaStream_t s) {
   int st = device_check();
   if (st != WSL_OK) return st;
   st = rms_check(x, ldx, rows, D, is_f32, cs, sn, heads, seq);
@@ -526,44 +529,54 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const float* w, void* y, lo
   const unsigned gb = static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block);
   const int d = static_cast<int>(D), h = static_cast<int>(heads), sq = static_cast<int>(seq);
   const int kvn = static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
-  if (row_staged_enabled() && ldx == D && (!cs || (heads % 4 == 0 && aligned16(cs) && aligned16(sn)))) {
+  const bool fused = res != nullptr;
+  if (fused && (cs || !h_out || ldx != D || !aligned16(res) || !aligned16(h_out))) return WSL_ERR_BAD_ARG;
+  if ((fused || row_staged_enabled()) && ldx == D &&
+      (!cs || (heads % 4 == 0 && aligned16(cs) && aligned16(sn)))) {
     // rotary rows: two half-row vectors per lane (the staged kernels' layout), else as above
     const int kvn = cs ? 2 : static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
     const int lpr = cs ? static_cast<int>(D / (2 * (is_f32 ? 4 : 8))) : rms_lanes(D, is_f32 ? 4 : 8);
     const long long tile_rows = static_cast<long long>(RN_WARPS) * (32 / lpr) * (8 / kvn);
     const long long n_tiles = (rows + tile_rows - 1) / tile_rows;
     const unsigned sgb = static_cast<unsigned>(n_tiles < device_sm_count() ? n_tiles : device_sm_count());
-    const size_t ssmem = rn_fwd_staged_smem(d);
-#define WSL_RNFS(T, R, KVN)                                                                        \
+    const size_t ssmem = rn_fwd_staged_smem(d, fused);
+#define WSL_RNFS(T, R, KVN, RES)                                                                   \
   do {                                                                                             \
     static bool attr_set = false;                                                                  \
     if (!attr_set) {                                                                               \
-      if (cudaFuncSetAttribute(rmsnorm_fwd_staged_kernel<T, R, KVN>,                               \
+      if (cudaFuncSetAttribute(rmsnorm_fwd_staged_kernel<T, R, KVN, RES>,                          \
                                cudaFuncAttributeMaxDynamicSharedMemorySize,                        \
-                               static_cast<int>(rn_fwd_staged_smem(2048))) != cudaSuccess)         \
+                               static_cast<int>(rn_fwd_staged_smem(2048, RES))) != cudaSuccess)    \
         return WSL_ERR_CUDA;                                                                       \
       attr_set = true;                                                                             \
     }                                                                                              \
-    rmsnorm_fwd_staged_kernel<T, R, KVN><<<sgb, (RN_WARPS + 1) * 32, ssmem, s>>>(                  \
-        static_cast<const T*>(x), w, static_cast<T*>(y), ldy, rstd, rows, d, lpr, eps, cs, sn, h,  \
-        sq, n_tiles);                                                                              \
+    rmsnorm_fwd_staged_kernel<T, R, KVN, RES><<<sgb, (RN_WARPS + 1) * 32, ssmem, s>>>(             \
+        static_cast<const T*>(x), static_cast<const T*>(res), static_cast<T*>(h_out), w,           \
+        static_cast<T*>(y), ldy, rstd, rows, d, lpr, eps, cs, sn, h, sq, n_tiles);                 \
+  } while (0)
+#define WSL_RNFS_RES(T, KVN)                                      \
+  do {                                                            \
+    if (fused) WSL_RNFS(T, false, KVN, true);                     \
+    else WSL_RNFS(T, false, KVN, false);                          \
   } while (0)
 #define WSL_RNFS_KV(T)                                            \
   do {                                                            \
-    if (cs) WSL_RNFS(T, true, 2);                                 \
-    else if (kvn == 1) WSL_RNFS(T, false, 1);                     \
-    else if (kvn == 2) WSL_RNFS(T, false, 2);                     \
-    else if (kvn == 4) WSL_RNFS(T, false, 4);                     \
-    else if (kvn == 8) WSL_RNFS(T, false, 8);                     \
+    if (cs) WSL_RNFS(T, true, 2, false);                          \
+    else if (kvn == 1) WSL_RNFS_RES(T, 1);                        \
+    else if (kvn == 2) WSL_RNFS_RES(T, 2);                        \
+    else if (kvn == 4) WSL_RNFS_RES(T, 4);                        \
+    else if (kvn == 8) WSL_RNFS_RES(T, 8);                        \
     else return WSL_ERR_TOO_LARGE;                                \
   } while (0)
     if (is_f32) WSL_RNFS_KV(float); else WSL_RNFS_KV(__nv_bfloat16);
 #undef WSL_RNFS_KV
+#undef WSL_RNFS_RES
 #undef WSL_RNFS
     if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
     ++g_launch_count;
     return WSL_OK;
   }
+  if (fused) return WSL_ERR_BAD_ARG;   // the direct kernel has no residual input
 #define WSL_RN(T, R, KVN)                                                                          \
   rmsnorm_fwd_kernel<T, R, KVN><<<gb, RN_WARPS * 32, 0, s>>>(                                      \
       static_cast<const T*>(x), ldx, w, static_cast<T*>(y), ldy, rstd, rows, d, lpr, eps, cs, sn, \
@@ -585,9 +598,11 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const float* w, void* y, lo
   return WSL_OK;
 }
 
-int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long ldx, const float* w,
-                       const float* rstd, void* dx, long long lddx, float* dw, long long rows,
-                       long long D, const float* cs, const float* sn, long long heads,
+// dres: optional gradient of the residual stream (dense [rows, D]) that is added to dx. Only
+// the staged kernel does that: rows must be dense.
+int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long ldx, const void* dres,
+                       const float* w, const float* rstd, void* dx, long long lddx, float* dw,
+                       long long rows, long long D, const float* cs, const float* sn, long long heads,
                        long long seq, int is_f32, cudaStream_t s) {
   int st = device_check();
   if (st != WSL_OK) return st;
@@ -609,7 +624,9 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
   const size_t smem = static_cast<size_t>(D) * sizeof(float);
   const int kvn = static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
   // contiguous rows take the staged kernel (bulk copies need 16-byte aligned, dense tiles)
-  if (row_staged_enabled() && lddy == D && ldx == D &&
+  const bool fused = dres != nullptr;
+  if (fused && (cs || lddy != D || ldx != D || !aligned16(dres))) return WSL_ERR_BAD_ARG;
+  if ((fused || row_staged_enabled()) && lddy == D && ldx == D &&
       (!cs || (heads % 4 == 0 && aligned16(cs) && aligned16(sn)))) {
     // rotary rows: two half-row vectors per lane (the staged kernels' layout), else as above
     const int kvn = cs ? 2 : static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
@@ -619,37 +636,44 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
     const long long tile_rows = static_cast<long long>(cw) * (32 / lpr) * rpg;
     const long long n_tiles = (rows + tile_rows - 1) / tile_rows;
     const unsigned sgb = static_cast<unsigned>(n_tiles < device_sm_count() ? n_tiles : device_sm_count());
-    const size_t ssmem = rn_staged_smem(d);
-#define WSL_RNS(T, R, KVN)                                                                         \
+    const size_t ssmem = rn_staged_smem(d, fused);
+#define WSL_RNS(T, R, KVN, DRES)                                                                   \
   do {                                                                                             \
     static bool attr_set = false;                                                                  \
     if (!attr_set) {                                                                               \
-      if (cudaFuncSetAttribute(rmsnorm_bwd_staged_kernel<T, R, KVN>,                               \
+      if (cudaFuncSetAttribute(rmsnorm_bwd_staged_kernel<T, R, KVN, DRES>,                         \
                                cudaFuncAttributeMaxDynamicSharedMemorySize,                        \
-                               static_cast<int>(rn_staged_smem(2048))) != cudaSuccess)             \
+                               static_cast<int>(rn_staged_smem(2048, DRES))) != cudaSuccess)       \
         return WSL_ERR_CUDA;                                                                       \
       attr_set = true;                                                                             \
     }                                                                                              \
-    rmsnorm_bwd_staged_kernel<T, R, KVN><<<sgb, (cw + 1) * 32, ssmem, s>>>(                           \
-        static_cast<const T*>(dy), static_cast<const T*>(x), w, rstd, static_cast<T*>(dx), lddx,   \
-        dw, rows, d, lpr, cs, sn, h, sq, n_tiles);                                                 \
+    rmsnorm_bwd_staged_kernel<T, R, KVN, DRES><<<sgb, (cw + 1) * 32, ssmem, s>>>(                  \
+        static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(dres), w, rstd, \
+        static_cast<T*>(dx), lddx, dw, rows, d, lpr, cs, sn, h, sq, n_tiles);                      \
+  } while (0)
+#define WSL_RNS_RES(T, KVN)                                       \
+  do {                                                            \
+    if (fused) WSL_RNS(T, false, KVN, true);                      \
+    else WSL_RNS(T, false, KVN, false);                           \
   } while (0)
 #define WSL_RNS_KV(T)                                             \
   do {                                                            \
-    if (cs) WSL_RNS(T, true, 2);                                  \
-    else if (kvn == 1) WSL_RNS(T, false, 1);                      \
-    else if (kvn == 2) WSL_RNS(T, false, 2);                      \
-    else if (kvn == 4) WSL_RNS(T, false, 4);                      \
-    else if (kvn == 8) WSL_RNS(T, false, 8);                      \
+    if (cs) WSL_RNS(T, true, 2, false);                           \
+    else if (kvn == 1) WSL_RNS_RES(T, 1);                         \
+    else if (kvn == 2) WSL_RNS_RES(T, 2);                         \
+    else if (kvn == 4) WSL_RNS_RES(T, 4);                         \
+    else if (kvn == 8) WSL_RNS_RES(T, 8);                         \
     else return WSL_ERR_TOO_LARGE;                                \
   } while (0)
     if (is_f32) WSL_RNS_KV(float); else WSL_RNS_KV(__nv_bfloat16);
 #undef WSL_RNS_KV
+#undef WSL_RNS_RES
 #undef WSL_RNS
     if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
     ++g_launch_count;
     return WSL_OK;
   }
+  if (fused) return WSL_ERR_BAD_ARG;   // the direct kernel has no residual-gradient input
 #define WSL_RNB(T, R, KVN)                                                                         \
   rmsnorm_bwd_kernel<T, R, KVN><<<gb, RN_WARPS * 32, smem, s>>>(                                   \
       static_cast<const T*>(dy), lddy, static_cast<const T*>(x), ldx, w, rstd, static_cast<T*>(dx), \

@@ -23,8 +23,8 @@
 
 namespace wsl {
 
-constexpr int RN_STAGES = 3;        // backward: stages of two operand tiles
-constexpr int RN_FWD_STAGES = 6;    // forward: stages of one tile
+// stages of the ring: as many as fit next to the scale copies, by operand tiles per stage
+__host__ __device__ constexpr int rn_stages(int nops) { return nops == 1 ? 6 : (nops == 2 ? 3 : 2); }
 constexpr int RN_TILE_BYTES = 32768;
 constexpr unsigned long long RN_WAIT_LIMIT_NS = 2000000000ull;
 
@@ -39,11 +39,12 @@ __host__ __device__ constexpr int rn_compute_warps(int elems_per_lane, bool rope
 __host__ __device__ constexpr size_t rn_head_bytes(int stages, int nops) {
   return static_cast<size_t>(stages) * nops * RN_TILE_BYTES + 2 * stages * sizeof(uint64_t) + 16;
 }
-__host__ __device__ constexpr size_t rn_staged_smem(int D) {
-  return rn_head_bytes(RN_STAGES, 2) + 2 * static_cast<size_t>(D) * sizeof(float);
+// backward: dy, x (+ the gradient of the residual stream); forward: x (+ the residual addend)
+__host__ __device__ constexpr size_t rn_staged_smem(int D, bool dres) {
+  return rn_head_bytes(rn_stages(dres ? 3 : 2), dres ? 3 : 2) + 2 * static_cast<size_t>(D) * sizeof(float);
 }
-__host__ __device__ constexpr size_t rn_fwd_staged_smem(int D) {
-  return rn_head_bytes(RN_FWD_STAGES, 1) + static_cast<size_t>(D) * sizeof(float);
+__host__ __device__ constexpr size_t rn_fwd_staged_smem(int D, bool res) {
+  return rn_head_bytes(rn_stages(res ? 2 : 1), res ? 2 : 1) + static_cast<size_t>(D) * sizeof(float);
 }
 
 template <typename T>
@@ -113,7 +114,7 @@ __device__ __forceinline__ void load_scale(const float* w_s, int k, int lpr, int
 // set the abort flag, and then waits (bounded) for the copies it had already asked for.
 template <int NOPS, int STAGES>
 __device__ __forceinline__ void rn_producer_loop(const unsigned char* src0, const unsigned char* src1,
-                                                 size_t row_bytes, int tile_rows, long long rows,
+                                                 const unsigned char* src2, size_t row_bytes, int tile_rows, long long rows,
                                                  int my_tiles, uint32_t stage0, uint32_t bar0,
                                                  volatile int* abortp, volatile int* drainp, int lane) {
   int issued = 0;
@@ -133,6 +134,7 @@ __device__ __forceinline__ void rn_producer_loop(const unsigned char* src0, cons
       mbar_arrive_expect_tx(bar0 + 8u * s, NOPS * bytes);
       bulk_load_1d(dst, src0 + r0 * row_bytes, bytes, bar0 + 8u * s);
       if (NOPS > 1) bulk_load_1d(dst + RN_TILE_BYTES, src1 + r0 * row_bytes, bytes, bar0 + 8u * s);
+      if (NOPS > 2) bulk_load_1d(dst + 2 * RN_TILE_BYTES, src2 + r0 * row_bytes, bytes, bar0 + 8u * s);
     }
     __syncwarp();
     ++issued;
@@ -164,22 +166,27 @@ __device__ __forceinline__ void zero_missing_rows(unsigned char* tile, int g, in
 // y = n * cos + rotate_half(n) * sin with n = x * rstd * w is evaluated as
 // rstd * (x[j] * (w[j] cos[j]) + x[p] * (w[p] sin'[j])), p = j +- D/2 the rotate_half partner
 // of j and sin' = -sin in the first half: the two coefficient vectors are built once per tile.
-template <typename T, bool ROPE, int KV>
+// RES: the row that is normalised is h = x + res (the residual add that precedes the norm),
+// rounded to the storage type exactly as a separate add kernel would, and also written out.
+template <typename T, bool ROPE, int KV, bool RES>
 __global__ void __launch_bounds__((RN_WARPS + 1) * 32, 1)
-rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
+rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T* __restrict__ h_out,
+                          const float* __restrict__ w, T* __restrict__ y,
                           long long ldy, float* __restrict__ rstd_out, long long rows, int D, int lpr,
                           float eps, const float* __restrict__ cs, const float* __restrict__ sn,
                           int heads, int seq, long long n_tiles) {
+  static_assert(!(ROPE && RES), "the residual add precedes hidden-size norms only");
   constexpr int NV = Vec<T>::N;
   constexpr int RPG = 8 / KV;
   constexpr int CW = RN_WARPS;
   constexpr int THREADS = (CW + 1) * 32;
-  constexpr int S = RN_FWD_STAGES;
+  constexpr int NOPS = RES ? 2 : 1;
+  constexpr int S = rn_stages(NOPS);
   extern __shared__ __align__(128) unsigned char rn_smem[];
-  uint64_t* bars = reinterpret_cast<uint64_t*>(rn_smem + S * RN_TILE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(rn_smem + S * NOPS * RN_TILE_BYTES);
   volatile int* abortp = reinterpret_cast<volatile int*>(bars + 2 * S);
   volatile int* drainp = abortp + 1;   // stays 0: the flag of the tear-down waits
-  float* w_s = reinterpret_cast<float*>(rn_smem + rn_head_bytes(S, 1));
+  float* w_s = reinterpret_cast<float*>(rn_smem + rn_head_bytes(S, NOPS));
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int rpw = 32 / lpr;
@@ -201,8 +208,9 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const float* __restrict__ w, 
   const int my_tiles = static_cast<int>((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
   const size_t row_bytes = static_cast<size_t>(D) * sizeof(T);
   if (warp == CW) {
-    rn_producer_loop<1, S>(reinterpret_cast<const unsigned char*>(x), nullptr, row_bytes, tile_rows,
-                           rows, my_tiles, stage0, bar0, abortp, drainp, lane);
+    rn_producer_loop<NOPS, S>(reinterpret_cast<const unsigned char*>(x),
+                              reinterpret_cast<const unsigned char*>(res), nullptr, row_bytes, tile_rows,
+                              rows, my_tiles, stage0, bar0, abortp, drainp, lane);
     return;
   }
   const float inv_D = 1.0f / static_cast<float>(D);
@@ -248,13 +256,17 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const float* __restrict__ w, 
       if (lane == 0) record_timeout(4, i);
       break;
     }
-    unsigned char* sx = rn_smem + static_cast<size_t>(s) * RN_TILE_BYTES;
+    unsigned char* sx = rn_smem + static_cast<size_t>(s) * NOPS * RN_TILE_BYTES;
     const long long row0 = (blockIdx.x + static_cast<long long>(i) * gridDim.x) * tile_rows +
                            static_cast<long long>(g) * RPG;
     const int have = static_cast<int>(min(static_cast<long long>(RPG), max(rows - row0, 0ll)));
-    if (have < RPG) zero_missing_rows<T, KV>(sx, g, RPG, have, row_bytes, lpr, l);
+    if (have < RPG) {
+      zero_missing_rows<T, KV>(sx, g, RPG, have, row_bytes, lpr, l);
+      if (RES) zero_missing_rows<T, KV>(sx + RN_TILE_BYTES, g, RPG, have, row_bytes, lpr, l);
+    }
     const unsigned char* srow = sx + static_cast<size_t>(g * RPG) * row_bytes + static_cast<size_t>(l) * NV * sizeof(T);
     T* yrow = y + row0 * ldy + l * NV;
+    T* hrow = RES ? h_out + row0 * D + l * NV : nullptr;
 #pragma unroll
     for (int r = 0; r < RPG; ++r) {
       float f[KV][NV];
@@ -263,6 +275,15 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const float* __restrict__ w, 
       for (int k = 0; k < KV; ++k) {
         const Vec<T> v = ldv<T>(reinterpret_cast<const T*>(srow + r * row_bytes) + k * lpr * NV);
         unpack<T>(v, f[k]);
+        if (RES) {
+          float a[NV];
+          unpack<T>(ldv<T>(reinterpret_cast<const T*>(srow + RN_TILE_BYTES + r * row_bytes) + k * lpr * NV), a);
+#pragma unroll
+          for (int e = 0; e < NV; ++e) f[k][e] += a[e];
+          const Vec<T> hv = pack<T>(f[k]);
+          if (r < have) stv<T>(hrow + static_cast<long long>(r) * D + k * lpr * NV, hv);
+          unpack<T>(hv, f[k]);   // normalise the value that was stored
+        }
 #pragma unroll
         for (int e = 0; e < NV; ++e) ss = fmaf(f[k][e], f[k][e], ss);
       }
@@ -295,11 +316,13 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const float* __restrict__ w, 
 }
 
 // -------------------------------------------------------------------------- backward
+// DRES: dx also receives dres, the gradient that reaches the same tensor through the residual
+// stream (the add that autograd would otherwise run as a kernel of its own).
 // dx = rstd * w * dn - x * rstd^3 * mean(dn * w * x), dn = un-rotated dy;
 // dw[j] += sum_rows dn[j] * x[j] * rstd (registers -> shared-memory partials -> atomics).
-template <typename T, bool ROPE, int KV>
+template <typename T, bool ROPE, int KV, bool DRES>
 __global__ void __launch_bounds__((rn_compute_warps(KV * Vec<T>::N, ROPE) + 1) * 32, 1)
-rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ dres,
                           const float* __restrict__ w, const float* __restrict__ rstd_in,
                           T* __restrict__ dx, long long lddx, float* dw, long long rows, int D, int lpr,
                           const float* __restrict__ cs, const float* __restrict__ sn, int heads,
@@ -308,12 +331,14 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x,
   constexpr int RPG = 8 / KV;
   constexpr int CW = rn_compute_warps(KV * NV, ROPE);
   constexpr int THREADS = (CW + 1) * 32;
-  constexpr int S = RN_STAGES;
+  constexpr int NOPS = DRES ? 3 : 2;
+  constexpr int S = rn_stages(NOPS);
+  static_assert(!(ROPE && DRES), "the residual stream meets hidden-size norms only");
   extern __shared__ __align__(128) unsigned char rn_smem[];
-  uint64_t* bars = reinterpret_cast<uint64_t*>(rn_smem + S * 2 * RN_TILE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(rn_smem + S * NOPS * RN_TILE_BYTES);
   volatile int* abortp = reinterpret_cast<volatile int*>(bars + 2 * S);
   volatile int* drainp = abortp + 1;
-  float* w_s = reinterpret_cast<float*>(rn_smem + rn_head_bytes(S, 2));
+  float* w_s = reinterpret_cast<float*>(rn_smem + rn_head_bytes(S, NOPS));
   float* dw_part = w_s + D;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -340,9 +365,10 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x,
   const size_t row_bytes = static_cast<size_t>(D) * sizeof(T);
 
   if (warp == CW) {
-    rn_producer_loop<2, S>(reinterpret_cast<const unsigned char*>(dy),
-                           reinterpret_cast<const unsigned char*>(x), row_bytes, tile_rows, rows,
-                           my_tiles, stage0, bar0, abortp, drainp, lane);
+    rn_producer_loop<NOPS, S>(reinterpret_cast<const unsigned char*>(dy),
+                              reinterpret_cast<const unsigned char*>(x),
+                              reinterpret_cast<const unsigned char*>(dres), row_bytes, tile_rows, rows,
+                              my_tiles, stage0, bar0, abortp, drainp, lane);
   } else {
     const float inv_D = 1.0f / static_cast<float>(D);
     const int g = warp * rpw + lane / lpr;
@@ -400,14 +426,16 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x,
         if (lane == 0) record_timeout(4, i);
         break;
       }
-      unsigned char* sdy = rn_smem + static_cast<size_t>(s) * 2 * RN_TILE_BYTES;
+      unsigned char* sdy = rn_smem + static_cast<size_t>(s) * NOPS * RN_TILE_BYTES;
       unsigned char* sx = sdy + RN_TILE_BYTES;
+      unsigned char* sdr = sdy + 2 * RN_TILE_BYTES;   // DRES only
       const long long row0 = (blockIdx.x + static_cast<long long>(i) * gridDim.x) * tile_rows +
                              static_cast<long long>(g) * RPG;
       const int have = static_cast<int>(min(static_cast<long long>(RPG), max(rows - row0, 0ll)));
       if (have < RPG) {
         zero_missing_rows<T, KV>(sdy, g, RPG, have, row_bytes, lpr, l);
         zero_missing_rows<T, KV>(sx, g, RPG, have, row_bytes, lpr, l);
+        if (DRES) zero_missing_rows<T, KV>(sdr, g, RPG, have, row_bytes, lpr, l);
       }
       const size_t goff = static_cast<size_t>(g * RPG) * row_bytes + static_cast<size_t>(l) * NV * sizeof(T);
       T* dxrow = dx + row0 * lddx + l * NV;
@@ -475,6 +503,13 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x,
 #pragma unroll
           for (int e = 0; e < NV; ++e)
             o[e] = fmaf(dn[e] * (ROPE ? w_own[ROPE ? k : 0][e] : wk[e]), rstd, -(xf[e] * c3));
+          if (DRES) {
+            float a[NV];
+            const size_t off = goff + r * row_bytes + static_cast<size_t>(k) * lpr * NV * sizeof(T);
+            unpack<T>(ldv<T>(reinterpret_cast<const T*>(sdr + off)), a);
+#pragma unroll
+            for (int e = 0; e < NV; ++e) o[e] += a[e];
+          }
           if (r < have) stv<T>(dxrow + r * lddx + k * lpr * NV, pack<T>(o));
         }
       }

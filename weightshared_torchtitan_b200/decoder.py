@@ -120,6 +120,23 @@ def _rms(norm: nn.RMSNorm, x: torch.Tensor, rope=None) -> torch.Tensor:
     return y
 
 
+def _add_rms(norm: nn.RMSNorm, h: torch.Tensor, delta: torch.Tensor):
+    """(h + delta, norm(h + delta)): the residual add folded into the norm kernel where the
+    kernel covers the width, else the two PyTorch-level steps."""
+    D = h.shape[-1]
+    w = norm.weight
+    if (w.dtype == torch.float32 and h.is_cuda and h.dtype == delta.dtype and h.shape == delta.shape
+            and ops.rmsnorm_supported(D, h.dtype)):
+        sink = None
+        if torch.is_grad_enabled() and w.requires_grad and (h.requires_grad or delta.requires_grad):
+            if w.grad is None:
+                w.grad = torch.zeros_like(w)
+            sink = w.grad
+        return WF.add_rmsnorm(h, delta, w if sink is None else w.detach(), norm.eps, sink)
+    h = h + delta
+    return h, _rms(norm, h)
+
+
 def _rope(t: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     d = t.shape[-1]
     rot = torch.cat((-t[..., d // 2:], t[..., : d // 2]), dim=-1)
@@ -254,10 +271,15 @@ class WeightSharedDecoder(nn.Module):
             cos, sin = rope_tables(c.head_dim, s, c.rope_theta, h.device)
             self._rope = (cos.contiguous(), sin.contiguous())       # fp32 [s, head_dim]
         cos, sin = self._rope
+        pending = None   # output of the previous layer's down projection, not yet added to h
         for lyr in self.layers:
             # the layer's four projection groups hand their adapter-gradient work to one batch
             ab = WF.AdapterGradBatch(4) if torch.is_grad_enabled() else None
-            xn = _rms(lyr.attention_norm, h)
+            # every residual add is folded into the norm that reads the sum
+            if pending is None:
+                xn = _rms(lyr.attention_norm, h)
+            else:
+                h, xn = _add_rms(lyr.attention_norm, h, pending)
             q, k, v = self._group(lyr, ("wq", "wk", "wv"), xn, ab)
             q = _rms(lyr.q_norm, q.view(b, s, c.n_heads, c.head_dim), (cos, sin, c.n_heads, s))
             k = _rms(lyr.k_norm, k.view(b, s, c.n_kv_heads, c.head_dim), (cos, sin, c.n_kv_heads, s))
@@ -265,11 +287,12 @@ class WeightSharedDecoder(nn.Module):
             o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                                is_causal=True, enable_gqa=c.n_heads != c.n_kv_heads)
             o = o.transpose(1, 2).reshape(b, s, c.n_heads * c.head_dim)
-            h = h + self._group(lyr, ("wo",), o, ab)[0]
-            xn = _rms(lyr.ffn_norm, h)
+            h, xn = _add_rms(lyr.ffn_norm, h, self._group(lyr, ("wo",), o, ab)[0])
             gate, up = self._group(lyr, ("w1", "w3"), xn, ab)
-            h = h + self._group(lyr, ("w2",), WF.swiglu(gate, up), ab)[0]
-        return _rms(self.norm, h)
+            pending = self._group(lyr, ("w2",), WF.swiglu(gate, up), ab)[0]
+        if pending is None:
+            return _rms(self.norm, h)
+        return _add_rms(self.norm, h, pending)[1]
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         """fp32 logits [b, s, V] (evaluation / parity use; training uses loss())."""

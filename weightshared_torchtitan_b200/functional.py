@@ -413,5 +413,44 @@ class RMSNormFunction(torch.autograd.Function):
         return dx.view(ctx.shape), (dw.to(w.dtype) if dw is not None else None), None, None, None
 
 
+class AddRMSNormFunction(torch.autograd.Function):
+    """The residual add that precedes a norm, and the norm, in one pass:
+    forward(ctx, x, res, w, eps, sink) -> (h, y) with h = x + res and y = RMSNorm(h) * w
+    (``h = h + attention(...)`` followed by ``ffn_norm(h)``,
+    torchtitan/experiments/qwen3/model/model.py:310-313). The backward adds the gradient that
+    reaches h through the residual stream to the norm's own dx in the same kernel; it is the
+    gradient of both x and res."""
+
+    @staticmethod
+    def forward(ctx, x, res, w, eps, sink):
+        D = x.shape[-1]
+        h2, y2, rstd = ops.add_rmsnorm_fwd(x.reshape(-1, D), res.reshape(-1, D), w, eps)
+        ctx.save_for_backward(h2, w, rstd)
+        ctx.sink = sink
+        ctx.shape = x.shape
+        return h2.view(x.shape), y2.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dh, dy):
+        h2, w, rstd = ctx.saved_tensors
+        D = h2.shape[-1]
+        dw = ctx.sink
+        if dw is None and ctx.needs_input_grad[2]:
+            dw = torch.zeros(D, device=h2.device, dtype=torch.float32)
+        if dy is None:
+            dx = dh
+        elif dh is None:
+            dx = ops.rmsnorm_bwd(dy.reshape(-1, D), h2, w, rstd, dw).view(ctx.shape)
+        else:
+            dx = ops.add_rmsnorm_bwd(dy.reshape(-1, D), h2, dh.reshape(-1, D), w, rstd, dw).view(ctx.shape)
+        gw = dw.to(w.dtype) if (ctx.sink is None and dw is not None) else None
+        return dx, dx, gw, None, None
+
+
+def add_rmsnorm(x: torch.Tensor, res: torch.Tensor, w: torch.Tensor, eps: float, sink=None):
+    """(x + res, RMSNorm(x + res) * w); see AddRMSNormFunction."""
+    return AddRMSNormFunction.apply(x, res, w, eps, sink)
+
+
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, rope=None, sink=None) -> torch.Tensor:
     return RMSNormFunction.apply(x, w, eps, rope, sink)

@@ -608,3 +608,38 @@ def rmsnorm_bwd(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, rstd: torc
     _toc(_e, "rmsnorm_bwd", 0.0, 3.0 * x2.element_size() * rows * D)
     _lib.check(st, "wsl_rmsnorm_bwd")
     return dx
+
+
+def add_rmsnorm_fwd(x2: torch.Tensor, res2: torch.Tensor, w: torch.Tensor, eps: float):
+    """h = x + res, y = RMSNorm(h) * w in one pass (dense rows). Returns (h, y, rstd)."""
+    x2, res2 = _mat(x2, "x").contiguous(), _mat(res2, "res").contiguous()
+    _same(_dtype_code(x2), res2)
+    rows, D = x2.shape
+    if res2.shape != x2.shape:
+        raise ValueError("x and res must have the same shape")
+    h = torch.empty_like(x2)
+    y = torch.empty_like(x2)
+    rstd = torch.empty(rows, device=x2.device, dtype=torch.float32)
+    _e = _tic()
+    st = _lib.lib().wsl_add_rmsnorm_fwd(x2.data_ptr(), res2.data_ptr(), w.data_ptr(), h.data_ptr(), y.data_ptr(),
+                                        rstd.data_ptr(), rows, D, float(eps), _dtype_code(x2), _stream())
+    _toc(_e, "rmsnorm_fwd", 0.0, 4.0 * x2.element_size() * rows * D)
+    _lib.check(st, "wsl_add_rmsnorm_fwd")
+    return h, y, rstd
+
+
+def add_rmsnorm_bwd(dy2: torch.Tensor, h2: torch.Tensor, dres2: torch.Tensor, w: torch.Tensor,
+                    rstd: torch.Tensor, dw: Optional[torch.Tensor]) -> torch.Tensor:
+    """dx = dRMSNorm(dy; h, w, rstd) + dres (dense rows); dw accumulates in place."""
+    dy2, h2, dres2 = _mat(dy2, "dy").contiguous(), _mat(h2, "h").contiguous(), _mat(dres2, "dres").contiguous()
+    _same(_dtype_code(h2), dy2, dres2)
+    rows, D = h2.shape
+    dx = torch.empty_like(h2)
+    _e = _tic()
+    st = _lib.lib().wsl_add_rmsnorm_bwd(dy2.data_ptr(), h2.data_ptr(), dres2.data_ptr(), w.data_ptr(),
+                                        rstd.data_ptr(), dx.data_ptr(),
+                                        dw.data_ptr() if dw is not None else None, rows, D,
+                                        _dtype_code(h2), _stream())
+    _toc(_e, "rmsnorm_bwd", 0.0, 4.0 * h2.element_size() * rows * D)
+    _lib.check(st, "wsl_add_rmsnorm_bwd")
+    return dx
