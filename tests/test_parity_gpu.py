@@ -472,7 +472,8 @@ def test_merge_weight(wsl):
     one bf16 ulp apart)."""
     g = torch.Generator().manual_seed(101)
     bf = torch.bfloat16
-    for N, K, r in [(1024, 1024, 16), (264, 520, 8), (3072, 1024, 64)]:
+    # the last shape is large enough for the 4-rows-per-thread variant, with a ragged row count
+    for N, K, r in [(1024, 1024, 16), (264, 520, 8), (3072, 1024, 64), (4102, 2560, 16)]:
         W = (torch.randn(N, K, generator=g) * 0.03).cuda().to(bf)
         A = (torch.randn(r, K, generator=g) * 0.05).cuda().to(bf)
         B = (torch.randn(N, r, generator=g) * 0.1).cuda().to(bf)

@@ -12,7 +12,8 @@
 
 namespace wsl {
 
-constexpr int MERGE_ROWS = 4;   // rows of W per thread (the unpacked A values are shared by them)
+// A thread owns ROWS rows x 8 columns of W; the unpacked A values are shared by its rows, so
+// 4 rows cost fewer instructions per element, 2 rows give small matrices twice the threads.
 
 struct MergeProj {
   const __nv_bfloat16* W;
@@ -20,7 +21,7 @@ struct MergeProj {
   const __nv_bfloat16* B;
   __nv_bfloat16* out;
   long long N;
-  long long begin;   // first work item of this projection (item = MERGE_ROWS rows x 8 columns)
+  long long begin;   // first work item of this projection (item = ROWS rows x 8 columns)
 };
 struct MergeParams {
   MergeProj proj[WSL_MAX_PROJ];
@@ -39,11 +40,12 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   }
 }
 
-// R = rank (multiple of 8). Work item i of a projection: rows [4 * (i / K8), +4), columns
+// R = rank (multiple of 8). Work item i of a projection: rows [ROWS * (i / K8), +ROWS), columns
 // [8 * (i % K8), +8); consecutive threads take consecutive column groups of the same rows.
-template <int R>
+template <int R, int ROWS>
 __global__ void __launch_bounds__(256)
 lora_merge_kernel(const __grid_constant__ MergeParams mp) {
+  constexpr int MERGE_ROWS = ROWS;
   for (long long gi = blockIdx.x * 256ll + threadIdx.x; gi < mp.total; gi += gridDim.x * 256ll) {
     int p = 0;
     while (p + 1 < mp.nproj && gi >= mp.proj[p + 1].begin) ++p;
@@ -52,6 +54,13 @@ lora_merge_kernel(const __grid_constant__ MergeParams mp) {
     const long long n0 = (i / mp.K8) * MERGE_ROWS;
     const int k8 = static_cast<int>(i % mp.K8);
     const int K = mp.K8 * 8;
+    // the row of W is needed last but asked for first: its latency hides behind the products
+    uint4 wv[MERGE_ROWS];
+#pragma unroll
+    for (int q = 0; q < MERGE_ROWS; ++q) {
+      const long long n = n0 + q < P.N ? n0 + q : P.N - 1;
+      wv[q] = *reinterpret_cast<const uint4*>(P.W + n * K + k8 * 8);
+    }
     float d[MERGE_ROWS][8];
 #pragma unroll
     for (int q = 0; q < MERGE_ROWS; ++q)
@@ -79,7 +88,7 @@ lora_merge_kernel(const __grid_constant__ MergeParams mp) {
     for (int q = 0; q < MERGE_ROWS; ++q) {
       if (n0 + q < P.N) {
         float w[8];
-        unpack8(*reinterpret_cast<const uint4*>(P.W + (n0 + q) * K + k8 * 8), w);
+        unpack8(wv[q], w);
         uint4 ov;
         uint32_t* ou = reinterpret_cast<uint32_t*>(&ov);
 #pragma unroll
@@ -120,20 +129,35 @@ int launch_lora_merge(int nproj, const void* const* W, const void* const* A, con
     mp.proj[p].out = static_cast<__nv_bfloat16*>(out[p]);
     mp.proj[p].N = N[p];
     mp.proj[p].begin = total;
-    total += ((N[p] + MERGE_ROWS - 1) / MERGE_ROWS) * mp.K8;
+    total += ((N[p] + 3) / 4) * mp.K8;
+  }
+  // small matrices: 2 rows per thread so that every SM holds a full set of warps
+  const bool two = total < 2048ll * device_sm_count();
+  if (two) {
+    total = 0;
+    for (int p = 0; p < nproj; ++p) {
+      mp.proj[p].begin = total;
+      total += ((N[p] + 1) / 2) * mp.K8;
+    }
   }
   mp.total = total;
   long long blocks = (total + 255) / 256;
   const long long cap = 8ll * device_sm_count();
   if (blocks > cap) blocks = cap;
   const unsigned gb = static_cast<unsigned>(blocks);
+#define WSL_MERGE(R)                                                    \
+  do {                                                                  \
+    if (two) lora_merge_kernel<R, 2><<<gb, 256, 0, stream>>>(mp);       \
+    else lora_merge_kernel<R, 4><<<gb, 256, 0, stream>>>(mp);           \
+  } while (0)
   switch (r) {
-    case 8: lora_merge_kernel<8><<<gb, 256, 0, stream>>>(mp); break;
-    case 16: lora_merge_kernel<16><<<gb, 256, 0, stream>>>(mp); break;
-    case 32: lora_merge_kernel<32><<<gb, 256, 0, stream>>>(mp); break;
-    case 64: lora_merge_kernel<64><<<gb, 256, 0, stream>>>(mp); break;
-    default: lora_merge_kernel<128><<<gb, 256, 0, stream>>>(mp); break;
+    case 8: WSL_MERGE(8); break;
+    case 16: WSL_MERGE(16); break;
+    case 32: WSL_MERGE(32); break;
+    case 64: WSL_MERGE(64); break;
+    default: WSL_MERGE(128); break;
   }
+#undef WSL_MERGE
   if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
   ++g_launch_count;
   return WSL_OK;
