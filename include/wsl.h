@@ -60,7 +60,8 @@ unsigned long long wsl_launch_count(void);
 /*
  * Device-side status words of the CURRENT device: words[0] = 0 or the first
  * recorded WSL_ERR_TIMEOUT, words[1] = role that gave up (1 producer, 2 MMA
- * issuer, 3 epilogue), words[2] = block index, words[3] = tile index.
+ * issuer, 3 epilogue of the GEMM; 4 a warp of the staged row kernels), words[2] = block index,
+ * words[3] = tile index.
  * Copies from the device, so it waits for work already enqueued on the legacy
  * default stream's peers to the extent cudaMemcpyFromSymbol does; call it
  * after synchronising the stream of interest. Returns words[0].

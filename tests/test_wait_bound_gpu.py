@@ -42,3 +42,40 @@ def test_wait_runs_out_status_is_reported_and_context_survives():
     ref = x.float() @ W.float().T
     assert ((y.float() - ref).abs().max() / ref.abs().max()).item() < 1e-2
     assert _lib.poll_status()[0] == 0
+
+
+def test_row_kernel_wait_runs_out_and_context_survives():
+    """Same for the staged RMSNorm kernels: with their producer warp kept idle, the compute
+    warps' wait on the `full` barrier of the first stage runs into its bound, the kernel records
+    role 4 and ends; afterwards the same call computes correctly."""
+    if not torch.cuda.is_available():
+        pytest.fail("gpu tests need a CUDA device")
+    import torch.nn.functional as F
+    from weightshared_torchtitan_b200 import _lib, ops
+    lib = _lib.lib()
+    torch.cuda.synchronize()
+    assert lib.wsl_reset_status() == 0
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(256, 1024, generator=g).cuda().to(torch.bfloat16)
+    dy = torch.randn(256, 1024, generator=g).cuda().to(torch.bfloat16)
+    w = torch.ones(1024, device="cuda")
+    _, rstd = ops.rmsnorm_fwd(x, w, 1e-6)
+    for call in (lambda: ops.rmsnorm_fwd(x, w, 1e-6),
+                 lambda: ops.rmsnorm_bwd(dy, x, w, rstd, torch.zeros(1024, device="cuda"))):
+        os.environ["WSL_DBG"] = "64"
+        os.environ["WSL_WAIT_LIMIT_MS"] = "200"
+        try:
+            call()
+            torch.cuda.synchronize()        # no CUDA error: the kernel ended by itself
+        finally:
+            del os.environ["WSL_DBG"]
+            del os.environ["WSL_WAIT_LIMIT_MS"]
+        st, words = _lib.poll_status()
+        assert st == _lib.WSL_ERR_TIMEOUT, (st, words)
+        assert words[1] == 4
+        assert lib.wsl_reset_status() == 0
+    y, _ = ops.rmsnorm_fwd(x, w, 1e-6)
+    torch.cuda.synchronize()
+    ref = F.rms_norm(x.float(), (1024,), w, 1e-6)
+    assert ((y.float() - ref).abs().max() / ref.abs().max()).item() < 1e-2
+    assert _lib.poll_status()[0] == 0

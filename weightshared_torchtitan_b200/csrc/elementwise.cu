@@ -423,6 +423,20 @@ static bool row_staged_enabled() {
   return on;
 }
 
+// Wait bound and diagnostic switch of the staged kernels, read at launch like the GEMM's:
+// WSL_WAIT_LIMIT_MS shortens the bound, bit 64 of WSL_DBG keeps the producer warp idle.
+static RnKnobs rn_knobs() {
+  RnKnobs k;
+  k.wait_limit_ns = RN_WAIT_LIMIT_NS;
+  k.producer_idle = 0;
+  if (const char* e = getenv("WSL_WAIT_LIMIT_MS")) {
+    const long ms = atol(e);
+    if (ms > 0 && ms <= 10000) k.wait_limit_ns = static_cast<unsigned long long>(ms) * 1000000ull;
+  }
+  if (const char* e = getenv("WSL_DBG")) k.producer_idle = (atoi(e) & 64) ? 1 : 0;
+  return k;
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <typename T>
@@ -552,7 +566,7 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const void* res, void* h_ou
     }                                                                                              \
     rmsnorm_fwd_staged_kernel<T, R, KVN, RES><<<sgb, (RN_WARPS + 1) * 32, ssmem, s>>>(             \
         static_cast<const T*>(x), static_cast<const T*>(res), static_cast<T*>(h_out), w,           \
-        static_cast<T*>(y), ldy, rstd, rows, d, lpr, eps, cs, sn, h, sq, n_tiles);                 \
+        static_cast<T*>(y), ldy, rstd, rows, d, lpr, eps, cs, sn, h, sq, n_tiles, rn_knobs());     \
   } while (0)
 #define WSL_RNFS_RES(T, KVN)                                      \
   do {                                                            \
@@ -649,7 +663,7 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
     }                                                                                              \
     rmsnorm_bwd_staged_kernel<T, R, KVN, DRES><<<sgb, (cw + 1) * 32, ssmem, s>>>(                  \
         static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(dres), w, rstd, \
-        static_cast<T*>(dx), lddx, dw, rows, d, lpr, cs, sn, h, sq, n_tiles);                      \
+        static_cast<T*>(dx), lddx, dw, rows, d, lpr, cs, sn, h, sq, n_tiles, rn_knobs());          \
   } while (0)
 #define WSL_RNS_RES(T, KVN)                                       \
   do {                                                            \

@@ -26,7 +26,14 @@ namespace wsl {
 // stages of the ring: as many as fit next to the scale copies, by operand tiles per stage
 __host__ __device__ constexpr int rn_stages(int nops) { return nops == 1 ? 6 : (nops == 2 ? 3 : 2); }
 constexpr int RN_TILE_BYTES = 32768;
-constexpr unsigned long long RN_WAIT_LIMIT_NS = 2000000000ull;
+constexpr unsigned long long RN_WAIT_LIMIT_NS = 2000000000ull;   // default bound of every wait
+
+// Launch-time knobs shared by the staged kernels: the bound of the mbarrier waits and the
+// diagnostic switch "the producer never fills the ring" (exercises the bounded waits).
+struct RnKnobs {
+  unsigned long long wait_limit_ns;
+  int producer_idle;
+};
 
 // compute warps of the backward: rows of 32+ elements per lane, and rotary rows (two sets of
 // cos/sin registers), need more than the 168 registers a 9-warp CTA leaves each thread, so
@@ -116,13 +123,15 @@ template <int NOPS, int STAGES>
 __device__ __forceinline__ void rn_producer_loop(const unsigned char* src0, const unsigned char* src1,
                                                  const unsigned char* src2, size_t row_bytes, int tile_rows, long long rows,
                                                  int my_tiles, uint32_t stage0, uint32_t bar0,
-                                                 volatile int* abortp, volatile int* drainp, int lane) {
+                                                 volatile int* abortp, volatile int* drainp, int lane,
+                                                 const RnKnobs& knobs) {
   int issued = 0;
   int s = 0;
   uint32_t ph = 0;
+  if (knobs.producer_idle) return;   // diagnostic: the consumers' waits must run out by themselves
   for (int i = 0; i < my_tiles; ++i) {
     if (i >= STAGES &&
-        !__all_sync(0xffffffffu, mbar_wait(bar0 + 8u * (STAGES + s), ph ^ 1u, abortp, RN_WAIT_LIMIT_NS))) {
+        !__all_sync(0xffffffffu, mbar_wait(bar0 + 8u * (STAGES + s), ph ^ 1u, abortp, knobs.wait_limit_ns))) {
       if (lane == 0) record_timeout(4, i);
       break;
     }
@@ -146,7 +155,7 @@ __device__ __forceinline__ void rn_producer_loop(const unsigned char* src0, cons
   if (*abortp != 0) {
     for (int i = max(issued - STAGES, 0); i < issued; ++i)
       mbar_wait(bar0 + 8u * (i % STAGES), static_cast<uint32_t>(i / STAGES) & 1u, drainp,
-                RN_WAIT_LIMIT_NS);
+                knobs.wait_limit_ns);
   }
 }
 
@@ -174,7 +183,7 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
                           const float* __restrict__ w, T* __restrict__ y,
                           long long ldy, float* __restrict__ rstd_out, long long rows, int D, int lpr,
                           float eps, const float* __restrict__ cs, const float* __restrict__ sn,
-                          int heads, int seq, long long n_tiles) {
+                          int heads, int seq, long long n_tiles, const RnKnobs knobs) {
   static_assert(!(ROPE && RES), "the residual add precedes hidden-size norms only");
   constexpr int NV = Vec<T>::N;
   constexpr int RPG = 8 / KV;
@@ -210,7 +219,7 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
   if (warp == CW) {
     rn_producer_loop<NOPS, S>(reinterpret_cast<const unsigned char*>(x),
                               reinterpret_cast<const unsigned char*>(res), nullptr, row_bytes, tile_rows,
-                              rows, my_tiles, stage0, bar0, abortp, drainp, lane);
+                              rows, my_tiles, stage0, bar0, abortp, drainp, lane, knobs);
     return;
   }
   const float inv_D = 1.0f / static_cast<float>(D);
@@ -252,7 +261,7 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
         }
       if (i + 1 < my_tiles) prefetch(i + 1);
     }
-    if (!__all_sync(0xffffffffu, mbar_wait(bar0 + 8u * s, ph, abortp, RN_WAIT_LIMIT_NS))) {
+    if (!__all_sync(0xffffffffu, mbar_wait(bar0 + 8u * s, ph, abortp, knobs.wait_limit_ns))) {
       if (lane == 0) record_timeout(4, i);
       break;
     }
@@ -326,7 +335,7 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
                           const float* __restrict__ w, const float* __restrict__ rstd_in,
                           T* __restrict__ dx, long long lddx, float* dw, long long rows, int D, int lpr,
                           const float* __restrict__ cs, const float* __restrict__ sn, int heads,
-                          int seq, long long n_tiles) {
+                          int seq, long long n_tiles, const RnKnobs knobs) {
   constexpr int NV = Vec<T>::N;
   constexpr int RPG = 8 / KV;
   constexpr int CW = rn_compute_warps(KV * NV, ROPE);
@@ -368,7 +377,7 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
     rn_producer_loop<NOPS, S>(reinterpret_cast<const unsigned char*>(dy),
                               reinterpret_cast<const unsigned char*>(x),
                               reinterpret_cast<const unsigned char*>(dres), row_bytes, tile_rows, rows,
-                              my_tiles, stage0, bar0, abortp, drainp, lane);
+                              my_tiles, stage0, bar0, abortp, drainp, lane, knobs);
   } else {
     const float inv_D = 1.0f / static_cast<float>(D);
     const int g = warp * rpw + lane / lpr;
@@ -422,7 +431,7 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
           }
       }
       if (i + 1 < my_tiles) prefetch(i + 1);
-      if (!__all_sync(0xffffffffu, mbar_wait(bar0 + 8u * s, ph, abortp, RN_WAIT_LIMIT_NS))) {
+      if (!__all_sync(0xffffffffu, mbar_wait(bar0 + 8u * s, ph, abortp, knobs.wait_limit_ns))) {
         if (lane == 0) record_timeout(4, i);
         break;
       }
