@@ -227,6 +227,7 @@ def test_rmsnorm_supported_widths():
     from weightshared_torchtitan_b200 import ops
     bf, f32 = torch.bfloat16, torch.float32
     assert all(ops.rmsnorm_supported(d, bf) for d in (16, 64, 128, 256, 512, 1024, 2048))
-    assert not ops.rmsnorm_supported(2560, bf) and not ops.rmsnorm_supported(4096, bf)
+    assert ops.rmsnorm_supported(2560, bf) and ops.rmsnorm_supported(4096, bf)      # hidden sizes of the 4B / 8B shapes
+    assert not ops.rmsnorm_supported(5120, bf) and not ops.rmsnorm_supported(2560, f32)
     assert ops.rmsnorm_supported(128, bf, rope=True) and not ops.rmsnorm_supported(512, bf, rope=True)
     assert ops.rmsnorm_supported(1024, f32) and not ops.rmsnorm_supported(2048, f32)

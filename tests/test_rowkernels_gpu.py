@@ -72,7 +72,7 @@ def test_swiglu(dtype, tol):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-5), (torch.bfloat16, 1e-2)])
-@pytest.mark.parametrize("D", [16, 64, 128, 1024, 2048])
+@pytest.mark.parametrize("D", [16, 64, 128, 1024, 2048, 2560, 4096])
 def test_rmsnorm(dtype, tol, D):
     from weightshared_torchtitan_b200 import ops
     from weightshared_torchtitan_b200.functional import rmsnorm
@@ -126,7 +126,8 @@ def test_head_norm_with_rotary(dtype, tol, D, heads):
 
 
 @pytest.mark.parametrize("D,rows,heads", [(128, 100_003, 0), (128, 80_000, 16), (1024, 9_477, 0),
-                                          (2048, 5_000, 0), (256, 40_001, 0)])
+                                          (2048, 5_000, 0), (256, 40_001, 0), (2560, 4_003, 0),
+                                          (4096, 3_001, 0)])
 def test_rmsnorm_backward_over_many_tiles(D, rows, heads):
     """Row counts at which every CTA of the staged backward walks its ring of shared-memory
     stages several times (so the barrier phases flip) and the last tile is ragged."""
@@ -176,7 +177,8 @@ def test_rmsnorm_strided_rows_take_the_direct_kernel():
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-5), (torch.bfloat16, 1e-2)])
-@pytest.mark.parametrize("D,rows", [(1024, 333), (2048, 5_003), (256, 40_001), (64, 77)])
+@pytest.mark.parametrize("D,rows", [(1024, 333), (2048, 5_003), (256, 40_001), (64, 77), (2560, 3_001),
+                                    (4096, 2_005)])
 def test_residual_add_folded_into_the_norm(dtype, tol, D, rows):
     """h = x + res and y = RMSNorm(h) in one kernel; the backward adds the gradient of the
     residual stream to the norm's dx. Against the same three steps in fp32 PyTorch; h must be

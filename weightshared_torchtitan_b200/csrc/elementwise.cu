@@ -504,8 +504,10 @@ static int rms_lanes(long long D, int nv) {
   if (D <= 0 || (D % nv) != 0) return 0;
   long long lanes = D / nv;
   if (lanes >= 32) {
+    // kv = 10 and 16 (hidden sizes 2560 and 4096 in bf16) exist as staged kernels only
     const long long kv = D / (32 * nv);
-    return (D % (32 * nv)) == 0 && (kv == 1 || kv == 2 || kv == 4 || kv == 8) ? 32 : 0;
+    return (D % (32 * nv)) == 0 && (kv == 1 || kv == 2 || kv == 4 || kv == 8 || (nv == 8 && (kv == 10 || kv == 16)))
+               ? 32 : 0;
   }
   return (lanes & (lanes - 1)) == 0 ? static_cast<int>(lanes) : 0;
 }
@@ -550,7 +552,8 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const void* res, void* h_ou
     // rotary rows: two half-row vectors per lane (the staged kernels' layout), else as above
     const int kvn = cs ? 2 : static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
     const int lpr = cs ? static_cast<int>(D / (2 * (is_f32 ? 4 : 8))) : rms_lanes(D, is_f32 ? 4 : 8);
-    const long long tile_rows = static_cast<long long>(RN_WARPS) * (32 / lpr) * (8 / kvn);
+    const int cw = rn_fwd_compute_warps(kvn);
+    const long long tile_rows = static_cast<long long>(cw) * (32 / lpr) * rn_rows_per_group(kvn);
     const long long n_tiles = (rows + tile_rows - 1) / tile_rows;
     const unsigned sgb = static_cast<unsigned>(n_tiles < device_sm_count() ? n_tiles : device_sm_count());
     const size_t ssmem = rn_fwd_staged_smem(d, fused);
@@ -560,11 +563,11 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const void* res, void* h_ou
     if (!attr_set) {                                                                               \
       if (cudaFuncSetAttribute(rmsnorm_fwd_staged_kernel<T, R, KVN, RES>,                          \
                                cudaFuncAttributeMaxDynamicSharedMemorySize,                        \
-                               static_cast<int>(rn_fwd_staged_smem(2048, RES))) != cudaSuccess)    \
+                               static_cast<int>(rn_fwd_staged_smem(4096, RES))) != cudaSuccess)    \
         return WSL_ERR_CUDA;                                                                       \
       attr_set = true;                                                                             \
     }                                                                                              \
-    rmsnorm_fwd_staged_kernel<T, R, KVN, RES><<<sgb, (RN_WARPS + 1) * 32, ssmem, s>>>(             \
+    rmsnorm_fwd_staged_kernel<T, R, KVN, RES><<<sgb, (cw + 1) * 32, ssmem, s>>>(                   \
         static_cast<const T*>(x), static_cast<const T*>(res), static_cast<T*>(h_out), w,           \
         static_cast<T*>(y), ldy, rstd, rows, d, lpr, eps, cs, sn, h, sq, n_tiles, rn_knobs());     \
   } while (0)
@@ -582,7 +585,10 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const void* res, void* h_ou
     else if (kvn == 8) WSL_RNFS_RES(T, 8);                        \
     else return WSL_ERR_TOO_LARGE;                                \
   } while (0)
-    if (is_f32) WSL_RNFS_KV(float); else WSL_RNFS_KV(__nv_bfloat16);
+    if (is_f32) WSL_RNFS_KV(float);
+    else if (kvn == 10) WSL_RNFS_RES(__nv_bfloat16, 10);
+    else if (kvn == 16) WSL_RNFS_RES(__nv_bfloat16, 16);
+    else WSL_RNFS_KV(__nv_bfloat16);
 #undef WSL_RNFS_KV
 #undef WSL_RNFS_RES
 #undef WSL_RNFS
@@ -591,6 +597,7 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const void* res, void* h_ou
     return WSL_OK;
   }
   if (fused) return WSL_ERR_BAD_ARG;   // the direct kernel has no residual input
+  if (kvn > 8) return WSL_ERR_TOO_LARGE;   // rows this wide exist as staged kernels (dense rows) only
 #define WSL_RN(T, R, KVN)                                                                          \
   rmsnorm_fwd_kernel<T, R, KVN><<<gb, RN_WARPS * 32, 0, s>>>(                                      \
       static_cast<const T*>(x), ldx, w, static_cast<T*>(y), ldy, rstd, rows, d, lpr, eps, cs, sn, \
@@ -645,8 +652,8 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
     // rotary rows: two half-row vectors per lane (the staged kernels' layout), else as above
     const int kvn = cs ? 2 : static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
     const int lpr = cs ? static_cast<int>(D / (2 * (is_f32 ? 4 : 8))) : rms_lanes(D, is_f32 ? 4 : 8);
-    const int rpg = 8 / kvn;
-    const int cw = rn_compute_warps(kvn * (is_f32 ? 4 : 8), cs != nullptr);
+    const int rpg = rn_rows_per_group(kvn);
+    const int cw = rn_compute_warps(kvn, kvn * (is_f32 ? 4 : 8), cs != nullptr);
     const long long tile_rows = static_cast<long long>(cw) * (32 / lpr) * rpg;
     const long long n_tiles = (rows + tile_rows - 1) / tile_rows;
     const unsigned sgb = static_cast<unsigned>(n_tiles < device_sm_count() ? n_tiles : device_sm_count());
@@ -657,7 +664,7 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
     if (!attr_set) {                                                                               \
       if (cudaFuncSetAttribute(rmsnorm_bwd_staged_kernel<T, R, KVN, DRES>,                         \
                                cudaFuncAttributeMaxDynamicSharedMemorySize,                        \
-                               static_cast<int>(rn_staged_smem(2048, DRES))) != cudaSuccess)       \
+                               static_cast<int>(rn_staged_smem(4096, DRES))) != cudaSuccess)       \
         return WSL_ERR_CUDA;                                                                       \
       attr_set = true;                                                                             \
     }                                                                                              \
@@ -679,7 +686,10 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
     else if (kvn == 8) WSL_RNS_RES(T, 8);                         \
     else return WSL_ERR_TOO_LARGE;                                \
   } while (0)
-    if (is_f32) WSL_RNS_KV(float); else WSL_RNS_KV(__nv_bfloat16);
+    if (is_f32) WSL_RNS_KV(float);
+    else if (kvn == 10) WSL_RNS_RES(__nv_bfloat16, 10);
+    else if (kvn == 16) WSL_RNS_RES(__nv_bfloat16, 16);
+    else WSL_RNS_KV(__nv_bfloat16);
 #undef WSL_RNS_KV
 #undef WSL_RNS_RES
 #undef WSL_RNS
@@ -688,6 +698,7 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
     return WSL_OK;
   }
   if (fused) return WSL_ERR_BAD_ARG;   // the direct kernel has no residual-gradient input
+  if (kvn > 8) return WSL_ERR_TOO_LARGE;   // rows this wide exist as staged kernels (dense rows) only
 #define WSL_RNB(T, R, KVN)                                                                         \
   rmsnorm_bwd_kernel<T, R, KVN><<<gb, RN_WARPS * 32, smem, s>>>(                                   \
       static_cast<const T*>(dy), lddy, static_cast<const T*>(x), ldx, w, rstd, static_cast<T*>(dx), \

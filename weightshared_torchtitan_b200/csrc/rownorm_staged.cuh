@@ -38,8 +38,12 @@ struct RnKnobs {
 // compute warps of the backward: rows of 32+ elements per lane, and rotary rows (two sets of
 // cos/sin registers), need more than the 168 registers a 9-warp CTA leaves each thread, so
 // they run 7 compute warps (8 warps in all: 255 registers)
-__host__ __device__ constexpr int rn_compute_warps(int elems_per_lane, bool rope) {
-  return (elems_per_lane >= 32 || rope) ? 7 : 8;
+// Rows wider than 8 vectors per lane (KV = 10, 16: hidden sizes 2560 and 4096 in bf16) take one
+// row per warp and tile, and as many compute warps as fit a 32 KB tile (512 KV bytes per row).
+__host__ __device__ constexpr int rn_rows_per_group(int kv) { return kv <= 8 ? 8 / kv : 1; }
+__host__ __device__ constexpr int rn_fwd_compute_warps(int kv) { return kv <= 8 ? 8 : 64 / kv; }
+__host__ __device__ constexpr int rn_compute_warps(int kv, int elems_per_lane, bool rope) {
+  return kv > 8 ? 64 / kv : ((elems_per_lane >= 32 || rope) ? 7 : 8);
 }
 
 // shared memory: stages | barriers (full[S], empty[S]) | abort, drain words | w[D] | dw[D]
@@ -178,7 +182,7 @@ __device__ __forceinline__ void zero_missing_rows(unsigned char* tile, int g, in
 // RES: the row that is normalised is h = x + res (the residual add that precedes the norm),
 // rounded to the storage type exactly as a separate add kernel would, and also written out.
 template <typename T, bool ROPE, int KV, bool RES>
-__global__ void __launch_bounds__((RN_WARPS + 1) * 32, 1)
+__global__ void __launch_bounds__((rn_fwd_compute_warps(KV) + 1) * 32, 1)
 rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T* __restrict__ h_out,
                           const float* __restrict__ w, T* __restrict__ y,
                           long long ldy, float* __restrict__ rstd_out, long long rows, int D, int lpr,
@@ -186,10 +190,13 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
                           int heads, int seq, long long n_tiles, const RnKnobs knobs) {
   static_assert(!(ROPE && RES), "the residual add precedes hidden-size norms only");
   constexpr int NV = Vec<T>::N;
-  constexpr int RPG = 8 / KV;
-  constexpr int CW = RN_WARPS;
+  constexpr int RPG = rn_rows_per_group(KV);
+  constexpr int CW = rn_fwd_compute_warps(KV);
   constexpr int THREADS = (CW + 1) * 32;
   constexpr int NOPS = RES ? 2 : 1;
+  // very wide rows do not fit in registers: they are read from shared memory twice
+  constexpr bool PACKED = KV * NV > 64;
+  constexpr int KF = PACKED ? 1 : KV;
   constexpr int S = rn_stages(NOPS);
   extern __shared__ __align__(128) unsigned char rn_smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(rn_smem + S * NOPS * RN_TILE_BYTES);
@@ -278,24 +285,30 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
     T* hrow = RES ? h_out + row0 * D + l * NV : nullptr;
 #pragma unroll
     for (int r = 0; r < RPG; ++r) {
-      float f[KV][NV];
-      float ss = 0.f;
-#pragma unroll
-      for (int k = 0; k < KV; ++k) {
+      float f_[KF][NV];
+      // vector k of the row (x, or x + res rounded to the storage type) as floats
+      auto load_vec = [&](int k, float (&f)[NV], bool store_h) {
         const Vec<T> v = ldv<T>(reinterpret_cast<const T*>(srow + r * row_bytes) + k * lpr * NV);
-        unpack<T>(v, f[k]);
+        unpack<T>(v, f);
         if (RES) {
           float a[NV];
           unpack<T>(ldv<T>(reinterpret_cast<const T*>(srow + RN_TILE_BYTES + r * row_bytes) + k * lpr * NV), a);
 #pragma unroll
-          for (int e = 0; e < NV; ++e) f[k][e] += a[e];
-          const Vec<T> hv = pack<T>(f[k]);
-          if (r < have) stv<T>(hrow + static_cast<long long>(r) * D + k * lpr * NV, hv);
-          unpack<T>(hv, f[k]);   // normalise the value that was stored
+          for (int e = 0; e < NV; ++e) f[e] += a[e];
+          const Vec<T> hv = pack<T>(f);
+          if (store_h && r < have) stv<T>(hrow + static_cast<long long>(r) * D + k * lpr * NV, hv);
+          unpack<T>(hv, f);   // normalise the value that was stored
         }
+      };
+      float ss = 0.f;
 #pragma unroll
-        for (int e = 0; e < NV; ++e) ss = fmaf(f[k][e], f[k][e], ss);
+      for (int k = 0; k < KV; ++k) {
+        float (&f)[NV] = f_[PACKED ? 0 : k];
+        load_vec(k, f, true);
+#pragma unroll
+        for (int e = 0; e < NV; ++e) ss = fmaf(f[e], f[e], ss);
       }
+      if (PACKED) asm volatile("" ::: "memory");   // keep the second read a read, not 128 live registers
       ss = group_sum(ss, lpr);
       const float rstd = rsqrt_refined(fmaf(ss, inv_D, eps));
       if (r < have && l == 0 && rstd_out) rstd_out[row0 + r] = rstd;
@@ -305,12 +318,15 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
         if (ROPE) {
 #pragma unroll
           for (int e = 0; e < NV; ++e)
-            o[e] = fmaf(f[KV - 1 - k][e], ws[ROPE ? k : 0][e], f[k][e] * wc[ROPE ? k : 0][e]) * rstd;
+            o[e] = fmaf(f_[PACKED ? 0 : KV - 1 - k][e], ws[ROPE ? k : 0][e],
+                        f_[PACKED ? 0 : k][e] * wc[ROPE ? k : 0][e]) * rstd;
         } else {
+          float (&f)[NV] = f_[PACKED ? 0 : k];
+          if (PACKED) load_vec(k, f, false);
           float wk[NV];
           load_scale<NV>(w_s, k, lpr, l, wk);
 #pragma unroll
-          for (int e = 0; e < NV; ++e) o[e] = f[k][e] * rstd * wk[e];
+          for (int e = 0; e < NV; ++e) o[e] = f[e] * rstd * wk[e];
         }
         if (r < have) stv<T>(yrow + r * ldy + k * lpr * NV, pack<T>(o));
       }
@@ -330,15 +346,15 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
 // dx = rstd * w * dn - x * rstd^3 * mean(dn * w * x), dn = un-rotated dy;
 // dw[j] += sum_rows dn[j] * x[j] * rstd (registers -> shared-memory partials -> atomics).
 template <typename T, bool ROPE, int KV, bool DRES>
-__global__ void __launch_bounds__((rn_compute_warps(KV * Vec<T>::N, ROPE) + 1) * 32, 1)
+__global__ void __launch_bounds__((rn_compute_warps(KV, KV * Vec<T>::N, ROPE) + 1) * 32, 1)
 rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ dres,
                           const float* __restrict__ w, const float* __restrict__ rstd_in,
                           T* __restrict__ dx, long long lddx, float* dw, long long rows, int D, int lpr,
                           const float* __restrict__ cs, const float* __restrict__ sn, int heads,
                           int seq, long long n_tiles, const RnKnobs knobs) {
   constexpr int NV = Vec<T>::N;
-  constexpr int RPG = 8 / KV;
-  constexpr int CW = rn_compute_warps(KV * NV, ROPE);
+  constexpr int RPG = rn_rows_per_group(KV);
+  constexpr int CW = rn_compute_warps(KV, KV * NV, ROPE);
   constexpr int THREADS = (CW + 1) * 32;
   constexpr int NOPS = DRES ? 3 : 2;
   constexpr int S = rn_stages(NOPS);

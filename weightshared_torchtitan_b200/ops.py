@@ -566,7 +566,8 @@ def rmsnorm_supported(D: int, dtype: torch.dtype, rope: bool = False) -> bool:
     if rope:
         return 2 <= lanes <= 32 and lanes & (lanes - 1) == 0
     if lanes >= 32:
-        return D % (32 * nv) == 0 and D // (32 * nv) in (1, 2, 4, 8)
+        # 10 and 16 vectors per lane (hidden sizes 2560, 4096): bf16, dense rows only
+        return D % (32 * nv) == 0 and D // (32 * nv) in ((1, 2, 4, 8, 10, 16) if nv == 8 else (1, 2, 4, 8))
     return lanes & (lanes - 1) == 0
 
 
@@ -575,6 +576,8 @@ def rmsnorm_fwd(x2: torch.Tensor, w: torch.Tensor, eps: float, rope=None):
     Returns (y, rstd)."""
     x2 = _mat(x2, "x")
     rows, D = x2.shape
+    if D > 2048:
+        x2 = x2.contiguous()   # rows this wide are covered by the dense-row kernels only
     y = torch.empty((rows, D), device=x2.device, dtype=x2.dtype)
     rstd = torch.empty(rows, device=x2.device, dtype=torch.float32)
     cs = sn = None
@@ -594,6 +597,8 @@ def rmsnorm_bwd(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, rstd: torc
                 dw: Optional[torch.Tensor], rope=None) -> torch.Tensor:
     dy2, x2 = _mat(dy2, "dy"), _mat(x2, "x")
     rows, D = x2.shape
+    if D > 2048:
+        dy2, x2 = dy2.contiguous(), x2.contiguous()
     dx = torch.empty((rows, D), device=x2.device, dtype=x2.dtype)
     cs = sn = None
     heads = seq = 0

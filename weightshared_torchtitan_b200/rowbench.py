@@ -46,8 +46,9 @@ def main():
     M, S = args.tokens, args.seq
     bf = torch.bfloat16
     if args.what in ("all", "rmsnorm"):
-        # hidden rows (configurations 1 and 2) and head rows with the rotary embedding (16 and 8 heads)
-        for rows, D, heads in [(M, 1024, 0), (M, 2048, 0), (M * 16, 128, 16), (M * 8, 128, 8)]:
+        # hidden rows (configurations 1 to 4) and head rows with the rotary embedding (16 and 8 heads)
+        for rows, D, heads in [(M, 1024, 0), (M, 2048, 0), (M // 2, 2560, 0), (M // 2, 4096, 0), (M * 16, 128, 16),
+                               (M * 8, 128, 8)]:
             x = torch.randn(rows, D, device="cuda").to(bf)
             dy = torch.randn(rows, D, device="cuda").to(bf)
             w = torch.ones(D, device="cuda")
