@@ -50,6 +50,8 @@ def test_row_kernel_wait_runs_out_and_context_survives():
     role 4 and ends; afterwards the same call computes correctly."""
     if not torch.cuda.is_available():
         pytest.fail("gpu tests need a CUDA device")
+    if os.environ.get("WSL_ROW_STAGED") == "0":
+        pytest.skip("the diagnostic switch sends these calls to the direct kernels, which have no waits")
     import torch.nn.functional as F
     from weightshared_torchtitan_b200 import _lib, ops
     lib = _lib.lib()

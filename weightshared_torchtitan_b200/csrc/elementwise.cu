@@ -547,7 +547,7 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const void* res, void* h_ou
   const int kvn = static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
   const bool fused = res != nullptr;
   if (fused && (cs || !h_out || ldx != D || !aligned16(res) || !aligned16(h_out))) return WSL_ERR_BAD_ARG;
-  if ((fused || row_staged_enabled()) && ldx == D &&
+  if ((fused || kvn > 8 || row_staged_enabled()) && ldx == D &&
       (!cs || (heads % 4 == 0 && aligned16(cs) && aligned16(sn)))) {
     // rotary rows: two half-row vectors per lane (the staged kernels' layout), else as above
     const int kvn = cs ? 2 : static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
@@ -647,7 +647,7 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
   // contiguous rows take the staged kernel (bulk copies need 16-byte aligned, dense tiles)
   const bool fused = dres != nullptr;
   if (fused && (cs || lddy != D || ldx != D || !aligned16(dres))) return WSL_ERR_BAD_ARG;
-  if ((fused || row_staged_enabled()) && lddy == D && ldx == D &&
+  if ((fused || kvn > 8 || row_staged_enabled()) && lddy == D && ldx == D &&
       (!cs || (heads % 4 == 0 && aligned16(cs) && aligned16(sn)))) {
     // rotary rows: two half-row vectors per lane (the staged kernels' layout), else as above
     const int kvn = cs ? 2 : static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
