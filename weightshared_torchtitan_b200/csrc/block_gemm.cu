@@ -80,6 +80,8 @@ struct GemmParams {
   int total_tiles;
   int total_units;    // work units over all regions (tiles x the region's split factor)
   int kb_total;       // k-blocks summed over the segments
+  int stages;         // one-CTA variant: depth of the operand ring (4, or 8 in the narrow form)
+  int stage_bytes;    // one-CTA variant: bytes per stage (48 KiB, or 24 KiB in the narrow form)
   float* workspace;   // [splits][rows x cols] fp32 partials per region when splits > 1
   // Diagnostic switches (environment variable WSL_DBG, a bit mask; 0 in normal use):
   // 1 skip epilogue stores, 2 skip TMA loads, 4 skip MMAs (time the other parts alone),
@@ -211,14 +213,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Per-variant constants. PAIR = two CTAs (a cluster of 2, tcgen05 cta_group::2) share one
 // 256 x bn tile: each CTA owns 128 rows of A and of the accumulator and loads HALF of the
 // B tile, so a stage is 32 KiB (6-deep ring) instead of 48 KiB (4-deep).
+// The one-CTA variant also has a NARROW form for launches whose tiles are at most 64 columns
+// wide (rank-r pre-passes, adapter gradients): the B tile is then 8 KiB, a stage 24 KiB, and
+// the same shared memory holds an 8-deep ring, which doubles the bytes in flight of these
+// HBM-latency-bound launches. Stage count and size of the one-CTA variant are therefore
+// run-time values (GemmParams::stages, stage_bytes); kMaxStages sizes the barrier array.
 template <bool PAIR>
 struct Cfg {
   static constexpr int kStages = PAIR ? 6 : 4;
+  static constexpr int kMaxStages = PAIR ? 6 : 8;
   static constexpr int kBStageBytes = PAIR ? B_STAGE_BYTES / 2 : B_STAGE_BYTES;
   static constexpr int kStageBytes = A_STAGE_BYTES + kBStageBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + 2 * EPI_STAGE_BYTES + 1024;
   static constexpr int kTileM = PAIR ? 2 * BM : BM;
 };
+constexpr int NARROW_BN = 64;
+constexpr int NARROW_STAGES = 8;
+constexpr int NARROW_STAGE_BYTES = A_STAGE_BYTES + NARROW_BN * 128;   // 24 KiB
+static_assert(NARROW_STAGES * NARROW_STAGE_BYTES == Cfg<false>::kStages * Cfg<false>::kStageBytes,
+              "both forms of the one-CTA ring fill the same shared memory");
 
 // Work unit u -> (region, tile, split). Units are ordered region by region (the large
 // region first), and inside a region split-major, so with round-robin assignment every
@@ -252,9 +265,11 @@ template <bool A_MN, bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 block_gemm_kernel(const __grid_constant__ GemmParams p) {
   using C = Cfg<PAIR>;
-  constexpr int S = C::kStages;
+  constexpr int SMAX = C::kMaxStages;
+  const int S = PAIR ? C::kStages : p.stages;
+  const uint32_t stage_bytes = PAIR ? static_cast<uint32_t>(C::kStageBytes) : static_cast<uint32_t>(p.stage_bytes);
   extern __shared__ __align__(1024) uint8_t smem_dyn[];
-  __shared__ __align__(8) uint64_t bars[2 * S + 4];
+  __shared__ __align__(8) uint64_t bars[2 * SMAX + 4];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
 
@@ -267,9 +282,9 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
-  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * S + b); };
-  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * S + 2 + b); };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (SMAX + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * SMAX + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * SMAX + 2 + b); };
   volatile int* abortp = &abort_flag;
 
   if (threadIdx.x == 0) {
@@ -336,7 +351,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
             break;
           }
           if (elect_one() && !(dbg & 64)) {
-            const uint32_t sa = smem_base + s * C::kStageBytes;
+            const uint32_t sa = smem_base + s * stage_bytes;
             const uint32_t sb = sa + A_STAGE_BYTES;
             if (dbg & 2) {
               if (rank == 0) mbar_arrive(full_bar(s));
@@ -378,7 +393,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
             // Gathered operand: every lane fetches 4 rows (512 B) per tile::gather4; a row
             // id outside the matrix reads as zeros.
             const uint32_t fb = full_bar(s);
-            const uint32_t sa = smem_base + s * C::kStageBytes;
+            const uint32_t sa = smem_base + s * stage_bytes;
             const uint32_t sb = sa + A_STAGE_BYTES;
             if (!A_MN && p.gather_a) {
               int r4[4];
@@ -457,7 +472,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
             tc_fence_after_sync();
             const int kvalid = min(BK, klen - kk);
             const int nk = (dbg & 4) ? 0 : ((kvalid + 15) >> 4);
-            const uint32_t sa = smem_base + s * C::kStageBytes;
+            const uint32_t sa = smem_base + s * stage_bytes;
             const uint32_t sb = sa + A_STAGE_BYTES;
             const uint32_t a_lo = (sa & 0x3FFFFu) >> 4;
             const uint32_t b_lo = (sb & 0x3FFFFu) >> 4;
@@ -495,7 +510,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
     const int q = warp & 3;   // TMEM lane quarter this warp may read
     const int trow = q * 32 + lane;                       // row inside this CTA's 128-row tile
     const bool issuer = (warp == 2 && lane == 0);         // issues the TMA stores
-    const uint32_t epi_base = smem_base + S * C::kStageBytes;
+    const uint32_t epi_base = smem_base + S * stage_bytes;
     uint32_t chunk_ctr = 0;
     int it = 0;
     for (int u = worker; u < units; u += nworkers, ++it) {
@@ -1038,6 +1053,13 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   int kb_total = 0;
   for (int sgi = 0; sgi < g.nseg; ++sgi) kb_total += (g.seg_k[sgi] + BK - 1) / BK;
   p.kb_total = kb_total;
+  {
+    int max_bn = 0;
+    for (int r = 0; r < g.nregion; ++r) max_bn = p.reg[r].bn > max_bn ? p.reg[r].bn : max_bn;
+    const bool narrow = !pair && max_bn <= NARROW_BN;
+    p.stages = narrow ? NARROW_STAGES : Cfg<false>::kStages;
+    p.stage_bytes = narrow ? NARROW_STAGE_BYTES : Cfg<false>::kStageBytes;
+  }
   p.workspace = nullptr;
   int plan[kMaxRegion];
   for (int r = 0; r < kMaxRegion; ++r) plan[r] = 1;

@@ -550,10 +550,10 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const void* res, void* h_ou
   if ((fused || kvn > 8 || row_staged_enabled()) && ldx == D &&
       (!cs || (heads % 4 == 0 && aligned16(cs) && aligned16(sn)))) {
     // rotary rows: two half-row vectors per lane (the staged kernels' layout), else as above
-    const int kvn = cs ? 2 : static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
-    const int lpr = cs ? static_cast<int>(D / (2 * (is_f32 ? 4 : 8))) : rms_lanes(D, is_f32 ? 4 : 8);
-    const int cw = rn_fwd_compute_warps(kvn);
-    const long long tile_rows = static_cast<long long>(cw) * (32 / lpr) * rn_rows_per_group(kvn);
+    const int s_kv = cs ? 2 : kvn;
+    const int s_lpr = cs ? static_cast<int>(D / (2 * (is_f32 ? 4 : 8))) : lpr;
+    const int cw = rn_fwd_compute_warps(s_kv);
+    const long long tile_rows = static_cast<long long>(cw) * (32 / s_lpr) * rn_rows_per_group(s_kv);
     const long long n_tiles = (rows + tile_rows - 1) / tile_rows;
     const unsigned sgb = static_cast<unsigned>(n_tiles < device_sm_count() ? n_tiles : device_sm_count());
     const size_t ssmem = rn_fwd_staged_smem(d, fused);
@@ -569,7 +569,7 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const void* res, void* h_ou
     }                                                                                              \
     rmsnorm_fwd_staged_kernel<T, R, KVN, RES><<<sgb, (cw + 1) * 32, ssmem, s>>>(                   \
         static_cast<const T*>(x), static_cast<const T*>(res), static_cast<T*>(h_out), w,           \
-        static_cast<T*>(y), ldy, rstd, rows, d, lpr, eps, cs, sn, h, sq, n_tiles, rn_knobs());     \
+        static_cast<T*>(y), ldy, rstd, rows, d, s_lpr, eps, cs, sn, h, sq, n_tiles, rn_knobs());   \
   } while (0)
 #define WSL_RNFS_RES(T, KVN)                                      \
   do {                                                            \
@@ -579,15 +579,15 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const void* res, void* h_ou
 #define WSL_RNFS_KV(T)                                            \
   do {                                                            \
     if (cs) WSL_RNFS(T, true, 2, false);                          \
-    else if (kvn == 1) WSL_RNFS_RES(T, 1);                        \
-    else if (kvn == 2) WSL_RNFS_RES(T, 2);                        \
-    else if (kvn == 4) WSL_RNFS_RES(T, 4);                        \
-    else if (kvn == 8) WSL_RNFS_RES(T, 8);                        \
+    else if (s_kv == 1) WSL_RNFS_RES(T, 1);                       \
+    else if (s_kv == 2) WSL_RNFS_RES(T, 2);                       \
+    else if (s_kv == 4) WSL_RNFS_RES(T, 4);                       \
+    else if (s_kv == 8) WSL_RNFS_RES(T, 8);                       \
     else return WSL_ERR_TOO_LARGE;                                \
   } while (0)
     if (is_f32) WSL_RNFS_KV(float);
-    else if (kvn == 10) WSL_RNFS_RES(__nv_bfloat16, 10);
-    else if (kvn == 16) WSL_RNFS_RES(__nv_bfloat16, 16);
+    else if (s_kv == 10) WSL_RNFS_RES(__nv_bfloat16, 10);
+    else if (s_kv == 16) WSL_RNFS_RES(__nv_bfloat16, 16);
     else WSL_RNFS_KV(__nv_bfloat16);
 #undef WSL_RNFS_KV
 #undef WSL_RNFS_RES
@@ -650,11 +650,11 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
   if ((fused || kvn > 8 || row_staged_enabled()) && lddy == D && ldx == D &&
       (!cs || (heads % 4 == 0 && aligned16(cs) && aligned16(sn)))) {
     // rotary rows: two half-row vectors per lane (the staged kernels' layout), else as above
-    const int kvn = cs ? 2 : static_cast<int>(D / (static_cast<long long>(lpr) * (is_f32 ? 4 : 8)));
-    const int lpr = cs ? static_cast<int>(D / (2 * (is_f32 ? 4 : 8))) : rms_lanes(D, is_f32 ? 4 : 8);
-    const int rpg = rn_rows_per_group(kvn);
-    const int cw = rn_compute_warps(kvn, kvn * (is_f32 ? 4 : 8), cs != nullptr);
-    const long long tile_rows = static_cast<long long>(cw) * (32 / lpr) * rpg;
+    const int s_kv = cs ? 2 : kvn;
+    const int s_lpr = cs ? static_cast<int>(D / (2 * (is_f32 ? 4 : 8))) : lpr;
+    const int rpg = rn_rows_per_group(s_kv);
+    const int cw = rn_compute_warps(s_kv, s_kv * (is_f32 ? 4 : 8), cs != nullptr);
+    const long long tile_rows = static_cast<long long>(cw) * (32 / s_lpr) * rpg;
     const long long n_tiles = (rows + tile_rows - 1) / tile_rows;
     const unsigned sgb = static_cast<unsigned>(n_tiles < device_sm_count() ? n_tiles : device_sm_count());
     const size_t ssmem = rn_staged_smem(d, fused);
@@ -670,7 +670,7 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
     }                                                                                              \
     rmsnorm_bwd_staged_kernel<T, R, KVN, DRES><<<sgb, (cw + 1) * 32, ssmem, s>>>(                  \
         static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(dres), w, rstd, \
-        static_cast<T*>(dx), lddx, dw, rows, d, lpr, cs, sn, h, sq, n_tiles, rn_knobs());          \
+        static_cast<T*>(dx), lddx, dw, rows, d, s_lpr, cs, sn, h, sq, n_tiles, rn_knobs());        \
   } while (0)
 #define WSL_RNS_RES(T, KVN)                                       \
   do {                                                            \
@@ -680,15 +680,15 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
 #define WSL_RNS_KV(T)                                             \
   do {                                                            \
     if (cs) WSL_RNS(T, true, 2, false);                           \
-    else if (kvn == 1) WSL_RNS_RES(T, 1);                         \
-    else if (kvn == 2) WSL_RNS_RES(T, 2);                         \
-    else if (kvn == 4) WSL_RNS_RES(T, 4);                         \
-    else if (kvn == 8) WSL_RNS_RES(T, 8);                         \
+    else if (s_kv == 1) WSL_RNS_RES(T, 1);                        \
+    else if (s_kv == 2) WSL_RNS_RES(T, 2);                        \
+    else if (s_kv == 4) WSL_RNS_RES(T, 4);                        \
+    else if (s_kv == 8) WSL_RNS_RES(T, 8);                        \
     else return WSL_ERR_TOO_LARGE;                                \
   } while (0)
     if (is_f32) WSL_RNS_KV(float);
-    else if (kvn == 10) WSL_RNS_RES(__nv_bfloat16, 10);
-    else if (kvn == 16) WSL_RNS_RES(__nv_bfloat16, 16);
+    else if (s_kv == 10) WSL_RNS_RES(__nv_bfloat16, 10);
+    else if (s_kv == 16) WSL_RNS_RES(__nv_bfloat16, 16);
     else WSL_RNS_KV(__nv_bfloat16);
 #undef WSL_RNS_KV
 #undef WSL_RNS_RES
