@@ -176,13 +176,26 @@ def test_tiny_decoder_bf16_close_to_reference_golden(golden_dir, through_layer_g
         assert rel(_grad_of(m, key[2:]), _t(g[key])) < 6e-2, (key, rel(_grad_of(m, key[2:]), _t(g[key])))
 
 
-def test_train_step_reduces_loss():
+@pytest.mark.parametrize("flat", [True, False])
+def test_train_step_reduces_loss(flat):
+    """Steps on one repeated batch: the loss falls, and after every step the bf16 copies the
+    kernels read are the optimizer's new master weights (flat arena: one refresh pass; per-
+    parameter storage: the post-optimizer hook), for every kind of parameter."""
     from weightshared_torchtitan_b200.train_step import TrainStep
     a, p, m = _build_tiny(torch.bfloat16)
-    step = TrainStep(m, lr=3e-3, weight_decay=0.0)
+    step = TrainStep(m, lr=3e-3, weight_decay=0.0, flat=flat)
     g = torch.Generator().manual_seed(0)
     tokens = torch.randint(0, a.vocab_size, (4, a.max_seq_len), generator=g).cuda()
     labels = torch.randint(0, a.vocab_size, (4, a.max_seq_len), generator=g).cuda()
-    losses = [step(tokens, labels).item() for _ in range(8)]
+    watched = {"shared W": m.blocks[0].wq.weight, "adapter A": m.layers[1].w2_offset.w_a.weight,
+               "adapter B": m.layers[3].wq_offset.w_b.weight, "head": m.output.weight,
+               "embedding": m.tok_embeddings.proj.weight}
+    losses = []
+    for _ in range(8):
+        before = {k: w.detach().clone() for k, w in watched.items()}
+        losses.append(step(tokens, labels).item())
+        for k, w in watched.items():
+            assert not torch.equal(w.detach(), before[k]), k
+            assert torch.equal(m._cache.get(torch.bfloat16, w), w.detach().to(torch.bfloat16)), k
     step.arena.check_attached()
-    assert all(np.isfinite(losses)) and losses[-1] < losses[0]
+    assert all(np.isfinite(losses)) and losses[-1] < losses[0] - 0.05, losses

@@ -115,6 +115,34 @@ def test_copy_cache_refreshes_on_update():
     assert c.get(torch.float32, p).data_ptr() == p.data_ptr()
 
 
+def test_fused_optimizers_leave_version_counters_alone_so_the_cache_must_be_told():
+    """Why the cache is bound to the arena (or cleared by the post-optimizer hook): a copy
+    keyed on the version counter alone would go stale under a fused optimizer."""
+    from weightshared_torchtitan_b200.dp import GradArena
+    from weightshared_torchtitan_b200.modules import CopyCache
+    m = nn.Sequential(nn.Linear(8, 16, bias=False), nn.Linear(16, 4, bias=False))
+    w0 = m[0].weight.detach().clone()
+    arena = GradArena(m)
+    flat = arena.flatten_parameters()
+    assert torch.equal(m[0].weight.detach(), w0) and m[0].weight.data_ptr() == flat.data_ptr()
+    assert m[1].weight.data_ptr() == flat.data_ptr() + 4 * arena.offsets[1]
+    cache = CopyCache()
+    cache.bind(arena)
+    c = cache.get(torch.bfloat16, m[0].weight)
+    assert c.shape == (16, 8) and torch.equal(c, w0.to(torch.bfloat16))
+    P = nn.Parameter(flat)
+    P.grad = arena.buffer
+    arena.buffer.fill_(1.0)
+    v0 = m[0].weight._version
+    torch.optim.AdamW([P], lr=0.1, fused=True).step()
+    assert not torch.equal(m[0].weight.detach(), w0)            # the master moved ...
+    assert m[0].weight._version == v0                            # ... and no counter noticed
+    assert torch.equal(cache.get(torch.bfloat16, m[0].weight), w0.to(torch.bfloat16))
+    arena.refresh_compute_copies()
+    assert torch.equal(cache.get(torch.bfloat16, m[0].weight), m[0].weight.detach().to(torch.bfloat16))
+    assert cache.get(torch.bfloat16, m[0].weight).data_ptr() == c.data_ptr()   # same view, new values
+
+
 class _TinyAttn(nn.Module):
     def __init__(self):
         super().__init__()

@@ -231,6 +231,12 @@ class WeightSharedDecoder(nn.Module):
         self.output.weight.copy_(p["output"])
 
     # ------------------------------------------------------------------------ helpers
+    def post_optimizer_hook(self) -> None:
+        """The master weights changed: drop the compute-dtype copies so that the next forward
+        re-casts them (the reference's post_optimizer_hook slot, torchtitan/train.py:494-497).
+        A cache bound to a flat arena is refreshed by the arena's owner instead."""
+        self._cache.clear()
+
     @staticmethod
     def _sink(p: torch.Tensor) -> torch.Tensor:
         if p.grad is None:

@@ -55,6 +55,45 @@ class GradArena:
             p.grad = self.buffer[off:off + p.numel()].view(p.shape)
         self.group = process_group
         self.section_bounds = self._sections()
+        self.master: Optional[torch.Tensor] = None      # flat fp32 parameters (flatten_parameters)
+        self._copies = {}                                # dtype -> flat compute copy of `master`
+        self._slot = {id(p): (off, p.numel()) for p, off in zip(self.params, self.offsets)}
+
+    # ------------------------------------------------------------- flat master parameters
+    def flatten_parameters(self) -> torch.Tensor:
+        """Moves every parameter into ONE flat fp32 buffer with the arena's layout (param.data
+        becomes a view of it), so that the optimizer, the clip and the refresh of the
+        compute-dtype copies each run as one pass over one tensor. Call it before the optimizer
+        is built. Returns the flat buffer."""
+        if self.master is None:
+            self.master = torch.zeros_like(self.buffer)
+            with torch.no_grad():
+                for p, off in zip(self.params, self.offsets):
+                    v = self.master[off:off + p.numel()].view(p.shape)
+                    v.copy_(p.data)
+                    p.data = v
+        return self.master
+
+    def compute_view(self, p: torch.Tensor, dtype: torch.dtype) -> Optional[torch.Tensor]:
+        """The compute-dtype copy of parameter `p` as a view of one flat buffer that
+        refresh_compute_copies() re-casts from the master in a single pass; None when `p` is
+        not in the arena or the parameters have not been flattened."""
+        slot = self._slot.get(id(p))
+        if slot is None or self.master is None:
+            return None
+        buf = self._copies.get(dtype)
+        if buf is None:
+            buf = self.master.to(dtype)
+            self._copies[dtype] = buf
+        off, n = slot
+        return buf[off:off + n].view(p.shape)
+
+    def refresh_compute_copies(self) -> None:
+        """After the optimizer changed the master parameters: one cast kernel per compute dtype
+        (fused optimizers do not bump the tensors' version counters, so nothing else would
+        notice the change)."""
+        for buf in self._copies.values():
+            buf.copy_(self.master)
 
     def _sections(self) -> List[Tuple[str, int, int]]:
         """(label, begin, end) element ranges of the four layout classes."""

@@ -52,16 +52,33 @@ class CopyCache:
     The reference runs fp32 master weights under torch.autocast(bfloat16)
     (torchtitan/distributed/utils.py:219-239), which re-casts every weight on every use. A
     base weight shared by L layers would be cast L times per pass; this cache casts once per
-    optimizer step (tensor version counter) and hands every user the same bf16 tensor.
+    optimizer step and hands every user the same bf16 tensor.
+
+    A copy is re-cast when the parameter's version counter or address changed. Fused and
+    foreach optimizers update parameters WITHOUT bumping the version counter, so whoever runs
+    the optimizer step must also call clear() (the reference's post_optimizer_hook slot does),
+    or bind() the cache to a source that refreshes all copies in one pass.
     """
 
     def __init__(self):
         self._store: Dict[Tuple[int, ...], Tuple[Tuple[int, ...], torch.Tensor]] = {}
+        self._source = None
+
+    def bind(self, source) -> None:
+        """`source.compute_view(param, dtype)` (dp.GradArena with flattened parameters) then
+        supplies the copies: views of one flat buffer that the owner of the optimizer step
+        re-casts in a single pass, instead of one cast per parameter keyed on its version."""
+        self._source = source
+        self._store.clear()
 
     def get(self, dtype: torch.dtype, *params: torch.Tensor) -> torch.Tensor:
         """Copy of `params` (concatenated along dim 0 if several) in `dtype`."""
         if len(params) == 1 and params[0].dtype == dtype:
             return params[0].detach()
+        if self._source is not None and len(params) == 1:
+            v = self._source.compute_view(params[0], dtype)
+            if v is not None:
+                return v
         key = tuple(id(p) for p in params) + (hash(dtype),)
         ver = tuple(p._version for p in params) + tuple(p.data_ptr() for p in params)
         hit = self._store.get(key)
