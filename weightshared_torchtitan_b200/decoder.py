@@ -233,7 +233,7 @@ class WeightSharedDecoder(nn.Module):
     # ------------------------------------------------------------------------ helpers
     def post_optimizer_hook(self) -> None:
         """The master weights changed: drop the compute-dtype copies so that the next forward
-        re-casts them (the reference's post_optimizer_hook slot, torchtitan/train.py:494-497).
+        re-casts them (the reference's post_optimizer_hook slot, torchtitan/train.py:288-295).
         A cache bound to a flat arena is refreshed by the arena's owner instead."""
         self._cache.clear()
 
