@@ -113,6 +113,15 @@ def test_copy_cache_refreshes_on_update():
     cat = c.get(torch.bfloat16, p, q)
     assert cat.shape == (6, 4)
     assert c.get(torch.float32, p).data_ptr() == p.data_ptr()
+    # a fused optimizer moves the parameter without touching its version counter: the global
+    # post-step hook drops the copy all the same
+    before = c.get(torch.bfloat16, p)
+    p.grad = torch.ones_like(p)
+    v = p._version
+    torch.optim.AdamW([p], lr=0.5, fused=True).step()
+    assert p._version == v
+    after = c.get(torch.bfloat16, p)
+    assert after is not before and torch.equal(after, p.detach().to(torch.bfloat16))
 
 
 def test_fused_optimizers_leave_version_counters_alone_so_the_cache_must_be_told():

@@ -20,10 +20,12 @@ All compute goes through libwsl.so; CPU tensors raise.
 from __future__ import annotations
 
 import math
+import weakref
 from typing import Dict, Optional, Tuple
 
 import torch
 import torch.nn as nn
+from torch.optim.optimizer import register_optimizer_step_post_hook
 
 from . import functional as WF
 from . import ops
@@ -55,14 +57,19 @@ class CopyCache:
     optimizer step and hands every user the same bf16 tensor.
 
     A copy is re-cast when the parameter's version counter or address changed. Fused and
-    foreach optimizers update parameters WITHOUT bumping the version counter, so whoever runs
-    the optimizer step must also call clear() (the reference's post_optimizer_hook slot does),
-    or bind() the cache to a source that refreshes all copies in one pass.
+    foreach optimizers update parameters WITHOUT bumping the version counter, so the copies of
+    every cache that is not bound to a source are also dropped after EVERY optimizer step of
+    the process (a global post-step hook, registered below); the reference's
+    post_optimizer_hook slot does the same explicitly. A cache bound with bind() is refreshed
+    by the owner of its source in one pass instead.
     """
+
+    _live: "weakref.WeakSet[CopyCache]" = weakref.WeakSet()
 
     def __init__(self):
         self._store: Dict[Tuple[int, ...], Tuple[Tuple[int, ...], torch.Tensor]] = {}
         self._source = None
+        CopyCache._live.add(self)
 
     def bind(self, source) -> None:
         """`source.compute_view(param, dtype)` (dp.GradArena with flattened parameters) then
@@ -93,6 +100,13 @@ class CopyCache:
     def clear(self) -> None:
         self._store.clear()
 
+
+def _drop_copies_after_optimizer_step(optimizer, args, kwargs) -> None:
+    for cache in list(CopyCache._live):
+        cache.clear()
+
+
+register_optimizer_step_post_hook(_drop_copies_after_optimizer_step)
 
 GLOBAL_COPY_CACHE = CopyCache()
 
