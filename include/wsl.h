@@ -348,6 +348,28 @@ int wsl_add_rmsnorm_bwd(const void* dy, const void* h, const void* dres, const f
                         const float* rstd, void* dx, float* dw, long long rows, long long D,
                         int dtype, void* stream);
 
+/*
+ * The optimizer step over flat fp32 arenas (parameters p, gradients g, AdamW moments m and v,
+ * n elements each, the same layout): global-norm clipping, AdamW with decoupled weight decay
+ * and the refresh of the bf16 compute copy of the parameters, in one pass over the gradients
+ * (wsl_grad_sumsq_partials: WSL_SUMSQ_PARTIALS partial sums of g^2, fixed order) and one pass
+ * over everything (wsl_adamw_flat_step: folds the partials into the norm, then per element
+ *   g' = g * min(1, max_norm / (norm + 1e-6));  m = b1 m + (1-b1) g';  v = b2 v + (1-b2) g'^2;
+ *   p = p (1 - lr wd) - (lr / bias_corr1) m / (sqrt(v) / sqrt(bias_corr2) + eps),
+ * bias_corr = 1 - beta^t from the host; p_copy, if not NULL, receives p as bf16).
+ * max_norm <= 0 skips the clip (partials may then be NULL). n a multiple of 4, 16-byte
+ * aligned buffers. g itself is left as it is (not scaled in place).
+ * Replaces torch.nn.utils.clip_grad_norm_ + torch.optim.AdamW.step + the per-use weight casts
+ * of autocast: torchtitan/distributed/utils.py:316-394, torchtitan/components/optimizer.py:243-326,
+ * torchtitan/train.py:479-497.
+ */
+#define WSL_SUMSQ_PARTIALS 1184
+int wsl_grad_sumsq_partials(const float* g, long long n, float* partials, void* stream);
+int wsl_adamw_flat_step(float* p, const float* g, float* m, float* v, void* p_copy, long long n,
+                        float lr, float beta1, float beta2, float eps, float weight_decay,
+                        float bias_corr1, float bias_corr2, const float* sumsq_partials,
+                        int n_partials, float max_norm, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -199,3 +199,33 @@ def test_train_step_reduces_loss(flat):
             assert torch.equal(m._cache.get(torch.bfloat16, w), w.detach().to(torch.bfloat16)), k
     step.arena.check_attached()
     assert all(np.isfinite(losses)) and losses[-1] < losses[0] - 0.05, losses
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-4), (torch.bfloat16, 2e-2)])
+def test_several_training_steps_follow_the_oracle(dtype, tol):
+    """Five optimisation steps (clip 1.0, AdamW, weight decay) of the decoder on the GPU against
+    the same five steps of the CPU oracle with torch.optim.AdamW on its fp32 parameters: the
+    loss curves must coincide, which they only do if every step computes with the weights the
+    previous step produced."""
+    from weightshared_torchtitan_b200.train_step import TrainStep
+    a, p, m = _build_tiny(dtype)
+    g = torch.Generator().manual_seed(3)
+    tokens = torch.randint(0, a.vocab_size, (4, a.max_seq_len), generator=g)
+    labels = torch.randint(0, a.vocab_size, (4, a.max_seq_len), generator=g)
+    lr, wd = 3e-3, 0.1
+    # oracle: plain autograd + AdamW over the parameter dictionary
+    po = {k: v.detach().clone().requires_grad_(True) for k, v in p.items()}
+    opt = torch.optim.AdamW(list(po.values()), lr=lr, betas=(0.9, 0.95), eps=1e-8, weight_decay=wd)
+    want = []
+    for _ in range(5):
+        opt.zero_grad()
+        loss = O.decoder_loss(a, po, tokens, labels)
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(list(po.values()), 1.0)
+        opt.step()
+        want.append(loss.item())
+    step = TrainStep(m, lr=lr, weight_decay=wd, max_norm=1.0)
+    got = [step(tokens.cuda(), labels.cuda()).item() for _ in range(5)]
+    assert want[-1] < want[0] - 0.02          # the curve moves, so stale weights would show
+    for w, x in zip(want, got):
+        assert abs(w - x) < tol * abs(w), (want, got)

@@ -213,3 +213,33 @@ def test_residual_add_folded_into_the_norm(dtype, tol, D, rows):
     xr2, rr2 = leaf(x, "cuda", dtype=torch.float32), leaf(res, "cuda", dtype=torch.float32)
     F.rms_norm(xr2 + rr2, (D,), wr.detach(), 1e-6).backward(dy.cuda().float())
     assert rel(xc2.grad, xr2.grad) < tol
+
+
+@pytest.mark.parametrize("max_norm", [None, 1.0, 1e9])
+def test_flat_adamw_step_matches_torch(max_norm):
+    """Clip + AdamW + bf16 copy in one pass over flat arenas against clip_grad_norm_ and
+    torch.optim.AdamW on the same numbers, three steps."""
+    from weightshared_torchtitan_b200 import ops
+    g = torch.Generator().manual_seed(17)
+    n = 4 * 70_001
+    p0 = torch.randn(n, generator=g)
+    lr, b1, b2, eps, wd = 3e-3, 0.9, 0.95, 1e-8, 0.1
+    pr = torch.nn.Parameter(p0.clone())
+    opt = torch.optim.AdamW([pr], lr=lr, betas=(b1, b2), eps=eps, weight_decay=wd)
+    p = p0.clone().cuda()
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    copy = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    for step in range(1, 4):
+        grad = torch.randn(n, generator=g) * (0.5 if step != 2 else 1e-3)
+        pr.grad = grad.clone()
+        if max_norm is not None:
+            want_norm = torch.nn.utils.clip_grad_norm_([pr], max_norm)
+        opt.step()
+        gc = grad.cuda()
+        partials = ops.grad_sumsq_partials(gc) if max_norm is not None else None
+        ops.adamw_flat_step(p, gc, m, v, copy, lr, b1, b2, eps, wd, step, partials, max_norm)
+        if max_norm is not None:
+            assert abs(partials.sum().sqrt().item() - want_norm.item()) < 1e-5 * want_norm.item()
+        assert torch.equal(gc.cpu(), grad)                      # gradients are left as they were
+        assert rel(p, pr.detach()) < 2e-6
+        assert torch.equal(copy, p.to(torch.bfloat16))

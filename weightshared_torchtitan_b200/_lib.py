@@ -61,6 +61,8 @@ SIGNATURES = {
     "wsl_rmsnorm_fwd": (_i, [_vp, _ll, _vp, _vp, _ll, _vp, _ll, _ll, _f, _vp, _vp, _ll, _ll, _i, _vp]),
     "wsl_rmsnorm_bwd": (_i, [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _i, _vp]),
     "wsl_add_rmsnorm_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _f, _i, _vp]),
+    "wsl_grad_sumsq_partials": (_i, [_vp, _ll, _vp, _vp]),
+    "wsl_adamw_flat_step": (_i, [_vp, _vp, _vp, _vp, _vp, _ll, _f, _f, _f, _f, _f, _f, _f, _vp, _i, _f, _vp]),
     "wsl_add_rmsnorm_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _vp]),
     "wsl_embed_fwd": (_i, [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _vp]),
     "wsl_embed_bwd_dproj": (_i, [_vp, _vp, _ll, _vp, _vp, _ll, _ll, _ll, _ll, _vp, ctypes.c_ulonglong, _vp]),

@@ -7,6 +7,7 @@
 #include "static_scratch.cu"
 #include "elementwise.cu"
 #include "lora_merge.cu"
+#include "flat_adamw.cu"
 
 namespace wsl {
 int launch_simt_gemm_f32(const float* A, long long sai, long long sak, const float* B,
@@ -628,6 +629,19 @@ int wsl_rmsnorm_fwd(const void* x, long long ldx, const float* w, void* y, long 
   if (bad_dtype(dtype)) return WSL_ERR_BAD_ARG;
   return launch_rmsnorm_fwd(x, ldx, nullptr, nullptr, w, y, ldy, rstd, rows, D, eps, rope_cos, rope_sin,
                             heads, seq, dtype == WSL_F32, static_cast<cudaStream_t>(stream));
+}
+
+int wsl_grad_sumsq_partials(const float* g, long long n, float* partials, void* stream) {
+  return launch_grad_sumsq(g, n, partials, static_cast<cudaStream_t>(stream));
+}
+
+int wsl_adamw_flat_step(float* p, const float* g, float* m, float* v, void* p_copy, long long n,
+                        float lr, float beta1, float beta2, float eps, float weight_decay,
+                        float bias_corr1, float bias_corr2, const float* sumsq_partials,
+                        int n_partials, float max_norm, void* stream) {
+  const AdamwArgs a = {lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, max_norm};
+  return launch_adamw_flat(p, g, m, v, p_copy, n, a, sumsq_partials, n_partials,
+                           static_cast<cudaStream_t>(stream));
 }
 
 int wsl_add_rmsnorm_fwd(const void* x, const void* res, const float* w, void* h, void* y, float* rstd,

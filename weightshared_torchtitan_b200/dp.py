@@ -81,19 +81,24 @@ class GradArena:
         slot = self._slot.get(id(p))
         if slot is None or self.master is None:
             return None
+        off, n = slot
+        return self.compute_buffer(dtype)[off:off + n].view(p.shape)
+
+    def compute_buffer(self, dtype: torch.dtype) -> torch.Tensor:
+        """The flat compute copy in `dtype` (created on first use)."""
         buf = self._copies.get(dtype)
         if buf is None:
             buf = self.master.to(dtype)
             self._copies[dtype] = buf
-        off, n = slot
-        return buf[off:off + n].view(p.shape)
+        return buf
 
-    def refresh_compute_copies(self) -> None:
+    def refresh_compute_copies(self, skip: Optional[torch.Tensor] = None) -> None:
         """After the optimizer changed the master parameters: one cast kernel per compute dtype
         (fused optimizers do not bump the tensors' version counters, so nothing else would
-        notice the change)."""
+        notice the change). `skip`: a copy the optimizer kernel has already rewritten."""
         for buf in self._copies.values():
-            buf.copy_(self.master)
+            if buf is not skip:
+                buf.copy_(self.master)
 
     def _sections(self) -> List[Tuple[str, int, int]]:
         """(label, begin, end) element ranges of the four layout classes."""

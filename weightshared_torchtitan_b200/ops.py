@@ -648,3 +648,44 @@ def add_rmsnorm_bwd(dy2: torch.Tensor, h2: torch.Tensor, dres2: torch.Tensor, w:
     _toc(_e, "rmsnorm_bwd", 0.0, 4.0 * h2.element_size() * rows * D)
     _lib.check(st, "wsl_add_rmsnorm_bwd")
     return dx
+
+
+SUMSQ_PARTIALS = 1184   # WSL_SUMSQ_PARTIALS
+
+
+def grad_sumsq_partials(g: torch.Tensor, partials: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Partial sums of g^2 over a flat fp32 buffer (fixed grid, fixed order); their sum is the
+    squared global gradient norm."""
+    if not g.is_cuda or g.dtype != torch.float32 or not g.is_contiguous():
+        raise TypeError("g must be a contiguous CUDA float32 tensor")
+    if partials is None:
+        partials = torch.empty(SUMSQ_PARTIALS, device=g.device, dtype=torch.float32)
+    _e = _tic()
+    st = _lib.lib().wsl_grad_sumsq_partials(g.data_ptr(), g.numel(), partials.data_ptr(), _stream())
+    _toc(_e, "grad_sumsq", 0.0, 4.0 * g.numel())
+    _lib.check(st, "wsl_grad_sumsq_partials")
+    return partials
+
+
+def adamw_flat_step(p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor,
+                    p_copy: Optional[torch.Tensor], lr: float, beta1: float, beta2: float, eps: float,
+                    weight_decay: float, step: int, partials: Optional[torch.Tensor],
+                    max_norm: Optional[float]) -> None:
+    """Clip by the global norm (from `partials`), AdamW step number `step` (1-based) on the flat
+    fp32 buffers, and the bf16 copy of the new parameters, in one pass."""
+    for t in (p, g, m, v):
+        if not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != p.numel():
+            raise TypeError("p, g, m, v must be contiguous CUDA float32 tensors of one size")
+    if p_copy is not None and (p_copy.dtype != torch.bfloat16 or p_copy.numel() != p.numel()
+                               or not p_copy.is_contiguous()):
+        raise TypeError("p_copy must be a contiguous bfloat16 tensor of the size of p")
+    clip = max_norm is not None and max_norm > 0
+    _e = _tic()
+    st = _lib.lib().wsl_adamw_flat_step(
+        p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(),
+        p_copy.data_ptr() if p_copy is not None else None, p.numel(), float(lr), float(beta1), float(beta2),
+        float(eps), float(weight_decay), 1.0 - beta1 ** step, 1.0 - beta2 ** step,
+        partials.data_ptr() if clip else None, partials.numel() if clip else 0,
+        float(max_norm) if clip else 0.0, _stream())
+    _toc(_e, "adamw", 0.0, 30.0 * p.numel())
+    _lib.check(st, "wsl_adamw_flat_step")
