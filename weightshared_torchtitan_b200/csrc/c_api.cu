@@ -95,7 +95,7 @@ using namespace wsl;
 
 extern "C" {
 
-int wsl_version(void) { return (0 << 16) | 3; }
+int wsl_version(void) { return (0 << 16) | 4; }
 
 const char* wsl_status_string(int status) {
   switch (status) {
