@@ -597,6 +597,45 @@ def test_adapter_gradients_of_a_whole_layer_in_one_call(wsl):
         assert rel(dBs[p] - 0.5, s * Gs[p].float() @ As[p].float().T) < 1e-4
 
 
+def test_adapter_gradient_batch_with_a_group_on_the_direct_formulation(wsl):
+    """One group goes through its weight gradient, the other computes dA/dB directly: the
+    second still reports to the batch, which therefore runs as soon as both are done (inside
+    the backward pass, not from the end-of-pass callback)."""
+    from weightshared_torchtitan_b200 import functional as Fn
+    g = torch.Generator().manual_seed(77)
+    bf = torch.bfloat16
+    M, K, r, s = 1024, 512, 16, 2.0
+    x = torch.randn(M, K, generator=g).to(bf)
+    xc = x.cuda().requires_grad_(True)
+    batch = Fn.AdapterGradBatch(2)
+    saved = Fn.DERIVED_ADAPTER_GRADS
+    outs, dYs_all, all_sinks, want = [], [], [], []
+    try:
+        for n, derived in ((768, True), (256, False)):
+            Fn.DERIVED_ADAPTER_GRADS = derived
+            W = (torch.randn(n, K, generator=g) * 0.03).to(bf)
+            A = (torch.randn(r, K, generator=g) * 0.05).to(bf)
+            B = (torch.randn(n, r, generator=g) * 0.1).to(bf)
+            dY = (torch.randn(M, n, generator=g) * 0.1).to(bf)
+            want.append(oracle_projection(x, W, A, B, dY))
+            sinks = [(torch.zeros(n, K, device="cuda"), torch.zeros(r, K, device="cuda"),
+                      torch.zeros(n, r, device="cuda"))]
+            outs += list(Fn.lora_linear_group(xc, [W.cuda()], [A.cuda()], [B.cuda()], s, sinks, (), batch))
+            dYs_all.append(dY.cuda())
+            all_sinks += sinks
+    finally:
+        Fn.DERIVED_ADAPTER_GRADS = saved
+    flushed_inside = []
+    real_flush = batch.flush
+    batch.flush = lambda: (flushed_inside.append(len(batch.pending)), real_flush())[1]
+    torch.autograd.backward(outs, dYs_all)
+    assert flushed_inside and flushed_inside[0] == 1 and not batch.pending
+    assert rel(xc.grad, sum(w[1] for w in want)) < TOL_BF16
+    for sk, w in zip(all_sinks, want):
+        for got, ref in zip(sk, w[2:]):
+            assert rel(got, ref) < TOL_BF16
+
+
 @pytest.mark.parametrize("expected", [2, 3])
 def test_adapter_gradient_batch_across_groups(wsl, expected):
     """Two projection groups share an AdapterGradBatch: with expected = 2 it runs when the

@@ -80,8 +80,17 @@ class AdapterGradBatch:
         if self.count >= self.expected:
             self.flush()
 
+    def nothing_to_add(self) -> None:
+        """A group that computed its adapter gradients itself (direct formulation) still counts,
+        so that the others do not wait for the end of the backward pass."""
+        self.count += 1
+        if self.count >= self.expected:
+            self.flush()
+
     def flush(self) -> None:
         todo, self.pending, self.count = self.pending, [], 0
+        if not todo:
+            return
         for i in range(0, len(todo), ops.MAX_ADAPTER_PROJ):
             g, a, b, da, db = zip(*todo[i:i + ops.MAX_ADAPTER_PROJ])
             ops.lora_adapter_grads_from_dw(g, a, b, da, db, self.s)
@@ -141,6 +150,8 @@ class LoRALinearGroupFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *dYs):
         if ctx.empty:
+            if ctx.batch is not None:
+                ctx.batch.nothing_to_add()
             wab = ctx.saved_tensors
             dX = wab[0].new_zeros(ctx.x_shape) if ctx.needs_input_grad[0] else None
             grads = [None] * (3 * ctx.P)
@@ -175,6 +186,8 @@ class LoRALinearGroupFunction(torch.autograd.Function):
                 ops.lora_adapter_grads_from_dw(dWls, As, Bs, [t[1] for t in ctx.sinks],
                                                [t[2] for t in ctx.sinks], ctx.s)
             return (dX, None, None, None, None, *([None] * (3 * P)))
+        if ctx.batch is not None:
+            ctx.batch.nothing_to_add()
         dY2, Us = [], []
         # the U of all projections side by side, so that dX contracts [U_0 | U_1 | ...] with
         # the stacked A matrices in ONE rank-sum segment instead of one tiny segment each
