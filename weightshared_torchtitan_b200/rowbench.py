@@ -5,7 +5,8 @@ L2 flushed by a read of a 256 MB buffer between iterations).
     python -m weightshared_torchtitan_b200.rowbench --what rmsnorm --iters 1 --tokens 8192
 
 Prints one JSON line per kernel and shape: microseconds and GB/s over the algorithmic bytes
-(RMSNorm forward 2 passes, backward 3; SwiGLU 3 / 5; cross-entropy 3). `--what` / `--iters`
+(RMSNorm forward 2 passes, backward 3; SwiGLU 3 / 5; cross-entropy 3; optimizer step 4 B per
+parameter for the norm, 30 B for clip + AdamW + bf16 copy). `--what` / `--iters`
 give the small single-launch runs that ncu captures are taken from.
 """
 from __future__ import annotations
@@ -41,7 +42,7 @@ def main():
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=2)
-    ap.add_argument("--what", default="all", choices=["all", "rmsnorm", "swiglu", "ce"])
+    ap.add_argument("--what", default="all", choices=["all", "rmsnorm", "swiglu", "ce", "adamw"])
     args = ap.parse_args()
     M, S = args.tokens, args.seq
     bf = torch.bfloat16
@@ -80,6 +81,20 @@ def main():
         nb = logits.numel() * 2
         t = time_us(lambda: ops.ce_fwd_bwd(logits, labels, 1.0 / rows), args.iters, args.warmup)
         print(json.dumps({"kernel": "ce_fwd_bwd", "rows": rows, "V": V, "us": t, "gbs": 3 * nb / t / 1e3}), flush=True)
+
+
+    if args.what in ("all", "adamw"):
+        n = 64 * 1024 * 1024 if args.what == "adamw" and args.iters == 1 else 268 * 1000 * 1000
+        p = torch.randn(n, device="cuda")
+        g = torch.randn(n, device="cuda")
+        m, v = torch.zeros_like(p), torch.zeros_like(p)
+        copy = torch.empty(n, device="cuda", dtype=bf)
+        part = torch.empty(ops.SUMSQ_PARTIALS, device="cuda")
+        ts = time_us(lambda: ops.grad_sumsq_partials(g, part), args.iters, args.warmup)
+        ta = time_us(lambda: ops.adamw_flat_step(p, g, m, v, copy, 3e-4, 0.9, 0.95, 1e-8, 0.1, 5, part, 1.0),
+                     args.iters, args.warmup)
+        print(json.dumps({"kernel": "flat optimizer step", "n": n, "sumsq_us": ts, "sumsq_gbs": 4.0 * n / ts / 1e3,
+                          "adamw_us": ta, "adamw_gbs": 30.0 * n / ta / 1e3}), flush=True)
 
 
 if __name__ == "__main__":
