@@ -42,7 +42,7 @@ def main():
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=2)
-    ap.add_argument("--what", default="all", choices=["all", "rmsnorm", "swiglu", "ce", "adamw"])
+    ap.add_argument("--what", default="all", choices=["all", "rmsnorm", "swiglu", "ce", "adamw", "embed"])
     args = ap.parse_args()
     M, S = args.tokens, args.seq
     bf = torch.bfloat16
@@ -83,6 +83,19 @@ def main():
         print(json.dumps({"kernel": "ce_fwd_bwd", "rows": rows, "V": V, "us": t, "gbs": 3 * nb / t / 1e3}), flush=True)
 
 
+    if args.what in ("all", "embed"):
+        # factorized embedding of configuration 1: gather from E_small [V, r_e] alone, and fused
+        # into the projection GEMM (rows fetched by TMA gather4 inside the producer)
+        V, r_e, d = 151936, 256, 1024
+        tok = torch.randint(0, V, (M,), device="cuda")
+        E = torch.randn(V, r_e, device="cuda").to(bf)
+        P = (torch.randn(d, r_e, device="cuda") * 0.02).to(bf)
+        tg = time_us(lambda: ops.embed_gather(tok, E), args.iters, args.warmup)
+        tf = time_us(lambda: ops.embed_fwd(tok, E, P), args.iters, args.warmup)
+        print(json.dumps({"kernel": "embedding", "tokens": M, "V": V, "r_e": r_e, "d": d,
+                          "gather_us": tg, "gather_gbs": (8.0 * M + 4.0 * M * r_e) / tg / 1e3,
+                          "fused_fwd_us": tf, "fused_fwd_gbs": (8.0 * M + 2.0 * M * (r_e + d)) / tf / 1e3,
+                          "fused_fwd_tflops": 2.0 * M * r_e * d / tf / 1e6}), flush=True)
     if args.what in ("all", "adamw"):
         n = 64 * 1024 * 1024 if args.what == "adamw" and args.iters == 1 else 268 * 1000 * 1000
         p = torch.randn(n, device="cuda")
