@@ -268,3 +268,73 @@ def test_rmsnorm_supported_widths():
     assert not ops.rmsnorm_supported(5120, bf) and not ops.rmsnorm_supported(2560, f32)
     assert ops.rmsnorm_supported(128, bf, rope=True) and not ops.rmsnorm_supported(512, bf, rope=True)
     assert ops.rmsnorm_supported(1024, f32) and not ops.rmsnorm_supported(2048, f32)
+
+
+class _QAttn(nn.Module):
+    def __init__(self, dim, heads, kv, hd):
+        super().__init__()
+        self.wq = nn.Linear(dim, heads * hd, bias=False)
+        self.wk = nn.Linear(dim, kv * hd, bias=False)
+        self.wv = nn.Linear(dim, kv * hd, bias=False)
+        self.wo = nn.Linear(heads * hd, dim, bias=False)
+        self.q_norm, self.k_norm = nn.RMSNorm(hd), nn.RMSNorm(hd)
+
+
+class _QFfn(nn.Module):
+    def __init__(self, dim, hidden):
+        super().__init__()
+        self.w1, self.w2, self.w3 = (nn.Linear(dim, hidden, bias=False), nn.Linear(hidden, dim, bias=False),
+                                     nn.Linear(dim, hidden, bias=False))
+
+
+class _QBlock(nn.Module):
+    def __init__(self, dim, hidden, heads, kv, hd):
+        super().__init__()
+        self.attention, self.feed_forward = _QAttn(dim, heads, kv, hd), _QFfn(dim, hidden)
+        self.attention_norm, self.ffn_norm = nn.RMSNorm(dim), nn.RMSNorm(dim)
+
+
+class _QModel(nn.Module):
+    """Module tree with the attribute names of the reference's Qwen3Model."""
+
+    def __init__(self, vocab, dim, hidden, n_layers, heads, kv, hd):
+        super().__init__()
+        self.tok_embeddings = nn.Embedding(vocab, dim)
+        self.layers = nn.ModuleDict({str(i): _QBlock(dim, hidden, heads, kv, hd) for i in range(n_layers)})
+        self.norm = nn.RMSNorm(dim)
+        self.output = nn.Linear(dim, vocab, bias=False)
+
+
+def test_state_dict_round_trip_with_the_converted_reference_layout():
+    """The decoder's parameters under the converted reference model's names load strictly into
+    such a model (same keys, same shapes, shared bases aliased the same way), come back
+    unchanged, and de-duplicate to one tensor per unique block."""
+    from weightshared_torchtitan_b200 import converter as C
+    from weightshared_torchtitan_b200 import state_dict_adapter as A
+    from weightshared_torchtitan_b200.decoder import DecoderConfig, WeightSharedDecoder
+    c = DecoderConfig(dim=64, hidden_dim=160, n_layers=4, n_unique=2, n_heads=4, n_kv_heads=2, head_dim=16,
+                      rank=8, vocab_size=512, embed_rank=32, max_seq_len=24, loss_chunk=32)
+    torch.manual_seed(0)
+    dec = WeightSharedDecoder(c)
+    for p in dec.parameters():
+        nn.init.normal_(p, 0.0, 0.1)
+    ref = _QModel(512, 64, 160, 4, 4, 2, 16)
+    job = types.SimpleNamespace(model=types.SimpleNamespace(converters=["shared_lora"]),
+                                shared_lora=types.SimpleNamespace(n_unique=2, rank=8, embed_rank=32))
+    C.build_model_converters(job, None).convert(ref)
+    sd = A.to_reference(dec)
+    assert set(sd) == set(ref.state_dict())
+    ref.load_state_dict(sd, strict=True)
+    assert sd["layers.0.attention.wq.base.weight"] is sd["layers.2.attention.wq.base.weight"]
+    assert ref.layers["0"].attention.wq.base is ref.layers["2"].attention.wq.base
+    unique, aliases = A.deduplicate(sd)
+    assert len(aliases) == 7 * (4 - 2) and len(unique) + len(aliases) == len(sd)
+    assert set(A.expand(unique, aliases)) == set(sd)
+    dec2 = WeightSharedDecoder(c)
+    A.from_reference(dec2, ref.state_dict())
+    for (k, a), (_, b) in zip(dec.named_parameters(), dec2.named_parameters()):
+        assert torch.equal(a, b), k
+    bad = {k: v.clone() for k, v in ref.state_dict().items()}
+    bad["layers.2.attention.wq.base.weight"] += 1.0
+    with pytest.raises(ValueError):
+        A.from_reference(WeightSharedDecoder(c), bad)
