@@ -72,6 +72,32 @@ int wsl_poll_status(int words[4]);
 int wsl_reset_status(void);
 
 /*
+ * Run-time options of the library (process-wide). Initial values come from the environment,
+ * read once when the library is first used: WSL_PAIR (PAIR_TILES), WSL_ROW_STAGED
+ * (ROW_STAGED), WSL_WAIT_LIMIT_MS (WAIT_LIMIT_MS). wsl_set_option returns WSL_OK or
+ * WSL_ERR_BAD_ARG; wsl_get_option returns the value.
+ *   WAIT_LIMIT_MS   bound of every device-side wait, 1..10000 ms (default 2000)
+ *   STALL_PRODUCER  test aid: the copy-issuing warps never fill their rings, so the waits
+ *                   of the other warps run into the bound and WSL_ERR_TIMEOUT is recorded
+ *   PAIR_TILES      0 keeps the large GEMMs on single CTAs instead of CTA pairs
+ *   ROW_STAGED      0 sends the RMSNorm calls to their direct (non-staged) kernels
+ *   RESERVED_SMS    0..64 SMs the persistent kernels leave unoccupied, for a collective that
+ *                   runs beside them on another stream (the gradient all-reduce overlapped
+ *                   with the backward pass; the reference overlaps by DDP buckets,
+ *                   torchtitan/models/llama3/infra/parallelize.py:428-444)
+ *   PROFILE_BITS    only honoured by builds compiled with -DWSL_PROFILE_SWITCHES
+ * No counterpart in the reference (its knobs are Python config fields).
+ */
+#define WSL_OPT_WAIT_LIMIT_MS 1
+#define WSL_OPT_STALL_PRODUCER 2
+#define WSL_OPT_PAIR_TILES 3
+#define WSL_OPT_ROW_STAGED 4
+#define WSL_OPT_RESERVED_SMS 5
+#define WSL_OPT_PROFILE_BITS 6
+int wsl_set_option(int option, long long value);
+long long wsl_get_option(int option);
+
+/*
  * y[M,N] = x[M,K] * W[N,K]^T           (plain projection, no adapter)
  * Replaces F.linear of the base projections: torchtitan/models/llama3/model/
  * model.py:392-394 and torchtitan/experiments/qwen3/model/model.py:184,218,251.
@@ -294,13 +320,16 @@ int wsl_embed_scatter_add(const long long* tokens, const void* dG, float* dE, lo
  *   row_loss[i] = logsumexp(logits[i,:]) - logits[i, labels[i]]
  *   logits[i,j] <- scale * (softmax(logits[i,:])[j] - [j == labels[i]])
  * logits is [rows, V] (pitch ld) in the storage type; a label outside [0, V) marks an
- * ignored row (zero loss, zero gradient). The caller sums row_loss and passes
- * scale = 1 / (number of counted rows).
- * Replaces F.cross_entropy(pred.flatten(0,1).float(), labels.flatten(0,1)) and its
- * backward: torchtitan/components/loss.py:18-22.
+ * ignored row (zero loss, zero gradient), as ignore_index = -100 does in the reference. The
+ * caller sums row_loss; the gradient scale is scale * (*scale_dev), where scale_dev is an
+ * optional device scalar (NULL = 1): pass 1 / (number of counted rows) in one of the two --
+ * the device scalar lets a caller derive the count from the labels without a host round trip.
+ * Replaces F.cross_entropy(pred.flatten(0,1).float(), labels.flatten(0,1)) with
+ * reduction='mean' and its backward: torchtitan/components/loss.py:18-22.
  */
 int wsl_ce_fwd_bwd(void* logits, long long ld, const long long* labels, float* row_loss,
-                   long long rows, long long V, float scale, int dtype, void* stream);
+                   long long rows, long long V, float scale, const float* scale_dev, int dtype,
+                   void* stream);
 
 /*
  * out = silu(gate) * up over n contiguous elements (n % 8 == 0 for bf16, % 4 for fp32), and

@@ -1,6 +1,7 @@
 """Token data parallelism on CPU ranks (gloo, world_size 2): the flat gradient arena is
-averaged by one all-reduce, replicas stay identical, and a rank that never joins makes the
-collective fail with an error instead of hanging."""
+averaged by one all-reduce or by buckets launched as the gradients become final, replicas
+stay identical (also the bf16 compute copies of a model already bound to a training step),
+and a rank that never joins makes the collective fail with an error instead of hanging."""
 import os
 import socket
 import sys
@@ -44,7 +45,19 @@ def _worker(rank, world, port, q):
     dist.all_gather(allp, psum)
     ok_rep = all(torch.equal(allp[0], t) for t in allp)
     b, e = shard_tokens(8, rank, world)
-    q.put((rank, ok_avg, ok_rep, (b, e)))
+    # the same exchange in buckets, driven the way backward drives it: ranks become final in
+    # ascending order; nothing may be sent before it is final, everything is averaged at the end
+    arena.buffer.copy_(base * (rank + 1))
+    sent = []
+    arena.on_bucket = sent.append
+    arena.begin_overlap(bucket_bytes=4 * 2000)
+    for r, rb, re in arena.ready_bounds:
+        arena.notify_ready(r)
+        assert arena._ov_sent <= re
+    arena.finish_overlap()
+    ok_ov = torch.allclose(arena.buffer, want, rtol=1e-6, atol=1e-6) and len(sent) >= 2 \
+        and sum(sent) == 4 * arena.buffer.numel()
+    q.put((rank, ok_avg, ok_rep, (b, e), ok_ov))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -64,6 +77,47 @@ def test_arena_all_reduce_two_ranks():
     assert [r[1] for r in res] == [True, True]
     assert [r[2] for r in res] == [True, True]
     assert [r[3] for r in res] == [(0, 4), (4, 8)]
+    assert [r[4] for r in res] == [True, True]
+
+
+def _bound_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from weightshared_torchtitan_b200.decoder import DecoderConfig, WeightSharedDecoder
+    from weightshared_torchtitan_b200.dp import broadcast_parameters
+    from weightshared_torchtitan_b200.train_step import TrainStep
+    torch.manual_seed(200 + rank)
+    m = WeightSharedDecoder(DecoderConfig(dim=32, hidden_dim=64, n_layers=2, n_unique=1, n_heads=2, n_kv_heads=1,
+                                          head_dim=16, rank=8, vocab_size=64, embed_rank=16, max_seq_len=8))
+    step = TrainStep(m)                       # binds the model's copy cache to the flat arena
+    W = m.blocks[0].wq.weight
+    stale = m._cache.get(torch.bfloat16, W).clone()     # creates the flat bf16 copy
+    broadcast_parameters(m, src=0)            # rank 1 receives other values
+    fresh = m._cache.get(torch.bfloat16, W)
+    ok = torch.equal(fresh, W.detach().to(torch.bfloat16))
+    changed = not torch.equal(fresh, stale)
+    q.put((rank, ok, changed))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_broadcast_refreshes_copies_of_a_bound_model():
+    """dp.broadcast_parameters after a TrainStep was built: the flat bf16 copy the kernels read
+    follows the received values on every rank."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_bound_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert [r[1] for r in res] == [True, True]
+    assert res[1][2] is True                  # rank 1's values really changed
 
 
 def _lonely(rank, world, port, q):

@@ -210,11 +210,17 @@ def test_grad_arena_layout_and_clip():
     m = WeightSharedDecoder(DecoderConfig(dim=32, hidden_dim=64, n_layers=4, n_unique=2, n_heads=2, n_kv_heads=1,
                                           head_dim=16, rank=8, vocab_size=64, embed_rank=16, max_seq_len=8))
     a = GradArena(m)
-    labels = [s[0] for s in a.section_bounds]
-    assert labels == ["shared", "adapters", "embedding", "other"]
-    assert a.section_bounds[0][1] == 0 and a.section_bounds[-1][2] == a.buffer.numel()
-    for (_, b0, e0), (_, b1, _) in zip(a.section_bounds, a.section_bounds[1:]):
+    # laid out in the order the gradients become final: head, (final norm, last layer), ...,
+    # (layer 1, shared block 1), (layer 0, shared block 0), embedding
+    assert [r for r, _, _ in a.ready_bounds] == [0, 1, 2, 3, 4, 5]
+    assert a.ready_bounds[0][1] == 0 and a.ready_bounds[-1][2] == a.buffer.numel()
+    for (_, b0, e0), (_, b1, _) in zip(a.ready_bounds, a.ready_bounds[1:]):
         assert e0 == b1
+    rank_of = dict(zip(a.names, (m.grad_ready_rank(n) for n in a.names)))
+    assert rank_of["output.weight"] == 0 and rank_of["norm.weight"] == 1
+    assert rank_of["layers.3.w2_offset.w_b.weight"] == 1 and rank_of["layers.0.attention_norm.weight"] == 4
+    assert rank_of["blocks.1.wq.weight"] == 3 and rank_of["blocks.0.w2.weight"] == 4
+    assert rank_of["tok_embeddings.embed.weight"] == 5
     for p, off in zip(a.params, a.offsets):
         assert off % 64 == 0 and p.grad.data_ptr() == a.buffer.data_ptr() + 4 * off
     assert len(a.params) == len(list(m.parameters()))       # shared weights appear once
@@ -249,8 +255,8 @@ def test_row_kernel_entry_points_validate_arguments():
     from weightshared_torchtitan_b200 import _lib
     lib = _lib.lib()
     bad = {_lib.WSL_ERR_BAD_ARG, _lib.WSL_ERR_DEVICE}
-    assert lib.wsl_ce_fwd_bwd(None, 8, None, None, 1, 8, 1.0, 0, None) in bad
-    assert lib.wsl_ce_fwd_bwd(None, 8, None, None, 1, 8, 1.0, 9, None) == _lib.WSL_ERR_BAD_ARG
+    assert lib.wsl_ce_fwd_bwd(None, 8, None, None, 1, 8, 1.0, None, 0, None) in bad
+    assert lib.wsl_ce_fwd_bwd(None, 8, None, None, 1, 8, 1.0, None, 9, None) == _lib.WSL_ERR_BAD_ARG
     assert lib.wsl_swiglu_fwd(None, None, None, 8, 0, None) in bad
     assert lib.wsl_swiglu_bwd(None, None, None, None, None, 8, 0, None) == _lib.WSL_ERR_BAD_ARG
     assert lib.wsl_rmsnorm_fwd(None, 8, None, None, 8, None, 1, 8, 1e-6, None, None, 0, 0, 0, None) in bad

@@ -1,16 +1,30 @@
 """The bounded device-side waits: a wait that can never be satisfied ends the kernel with
 WSL_ERR_TIMEOUT in the status words, and the CUDA context stays usable.
 
-The failure is made without faulting anything: a debug switch of the library makes the TMA
-producer skip filling the ring, so the MMA warp's wait on the `full` barrier (a flag that
-nothing sets) runs into its bound (shortened to 0.2 s here), records the status, raises the
-CTA's abort flag, and every role falls through to the normal tear-down."""
-import os
+The failure is made without faulting anything: a test option of the library
+(WSL_OPT_STALL_PRODUCER) makes the TMA producer skip filling the ring, so the MMA warp's wait
+on the `full` barrier (a flag that nothing sets) runs into its bound (shortened to 0.2 s
+here), records the status, raises the CTA's abort flag, and every role falls through to the
+normal tear-down."""
+import contextlib
 
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
+
+
+@contextlib.contextmanager
+def stalled_producer(limit_ms=200):
+    from weightshared_torchtitan_b200 import _lib
+    old = _lib.get_option(_lib.OPT_WAIT_LIMIT_MS)
+    _lib.set_option(_lib.OPT_STALL_PRODUCER, 1)
+    _lib.set_option(_lib.OPT_WAIT_LIMIT_MS, limit_ms)
+    try:
+        yield
+    finally:
+        _lib.set_option(_lib.OPT_STALL_PRODUCER, 0)
+        _lib.set_option(_lib.OPT_WAIT_LIMIT_MS, old)
 
 
 def test_wait_runs_out_status_is_reported_and_context_survives():
@@ -23,14 +37,9 @@ def test_wait_runs_out_status_is_reported_and_context_survives():
     g = torch.Generator().manual_seed(0)
     x = torch.randn(128, 64, generator=g).cuda().to(torch.bfloat16)
     W = torch.randn(64, 64, generator=g).cuda().to(torch.bfloat16)
-    os.environ["WSL_DBG"] = "64"
-    os.environ["WSL_WAIT_LIMIT_MS"] = "200"
-    try:
+    with stalled_producer():
         ops.linear_fwd(x, W)            # one tile, one CTA; returns after the bound
         torch.cuda.synchronize()        # no CUDA error: the kernel ended by itself
-    finally:
-        del os.environ["WSL_DBG"]
-        del os.environ["WSL_WAIT_LIMIT_MS"]
     st, words = _lib.poll_status()
     assert st == _lib.WSL_ERR_TIMEOUT, (st, words)
     assert words[1] in (1, 2, 3) and words[2] == 0
@@ -50,10 +59,10 @@ def test_row_kernel_wait_runs_out_and_context_survives():
     role 4 and ends; afterwards the same call computes correctly."""
     if not torch.cuda.is_available():
         pytest.fail("gpu tests need a CUDA device")
-    if os.environ.get("WSL_ROW_STAGED") == "0":
-        pytest.skip("the diagnostic switch sends these calls to the direct kernels, which have no waits")
     import torch.nn.functional as F
     from weightshared_torchtitan_b200 import _lib, ops
+    if _lib.get_option(_lib.OPT_ROW_STAGED) == 0:
+        pytest.skip("the option sends these calls to the direct kernels, which have no waits")
     lib = _lib.lib()
     torch.cuda.synchronize()
     assert lib.wsl_reset_status() == 0
@@ -64,14 +73,9 @@ def test_row_kernel_wait_runs_out_and_context_survives():
     _, rstd = ops.rmsnorm_fwd(x, w, 1e-6)
     for call in (lambda: ops.rmsnorm_fwd(x, w, 1e-6),
                  lambda: ops.rmsnorm_bwd(dy, x, w, rstd, torch.zeros(1024, device="cuda"))):
-        os.environ["WSL_DBG"] = "64"
-        os.environ["WSL_WAIT_LIMIT_MS"] = "200"
-        try:
+        with stalled_producer():
             call()
             torch.cuda.synchronize()        # no CUDA error: the kernel ended by itself
-        finally:
-            del os.environ["WSL_DBG"]
-            del os.environ["WSL_WAIT_LIMIT_MS"]
         st, words = _lib.poll_status()
         assert st == _lib.WSL_ERR_TIMEOUT, (st, words)
         assert words[1] == 4

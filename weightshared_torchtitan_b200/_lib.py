@@ -22,6 +22,14 @@ WSL_ERR_TIMEOUT = -5
 WSL_ERR_DRIVER = -6
 WSL_ERR_TOO_LARGE = -7
 
+# wsl_set_option / wsl_get_option keys
+OPT_WAIT_LIMIT_MS = 1
+OPT_STALL_PRODUCER = 2
+OPT_PAIR_TILES = 3
+OPT_ROW_STAGED = 4
+OPT_RESERVED_SMS = 5
+OPT_PROFILE_BITS = 6
+
 _vp = ctypes.c_void_p
 _ll = ctypes.c_longlong
 _i = ctypes.c_int
@@ -36,6 +44,8 @@ SIGNATURES = {
     "wsl_launch_count": (ctypes.c_ulonglong, []),
     "wsl_poll_status": (_i, [ctypes.POINTER(_i)]),
     "wsl_reset_status": (_i, []),
+    "wsl_set_option": (_i, [_i, _ll]),
+    "wsl_get_option": (_ll, [_i]),
     "wsl_linear_fwd": (_i, [_vp, _ll, _vp, _vp, _ll, _ll, _ll, _ll, _i, _i, _vp]),
     "wsl_lora_prepass": (_i, [_vp, _ll, _vp, _vp, _ll, _ll, _ll, _ll, _f, _i, _vp]),
     "wsl_lora_linear_fwd": (_i, [_vp, _ll, _vp, _vp, _ll, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _i, _vp]),
@@ -55,7 +65,7 @@ SIGNATURES = {
     "wsl_lora_adapter_grads_from_dw": (_i, [_i, _vpp, _vpp, _vpp, _vpp, _vpp, _llp, _llp, _llp, _f, _vp,
                                             ctypes.c_ulonglong, _vp]),
     "wsl_bwd_dw_workspace_bytes": (ctypes.c_ulonglong, [_ll, _ll, _ll, _ll, _i, _i, _i]),
-    "wsl_ce_fwd_bwd": (_i, [_vp, _ll, _vp, _vp, _ll, _ll, _f, _i, _vp]),
+    "wsl_ce_fwd_bwd": (_i, [_vp, _ll, _vp, _vp, _ll, _ll, _f, _vp, _i, _vp]),
     "wsl_swiglu_fwd": (_i, [_vp, _vp, _vp, _ll, _i, _vp]),
     "wsl_swiglu_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _ll, _i, _vp]),
     "wsl_rmsnorm_fwd": (_i, [_vp, _ll, _vp, _vp, _ll, _vp, _ll, _ll, _f, _vp, _vp, _ll, _ll, _i, _vp]),
@@ -116,3 +126,12 @@ def poll_status():
 
 def launch_count() -> int:
     return int(lib().wsl_launch_count())
+
+
+def set_option(option: int, value: int) -> None:
+    """Process-wide run-time option of the library (see wsl_set_option in include/wsl.h)."""
+    check(lib().wsl_set_option(option, int(value)), "wsl_set_option")
+
+
+def get_option(option: int) -> int:
+    return int(lib().wsl_get_option(option))

@@ -29,7 +29,9 @@
 #include <cudaTypedefs.h>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <cmath>
+#include <mutex>
 
 #include "../../include/wsl.h"
 
@@ -83,11 +85,11 @@ struct GemmParams {
   int stages;         // one-CTA variant: depth of the operand ring (4, or 8 in the narrow form)
   int stage_bytes;    // one-CTA variant: bytes per stage (48 KiB, or 24 KiB in the narrow form)
   float* workspace;   // [splits][rows x cols] fp32 partials per region when splits > 1
-  // Diagnostic switches (environment variable WSL_DBG, a bit mask; 0 in normal use):
-  // 1 skip epilogue stores, 2 skip TMA loads, 4 skip MMAs (time the other parts alone),
-  // 32 direct-store epilogue instead of the staged TMA store, 64 the producer never fills
-  // the ring (exercises the bounded waits).
+  // Profiling switches, a bit mask that only builds with WSL_PROFILE_SWITCHES look at (normal
+  // builds compile the tests out): 1 skip epilogue stores, 2 skip TMA loads, 4 skip MMAs (time
+  // the other parts alone), 32 direct-store epilogue instead of the staged TMA store.
   int dbg;
+  int stall_producer;                 // test aid: the producer never fills the ring (bounded waits)
   unsigned long long wait_limit_ns;   // bound of every mbarrier wait
   // Row gather (factorized embedding): when set, the rows of region 0 / segment 0's A operand
   // (gather_a, K-major) or the k-rows of its B operand (gather_b, MN-major) are the rows
@@ -315,7 +317,11 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_base_smem);
   const int units = p.total_units;
+#ifdef WSL_PROFILE_SWITCHES
   const int dbg = p.dbg;
+#else
+  constexpr int dbg = 0;
+#endif
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -334,6 +340,17 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t tx_cta = A_STAGE_BYTES + (B_MN ? b_slabs * SLAB_BYTES : b_rows * BK * 2);
       const int m0 = ti.m0 + BM * rank;
       const int n0 = ti.n0 + b_rows * rank;
+      // Gathered A operand: the four row ids of this lane depend on the tile only, so they are
+      // read once per tile, not once per k-block (a dependent global load in front of every
+      // stage would set the pace of the whole ring).
+      int ga4[4] = {-1, -1, -1, -1};
+      if (!PAIR && !A_MN && p.gather_tokens != nullptr && p.gather_a && ti.r == 0) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const long long row = static_cast<long long>(m0) + 4 * lane + e;
+          if (row < p.gather_count) ga4[e] = static_cast<int>(__ldg(p.gather_tokens + row));
+        }
+      }
       int kb_base = 0;
       for (int sg = 0; ok && sg < p.nseg; ++sg) {
         const bool gather = p.gather_tokens != nullptr && ti.r == 0 && sg == 0;
@@ -345,12 +362,23 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
         split_range(p.kb_total, R.splits, split, kb_base, nkb, lo, hi);
         kb_base += nkb;
         for (int kk = lo * BK; kk < hi * BK; kk += BK) {
+          // Gathered B operand: the k-rows of this block are 64 token ids; lane l fetches rows
+          // 4 (l mod 16) .. +3 of every slab, so it needs four ids per k-block. They are read
+          // BEFORE the wait for a free stage, which hides their latency behind the ring.
+          int gb4[4] = {-1, -1, -1, -1};
+          if (!PAIR && B_MN && gather && p.gather_b) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const long long row = static_cast<long long>(kk) + 4 * (lane & 15) + e;
+              if (row < p.gather_count) gb4[e] = static_cast<int>(__ldg(p.gather_tokens + row));
+            }
+          }
           ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1u, abortp, p.wait_limit_ns));
           if (!ok) {
             if (lane == 0) record_timeout(1, t);
             break;
           }
-          if (elect_one() && !(dbg & 64)) {
+          if (elect_one() && !p.stall_producer) {
             const uint32_t sa = smem_base + s * stage_bytes;
             const uint32_t sb = sa + A_STAGE_BYTES;
             if (dbg & 2) {
@@ -389,32 +417,20 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
               }
             }
           }
-          if (!PAIR && gather && !(dbg & (2 | 64))) {
+          if (!PAIR && gather && !(dbg & 2) && !p.stall_producer) {
             // Gathered operand: every lane fetches 4 rows (512 B) per tile::gather4; a row
             // id outside the matrix reads as zeros.
             const uint32_t fb = full_bar(s);
             const uint32_t sa = smem_base + s * stage_bytes;
             const uint32_t sb = sa + A_STAGE_BYTES;
-            if (!A_MN && p.gather_a) {
-              int r4[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const long long row = static_cast<long long>(m0) + 4 * lane + e;
-                r4[e] = row < p.gather_count ? static_cast<int>(p.gather_tokens[row]) : -1;
-              }
-              tma_gather4_2d(sa + lane * 512, ma, fb, kk, r4[0], r4[1], r4[2], r4[3]);
-            }
+            if (!A_MN && p.gather_a)
+              tma_gather4_2d(sa + lane * 512, ma, fb, kk, ga4[0], ga4[1], ga4[2], ga4[3]);
             if (B_MN && p.gather_b) {
               for (int q4 = lane; q4 < 16 * b_slabs; q4 += 32) {
                 const int j = q4 >> 4;            // slab
-                const int g4 = q4 & 15;           // group of 4 k-rows inside the slab
-                int r4[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const long long row = static_cast<long long>(kk) + 4 * g4 + e;
-                  r4[e] = row < p.gather_count ? static_cast<int>(p.gather_tokens[row]) : -1;
-                }
-                tma_gather4_2d(sb + j * SLAB_BYTES + g4 * 512, mb, fb, n0 + 64 * j, r4[0], r4[1], r4[2], r4[3]);
+                const int g4 = q4 & 15;           // group of 4 k-rows inside the slab (= lane & 15)
+                tma_gather4_2d(sb + j * SLAB_BYTES + g4 * 512, mb, fb, n0 + 64 * j, gb4[0], gb4[1], gb4[2],
+                               gb4[3]);
               }
             }
           }
@@ -715,35 +731,73 @@ splitk_reduce_kernel(const __grid_constant__ ReduceParams rp) {
 unsigned long long g_launch_count = 0;
 
 static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
-static int g_num_sms = 0;
-static int g_device_ok = 0;   // 0 unknown, 1 ok, -1 not sm_100 / no device
 
-static int ensure_device() {
-  if (g_device_ok != 0) return g_device_ok > 0 ? WSL_OK : WSL_ERR_DEVICE;
-  int dev = 0;
+static DeviceInfo g_devices[kMaxDevices] = {};
+
+int current_device_index() {
+  int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess) {
     cudaGetLastError();
-    g_device_ok = -1;
-    return WSL_ERR_DEVICE;
+    return -1;
   }
-  int major = 0, sms = 0;
-  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
-    cudaGetLastError();
-    g_device_ok = -1;
-    return WSL_ERR_DEVICE;
-  }
-  if (major != 10) {
-    g_device_ok = -1;
-    return WSL_ERR_DEVICE;
-  }
-  g_num_sms = sms;
-  g_device_ok = 1;
-  return WSL_OK;
+  return (dev >= 0 && dev < kMaxDevices) ? dev : -1;
 }
 
-int device_check() { return ensure_device(); }
-int device_sm_count() { return g_num_sms; }
+DeviceInfo* current_device_info() {
+  const int dev = current_device_index();
+  if (dev < 0) return nullptr;
+  DeviceInfo& d = g_devices[dev];
+  if (d.state == 0) {
+    int major = 0, sms = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+      cudaGetLastError();
+      d.state = -1;
+    } else if (major != 10) {
+      d.state = -1;
+    } else {
+      d.sms = sms;
+      d.state = 1;
+    }
+  }
+  return d.state > 0 ? &d : nullptr;
+}
+
+int device_check() { return current_device_info() != nullptr ? WSL_OK : WSL_ERR_DEVICE; }
+
+Options& options() {
+  static Options o = [] {
+    Options v;
+    const char* e = getenv("WSL_PAIR");
+    v.pair_tiles = (e && e[0] == '0') ? 0 : 1;
+    e = getenv("WSL_ROW_STAGED");
+    v.row_staged = (e && e[0] == '0') ? 0 : 1;
+    v.stall_producer = 0;
+    v.wait_limit_ns = WAIT_LIMIT_NS;
+    if ((e = getenv("WSL_WAIT_LIMIT_MS")) != nullptr) {
+      const long ms = atol(e);
+      if (ms > 0 && ms <= 10000) v.wait_limit_ns = static_cast<unsigned long long>(ms) * 1000000ull;
+    }
+    v.reserved_sms = 0;
+    v.profile_bits = 0;
+    if ((e = getenv("WSL_DBG")) != nullptr) v.profile_bits = atoi(e);
+    return v;
+  }();
+  return o;
+}
+
+// SMs the persistent kernels of the current launch may occupy: all of them, minus the ones
+// the caller reserved for a collective that runs beside them (wsl_set_option).
+static int usable_sms(const DeviceInfo& d) {
+  const int rsv = options().reserved_sms;
+  int n = d.sms - (rsv > 0 ? rsv : 0);
+  return n < 2 ? 2 : n;
+}
+// What every launcher sizes its grid with: the SMs of the current device minus the reserved ones.
+int device_sm_count() {
+  const DeviceInfo* d = current_device_info();
+  return d ? usable_sms(*d) : 0;
+}
 
 static int ensure_encode() {
   if (g_encode) return WSL_OK;
@@ -759,10 +813,61 @@ static int ensure_encode() {
   return WSL_OK;
 }
 
-// Tensor map over a row-major bf16 matrix [rows, cols] (pitch ld elements) with a
-// box of box_cols (<= 64) x box_rows, 128-byte swizzle, zero fill outside.
 // Tensor map over a row-major output matrix (bf16 or fp32) for the staged epilogue: box of
 // 128 bytes x 128 rows, 128-byte swizzle.
+// Encoded tensor maps are a pure function of (address, shape, pitch, box, type), and a training
+// step presents the same few hundred combinations again and again (weights never move, the
+// caching allocator hands activations the same addresses), so the 128-byte results are kept in
+// a small direct-mapped table instead of being re-encoded by the driver on every launch.
+struct MapKey {
+  const void* ptr;
+  long long rows, cols, ld;
+  int box_cols, box_rows, kind;   // kind: 0 bf16 operand, 1 bf16 output, 2 fp32 output
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_cols == o.box_cols &&
+           box_rows == o.box_rows && kind == o.kind;
+  }
+};
+struct MapSlot {
+  MapKey key;
+  int dev;
+  bool used;
+  alignas(64) CUtensorMap map;
+};
+constexpr int kMapSlots = 4096;
+static MapSlot* g_map_cache = nullptr;
+static std::mutex g_map_mutex;
+
+static inline size_t map_hash(const MapKey& k, int dev) {
+  unsigned long long h = reinterpret_cast<unsigned long long>(k.ptr) * 0x9E3779B97F4A7C15ull;
+  h ^= static_cast<unsigned long long>(k.rows) * 0xC2B2AE3D27D4EB4Full + (h >> 29);
+  h ^= static_cast<unsigned long long>(k.cols) * 0x165667B19E3779F9ull + (h << 7);
+  h ^= static_cast<unsigned long long>(k.ld) * 0x27D4EB2F165667C5ull + (h >> 31);
+  h ^= static_cast<unsigned long long>((k.box_cols << 12) ^ (k.box_rows << 2) ^ k.kind ^ (dev << 24)) *
+       0x85EBCA77C2B2AE63ull;
+  return static_cast<size_t>((h ^ (h >> 32)) & (kMapSlots - 1));
+}
+
+// Looks the key up; on a miss runs `encode` into the slot. Returns a WSL_* status.
+template <typename Encode>
+static int cached_map(CUtensorMap* out, const MapKey& key, Encode encode) {
+  const int dev = current_device_index();
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  if (g_map_cache == nullptr) g_map_cache = new MapSlot[kMapSlots]();
+  MapSlot& s = g_map_cache[map_hash(key, dev)];
+  if (!(s.used && s.dev == dev && s.key == key)) {
+    if (encode(&s.map) != CUDA_SUCCESS) {
+      s.used = false;
+      return WSL_ERR_DRIVER;
+    }
+    s.key = key;
+    s.dev = dev;
+    s.used = true;
+  }
+  memcpy(out, &s.map, sizeof(CUtensorMap));
+  return WSL_OK;
+}
+
 static int make_map_out(CUtensorMap* m, void* ptr, long long rows, long long cols, long long ld,
                         bool f32) {
   const int es = f32 ? 4 : 2;
@@ -770,13 +875,16 @@ static int make_map_out(CUtensorMap* m, void* ptr, long long rows, long long col
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * es};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / es), 128u};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                        ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? WSL_OK : WSL_ERR_DRIVER;
+  const MapKey key = {ptr, rows, cols, ld, 128 / es, 128, f32 ? 2 : 1};
+  return cached_map(m, key, [&](CUtensorMap* dst) {
+    return g_encode(dst, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr,
+                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  });
 }
 
+// Tensor map over a row-major bf16 matrix [rows, cols] (pitch ld elements) with a
+// box of box_cols (<= 64) x box_rows, 128-byte swizzle, zero fill outside.
 static int make_map_bf16(CUtensorMap* m, const Mat& t, int box_cols, int box_rows) {
   if (t.ptr == nullptr || t.rows <= 0 || t.cols <= 0) return WSL_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(t.ptr) & 15u) != 0 || (t.ld % 8) != 0 || t.ld < t.cols)
@@ -785,11 +893,12 @@ static int make_map_bf16(CUtensorMap* m, const Mat& t, int box_cols, int box_row
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(t.ld) * 2u};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(t.ptr), dims,
-                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? WSL_OK : WSL_ERR_DRIVER;
+  const MapKey key = {t.ptr, t.rows, t.cols, t.ld, box_cols, box_rows, 0};
+  return cached_map(m, key, [&](CUtensorMap* dst) {
+    return g_encode(dst, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(t.ptr), dims, strides, box,
+                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  });
 }
 
 // Relative cost of one k-block of a tile with MMA N = bn: wide tiles are bound by the
@@ -876,19 +985,20 @@ long long region_tiles(bool pair, long long mo, long long no) {
 int split_workers(bool pair, int num_sms) { return pair ? num_sms / 2 : num_sms; }
 int kblocks(long long k) { return static_cast<int>((k + BK - 1) / BK); }
 
-static int g_max_clusters = 0;   // co-resident CTA pairs of the PAIR variant
-
 template <bool A_MN, bool B_MN, bool PAIR>
 static int launch_variant(const GemmParams& p, long long units, cudaStream_t stream) {
-  static bool attr_set = false;   // per instantiation
+  static bool attr_set[kMaxDevices] = {};   // per instantiation and device
   auto kern = block_gemm_kernel<A_MN, B_MN, PAIR>;
   constexpr int smem = Cfg<PAIR>::kSmemBytes;
-  if (!attr_set) {
+  const int dev = current_device_index();
+  DeviceInfo* di = current_device_info();
+  if (dev < 0 || di == nullptr) return WSL_ERR_DEVICE;
+  if (!attr_set[dev]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
       cudaGetLastError();
       return WSL_ERR_CUDA;
     }
-    attr_set = true;
+    attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -902,20 +1012,22 @@ static int launch_variant(const GemmParams& p, long long units, cudaStream_t str
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   long long workers;
+  const int sms = usable_sms(*di);
   if (PAIR) {
-    if (g_max_clusters == 0) {
-      cfg.gridDim = dim3(2 * (g_num_sms / 2));
+    if (di->max_clusters == 0) {
+      cfg.gridDim = dim3(2 * (di->sms / 2));
       int n = 0;
       if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
         cudaGetLastError();
-        n = g_num_sms / 2;
+        n = di->sms / 2;
       }
-      g_max_clusters = n < g_num_sms / 2 ? n : g_num_sms / 2;
+      di->max_clusters = n < di->sms / 2 ? n : di->sms / 2;
     }
-    workers = units < g_max_clusters ? units : g_max_clusters;
+    const int cap = di->max_clusters < sms / 2 ? di->max_clusters : sms / 2;
+    workers = units < cap ? units : cap;
     cfg.gridDim = dim3(static_cast<unsigned>(2 * workers));
   } else {
-    workers = units < g_num_sms ? units : g_num_sms;
+    workers = units < sms ? units : sms;
     cfg.gridDim = dim3(static_cast<unsigned>(workers));
   }
   if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) {
@@ -926,23 +1038,17 @@ static int launch_variant(const GemmParams& p, long long units, cudaStream_t str
   return WSL_OK;
 }
 
-static bool pair_mode_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("WSL_PAIR");
-    v = (e && e[0] == '0') ? 0 : 1;
-  }
-  return v == 1;
-}
+static bool pair_mode_enabled() { return options().pair_tiles != 0; }
 
 bool use_pair_tiles(long long mo0, long long no0) {
   return pair_mode_enabled() && mo0 >= 512 && no0 >= 128;
 }
 
 int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
-  int st = ensure_device();
-  if (st != WSL_OK) return st;
-  st = ensure_encode();
+  const DeviceInfo* di = current_device_info();
+  if (di == nullptr) return WSL_ERR_DEVICE;
+  const int g_num_sms = usable_sms(*di);   // what the split planner and the grids may count on
+  int st = ensure_encode();
   if (st != WSL_OK) return st;
   if (g.nseg < 1 || g.nseg > kMaxSeg || g.nregion < 1 || g.nregion > kMaxRegion)
     return WSL_ERR_BAD_ARG;
@@ -1094,13 +1200,13 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   p.gather_count = g.gather_count;
   p.gather_a = g.gather_a ? 1 : 0;
   p.gather_b = g.gather_b ? 1 : 0;
+  const Options& opt = options();
+  p.dbg = opt.profile_bits & (1 | 2 | 4 | 32);
+  p.stall_producer = opt.stall_producer;
+  p.wait_limit_ns = opt.wait_limit_ns;
+#ifndef WSL_PROFILE_SWITCHES
   p.dbg = 0;
-  if (const char* e = getenv("WSL_DBG")) p.dbg = atoi(e);
-  p.wait_limit_ns = WAIT_LIMIT_NS;
-  if (const char* e = getenv("WSL_WAIT_LIMIT_MS")) {
-    const long ms = atol(e);
-    if (ms > 0 && ms <= 10000) p.wait_limit_ns = static_cast<unsigned long long>(ms) * 1000000ull;
-  }
+#endif
   if (!any_split && !(p.dbg & 32)) {
     // staged TMA-store epilogue where the tile width is a whole number of 128-byte chunks
     for (int r = 0; r < g.nregion; ++r) {

@@ -126,6 +126,38 @@ int wsl_poll_status(int words[4]) {
   return w[0];
 }
 
+int wsl_set_option(int option, long long value) {
+  Options& o = options();
+  switch (option) {
+    case WSL_OPT_WAIT_LIMIT_MS:
+      if (value <= 0 || value > 10000) return WSL_ERR_BAD_ARG;
+      o.wait_limit_ns = static_cast<unsigned long long>(value) * 1000000ull;
+      return WSL_OK;
+    case WSL_OPT_STALL_PRODUCER: o.stall_producer = value != 0; return WSL_OK;
+    case WSL_OPT_PAIR_TILES: o.pair_tiles = value != 0; return WSL_OK;
+    case WSL_OPT_ROW_STAGED: o.row_staged = value != 0; return WSL_OK;
+    case WSL_OPT_RESERVED_SMS:
+      if (value < 0 || value > 64) return WSL_ERR_BAD_ARG;
+      o.reserved_sms = static_cast<int>(value);
+      return WSL_OK;
+    case WSL_OPT_PROFILE_BITS: o.profile_bits = static_cast<int>(value); return WSL_OK;
+    default: return WSL_ERR_BAD_ARG;
+  }
+}
+
+long long wsl_get_option(int option) {
+  const Options& o = options();
+  switch (option) {
+    case WSL_OPT_WAIT_LIMIT_MS: return static_cast<long long>(o.wait_limit_ns / 1000000ull);
+    case WSL_OPT_STALL_PRODUCER: return o.stall_producer;
+    case WSL_OPT_PAIR_TILES: return o.pair_tiles;
+    case WSL_OPT_ROW_STAGED: return o.row_staged;
+    case WSL_OPT_RESERVED_SMS: return o.reserved_sms;
+    case WSL_OPT_PROFILE_BITS: return o.profile_bits;
+    default: return WSL_ERR_BAD_ARG;
+  }
+}
+
 int wsl_reset_status(void) {
   int st = device_check();
   if (st != WSL_OK) return st;
@@ -604,9 +636,10 @@ int wsl_embed_scatter_add(const long long* tokens, const void* dG, float* dE, lo
 }
 
 int wsl_ce_fwd_bwd(void* logits, long long ld, const long long* labels, float* row_loss,
-                   long long rows, long long V, float scale, int dtype, void* stream) {
+                   long long rows, long long V, float scale, const float* scale_dev, int dtype,
+                   void* stream) {
   if (bad_dtype(dtype)) return WSL_ERR_BAD_ARG;
-  return launch_ce(logits, ld, labels, row_loss, rows, V, scale, dtype == WSL_F32,
+  return launch_ce(logits, ld, labels, row_loss, rows, V, scale, scale_dev, dtype == WSL_F32,
                    static_cast<cudaStream_t>(stream));
 }
 

@@ -64,7 +64,11 @@ constexpr int CE_THREADS = 1024;
 template <typename T>
 __global__ void __launch_bounds__(CE_THREADS)
 ce_fwd_bwd_kernel(T* logits, long long ld, const long long* __restrict__ labels,
-                  float* __restrict__ row_loss, int V, float scale) {
+                  float* __restrict__ row_loss, int V, float scale_host,
+                  const float* __restrict__ scale_dev) {
+  // the gradient scale may have a factor that only exists on the device (1 / number of
+  // counted rows, computed from the labels without a host round trip)
+  const float scale = scale_dev != nullptr ? scale_host * __ldg(scale_dev) : scale_host;
   __shared__ float red_m[32];
   __shared__ float red_s[32];
   __shared__ float bcast[2];
@@ -413,27 +417,16 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, long long lddy, const T* __restrict
 namespace wsl {
 
 // ------------------------------------------------------------------ host launchers
-// Diagnostic switch: WSL_ROW_STAGED=0 sends every row-kernel call to the direct (register
-// pipelined) kernels, for A/B timing of the staged ones.
-static bool row_staged_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("WSL_ROW_STAGED");
-    return !(e && e[0] == '0');
-  }();
-  return on;
-}
+// Option row_staged = 0 sends every row-kernel call to the direct (register pipelined)
+// kernels, for A/B timing of the staged ones.
+static bool row_staged_enabled() { return options().row_staged != 0; }
 
-// Wait bound and diagnostic switch of the staged kernels, read at launch like the GEMM's:
-// WSL_WAIT_LIMIT_MS shortens the bound, bit 64 of WSL_DBG keeps the producer warp idle.
+// Wait bound and the bounded-wait test aid of the staged kernels, taken from the library's
+// options at launch like the GEMM's.
 static RnKnobs rn_knobs() {
   RnKnobs k;
-  k.wait_limit_ns = RN_WAIT_LIMIT_NS;
-  k.producer_idle = 0;
-  if (const char* e = getenv("WSL_WAIT_LIMIT_MS")) {
-    const long ms = atol(e);
-    if (ms > 0 && ms <= 10000) k.wait_limit_ns = static_cast<unsigned long long>(ms) * 1000000ull;
-  }
-  if (const char* e = getenv("WSL_DBG")) k.producer_idle = (atoi(e) & 64) ? 1 : 0;
+  k.wait_limit_ns = options().wait_limit_ns;
+  k.producer_idle = options().stall_producer ? 1 : 0;
   return k;
 }
 
@@ -441,22 +434,22 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 
 template <typename T>
 static int ce_launch(void* logits, long long ld, const long long* labels, float* row_loss,
-                     long long rows, long long V, float scale, cudaStream_t s) {
+                     long long rows, long long V, float scale, const float* scale_dev, cudaStream_t s) {
   ce_fwd_bwd_kernel<T><<<static_cast<unsigned>(rows), CE_THREADS, 0, s>>>(
-      static_cast<T*>(logits), ld, labels, row_loss, static_cast<int>(V), scale);
+      static_cast<T*>(logits), ld, labels, row_loss, static_cast<int>(V), scale, scale_dev);
   return cudaGetLastError() == cudaSuccess ? WSL_OK : WSL_ERR_CUDA;
 }
 
 int launch_ce(void* logits, long long ld, const long long* labels, float* row_loss, long long rows,
-              long long V, float scale, int is_f32, cudaStream_t s) {
+              long long V, float scale, const float* scale_dev, int is_f32, cudaStream_t s) {
   int st = device_check();
   if (st != WSL_OK) return st;
   if (!logits || !labels || !row_loss || rows <= 0 || V <= 0 || ld < V) return WSL_ERR_BAD_ARG;
   if (rows > 0x7fffffffLL || V > 0x7fffffffLL) return WSL_ERR_TOO_LARGE;
   const int nv = is_f32 ? 4 : 8;
   if (!aligned16(logits) || (ld % nv) != 0) return WSL_ERR_ALIGN;
-  st = is_f32 ? ce_launch<float>(logits, ld, labels, row_loss, rows, V, scale, s)
-              : ce_launch<__nv_bfloat16>(logits, ld, labels, row_loss, rows, V, scale, s);
+  st = is_f32 ? ce_launch<float>(logits, ld, labels, row_loss, rows, V, scale, scale_dev, s)
+              : ce_launch<__nv_bfloat16>(logits, ld, labels, row_loss, rows, V, scale, scale_dev, s);
   if (st == WSL_OK) ++g_launch_count;
   return st;
 }
@@ -559,13 +552,15 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const void* res, void* h_ou
     const size_t ssmem = rn_fwd_staged_smem(d, fused);
 #define WSL_RNFS(T, R, KVN, RES)                                                                   \
   do {                                                                                             \
-    static bool attr_set = false;                                                                  \
-    if (!attr_set) {                                                                               \
+    static bool attr_set_dev[kMaxDevices] = {};   /* the limit is a per-device setting */        \
+    const int dev_i = current_device_index();                                                      \
+    if (dev_i < 0) return WSL_ERR_DEVICE;                                                          \
+    if (!attr_set_dev[dev_i]) {                                                                    \
       if (cudaFuncSetAttribute(rmsnorm_fwd_staged_kernel<T, R, KVN, RES>,                          \
                                cudaFuncAttributeMaxDynamicSharedMemorySize,                        \
                                static_cast<int>(rn_fwd_staged_smem(4096, RES))) != cudaSuccess)    \
         return WSL_ERR_CUDA;                                                                       \
-      attr_set = true;                                                                             \
+      attr_set_dev[dev_i] = true;                                                                  \
     }                                                                                              \
     rmsnorm_fwd_staged_kernel<T, R, KVN, RES><<<sgb, (cw + 1) * 32, ssmem, s>>>(                   \
         static_cast<const T*>(x), static_cast<const T*>(res), static_cast<T*>(h_out), w,           \
@@ -660,13 +655,15 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
     const size_t ssmem = rn_staged_smem(d, fused);
 #define WSL_RNS(T, R, KVN, DRES)                                                                   \
   do {                                                                                             \
-    static bool attr_set = false;                                                                  \
-    if (!attr_set) {                                                                               \
+    static bool attr_set_dev[kMaxDevices] = {};   /* the limit is a per-device setting */        \
+    const int dev_i = current_device_index();                                                      \
+    if (dev_i < 0) return WSL_ERR_DEVICE;                                                          \
+    if (!attr_set_dev[dev_i]) {                                                                    \
       if (cudaFuncSetAttribute(rmsnorm_bwd_staged_kernel<T, R, KVN, DRES>,                         \
                                cudaFuncAttributeMaxDynamicSharedMemorySize,                        \
                                static_cast<int>(rn_staged_smem(4096, DRES))) != cudaSuccess)       \
         return WSL_ERR_CUDA;                                                                       \
-      attr_set = true;                                                                             \
+      attr_set_dev[dev_i] = true;                                                                  \
     }                                                                                              \
     rmsnorm_bwd_staged_kernel<T, R, KVN, DRES><<<sgb, (cw + 1) * 32, ssmem, s>>>(                  \
         static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(dres), w, rstd, \

@@ -25,7 +25,6 @@ void build_bwd_dw_desc(GemmDesc& g, const void* dY, long long lddy, const void* 
                        float* dA, float* dB, long long M, long long N, long long K, long long r);
 
 constexpr unsigned long long kStaticScratchBytes = WSL_NOALLOC_SCRATCH_BYTES;
-constexpr int kMaxDevices = 64;
 
 // Every device that loads this library holds these 64 MiB until the process exits.
 static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];

@@ -8,8 +8,9 @@ hot path: every projection is y = x W^T + s (x A^T) B^T with W taken from shared
 (layer mod n_unique) and a per-layer adapter, q|k|v and gate|up are issued as groups that
 read x once, and the token embedding is factorized.
 
-RMSNorm, RoPE, SDPA and the softmax of the loss stay PyTorch library calls (they are not
-on the path this package accelerates).
+The attention core (causal SDPA) stays a PyTorch library call; RMSNorm (+ residual add,
++ rotary embedding), SwiGLU and the softmax cross-entropy run as the library's row kernels
+where they cover the width, else as the PyTorch calls.
 
 Parameters are fp32 masters; compute is bf16 (the reference's autocast policy,
 torchtitan/distributed/utils.py:219-239) with fp32 accumulation; parameter gradients are
@@ -152,20 +153,25 @@ class _HeadLossFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h, Wc, labels, sink, chunk, anchor):
         M = h.shape[0]
+        V = Wc.shape[0]
         dH = torch.empty_like(h)
         total = torch.zeros((), device=h.device, dtype=torch.float32)
+        # reduction='mean' of F.cross_entropy divides by the number of COUNTED rows: labels
+        # outside [0, V) (ignore_index = -100: padding, packed documents) contribute neither
+        # loss nor gradient nor to the divisor. The count stays on the device.
+        inv_count = ((labels >= 0) & (labels < V)).sum().clamp_min(1).to(torch.float32).reciprocal().reshape(1)
         for m0 in range(0, M, chunk):
             hs = h[m0:m0 + chunk]
             # logits in the compute dtype (bf16 under the reference's autocast, cast up inside
             # the loss kernel), overwritten in place by their gradient
             logits = ops.linear_fwd(hs, Wc)
-            total += ops.ce_fwd_bwd(logits, labels[m0:m0 + chunk], 1.0 / M).sum()
+            total += ops.ce_fwd_bwd(logits, labels[m0:m0 + chunk], 1.0, inv_count).sum()
             dH[m0:m0 + chunk] = ops.lora_linear_bwd_dx([logits], [None], [Wc], [None])
             if sink is not None:
                 ops.lora_linear_bwd_dw(logits, None, hs, None, sink, None, None)
             del logits
         ctx.save_for_backward(dH)
-        return total / M
+        return total * inv_count[0]
 
     @staticmethod
     def backward(ctx, g):
@@ -185,6 +191,10 @@ class WeightSharedDecoder(nn.Module):
         self.compute_dtype = torch.bfloat16
         self._cache = CopyCache()
         self._rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
+        # Called during backward with a ready-rank k as soon as every parameter gradient of
+        # rank <= k is final (see grad_ready_rank); lets the owner of the gradient arena start
+        # exchanging finished ranges while backward still runs. None = nobody listens.
+        self.grad_ready_hook = None
 
     # ------------------------------------------------------------------ initialisation
     @torch.no_grad()
@@ -210,6 +220,7 @@ class WeightSharedDecoder(nn.Module):
         self.tok_embeddings.proj.weight.normal_(0.0, 0.02, generator=g)
         self.norm.weight.fill_(1.0)
         self.output.weight.normal_(0.0, self.config.dim ** -0.5, generator=g)
+        self.post_optimizer_hook()
 
     @torch.no_grad()
     def load_named_params(self, p: Dict[str, torch.Tensor]) -> None:
@@ -229,13 +240,43 @@ class WeightSharedDecoder(nn.Module):
         self.tok_embeddings.proj.weight.copy_(p["embed.P"])
         self.norm.weight.copy_(p["norm"])
         self.output.weight.copy_(p["output"])
+        self.post_optimizer_hook()
 
     # ------------------------------------------------------------------------ helpers
+    def grad_ready_rank(self, name: str) -> int:
+        """Order in which parameter gradients become final during one step (smaller = earlier).
+        The output head's gradient is complete when the loss has been computed (rank 0, before
+        backward starts); backward then walks the layers from last to first, so layer l is rank
+        n_layers - l, together with the final norm (rank 1) and with the shared block whose
+        FIRST user is layer l (every later user has already contributed); the embedding comes
+        last."""
+        L = self.config.n_layers
+        head = name.split(".", 2)
+        if head[0] == "output":
+            return 0
+        if head[0] == "norm":
+            return 1
+        if head[0] in ("layers", "blocks"):
+            return L - int(head[1])
+        return L + 1
+
+    def _notify_on_grad(self, t: torch.Tensor, rank: int) -> None:
+        """When the gradient of `t` has been computed, everything of ready-rank <= rank is final."""
+        hook = self.grad_ready_hook
+        if hook is not None and t.requires_grad:
+            def fire(grad, _hook=hook, _rank=rank):
+                _hook(_rank)
+                return None
+            t.register_hook(fire)
+
     def post_optimizer_hook(self) -> None:
-        """The master weights changed: drop the compute-dtype copies so that the next forward
-        re-casts them (the reference's post_optimizer_hook slot, torchtitan/train.py:288-295).
-        A cache bound to a flat arena is refreshed by the arena's owner instead."""
-        self._cache.clear()
+        """The master weights changed: the compute-dtype copies must follow before the next
+        forward (the reference's post_optimizer_hook slot, torchtitan/train.py:288-295). Copies
+        the cache made itself are dropped and re-cast on next use; when the cache is bound to a
+        flat arena (TrainStep) the arena's flat copy is re-cast here, in one pass. Call this
+        after anything that writes the parameters behind the optimizer's back: a state-dict
+        load, dp.broadcast_parameters, a re-initialisation."""
+        self._cache.invalidate()
 
     @staticmethod
     def _sink(p: torch.Tensor) -> torch.Tensor:
@@ -277,8 +318,16 @@ class WeightSharedDecoder(nn.Module):
             cos, sin = rope_tables(c.head_dim, s, c.rope_theta, h.device)
             self._rope = (cos.contiguous(), sin.contiguous())       # fp32 [s, head_dim]
         cos, sin = self._rope
+        L = c.n_layers
+        # layer 0 (and the shared block it is the first user of) is final once the gradient of
+        # the embedding output exists
+        self._notify_on_grad(h, L)
         pending = None   # output of the previous layer's down projection, not yet added to h
-        for lyr in self.layers:
+        for li, lyr in enumerate(self.layers):
+            if pending is not None:
+                # the gradient of the previous layer's output exists only after this layer's
+                # whole backward (its first norm included): layers >= li are final then
+                self._notify_on_grad(pending, L - li)
             # the layer's four projection groups hand their adapter-gradient work to one batch
             ab = WF.AdapterGradBatch(4) if torch.is_grad_enabled() else None
             # every residual add is folded into the norm that reads the sum

@@ -1,21 +1,26 @@
-"""Token data-parallel gradient exchange: one flat fp32 arena, one all-reduce per step.
+"""Token data-parallel gradient exchange: one flat fp32 arena, all-reduced once per step.
 
 Replaces the reference's DDP wrapper for this path: apply_ddp ->
 replicate(model, device_mesh, bucket_cap_mb=100), torchtitan/models/llama3/infra/
 parallelize.py:428-444, which averages every gradient across ranks through bucketed
-all-reduces fired by autograd hooks. Here the fused kernels accumulate weight gradients in
-place (no autograd hook ever fires for them), so all `param.grad` tensors are made views of
-ONE contiguous fp32 buffer laid out
+all-reduces fired by autograd hooks and overlapped with the backward pass. Here the fused
+kernels accumulate weight gradients in place (no autograd hook ever fires for them), so all
+`param.grad` tensors are made views of ONE contiguous fp32 buffer, laid out in the order in
+which the gradients become final during a step:
 
-    [ shared base weights (unique blocks) | adapters of all layers | embedding | norms, head ]
+    [ output head | final norm, last layer | ... | layer l adapters + norms, and the shared
+      block whose first user is layer l | ... | layer 0 | embedding ]
 
-and the whole buffer is averaged with a single all-reduce after backward. Weights are
-replicated; forward and dX need no communication. With NCCL this is one ncclAllReduce over
-NVLink/NVSwitch; the same code runs on gloo for CPU tests.
+The buffer is averaged either with a single all-reduce after backward (all_reduce_mean), or
+in buckets of contiguous ranges launched from the backward pass as soon as everything in
+them is final (begin_overlap / notify_ready / finish_overlap), which hides the exchange
+behind the remaining backward kernels as DDP's buckets do. Weights are replicated; forward
+and dX need no communication. With NCCL these are ncclAllReduce calls over NVLink/NVSwitch;
+the same code runs on gloo for CPU tests.
 """
 from __future__ import annotations
 
-from typing import Iterable, List, Optional, Tuple
+from typing import Callable, Iterable, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -23,6 +28,7 @@ import torch.nn as nn
 
 
 def _order_key(name: str) -> int:
+    """Layout class of a parameter when the model does not say when its gradients are final."""
     if name.startswith("blocks."):
         return 0
     if "_offset." in name:
@@ -33,11 +39,20 @@ def _order_key(name: str) -> int:
 
 
 class GradArena:
-    """Owns the flat gradient buffer of a model and points every param.grad into it."""
+    """Owns the flat gradient buffer of a model and points every param.grad into it.
+
+    If the model has ``grad_ready_rank(name) -> int`` (WeightSharedDecoder does), parameters
+    are laid out by that rank: rank k holds everything whose gradient is final once the model
+    has reported ``grad_ready_hook(k)`` during backward. Otherwise the four layout classes
+    (shared, adapters, embedding, other) are used and every range counts as final only at the
+    end of backward.
+    """
 
     def __init__(self, model: nn.Module, process_group: Optional[dist.ProcessGroup] = None):
         named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
-        named.sort(key=lambda np_: _order_key(np_[0]))   # stable: keeps registration order inside a class
+        rank_of: Callable[[str], int] = getattr(model, "grad_ready_rank", None) or _order_key
+        self.has_ready_order = hasattr(model, "grad_ready_rank")
+        named.sort(key=lambda np_: rank_of(np_[0]))   # stable: keeps registration order inside a rank
         for n, p in named:
             if p.dtype != torch.float32:
                 raise TypeError(f"GradArena needs fp32 master parameters; {n} is {p.dtype}")
@@ -54,10 +69,25 @@ class GradArena:
         for p, off in zip(self.params, self.offsets):
             p.grad = self.buffer[off:off + p.numel()].view(p.shape)
         self.group = process_group
-        self.section_bounds = self._sections()
+        # (rank, begin, end) element ranges, ascending in rank and contiguous
+        self.ready_bounds: List[Tuple[int, int, int]] = []
+        for n, p, off in zip(self.names, self.params, self.offsets):
+            r = rank_of(n)
+            end = off + (p.numel() + 63) // 64 * 64
+            if self.ready_bounds and self.ready_bounds[-1][0] == r:
+                self.ready_bounds[-1] = (r, self.ready_bounds[-1][1], end)
+            else:
+                self.ready_bounds.append((r, off, end))
         self.master: Optional[torch.Tensor] = None      # flat fp32 parameters (flatten_parameters)
         self._copies = {}                                # dtype -> flat compute copy of `master`
         self._slot = {id(p): (off, p.numel()) for p, off in zip(self.params, self.offsets)}
+        # state of an overlapped exchange (begin_overlap .. finish_overlap)
+        self._ov_active = False
+        self._ov_sent = 0
+        self._ov_ready = 0
+        self._ov_bucket = 0
+        self._ov_works: list = []
+        self.on_bucket: Optional[Callable[[int], None]] = None   # called with the bytes of each bucket launched
 
     # ------------------------------------------------------------- flat master parameters
     def flatten_parameters(self) -> torch.Tensor:
@@ -100,20 +130,6 @@ class GradArena:
             if buf is not skip:
                 buf.copy_(self.master)
 
-    def _sections(self) -> List[Tuple[str, int, int]]:
-        """(label, begin, end) element ranges of the four layout classes."""
-        labels = ("shared", "adapters", "embedding", "other")
-        out = []
-        for cls, label in enumerate(labels):
-            idx = [i for i, n in enumerate(self.names) if _order_key(n) == cls]
-            if not idx:
-                continue
-            b = self.offsets[idx[0]]
-            last = idx[-1]
-            e = self.offsets[last] + (self.params[last].numel() + 63) // 64 * 64
-            out.append((label, b, e))
-        return out
-
     @property
     def nbytes(self) -> int:
         return self.buffer.numel() * 4
@@ -128,19 +144,71 @@ class GradArena:
                 raise RuntimeError(f"gradient of {n} was detached from the arena "
                                    "(zero_grad(set_to_none=True)?); call GradArena.zero() instead")
 
+    def world_size(self) -> int:
+        if not dist.is_available() or not dist.is_initialized():
+            return 1
+        return dist.get_world_size(self.group)
+
+    def _reduce_range(self, begin: int, end: int, async_op: bool):
+        """Average buffer[begin:end] over the ranks; returns the work handle when async."""
+        view = self.buffer[begin:end]
+        if dist.get_backend(self.group) == "nccl":
+            return dist.all_reduce(view, op=dist.ReduceOp.AVG, group=self.group, async_op=async_op)
+        # gloo has no AVG: sum, then divide once the sum is there
+        work = dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group, async_op=async_op)
+        if not async_op:
+            view.div_(self.world_size())
+            return None
+        return _DivideAfter(work, view, self.world_size())
+
     def all_reduce_mean(self) -> None:
         """Average the arena over the data-parallel ranks (no-op for a single process)."""
-        if not dist.is_available() or not dist.is_initialized():
+        if self.world_size() == 1:
             return
-        world = dist.get_world_size(self.group)
-        if world == 1:
+        self._reduce_range(0, self.buffer.numel(), async_op=False)
+
+    # ---------------------------------------------- exchange overlapped with the backward pass
+    def begin_overlap(self, bucket_bytes: int = 256 << 20) -> None:
+        """Start of a step whose gradients are exchanged in buckets while backward still runs.
+        Ranges are launched (asynchronously, on the backend's own stream, ordered after the
+        kernels already enqueued on the current stream) once at least `bucket_bytes` of
+        contiguous final gradients are pending."""
+        self._ov_active = self.world_size() > 1
+        self._ov_sent = 0
+        self._ov_ready = 0
+        self._ov_bucket = max(int(bucket_bytes) // 4, 1)
+        self._ov_works = []
+
+    def notify_ready(self, rank: int) -> None:
+        """Everything of ready-rank <= `rank` is final (the model's grad_ready_hook)."""
+        if not self._ov_active:
             return
-        backend = dist.get_backend(self.group)
-        if backend == "nccl":
-            dist.all_reduce(self.buffer, op=dist.ReduceOp.AVG, group=self.group)
-        else:   # gloo has no AVG
-            dist.all_reduce(self.buffer, op=dist.ReduceOp.SUM, group=self.group)
-            self.buffer.div_(world)
+        for r, b, e in self.ready_bounds:
+            if r <= rank and e > self._ov_ready:
+                self._ov_ready = e
+        self._launch_pending(force=False)
+
+    def _launch_pending(self, force: bool) -> None:
+        n = self._ov_ready - self._ov_sent
+        if n <= 0 or (not force and n < self._ov_bucket):
+            return
+        work = self._reduce_range(self._ov_sent, self._ov_ready, async_op=True)
+        self._ov_works.append(work)
+        if self.on_bucket is not None:
+            self.on_bucket(4 * n)
+        self._ov_sent = self._ov_ready
+
+    def finish_overlap(self) -> None:
+        """End of backward: launch what is left and make the current stream wait for every
+        bucket. Afterwards the whole arena holds the averaged gradients."""
+        if not self._ov_active:
+            return
+        self._ov_ready = self.buffer.numel()
+        self._launch_pending(force=True)
+        for w in self._ov_works:
+            w.wait()
+        self._ov_works = []
+        self._ov_active = False
 
     def grad_norm(self) -> torch.Tensor:
         """Global L2 norm of all gradients (identical on every rank after all_reduce_mean, so
@@ -154,6 +222,17 @@ class GradArena:
         return norm
 
 
+class _DivideAfter:
+    """Work handle of a summing all-reduce whose result still has to be divided (gloo)."""
+
+    def __init__(self, work, view: torch.Tensor, world: int):
+        self.work, self.view, self.world = work, view, world
+
+    def wait(self) -> None:
+        self.work.wait()
+        self.view.div_(self.world)
+
+
 def broadcast_parameters(model: nn.Module, src: int = 0, group=None) -> None:
     """Make every rank's replica identical to rank `src` (weights are replicated in token DP)."""
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
@@ -161,6 +240,10 @@ def broadcast_parameters(model: nn.Module, src: int = 0, group=None) -> None:
     with torch.no_grad():
         for p in model.parameters():
             dist.broadcast(p.data, src=src, group=group)
+    # compute-dtype copies of the old values (also a flat copy bound to an arena) must follow
+    hook = getattr(model, "post_optimizer_hook", None)
+    if callable(hook):
+        hook()
 
 
 def shard_tokens(global_batch: int, rank: int, world: int) -> Tuple[int, int]:

@@ -98,7 +98,18 @@ class CopyCache:
         return c
 
     def clear(self) -> None:
+        """Drop the copies this cache made itself (they are re-cast on next use)."""
         self._store.clear()
+
+    def invalidate(self) -> None:
+        """The master parameters were changed by something other than the owner of the bound
+        source (a checkpoint load, a broadcast, a re-initialisation): drop the cache's own
+        copies AND re-cast the bound flat copy, whose views the kernels would otherwise keep
+        reading with the old values."""
+        self._store.clear()
+        src = self._source
+        if src is not None and getattr(src, "master", None) is not None:
+            src.refresh_compute_copies()
 
 
 def _drop_copies_after_optimizer_step(optimizer, args, kwargs) -> None:

@@ -35,7 +35,36 @@ def _tic():
     return e
 
 
+# SM reservation window (TrainStep with an overlapped gradient exchange): while a collective
+# is estimated to be in flight the library's persistent kernels leave `_RESERVED` SMs free.
+# The window is measured in estimated milliseconds of the kernels enqueued after it opened
+# (algorithmic FLOPs at ~1.2 PFLOP/s, bytes at ~5 TB/s), because the host runs ahead of the
+# device and cannot see when the collective really ends.
+_RESERVED = 0
+_RESERVE_MS = 0.0
+
+
+def reserve_sms(n: int, window_ms: float) -> None:
+    """Open (or extend by `window_ms`) a window during which launches leave `n` SMs free;
+    n <= 0 closes it at once."""
+    global _RESERVED, _RESERVE_MS
+    if n <= 0:
+        if _RESERVED:
+            _lib.set_option(_lib.OPT_RESERVED_SMS, 0)
+        _RESERVED, _RESERVE_MS = 0, 0.0
+        return
+    _RESERVE_MS += float(window_ms)
+    if _RESERVED != n:
+        _lib.set_option(_lib.OPT_RESERVED_SMS, n)
+        _RESERVED = n
+
+
 def _toc(e0, kind: str, flops: float, nbytes: float) -> None:
+    global _RESERVE_MS
+    if _RESERVED:
+        _RESERVE_MS -= max(flops / 1.2e12, nbytes / 5e9)
+        if _RESERVE_MS <= 0.0:
+            reserve_sms(0, 0.0)
     if e0 is None:
         return
     e1 = torch.cuda.Event(enable_timing=True)
@@ -518,8 +547,11 @@ def embed_scatter_add(tokens: torch.Tensor, dG: torch.Tensor, dE: torch.Tensor) 
 
 
 # ------------------------------------------------ rows either side of the projections
-def ce_fwd_bwd(logits: torch.Tensor, labels: torch.Tensor, scale: float) -> torch.Tensor:
-    """In place: logits <- scale * (softmax - onehot); returns per-row loss (fp32)."""
+def ce_fwd_bwd(logits: torch.Tensor, labels: torch.Tensor, scale: float,
+               scale_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """In place: logits <- scale * scale_dev * (softmax - onehot); returns per-row loss (fp32).
+    `scale_dev` is an optional one-element CUDA float32 tensor (a factor that exists only on
+    the device, such as 1 / the number of counted rows)."""
     logits = _mat(logits, "logits")
     lab = labels.reshape(-1)
     if lab.dtype != torch.int64 or not lab.is_cuda or lab.numel() != logits.shape[0]:
@@ -527,9 +559,13 @@ def ce_fwd_bwd(logits: torch.Tensor, labels: torch.Tensor, scale: float) -> torc
     lab = lab.contiguous()
     rows, V = logits.shape
     row_loss = torch.empty(rows, device=logits.device, dtype=torch.float32)
+    if scale_dev is not None and (scale_dev.dtype != torch.float32 or not scale_dev.is_cuda
+                                  or scale_dev.numel() != 1):
+        raise TypeError("scale_dev must be a one-element CUDA float32 tensor")
     _e = _tic()
     st = _lib.lib().wsl_ce_fwd_bwd(logits.data_ptr(), _ld(logits), lab.data_ptr(), row_loss.data_ptr(),
-                                   rows, V, float(scale), _dtype_code(logits), _stream())
+                                   rows, V, float(scale), scale_dev.data_ptr() if scale_dev is not None else None,
+                                   _dtype_code(logits), _stream())
     _toc(_e, "ce", 0.0, 3.0 * logits.element_size() * rows * V)
     _lib.check(st, "wsl_ce_fwd_bwd")
     return row_loss

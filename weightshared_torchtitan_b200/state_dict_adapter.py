@@ -73,7 +73,9 @@ def from_reference(model: WeightSharedDecoder, sd: Dict[str, torch.Tensor], chec
             continue
         dst.copy_(src.to(dst.device, dst.dtype))
         done[id(dst)] = k
-    model.post_optimizer_hook()   # the compute-dtype copies follow the new masters
+    # the compute-dtype copies follow the new masters, also the flat copy of a model that a
+    # TrainStep has already bound to its arena
+    model.post_optimizer_hook()
 
 
 def deduplicate(sd: Dict[str, torch.Tensor]) -> Tuple[Dict[str, torch.Tensor], Dict[str, str]]:

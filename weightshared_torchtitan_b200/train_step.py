@@ -2,16 +2,18 @@
 
 Mirrors the order of Trainer.train_step / forward_backward_step in the reference
 (torchtitan/train.py:404-527): zero grads -> forward + loss -> backward -> gradient
-averaging over the data-parallel ranks -> clip -> optimizer step. The averaging is one
-all-reduce of the flat arena (dp.GradArena) instead of DDP's bucketed hooks.
+averaging over the data-parallel ranks -> clip -> optimizer step. The averaging is an
+all-reduce of the flat arena (dp.GradArena) instead of DDP's bucketed hooks: either one call
+after backward, or buckets launched from inside backward as their gradients become final
+(``overlap=True``, what DDP's buckets do, torchtitan/models/llama3/infra/parallelize.py:428-444).
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Callable, Dict, Optional
 
 import torch
 
-from . import ops
+from . import _lib, ops
 from .decoder import WeightSharedDecoder
 from .dp import GradArena
 
@@ -23,19 +25,40 @@ class TrainStep:
     norm (``fused_update=True``: wsl_grad_sumsq_partials + wsl_adamw_flat_step); with
     ``fused_update=False`` torch.optim.AdamW steps the flat tensor and one cast kernel
     refreshes the copies. ``flat=False`` keeps per-parameter storage and lets the model re-cast
-    its copies one by one (the reference's post_optimizer_hook slot)."""
+    its copies one by one (the reference's post_optimizer_hook slot).
 
-    def __init__(self, model: WeightSharedDecoder, lr: float = 3e-4, weight_decay: float = 0.1,
+    ``lr`` may be a float or a callable ``step -> float`` (the slot of the reference's
+    LR scheduler, torchtitan/components/lr_scheduler.py); a per-call ``lr=`` overrides both.
+
+    ``overlap=True`` exchanges gradients in buckets of ``bucket_bytes`` while backward runs.
+    The persistent GEMM kernels of the library fill every SM, so a collective's kernel could
+    only start in the gaps between launches; while a bucket is estimated to be in flight the
+    GEMMs therefore leave ``reserved_sms`` SMs free (option RESERVED_SMS of the library).
+    ``link_gbs`` is the all-reduce rate used for that estimate.
+
+    ``status_every`` > 0: every that many steps the device status words are read (this waits
+    for the device) and a bounded wait that ran out in any kernel since raises WslError.
+    """
+
+    def __init__(self, model: WeightSharedDecoder, lr=3e-4, weight_decay: float = 0.1,
                  max_norm: Optional[float] = 1.0, process_group=None, flat: bool = True,
-                 fused_update: bool = True):
+                 fused_update: bool = True, overlap: bool = False, bucket_bytes: int = 256 << 20,
+                 reserved_sms: int = 16, link_gbs: float = 300.0, status_every: int = 64):
         self.model = model
         self.arena = GradArena(model, process_group)
         self.flat = bool(flat)
-        self.lr, self.weight_decay, self.betas, self.eps = lr, weight_decay, (0.9, 0.95), 1e-8
+        self.lr = lr
+        self.weight_decay, self.betas, self.eps = weight_decay, (0.9, 0.95), 1e-8
         self.max_norm = max_norm
         self.fused_update = bool(fused_update) and self.flat and self.arena.buffer.is_cuda
         self.optimizer = None
         self.steps = 0
+        self.status_every = int(status_every)
+        self.overlap = bool(overlap) and self.arena.has_ready_order
+        self.bucket_bytes = int(bucket_bytes)
+        self.reserved_sms = int(reserved_sms)
+        self.link_gbs = float(link_gbs)
+        self.timing: Optional[Dict[str, list]] = None    # set to {} to collect all-reduce events
         if self.flat:
             master = self.arena.flatten_parameters()
             model._cache.bind(self.arena)
@@ -51,8 +74,12 @@ class TrainStep:
         else:
             opt_params = self.arena.params
         # AdamW as in the reference's default optimizer (torchtitan/components/optimizer.py:243-326).
-        self.optimizer = torch.optim.AdamW(opt_params, lr=lr, betas=self.betas, eps=self.eps,
+        self.optimizer = torch.optim.AdamW(opt_params, lr=self._lr_at(1), betas=self.betas, eps=self.eps,
                                            weight_decay=weight_decay, fused=self.arena.buffer.is_cuda)
+
+    # ------------------------------------------------------------------------- helpers
+    def _lr_at(self, step: int) -> float:
+        return float(self.lr(step)) if callable(self.lr) else float(self.lr)
 
     def grad_norm(self) -> torch.Tensor:
         """Global gradient norm of the last step, before clipping."""
@@ -60,30 +87,104 @@ class TrainStep:
             return self._partials.sum().sqrt()
         return self._last_norm
 
-    def __call__(self, tokens: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
-        self.arena.zero()
-        loss = self.model.loss(tokens, labels)
-        loss.backward()
-        self.arena.all_reduce_mean()
+    def check_status(self) -> None:
+        """Raise WslError if a bounded device-side wait ran out in any kernel so far (the words
+        name the role, block and work unit). Waits for the device."""
+        if not self.arena.buffer.is_cuda:
+            return
+        torch.cuda.synchronize()
+        st, words = _lib.poll_status()
+        if st != 0:
+            raise _lib.WslError(st, f"device status words {words} (role, block, unit)")
+
+    # ------------------------------------------------------------------ checkpoint state
+    def state_dict(self) -> Dict[str, object]:
+        """Optimizer state of the step: the step count (bias correction) and, per parameter
+        under its arena name, the two AdamW moments -- the content of torch.optim.AdamW's
+        state ('step', 'exp_avg', 'exp_avg_sq'), so a run resumes with warm moments as the
+        reference does through OptimizersContainer (torchtitan/components/optimizer.py) and
+        its checkpointer."""
+        out: Dict[str, object] = {"steps": self.steps, "lr": None if callable(self.lr) else float(self.lr)}
+        if self.fused_update:
+            for n, p, off in zip(self.arena.names, self.arena.params, self.arena.offsets):
+                k = p.numel()
+                out[f"exp_avg.{n}"] = self.exp_avg[off:off + k].view(p.shape)
+                out[f"exp_avg_sq.{n}"] = self.exp_avg_sq[off:off + k].view(p.shape)
+        else:
+            out["optimizer"] = self.optimizer.state_dict()
+        return out
+
+    @torch.no_grad()
+    def load_state_dict(self, sd: Dict[str, object]) -> None:
+        self.steps = int(sd["steps"])
+        if sd.get("lr") is not None and not callable(self.lr):
+            self.lr = float(sd["lr"])
+        if self.fused_update:
+            for n, p, off in zip(self.arena.names, self.arena.params, self.arena.offsets):
+                k = p.numel()
+                self.exp_avg[off:off + k].view(p.shape).copy_(sd[f"exp_avg.{n}"])
+                self.exp_avg_sq[off:off + k].view(p.shape).copy_(sd[f"exp_avg_sq.{n}"])
+        else:
+            self.optimizer.load_state_dict(sd["optimizer"])
+
+    # ------------------------------------------------------------------------ the step
+    def _bucket_launched(self, nbytes: int) -> None:
+        """A bucket went to the collective's stream: the GEMMs enqueued from now on share the
+        GPU with it for about nbytes / link rate; they leave SMs free for that long."""
+        if self.reserved_sms > 0 and self.arena.buffer.is_cuda:
+            ops.reserve_sms(self.reserved_sms, 1.5 * nbytes / (self.link_gbs * 1e6))
+
+    def __call__(self, tokens: torch.Tensor, labels: torch.Tensor, lr: Optional[float] = None) -> torch.Tensor:
+        arena = self.arena
+        overlap = self.overlap and arena.world_size() > 1
+        arena.zero()
+        if overlap:
+            arena.on_bucket = self._bucket_launched
+            arena.begin_overlap(self.bucket_bytes)
+            self.model.grad_ready_hook = arena.notify_ready
+        try:
+            loss = self.model.loss(tokens, labels)
+            if overlap:
+                arena.notify_ready(0)        # the head's gradient is final before backward starts
+            loss.backward()
+        finally:
+            self.model.grad_ready_hook = None
+        ev = None
+        if self.timing is not None and arena.buffer.is_cuda:
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
+        if overlap:
+            arena.finish_overlap()
+            ops.reserve_sms(0, 0.0)
+        else:
+            arena.all_reduce_mean()
+        if ev is not None:
+            ev[1].record()
+            self.timing.setdefault("allreduce_wait", []).append(ev)
         self.steps += 1
+        step_lr = float(lr) if lr is not None else self._lr_at(self.steps)
         if self.fused_update:
             clip = self.max_norm is not None
             if clip:
-                ops.grad_sumsq_partials(self.arena.buffer, self._partials)
-            copy = self.arena.compute_buffer(self.model.compute_dtype) \
+                ops.grad_sumsq_partials(arena.buffer, self._partials)
+            copy = arena.compute_buffer(self.model.compute_dtype) \
                 if self.model.compute_dtype == torch.bfloat16 else None
-            ops.adamw_flat_step(self.arena.master, self.arena.buffer, self.exp_avg, self.exp_avg_sq, copy,
-                                self.lr, self.betas[0], self.betas[1], self.eps, self.weight_decay,
+            ops.adamw_flat_step(arena.master, arena.buffer, self.exp_avg, self.exp_avg_sq, copy,
+                                step_lr, self.betas[0], self.betas[1], self.eps, self.weight_decay,
                                 self.steps, self._partials if clip else None, self.max_norm)
-            self.arena.refresh_compute_copies(skip=copy)
-            return loss.detach()
-        if self.max_norm is not None:
-            self._last_norm = self.arena.clip_(self.max_norm)
-        self.optimizer.step()
-        # the master weights changed: the compute-dtype copies follow (fused optimizers leave
-        # the version counters alone, so this must be explicit)
-        if self.flat:
-            self.arena.refresh_compute_copies()
+            arena.refresh_compute_copies(skip=copy)
         else:
-            self.model.post_optimizer_hook()
+            if self.max_norm is not None:
+                self._last_norm = arena.clip_(self.max_norm)
+            for grp in self.optimizer.param_groups:
+                grp["lr"] = step_lr
+            self.optimizer.step()
+            # the master weights changed: the compute-dtype copies follow (fused optimizers leave
+            # the version counters alone, so this must be explicit)
+            if self.flat:
+                arena.refresh_compute_copies()
+            else:
+                self.model.post_optimizer_hook()
+        if self.status_every > 0 and self.steps % self.status_every == 0:
+            self.check_status()
         return loss.detach()
