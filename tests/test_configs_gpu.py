@@ -1,0 +1,96 @@
+"""The decoder at the TRUE widths of baseline configurations 1-4 against the CPU oracle.
+
+Every width-dependent piece that the small parity cases never reach runs here together, as it
+does in the benchmark: the staged RMSNorm variants for hidden sizes 1024 / 2048 / 2560 / 4096,
+head_dim-128 rotary rows inside a layer, ranks 16 / 32 / 64, the grouped q|k|v and gate|up
+launches (nine-region weight gradients) at real N, the output head sliced into chunks at
+V = 151936, the gather GEMM at r_e 256 - 1024, and both backward formulations of the
+projections. The layer count is cut to 2 x n_unique (every shared block used twice) and the
+batch to one sequence of 256 tokens, which the oracle finishes in seconds.
+
+Tolerance: 1e-2 per tensor (max|a-b| / max|b|), the bar for bf16 inputs with fp32 accumulation;
+the oracle runs in fp32 on the bf16-rounded parameter values the GPU computes with.
+"""
+import dataclasses
+
+import pytest
+import torch
+
+from oracle import lora_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2
+_ORACLE = {}
+
+
+def _oracle_case(name):
+    """Oracle loss and gradients of one configuration (cached: both routes compare with it)."""
+    if name in _ORACLE:
+        return _ORACLE[name]
+    from weightshared_torchtitan_b200.decoder import CONFIGS
+    c = CONFIGS[name]
+    L = 2 * c.n_unique
+    a = O.DecoderArgs(dim=c.dim, hidden_dim=c.hidden_dim, n_layers=L, n_unique=c.n_unique, n_heads=c.n_heads,
+                      n_kv_heads=c.n_kv_heads, head_dim=c.head_dim, rank=c.rank, vocab_size=c.vocab_size,
+                      embed_rank=c.embed_rank, max_seq_len=256)
+    torch.set_num_threads(max(torch.get_num_threads(), 1))
+    p = {k: v.to(torch.bfloat16).float().requires_grad_(True) for k, v in O.init_decoder_params(a, seed=77).items()}
+    g = torch.Generator().manual_seed(5)
+    tokens = torch.randint(0, a.vocab_size, (1, 256), generator=g)
+    labels = torch.randint(0, a.vocab_size, (1, 256), generator=g)
+    loss = O.decoder_loss(a, p, tokens, labels)
+    loss.backward()
+    _ORACLE.clear()            # keep one configuration's parameters on the host at a time
+    _ORACLE[name] = (a, p, tokens, labels, float(loss.item()))
+    return _ORACLE[name]
+
+
+@pytest.mark.parametrize("through_layer_gradient", [False, True])
+@pytest.mark.parametrize("name", ["qwen3-0.6b-ws", "qwen3-1.7b-ws", "qwen3-4b-ws", "qwen3-8b-ws"])
+def test_decoder_at_configuration_widths(name, through_layer_gradient):
+    if not torch.cuda.is_available():
+        pytest.fail("gpu tests need a CUDA device")
+    from weightshared_torchtitan_b200 import _lib
+    from weightshared_torchtitan_b200 import functional as Fn
+    from weightshared_torchtitan_b200.decoder import CONFIGS, WeightSharedDecoder
+    a, p, tokens, labels, loss_o = _oracle_case(name)
+    c = dataclasses.replace(CONFIGS[name], n_layers=a.n_layers, max_seq_len=256, loss_chunk=96)   # 3 chunks
+    m = WeightSharedDecoder(c).cuda()
+    m.load_named_params({k: v.detach().cuda() for k, v in p.items()})
+    saved = Fn.DERIVED_ADAPTER_GRADS
+    Fn.DERIVED_ADAPTER_GRADS = through_layer_gradient
+    try:
+        loss = m.loss(tokens.cuda(), labels.cuda())
+        loss.backward()
+    finally:
+        Fn.DERIVED_ADAPTER_GRADS = saved
+    torch.cuda.synchronize()
+    st, words = _lib.poll_status()
+    assert st == 0, (st, words)
+    assert abs(loss.item() - loss_o) < TOL * abs(loss_o), (loss.item(), loss_o)
+    L, U = c.n_layers, c.n_unique
+    got = {
+        "blocks.0.wq.weight": m.blocks[0].wq.weight.grad,
+        "blocks.0.wk.weight": m.blocks[0].wk.weight.grad,
+        f"blocks.{U - 1}.wo.weight": m.blocks[U - 1].wo.weight.grad,
+        f"blocks.{U - 1}.w1.weight": m.blocks[U - 1].w1.weight.grad,
+        "blocks.0.w2.weight": m.blocks[0].w2.weight.grad,
+        "layers.0.wq.w_a": m.layers[0].wq_offset.w_a.weight.grad,
+        "layers.0.wv.w_b": m.layers[0].wv_offset.w_b.weight.grad,
+        f"layers.{L - 1}.w3.w_a": m.layers[L - 1].w3_offset.w_a.weight.grad,
+        f"layers.{L - 1}.w2.w_b": m.layers[L - 1].w2_offset.w_b.weight.grad,
+        "embed.P": m.tok_embeddings.proj.weight.grad,
+        "layers.0.attention_norm": m.layers[0].attention_norm.weight.grad,
+        f"layers.{L - 1}.ffn_norm": m.layers[L - 1].ffn_norm.weight.grad,
+        "layers.1.q_norm": m.layers[1].q_norm.weight.grad,
+        "layers.1.k_norm": m.layers[1].k_norm.weight.grad,
+        "norm": m.norm.weight.grad,
+    }
+    errs = {k: O.max_rel_err(v, p[k].grad) for k, v in got.items()}
+    errs["output[::61]"] = O.max_rel_err(m.output.weight.grad[::61], p["output"].grad[::61])
+    tok_rows = tokens.flatten()[:16]
+    errs["embed.E_small[tokens]"] = O.max_rel_err(m.tok_embeddings.embed.weight.grad[tok_rows.cuda()],
+                                                  p["embed.E_small"].grad[tok_rows])
+    bad = {k: e for k, e in errs.items() if not e < TOL}
+    assert not bad, (name, through_layer_gradient, bad, errs)

@@ -229,3 +229,80 @@ def test_several_training_steps_follow_the_oracle(dtype, tol):
     assert want[-1] < want[0] - 0.02          # the curve moves, so stale weights would show
     for w, x in zip(want, got):
         assert abs(w - x) < tol * abs(w), (want, got)
+
+
+def test_state_dict_load_into_a_bound_model_reaches_the_kernels():
+    """A model that a TrainStep has already bound to its flat arena (its bf16 compute copies are
+    views of one flat buffer) takes other weights through state_dict_adapter.from_reference: the
+    next forward must compute with the loaded values, i.e. give the logits of a fresh model
+    loaded with the same values."""
+    from weightshared_torchtitan_b200 import state_dict_adapter as SDA
+    from weightshared_torchtitan_b200.train_step import TrainStep
+    a, p, m = _build_tiny(torch.bfloat16)
+    step = TrainStep(m, lr=1e-3)
+    g = torch.Generator().manual_seed(11)
+    tokens = torch.randint(0, a.vocab_size, (2, a.max_seq_len), generator=g).cuda()
+    labels = torch.randint(0, a.vocab_size, (2, a.max_seq_len), generator=g).cuda()
+    step(tokens, labels)                      # the flat bf16 copy now exists and holds stepped weights
+    _, p2, donor = _build_tiny(torch.bfloat16)
+    with torch.no_grad():
+        for q in donor.parameters():
+            q.mul_(1.25)
+    SDA.from_reference(m, {k: v.detach().clone() for k, v in SDA.to_reference(donor).items()})
+    with torch.no_grad():
+        got, want = m(tokens), donor(tokens)
+    assert torch.equal(got, want)
+    # and training goes on from the loaded weights with the step's own optimizer state
+    sd = {k: (v.clone() if torch.is_tensor(v) else v) for k, v in step.state_dict().items()}   # a snapshot
+    assert sd["steps"] == 1 and any(k.startswith("exp_avg.") for k in sd)
+    before = step(tokens, labels).item()
+    _, _, m2 = _build_tiny(torch.bfloat16)
+    step2 = TrainStep(m2, lr=1e-3)
+    SDA.from_reference(m2, {k: v.detach().clone() for k, v in SDA.to_reference(donor).items()})
+    step2.load_state_dict(sd)
+    assert step2.steps == 1
+    again = step2(tokens, labels).item()
+    assert abs(before - again) < 1e-6 * abs(before)
+    # (the embedding's scatter-add uses fp32 atomics, so the two runs may differ in the last bit)
+    assert torch.allclose(step.arena.master, step2.arena.master, rtol=1e-5, atol=1e-7)
+
+
+def test_ignored_labels_do_not_count_in_the_loss_mean():
+    """Labels of -100 (the ignore_index of F.cross_entropy that the reference's loss uses,
+    torchtitan/components/loss.py:18-22) are left out of the loss, of every gradient and of the
+    divisor of the mean."""
+    a, p, m = _build_tiny(torch.float32)
+    g = torch.Generator().manual_seed(12)
+    tokens = torch.randint(0, a.vocab_size, (2, a.max_seq_len), generator=g)
+    labels = torch.randint(0, a.vocab_size, (2, a.max_seq_len), generator=g)
+    labels[0, ::3] = -100
+    labels[1, 5:9] = -100
+    loss = m.loss(tokens.cuda(), labels.cuda())
+    loss.backward()
+    po = {k: v.detach().clone().requires_grad_(True) for k, v in p.items()}
+    want = O.decoder_loss(a, po, tokens, labels)
+    want.backward()
+    assert abs(loss.item() - want.item()) < 1e-4 * abs(want.item())
+    assert rel(m.blocks[0].wq.weight.grad, po["blocks.0.wq.weight"].grad) < 2e-4
+    assert rel(m.output.weight.grad, po["output"].grad) < 2e-4
+
+
+def test_lr_schedule_and_status_poll():
+    """lr as a callable of the step number (the reference's scheduler slot) and the periodic read
+    of the device status words inside the step."""
+    from weightshared_torchtitan_b200.train_step import TrainStep
+    a, p, m = _build_tiny(torch.bfloat16)
+    seen = []
+
+    def sched(step):
+        seen.append(step)
+        return 1e-3 / step
+
+    st = TrainStep(m, lr=sched, status_every=2)
+    g = torch.Generator().manual_seed(13)
+    tokens = torch.randint(0, a.vocab_size, (2, a.max_seq_len), generator=g).cuda()
+    labels = torch.randint(0, a.vocab_size, (2, a.max_seq_len), generator=g).cuda()
+    for _ in range(3):
+        st(tokens, labels)
+    assert seen == [1, 2, 3]
+    st.check_status()

@@ -134,9 +134,12 @@ class TrainStep:
         if self.reserved_sms > 0 and self.arena.buffer.is_cuda:
             ops.reserve_sms(self.reserved_sms, 1.5 * nbytes / (self.link_gbs * 1e6))
 
-    def __call__(self, tokens: torch.Tensor, labels: torch.Tensor, lr: Optional[float] = None) -> torch.Tensor:
+    def gradients(self, tokens: torch.Tensor, labels: torch.Tensor, exchange: bool = True) -> torch.Tensor:
+        """Zero the arena, forward + loss + backward and (``exchange``) the gradient average over
+        the data-parallel ranks, without the optimizer step: afterwards ``arena.buffer`` holds the
+        gradients the optimizer would see. Returns the detached loss of this rank's batch."""
         arena = self.arena
-        overlap = self.overlap and arena.world_size() > 1
+        overlap = exchange and self.overlap and arena.world_size() > 1
         arena.zero()
         if overlap:
             arena.on_bucket = self._bucket_launched
@@ -156,11 +159,16 @@ class TrainStep:
         if overlap:
             arena.finish_overlap()
             ops.reserve_sms(0, 0.0)
-        else:
+        elif exchange:
             arena.all_reduce_mean()
         if ev is not None:
             ev[1].record()
             self.timing.setdefault("allreduce_wait", []).append(ev)
+        return loss.detach()
+
+    def __call__(self, tokens: torch.Tensor, labels: torch.Tensor, lr: Optional[float] = None) -> torch.Tensor:
+        arena = self.arena
+        loss = self.gradients(tokens, labels, exchange=True)
         self.steps += 1
         step_lr = float(lr) if lr is not None else self._lr_at(self.steps)
         if self.fused_update:
@@ -187,4 +195,4 @@ class TrainStep:
                 self.model.post_optimizer_hook()
         if self.status_every > 0 and self.steps % self.status_every == 0:
             self.check_status()
-        return loss.detach()
+        return loss
