@@ -142,6 +142,27 @@ int wsl_lora_linear_fwd_group(int nproj, const void* x, long long ldx, const voi
                               const long long* r, long long M, long long K, void* stream);
 
 /*
+ * The gate and up projections of a SwiGLU MLP and the activation in ONE launch (bf16):
+ *   g[M,N] = x W_gate^T + T_cat[:, 0:r] B_gate^T
+ *   u[M,N] = x W_up^T   + T_cat[:, r:2r] B_up^T
+ *   h[M,N] = silu(g) * u        (from g and u as stored, i.e. rounded to bf16)
+ * Every accumulator tile holds 128 columns of g next to the same 128 columns of u (the two
+ * CTAs of a pair load the gate and the up weights), so the epilogue writes h without g and u
+ * being read back; g and u are still stored because the backward needs them. T_cat is the
+ * scaled pre-pass output of wsl_lora_prepass with A_cat = [A_gate; A_up].
+ * wsl_lora_swiglu_supported() tells whether a shape can take this path (N % 128 == 0, r % 8
+ * == 0, large enough for CTA-pair tiles); otherwise use wsl_lora_linear_fwd_group and
+ * wsl_swiglu_fwd, which give bit-identical results.
+ * Replaces F.silu(self.w1(x)) * self.w3(x) with LoRA on both projections:
+ * torchtitan/experiments/qwen3/model/model.py:251, torchtitan/models/llama3/model/model.py:189-192.
+ */
+int wsl_lora_swiglu_supported(long long M, long long N, long long K, long long r);
+int wsl_lora_swiglu_fwd(const void* x, long long ldx, const void* W_gate, const void* W_up,
+                        const void* T_cat, long long ldt, const void* B_gate, const void* B_up,
+                        void* g, void* u, void* h, long long ld_out, long long M, long long N,
+                        long long K, long long r, void* stream);
+
+/*
  * U[M,r] = s * dY[M,N] * B[N,r]
  * Backward pre-pass (the autograd MmBackward of w_b together with the
  * MulBackward of the scale): torchtitan/models/llama3/model/model.py:191.

@@ -784,3 +784,75 @@ def test_merged_weight_route_with_a_small_adapter(wsl):
     wsl.lora_adapter_grads_from_dw(G, [A], [B], [dA], [dB], 2.0)
     for got, w, name in zip((dX, dW, dA, dB), want[1:], ("dX", "dW", "dA", "dB")):
         assert rel(got, w) < TOL_BF16, (name, rel(got, w))
+
+
+# ------------------------------------------------- gate|up GEMM with the SwiGLU epilogue
+@pytest.mark.parametrize("M,N,K,r", [(1024, 256, 512, 16), (640, 384, 328, 8), (2048, 3072, 1024, 16),
+                                     (1000, 1280, 2560, 64), (512, 128, 64, 0)])
+def test_gate_up_swiglu_one_launch_matches_the_separate_kernels(wsl, M, N, K, r):
+    """wsl_lora_swiglu_fwd against wsl_lora_linear_fwd_group + wsl_swiglu_fwd: g, u and
+    h = silu(g) * u must be the same bits (the fused epilogue rounds g and u to bf16 before the
+    activation, as a pass over the stored matrices would), and h must agree with the oracle's
+    F.silu(w1 x) * w3 x within the bf16 tolerance. Ragged M and K, ranks 0 to 64."""
+    assert wsl.lora_swiglu_supported(M, N, K, r)
+    g_ = torch.Generator().manual_seed(90 + r)
+    bf = torch.bfloat16
+    x = torch.randn(M, K, generator=g_).cuda().to(bf)
+    Wg = (torch.randn(N, K, generator=g_) * 0.05).cuda().to(bf)
+    Wu = (torch.randn(N, K, generator=g_) * 0.05).cuda().to(bf)
+    if r:
+        Ag = ((torch.rand(r, K, generator=g_) * 2 - 1) / K ** 0.5).cuda().to(bf)
+        Au = ((torch.rand(r, K, generator=g_) * 2 - 1) / K ** 0.5).cuda().to(bf)
+        Bg = (torch.randn(N, r, generator=g_) * 0.05).cuda().to(bf)
+        Bu = (torch.randn(N, r, generator=g_) * 0.05).cuda().to(bf)
+        T_cat = wsl.lora_prepass(x, torch.cat((Ag, Au)), 2.0)
+        g1, u1, h1 = wsl.lora_swiglu_fwd(x, Wg, Wu, T_cat, Bg, Bu)
+        g0, u0 = wsl.lora_linear_fwd_group(x, [Wg, Wu], [T_cat[:, :r], T_cat[:, r:]], [Bg, Bu])
+        want_g = O.lora_linear(x.float().cpu(), Wg.float().cpu(), Ag.float().cpu(), Bg.float().cpu())
+        want_u = O.lora_linear(x.float().cpu(), Wu.float().cpu(), Au.float().cpu(), Bu.float().cpu())
+    else:
+        g1, u1, h1 = wsl.lora_swiglu_fwd(x, Wg, Wu, None, None, None)
+        g0, u0 = wsl.linear_fwd(x, Wg), wsl.linear_fwd(x, Wu)
+        want_g, want_u = x.float().cpu() @ Wg.float().cpu().T, x.float().cpu() @ Wu.float().cpu().T
+    h0 = wsl.swiglu_fwd(g0, u0)
+    assert torch.equal(g1, g0) and torch.equal(u1, u0)
+    assert torch.equal(h1, h0)
+    assert rel(g1, want_g) < TOL_BF16 and rel(u1, want_u) < TOL_BF16
+    assert rel(h1, torch.nn.functional.silu(want_g) * want_u) < TOL_BF16
+
+
+def test_gate_up_swiglu_function_gradients_match_the_unfused_composition(wsl):
+    """The autograd Function of the fused MLP front half against lora_linear_group + swiglu:
+    same output bits and the same in-place gradients, for both backward formulations."""
+    from weightshared_torchtitan_b200 import functional as Fn
+    M, N, K, r = 2048, 768, 512, 16
+    gen = torch.Generator().manual_seed(123)
+    bf = torch.bfloat16
+    x0 = torch.randn(M, K, generator=gen).cuda().to(bf)
+    Ws = [(torch.randn(N, K, generator=gen) * 0.05).cuda().to(bf) for _ in range(2)]
+    As = [((torch.rand(r, K, generator=gen) * 2 - 1) / K ** 0.5).cuda().to(bf) for _ in range(2)]
+    Bs = [(torch.randn(N, r, generator=gen) * 0.05).cuda().to(bf) for _ in range(2)]
+    dh = torch.randn(M, N, generator=gen).cuda().to(bf)
+    saved = Fn.DERIVED_ADAPTER_GRADS
+    try:
+        for flag in (False, True):
+            Fn.DERIVED_ADAPTER_GRADS = flag
+            res = []
+            for fused in (True, False):
+                x = x0.clone().requires_grad_(True)
+                sinks = [(torch.zeros(N, K, device="cuda"), torch.zeros(r, K, device="cuda"),
+                          torch.zeros(N, r, device="cuda")) for _ in range(2)]
+                if fused:
+                    h = Fn.lora_gate_up_swiglu(x, Ws, As, Bs, 2.0, sinks)
+                else:
+                    gate, up = Fn.lora_linear_group(x, Ws, As, Bs, 2.0, sinks)
+                    h = Fn.swiglu(gate, up)
+                h.backward(dh)
+                res.append((h.detach(), x.grad, sinks))
+            (h1, dx1, s1), (h0, dx0, s0) = res
+            assert torch.equal(h1, h0) and torch.equal(dx1, dx0)
+            for a, b in zip(s1, s0):
+                for ta, tb in zip(a, b):
+                    assert torch.equal(ta, tb)
+    finally:
+        Fn.DERIVED_ADAPTER_GRADS = saved

@@ -71,6 +71,12 @@ struct Region {
   int unit_begin;     // first work unit of this region (units = tiles * splits)
   void* copy;         // bf16 copy of alpha * acc (RegionDesc::copy), or nullptr
   long long ld_copy;
+  // kEpiSwiGLU regions (pair launches): the second CTA of a pair loads its half of the B tile
+  // from these maps at contraction coordinate kk - b2_shift; tensor maps out_map, out_map + 1
+  // and out_map + 2 are g, u and silu(g) * u.
+  signed char b2_map[kMaxSeg];
+  int b2_shift[kMaxSeg];
+  int swiglu;
 };
 
 struct GemmParams {
@@ -339,7 +345,10 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       const int b_slabs = (b_rows + 63) >> 6;
       const uint32_t tx_cta = A_STAGE_BYTES + (B_MN ? b_slabs * SLAB_BYTES : b_rows * BK * 2);
       const int m0 = ti.m0 + BM * rank;
-      const int n0 = ti.n0 + b_rows * rank;
+      // gate|up tiles: both CTAs load the SAME 128 weight rows, the leader from the gate
+      // matrices, its peer from the up matrices
+      const bool dual_b = PAIR && R.swiglu != 0;
+      const int n0 = dual_b ? (ti.n0 >> 1) : ti.n0 + b_rows * rank;
       // Gathered A operand: the four row ids of this lane depend on the tile only, so they are
       // read once per tile, not once per k-block (a dependent global load in front of every
       // stage would set the pace of the whole ring).
@@ -355,7 +364,8 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       for (int sg = 0; ok && sg < p.nseg; ++sg) {
         const bool gather = p.gather_tokens != nullptr && ti.r == 0 && sg == 0;
         const CUtensorMap* ma = &p.maps[R.a_map[sg]];
-        const CUtensorMap* mb = &p.maps[R.b_map[sg]];
+        const CUtensorMap* mb = &p.maps[(dual_b && rank == 1) ? R.b2_map[sg] : R.b_map[sg]];
+        const int b_kshift = (dual_b && rank == 1) ? R.b2_shift[sg] : 0;
         const int klen = p.seg_k[sg];
         const int nkb = (klen + BK - 1) / BK;
         int lo, hi;
@@ -397,7 +407,8 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
                 for (int j = 0; j < b_slabs; ++j)
                   tma_load_2d_pair(sb + j * SLAB_BYTES, mb, fb, n0 + 64 * j, kk);
               } else {
-                tma_load_2d_pair(sb, mb, fb, kk, n0);
+                // (a coordinate left of the matrix, or beyond its last column, reads as zeros)
+                tma_load_2d_pair(sb, mb, fb, kk - b_kshift, n0);
               }
             } else {
               const uint32_t fb = full_bar(s);
@@ -562,7 +573,55 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       const int row = row0 + trow;
       const uint32_t taddr =
           tmem_base + static_cast<uint32_t>(buf * BN_MAX) + (static_cast<uint32_t>(q * 32) << 16);
-      if (R.out_map >= 0) {
+      if (PAIR && R.swiglu != 0) {
+        // ---- gate|up tile: accumulator columns [0,128) are g, [128,256) are u for the same
+        // 128 output columns. Three staged 64-column stores per half: g, u (what the backward
+        // needs) and silu(g) * u computed from the bf16-rounded g and u, exactly what a
+        // separate pass over the stored matrices would produce.
+        const int ocol0 = ti.n0 >> 1;
+        const uint32_t swz = static_cast<uint32_t>(trow & 7);
+        for (int c = 0; c < 128; c += 64) {
+#pragma unroll 1
+          for (int part = 0; part < 3; ++part, ++chunk_ctr) {
+            const uint32_t sbuf = epi_base + (chunk_ctr & 1u) * EPI_STAGE_BYTES;
+            const uint32_t srow = sbuf + static_cast<uint32_t>(trow) * 128u;
+            if (issuer) tma_wait_group_read<1>();
+            epi_bar_sync();
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t v[32];
+              if (part < 2) {
+                tmem_ld_32x32(taddr + (part == 1 ? 128 : 0) + c + 32 * h, v);
+                tmem_ld_wait();
+              } else {
+                uint32_t w[32];
+                tmem_ld_32x32(taddr + c + 32 * h, v);
+                tmem_ld_32x32(taddr + 128 + c + 32 * h, w);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[j])));
+                  const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(w[j])));
+                  v[j] = __float_as_uint(g / (1.f + __expf(-g)) * u);
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                st_shared_v4(srow + ((static_cast<uint32_t>(4 * h + j) ^ swz) << 4),
+                             pack_bf16(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1])),
+                             pack_bf16(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3])),
+                             pack_bf16(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5])),
+                             pack_bf16(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7])));
+            }
+            fence_proxy_async_smem();
+            epi_bar_sync();
+            if (issuer && R.rows > 0) {
+              tma_store_2d(&p.maps[R.out_map + part], sbuf, ocol0 + c, row0);
+              tma_commit_group();
+            }
+          }
+        }
+      } else if (R.out_map >= 0) {
         // ---- staged epilogue: TMEM -> registers -> swizzled shared memory -> TMA store (or
         // TMA reduce-add for the in-place fp32 accumulation). 128-byte rows: 64 bf16 or 32 fp32
         // columns per chunk; two staging buffers so a store drains while the next chunk fills.
@@ -1076,7 +1135,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     const RegionDesc& rd = g.region[r];
     Region& R = p.reg[r];
     if (rd.mo <= 0 || rd.no <= 0 || rd.out == nullptr) return WSL_ERR_BAD_ARG;
-    const int vec = rd.mode == kEpiStoreBf16 ? 8 : 4;
+    const int vec = (rd.mode == kEpiStoreBf16 || rd.mode == kEpiSwiGLU) ? 8 : 4;
     if (rd.transposed) {
       if (rd.mode == kEpiStoreBf16) return WSL_ERR_BAD_ARG;
       if ((rd.mo % 4) != 0 || (rd.ld_out % 4) != 0 || rd.ld_out < rd.mo ||
@@ -1086,9 +1145,21 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
                (reinterpret_cast<uintptr_t>(rd.out) & 15u) != 0) {
       return WSL_ERR_ALIGN;
     }
-    const long long n_tiles = (rd.no + BN_MAX - 1) / BN_MAX;
+    const bool swiglu = rd.mode == kEpiSwiGLU;
+    if (swiglu) {
+      if (!pair || g.a_mn || g.b_mn || rd.transposed || rd.copy != nullptr || (rd.no % 128) != 0 ||
+          rd.out2 == nullptr || rd.out3 == nullptr || g.workspace != nullptr)
+        return WSL_ERR_BAD_ARG;
+      if (((reinterpret_cast<uintptr_t>(rd.out2) | reinterpret_cast<uintptr_t>(rd.out3)) & 15u) != 0)
+        return WSL_ERR_ALIGN;
+    }
+    long long n_tiles = (rd.no + BN_MAX - 1) / BN_MAX;
     long long bn = (rd.no + n_tiles - 1) / n_tiles;
     bn = (bn + bn_round - 1) / bn_round * bn_round;
+    if (swiglu) {   // one tile = 128 output columns of g next to the same 128 of u
+      n_tiles = rd.no / 128;
+      bn = BN_MAX;
+    }
     const long long m_tiles = (rd.mo + bm_tile - 1) / bm_tile;
     if (m_tiles * n_tiles + tiles > 0x7fffffffLL) return WSL_ERR_TOO_LARGE;
     R.m_tiles = static_cast<int>(m_tiles);
@@ -1104,6 +1175,11 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     R.ws_off = 0;
     R.transposed = rd.transposed ? 1 : 0;
     R.out_map = -1;
+    R.swiglu = swiglu ? 1 : 0;
+    for (int s = 0; s < kMaxSeg; ++s) {
+      R.b2_map[s] = 0;
+      R.b2_shift[s] = 0;
+    }
     if (rd.copy != nullptr) {
       if (rd.transposed || rd.mode == kEpiStoreBf16) return WSL_ERR_BAD_ARG;
       if ((rd.no % 8) != 0 || (rd.ld_copy % 8) != 0 || rd.ld_copy < rd.no ||
@@ -1139,7 +1215,11 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       const bool a_k_ok = g.a_mn ? (ga0 ? true : ak == g.seg_k[s]) : ak == g.seg_k[s];
       const bool b_k_ok = g.b_mn ? (gb0 ? true : bk == g.seg_k[s]) : bk == g.seg_k[s];
       const bool ragged_ok = g.ragged_k && ak == bk && ak > 0 && ak <= g.seg_k[s];
-      if (!((a_k_ok && b_k_ok) || ragged_ok)) return WSL_ERR_BAD_ARG;
+      // gate|up tiles: each of the two B matrices may cover only part of the segment
+      const bool dual_ok = swiglu && a_k_ok && bk > 0 && bk <= g.seg_k[s] && rd.b2[s].rows == rd.no &&
+                           rd.b2[s].cols > 0 && rd.b2_k_shift[s] >= 0 && (rd.b2_k_shift[s] % 8) == 0 &&
+                           rd.b2_k_shift[s] + rd.b2[s].cols <= g.seg_k[s];
+      if (swiglu ? !dual_ok : !((a_k_ok && b_k_ok) || ragged_ok)) return WSL_ERR_BAD_ARG;
       if (g.a_mn ? a.cols != rd.mo : (!ga0 && a.rows != rd.mo)) return WSL_ERR_BAD_ARG;
       if (g.b_mn ? b.cols != rd.no : b.rows != rd.no) return WSL_ERR_BAD_ARG;
       const bool ga = g.gather_tokens != nullptr && g.gather_a && r == 0 && s == 0;
@@ -1153,6 +1233,13 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
                        : make_map_bf16(&p.maps[nmaps], b, BK, static_cast<int>(pair ? bn / 2 : bn));
       if (st != WSL_OK) return st;
       R.b_map[s] = static_cast<signed char>(nmaps++);
+      if (swiglu) {
+        if (nmaps + 4 > kMaxMaps) return WSL_ERR_BAD_ARG;
+        st = make_map_bf16(&p.maps[nmaps], rd.b2[s], BK, static_cast<int>(bn / 2));
+        if (st != WSL_OK) return st;
+        R.b2_map[s] = static_cast<signed char>(nmaps++);
+        R.b2_shift[s] = rd.b2_k_shift[s];
+      }
     }
   }
   p.total_tiles = static_cast<int>(tiles);
@@ -1211,11 +1298,23 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     // staged TMA-store epilogue where the tile width is a whole number of 128-byte chunks
     for (int r = 0; r < g.nregion; ++r) {
       const RegionDesc& rd = g.region[r];
+      if (rd.mode == kEpiSwiGLU) continue;   // its three maps are made below
       const bool f32 = rd.mode != kEpiStoreBf16;
       if (rd.transposed || (p.reg[r].bn % (f32 ? 32 : 64)) != 0) continue;
       st = make_map_out(&p.maps[nmaps], rd.out, rd.mo, rd.no, rd.ld_out, f32);
       if (st != WSL_OK) return st;
       p.reg[r].out_map = nmaps++;
+    }
+  }
+  for (int r = 0; r < g.nregion; ++r) {
+    const RegionDesc& rd = g.region[r];
+    if (rd.mode != kEpiSwiGLU) continue;
+    if (nmaps + 3 > kMaxMaps) return WSL_ERR_BAD_ARG;
+    void* outs[3] = {rd.out, rd.out2, rd.out3};
+    p.reg[r].out_map = nmaps;
+    for (int i = 0; i < 3; ++i) {
+      st = make_map_out(&p.maps[nmaps++], outs[i], rd.mo, rd.no, rd.ld_out, false);
+      if (st != WSL_OK) return st;
     }
   }
   const long long units = p.total_units;

@@ -16,6 +16,9 @@ enum EpilogueMode : int {
   kEpiStoreBf16 = 0,   // out(bf16)  = alpha * acc
   kEpiStoreF32 = 1,    // out(fp32)  = alpha * acc
   kEpiAccumF32 = 2,    // out(fp32) += alpha * acc   (tiles own their outputs: plain RMW)
+  // Gate and up projection of a SwiGLU MLP in one accumulator tile (see RegionDesc::b2):
+  // out(bf16) = g, out2 = u, out3 = silu(g) * u with g, u rounded to bf16 first.
+  kEpiSwiGLU = 3,
 };
 
 // A row-major bf16 matrix in device memory: `rows` x `cols`, row pitch `ld` elements.
@@ -49,6 +52,19 @@ struct RegionDesc {
   // operand of a follow-up GEMM. nullptr = none.
   void* copy;
   long long ld_copy;
+  // kEpiSwiGLU only (K-major operands, CTA-pair launch): the 256-column accumulator tile holds
+  // 128 columns of  g = sum_seg A_seg b[seg]^T  and the SAME 128 output columns of
+  // u = sum_seg A_seg b2[seg]^T  side by side, so the epilogue has both halves of every
+  // silu(g) * u in front of it. `no` counts the output columns of ONE of them (a multiple of
+  // 128); out / out2 / out3 are the three [mo, no] bf16 results (pitch ld_out each).
+  // b2_k_shift[seg]: contraction offset of b2 inside the segment, in elements; b[seg] covers
+  // segment columns [0, b.cols) and b2[seg] covers [shift, shift + b2.cols), the rest of each
+  // reads as zeros. That expresses the block-diagonal adapter factor  [T_g | T_u] . [B_g 0; 0 B_u]^T
+  // without materialising the zero blocks.
+  Mat b2[kMaxSeg];
+  int b2_k_shift[kMaxSeg];
+  void* out2;
+  void* out3;
 };
 
 struct GemmDesc {

@@ -289,6 +289,47 @@ int wsl_lora_linear_fwd_group(int nproj, const void* x, long long ldx, const voi
   return launch_block_gemm(g, static_cast<cudaStream_t>(stream));
 }
 
+int wsl_lora_swiglu_supported(long long M, long long N, long long K, long long r) {
+  return (M > 0 && N > 0 && K > 0 && r >= 0 && (N % 128) == 0 && (r % 8) == 0 && use_pair_tiles(M, 2 * N)) ? 1 : 0;
+}
+
+int wsl_lora_swiglu_fwd(const void* x, long long ldx, const void* W_gate, const void* W_up,
+                        const void* T_cat, long long ldt, const void* B_gate, const void* B_up,
+                        void* g_out, void* u_out, void* h_out, long long ld_out, long long M,
+                        long long N, long long K, long long r, void* stream) {
+  if (!x || !W_gate || !W_up || !g_out || !u_out || !h_out || M <= 0 || N <= 0 || K <= 0 || r < 0)
+    return WSL_ERR_BAD_ARG;
+  if (r > 0 && (!T_cat || !B_gate || !B_up)) return WSL_ERR_BAD_ARG;
+  if (!wsl_lora_swiglu_supported(M, N, K, r)) return WSL_ERR_BAD_ARG;
+  GemmDesc g = {};
+  g.nseg = r > 0 ? 2 : 1;
+  g.seg_k[0] = static_cast<int>(K);
+  g.seg_k[1] = static_cast<int>(2 * r);
+  g.nregion = 1;
+  RegionDesc& r0 = g.region[0];
+  r0.a[0] = mat(x, M, K, ldx);
+  r0.b[0] = mat(W_gate, N, K, K);
+  r0.b2[0] = mat(W_up, N, K, K);
+  r0.b2_k_shift[0] = 0;
+  if (r > 0) {
+    // [T_gate | T_up] . [B_gate 0 ; 0 B_up]^T: the gate rows see columns [0, r) of T_cat, the
+    // up rows columns [r, 2r)
+    r0.a[1] = mat(T_cat, M, 2 * r, ldt);
+    r0.b[1] = mat(B_gate, N, r, r);
+    r0.b2[1] = mat(B_up, N, r, r);
+    r0.b2_k_shift[1] = static_cast<int>(r);
+  }
+  r0.mo = M;
+  r0.no = N;
+  r0.out = g_out;
+  r0.out2 = u_out;
+  r0.out3 = h_out;
+  r0.ld_out = ld_out;
+  r0.mode = kEpiSwiGLU;
+  r0.alpha = 1.f;
+  return launch_block_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
 int wsl_lora_bwd_prepass(const void* dY, long long lddy, const void* B, void* U, long long ldu,
                          long long M, long long N, long long r, float sc, int dtype,
                          void* stream) {

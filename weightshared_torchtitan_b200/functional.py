@@ -135,11 +135,7 @@ class LoRALinearGroupFunction(torch.autograd.Function):
         else:
             for p in range(P):
                 ys.append(ops.lora_linear_fwd(x2, Ws[p], Ts[p], Bs[p]).view(*x.shape[:-1], Ws[p].shape[0]))
-        ctx.derived = (DERIVED_ADAPTER_GRADS is not False and sinks is not None and x2.dtype == torch.bfloat16
-                       and all(t[0] is not None and t[1] is not None and t[2] is not None for t in sinks)
-                       and all(A.shape[0] in ops.MERGE_RANKS for A in As)
-                       and (DERIVED_ADAPTER_GRADS is True
-                            or _derived_pays(x2.shape[0], x2.shape[1], [W.shape[0] for W in Ws])))
+        ctx.derived = _derived_route(x2, sinks, Ws, As)
         ctx.save_for_backward(x2, None if ctx.derived else T_cat, *wab)
         ctx.s = float(s)
         ctx.sinks = sinks
@@ -160,40 +156,17 @@ class LoRALinearGroupFunction(torch.autograd.Function):
                          for w, need in zip(wab, ctx.needs_input_grad[5:])]
             return (dX, None, None, None, None, *grads)
         x2, T_cat, *wab = ctx.saved_tensors
-        P = ctx.P
-        Ws, As, Bs = list(wab[0::3]), list(wab[1::3]), list(wab[2::3])
-        if ctx.derived:
-            dY2 = []
-            for p in range(P):
-                d = dYs[p]
-                if d is None:
-                    d = torch.zeros(x2.shape[0], Ws[p].shape[0], device=x2.device, dtype=x2.dtype)
-                d = _flat(d)
-                if d.stride(-1) != 1:
-                    d = d.contiguous()
-                dY2.append(d)
-            dX = None
-            if ctx.needs_input_grad[0]:
-                if len({A.shape[0] for A in As}) == 1:
-                    Weffs = ops.lora_merge_weight(Ws, As, Bs, ctx.s)
-                else:
-                    Weffs = [ops.lora_merge_weight([Ws[p]], [As[p]], [Bs[p]], ctx.s)[0] for p in range(P)]
-                dX = ops.lora_linear_bwd_dx(dY2, [None] * P, Weffs, [None] * P).view(ctx.x_shape)
-            dWls = ops.bwd_dw_layer_group(dY2, x2, [t[0] for t in ctx.sinks])
-            if ctx.batch is not None:
-                ctx.batch.add(dWls, As, Bs, [t[1] for t in ctx.sinks], [t[2] for t in ctx.sinks], ctx.s)
-            else:
-                ops.lora_adapter_grads_from_dw(dWls, As, Bs, [t[1] for t in ctx.sinks],
-                                               [t[2] for t in ctx.sinks], ctx.s)
-            return (dX, None, None, None, None, *([None] * (3 * P)))
-        if ctx.batch is not None:
-            ctx.batch.nothing_to_add()
-        dY2, Us = [], []
-        # the U of all projections side by side, so that dX contracts [U_0 | U_1 | ...] with
-        # the stacked A matrices in ONE rank-sum segment instead of one tiny segment each
-        r_tot = sum(A.shape[0] for A in As)
-        U_cat = torch.empty(x2.shape[0], r_tot, device=x2.device, dtype=x2.dtype)
-        off = 0
+        return _group_backward(ctx, x2, T_cat, wab, dYs)
+
+
+def _group_backward(ctx, x2, T_cat, wab, dYs):
+    """Backward of P projections that read the same x (shared by LoRALinearGroupFunction and
+    the gate|up + SwiGLU Function): returns the gradient tuple of
+    (x, s, sinks, anchors, batch, W_0, A_0, B_0, ...)."""
+    P = ctx.P
+    Ws, As, Bs = list(wab[0::3]), list(wab[1::3]), list(wab[2::3])
+    if ctx.derived:
+        dY2 = []
         for p in range(P):
             d = dYs[p]
             if d is None:
@@ -202,50 +175,145 @@ class LoRALinearGroupFunction(torch.autograd.Function):
             if d.stride(-1) != 1:
                 d = d.contiguous()
             dY2.append(d)
-            r = As[p].shape[0]
-            Us.append(ops.lora_bwd_prepass(d, Bs[p], ctx.s, out=U_cat[:, off:off + r]))
-            off += r
         dX = None
         if ctx.needs_input_grad[0]:
-            if P == 1:
-                dX = ops.lora_linear_bwd_dx(dY2, Us, Ws, As)
+            if len({A.shape[0] for A in As}) == 1:
+                Weffs = ops.lora_merge_weight(Ws, As, Bs, ctx.s)
             else:
-                A_cat = torch.cat(As, dim=0)
-                dX = ops.lora_linear_bwd_dx(dY2, [U_cat] + [None] * (P - 1), Ws, [A_cat] + [None] * (P - 1))
-            dX = dX.view(ctx.x_shape)
-        grads: List[Optional[torch.Tensor]] = []
-        off = 0
-        if (ctx.sinks is not None and P > 1 and x2.dtype == torch.bfloat16
-                and all(s[0] is not None and s[1] is not None and s[2] is not None for s in ctx.sinks)):
-            # all projections of the group in one weight-gradient launch
-            Ts = []
-            for p in range(P):
-                r = As[p].shape[0]
-                Ts.append(T_cat[:, off:off + r])
-                off += r
-            ops.lora_linear_bwd_dw_group(dY2, Us, x2, Ts, [s[0] for s in ctx.sinks],
-                                         [s[1] for s in ctx.sinks], [s[2] for s in ctx.sinks])
-            return (dX, None, None, None, None, *([None] * (3 * P)))
+                Weffs = [ops.lora_merge_weight([Ws[p]], [As[p]], [Bs[p]], ctx.s)[0] for p in range(P)]
+            dX = ops.lora_linear_bwd_dx(dY2, [None] * P, Weffs, [None] * P).view(ctx.x_shape)
+        dWls = ops.bwd_dw_layer_group(dY2, x2, [t[0] for t in ctx.sinks])
+        if ctx.batch is not None:
+            ctx.batch.add(dWls, As, Bs, [t[1] for t in ctx.sinks], [t[2] for t in ctx.sinks], ctx.s)
+        else:
+            ops.lora_adapter_grads_from_dw(dWls, As, Bs, [t[1] for t in ctx.sinks],
+                                           [t[2] for t in ctx.sinks], ctx.s)
+        return (dX, None, None, None, None, *([None] * (3 * P)))
+    if ctx.batch is not None:
+        ctx.batch.nothing_to_add()
+    dY2, Us = [], []
+    # the U of all projections side by side, so that dX contracts [U_0 | U_1 | ...] with
+    # the stacked A matrices in ONE rank-sum segment instead of one tiny segment each
+    r_tot = sum(A.shape[0] for A in As)
+    U_cat = torch.empty(x2.shape[0], r_tot, device=x2.device, dtype=x2.dtype)
+    off = 0
+    for p in range(P):
+        d = dYs[p]
+        if d is None:
+            d = torch.zeros(x2.shape[0], Ws[p].shape[0], device=x2.device, dtype=x2.dtype)
+        d = _flat(d)
+        if d.stride(-1) != 1:
+            d = d.contiguous()
+        dY2.append(d)
+        r = As[p].shape[0]
+        Us.append(ops.lora_bwd_prepass(d, Bs[p], ctx.s, out=U_cat[:, off:off + r]))
+        off += r
+    dX = None
+    if ctx.needs_input_grad[0]:
+        if P == 1:
+            dX = ops.lora_linear_bwd_dx(dY2, Us, Ws, As)
+        else:
+            A_cat = torch.cat(As, dim=0)
+            dX = ops.lora_linear_bwd_dx(dY2, [U_cat] + [None] * (P - 1), Ws, [A_cat] + [None] * (P - 1))
+        dX = dX.view(ctx.x_shape)
+    grads: List[Optional[torch.Tensor]] = []
+    off = 0
+    if (ctx.sinks is not None and P > 1 and x2.dtype == torch.bfloat16
+            and all(s[0] is not None and s[1] is not None and s[2] is not None for s in ctx.sinks)):
+        # all projections of the group in one weight-gradient launch
+        Ts = []
         for p in range(P):
             r = As[p].shape[0]
-            T = T_cat[:, off:off + r]
+            Ts.append(T_cat[:, off:off + r])
             off += r
-            if ctx.sinks is not None:
-                dW, dA, dB = ctx.sinks[p]
-                if dW is not None or dA is not None or dB is not None:
-                    ops.lora_linear_bwd_dw(dY2[p], Us[p], x2, T, dW, dA, dB)
-                grads += [None, None, None]
-            else:
-                need = ctx.needs_input_grad[5 + 3 * p: 8 + 3 * p]
-                dev = x2.device
-                dW = torch.zeros(Ws[p].shape, device=dev, dtype=torch.float32) if need[0] else None
-                dA = torch.zeros(As[p].shape, device=dev, dtype=torch.float32) if need[1] else None
-                dB = torch.zeros(Bs[p].shape, device=dev, dtype=torch.float32) if need[2] else None
-                if any(need):
-                    ops.lora_linear_bwd_dw(dY2[p], Us[p], x2, T, dW, dA, dB)
-                grads += [g.to(w.dtype) if g is not None else None
-                          for g, w in ((dW, Ws[p]), (dA, As[p]), (dB, Bs[p]))]
-        return (dX, None, None, None, None, *grads)
+        ops.lora_linear_bwd_dw_group(dY2, Us, x2, Ts, [s[0] for s in ctx.sinks],
+                                     [s[1] for s in ctx.sinks], [s[2] for s in ctx.sinks])
+        return (dX, None, None, None, None, *([None] * (3 * P)))
+    for p in range(P):
+        r = As[p].shape[0]
+        T = T_cat[:, off:off + r]
+        off += r
+        if ctx.sinks is not None:
+            dW, dA, dB = ctx.sinks[p]
+            if dW is not None or dA is not None or dB is not None:
+                ops.lora_linear_bwd_dw(dY2[p], Us[p], x2, T, dW, dA, dB)
+            grads += [None, None, None]
+        else:
+            need = ctx.needs_input_grad[5 + 3 * p: 8 + 3 * p]
+            dev = x2.device
+            dW = torch.zeros(Ws[p].shape, device=dev, dtype=torch.float32) if need[0] else None
+            dA = torch.zeros(As[p].shape, device=dev, dtype=torch.float32) if need[1] else None
+            dB = torch.zeros(Bs[p].shape, device=dev, dtype=torch.float32) if need[2] else None
+            if any(need):
+                ops.lora_linear_bwd_dw(dY2[p], Us[p], x2, T, dW, dA, dB)
+            grads += [g.to(w.dtype) if g is not None else None
+                      for g, w in ((dW, Ws[p]), (dA, As[p]), (dB, Bs[p]))]
+    return (dX, None, None, None, None, *grads)
+
+
+def _derived_route(x2, sinks, Ws, As) -> bool:
+    """Whether the backward of this group goes through the layer's own weight gradient."""
+    return (DERIVED_ADAPTER_GRADS is not False and sinks is not None and x2.dtype == torch.bfloat16
+            and all(t[0] is not None and t[1] is not None and t[2] is not None for t in sinks)
+            and all(A.shape[0] in ops.MERGE_RANKS for A in As)
+            and (DERIVED_ADAPTER_GRADS is True
+                 or _derived_pays(x2.shape[0], x2.shape[1], [W.shape[0] for W in Ws])))
+
+
+class LoRAGateUpSwiGLUFunction(torch.autograd.Function):
+    """h = silu(x W_g^T + s (x A_g^T) B_g^T) * (x W_u^T + s (x A_u^T) B_u^T): the gate and up
+    projections of the MLP and the activation in one launch
+    (``w2(F.silu(w1(x)) * w3(x))`` without the w2, torchtitan/experiments/qwen3/model/model.py:251).
+
+    forward(ctx, x, s, sinks, anchors, batch, W_g, A_g, B_g, W_u, A_u, B_u) -> h
+
+    The accumulator tile of the GEMM holds matching columns of gate and up side by side, so the
+    activation is applied in the epilogue; gate and up are still written once (bf16) because the
+    backward needs them: d gate = dh u silu'(gate), d up = dh silu(gate), then the backward of a
+    two-projection group. Results are bit-identical to lora_linear_group followed by swiglu."""
+
+    @staticmethod
+    def forward(ctx, x, s, sinks, anchors, batch, Wg, Ag, Bg, Wu, Au, Bu):
+        x2 = _flat(x)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        T_cat = ops.lora_prepass(x2, torch.cat((Ag, Au), dim=0), s)
+        g, u, h = ops.lora_swiglu_fwd(x2, Wg, Wu, T_cat, Bg, Bu)
+        ctx.P = 2
+        ctx.batch = batch
+        ctx.s = float(s)
+        ctx.sinks = sinks
+        ctx.x_shape = x.shape
+        ctx.derived = _derived_route(x2, sinks, [Wg, Wu], [Ag, Au])
+        ctx.save_for_backward(x2, None if ctx.derived else T_cat, Wg, Ag, Bg, Wu, Au, Bu, g, u)
+        return h.view(*x.shape[:-1], Wg.shape[0])
+
+    @staticmethod
+    def backward(ctx, dh):
+        x2, T_cat, *rest = ctx.saved_tensors
+        wab, (g, u) = rest[:6], rest[6:]
+        d = _flat(dh)
+        if not d.is_contiguous():
+            d = d.contiguous()
+        dg, du = ops.swiglu_bwd(d, g, u)
+        return _group_backward(ctx, x2, T_cat, wab, (dg, du))
+
+
+def lora_gate_up_swiglu(x: torch.Tensor, Ws, As, Bs, s: float, sinks=None,
+                        anchors: Tuple[torch.Tensor, ...] = (),
+                        batch: Optional[AdapterGradBatch] = None) -> torch.Tensor:
+    """silu(gate(x)) * up(x) with Ws = (W_gate, W_up) etc. Takes the one-launch path where the
+    shapes allow it (see ops.lora_swiglu_supported), else the grouped forward followed by the
+    stand-alone activation kernel; both give the same bits."""
+    x2 = _flat(x)
+    Wg, Wu = Ws
+    if (x2.shape[0] > 0 and x2.dtype == torch.bfloat16 and As[0].shape[0] == As[1].shape[0]
+            and Wg.shape == Wu.shape
+            and ops.lora_swiglu_supported(x2.shape[0], Wg.shape[0], Wg.shape[1], As[0].shape[0])):
+        return LoRAGateUpSwiGLUFunction.apply(x, s, sinks, _Anchor(anchors, x), batch,
+                                              Wg, As[0], Bs[0], Wu, As[1], Bs[1])
+    gate, up = lora_linear_group(x, Ws, As, Bs, s, sinks, anchors, batch)
+    return swiglu(gate, up)
 
 
 def lora_linear_group(x: torch.Tensor, Ws: Sequence[torch.Tensor], As: Sequence[torch.Tensor],

@@ -207,6 +207,42 @@ def lora_linear_fwd_group(x: torch.Tensor, Ws, Ts, Bs):
     return ys
 
 
+def lora_swiglu_supported(M: int, N: int, K: int, r: int) -> bool:
+    """Whether lora_swiglu_fwd covers this shape (wsl_lora_swiglu_supported)."""
+    return bool(_lib.lib().wsl_lora_swiglu_supported(M, N, K, r))
+
+
+def lora_swiglu_fwd(x: torch.Tensor, Wg: torch.Tensor, Wu: torch.Tensor, T_cat: Optional[torch.Tensor],
+                    Bg: Optional[torch.Tensor], Bu: Optional[torch.Tensor]):
+    """(g, u, h) with g = x Wg^T + T_cat[:, :r] Bg^T, u = x Wu^T + T_cat[:, r:] Bu^T and
+    h = silu(g) * u, in one launch (wsl_lora_swiglu_fwd, bf16)."""
+    x, Wg, Wu = _mat(x, "x"), _mat(Wg, "W_gate").contiguous(), _mat(Wu, "W_up").contiguous()
+    _same(WSL_BF16, x, Wg, Wu)
+    M, K = x.shape
+    N = Wg.shape[0]
+    if Wg.shape != (N, K) or Wu.shape != (N, K):
+        raise ValueError("W_gate and W_up must both be [N, K]")
+    r = 0
+    tp = bgp = bup = None
+    ldt = 0
+    if T_cat is not None:
+        T_cat, Bg, Bu = _mat(T_cat, "T_cat"), _mat(Bg, "B_gate").contiguous(), _mat(Bu, "B_up").contiguous()
+        _same(WSL_BF16, T_cat, Bg, Bu)
+        r = Bg.shape[1]
+        if T_cat.shape != (M, 2 * r) or Bg.shape != (N, r) or Bu.shape != (N, r):
+            raise ValueError("T_cat must be [M, 2r], B_gate and B_up [N, r]")
+        tp, bgp, bup, ldt = T_cat.data_ptr(), Bg.data_ptr(), Bu.data_ptr(), _ld(T_cat)
+    g = torch.empty((M, N), device=x.device, dtype=x.dtype)
+    u = torch.empty_like(g)
+    h = torch.empty_like(g)
+    _e = _tic()
+    st = _lib.lib().wsl_lora_swiglu_fwd(x.data_ptr(), _ld(x), Wg.data_ptr(), Wu.data_ptr(), tp, ldt, bgp, bup,
+                                        g.data_ptr(), u.data_ptr(), h.data_ptr(), N, M, N, K, r, _stream())
+    _toc(_e, "fwd", 4.0 * M * N * (K + r), 2.0 * (M * K + 2 * N * K + 2 * M * r + 2 * N * r + 3 * M * N))
+    _lib.check(st, "wsl_lora_swiglu_fwd")
+    return g, u, h
+
+
 def lora_bwd_prepass(dY: torch.Tensor, B: torch.Tensor, s: float,
                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """U = s * dY @ B (wsl_lora_bwd_prepass). `out` may be a column slice [M, r] of a wider
