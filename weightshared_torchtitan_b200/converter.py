@@ -19,6 +19,7 @@ What convert() does to a model shaped like torchtitan/experiments/qwen3/model/mo
 """
 from __future__ import annotations
 
+import sys
 from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional, Type
 
@@ -33,7 +34,11 @@ FFN_PROJ = ("w1", "w2", "w3")
 @dataclass
 class SharedLoRAConfig:
     """The knobs the converter reads from ``job_config.shared_lora`` (any object with these
-    attributes; missing ones fall back to the defaults)."""
+    attributes; missing ones fall back to the defaults). The reference's JobConfig has no such
+    section; ``job_config_ext.JobConfig`` adds it through the reference's own extension
+    mechanism, ``--experimental.custom_args_module weightshared_torchtitan_b200.job_config_ext``
+    (torchtitan/config/manager.py:86-155), after which ``--shared_lora.rank 64`` etc. and a
+    ``[shared_lora]`` TOML table are parsed like any built-in section."""
     n_unique: int = 4
     rank: int = 16
     embed_rank: int = 0          # 0 keeps the full embedding
@@ -108,3 +113,23 @@ def build_model_converters(job_config, parallel_dims=None) -> ModelConvertersCon
 
 
 register_model_converter(SharedLoRAConverter, "shared_lora")
+
+
+def register_with_torchtitan() -> bool:
+    """Also enter the converter under the name ``shared_lora`` in the trainer's own registry,
+    torchtitan.protocols.model_converter (register_model_converter, l.41-50), so that
+    ``--model.converters shared_lora`` selects it. Returns False when torchtitan cannot be
+    imported. Runs by itself when this module is imported inside a process that already
+    loaded torchtitan (``--experimental.custom_import weightshared_torchtitan_b200.converter``,
+    torchtitan/train.py:78-79); importing torchtitan just for this would cost seconds."""
+    try:
+        from torchtitan.protocols import model_converter as mc
+    except Exception:   # noqa: BLE001 - absent, or a checkout that does not import here
+        return False
+    if "shared_lora" not in mc._registry_model_converter_cls:
+        mc.register_model_converter(SharedLoRAConverter, "shared_lora")
+    return True
+
+
+if "torchtitan" in sys.modules:
+    register_with_torchtitan()
