@@ -85,6 +85,7 @@ int wsl_reset_status(void);
  *                   runs beside them on another stream (the gradient all-reduce overlapped
  *                   with the backward pass; the reference overlaps by DDP buckets,
  *                   torchtitan/models/llama3/infra/parallelize.py:428-444)
+ *   MERGE_SIMT      1 runs wsl_lora_merge_weight on the CUDA cores instead of the tensor cores
  *   PROFILE_BITS    only honoured by builds compiled with -DWSL_PROFILE_SWITCHES
  * No counterpart in the reference (its knobs are Python config fields).
  */
@@ -94,6 +95,7 @@ int wsl_reset_status(void);
 #define WSL_OPT_ROW_STAGED 4
 #define WSL_OPT_RESERVED_SMS 5
 #define WSL_OPT_PROFILE_BITS 6
+#define WSL_OPT_MERGE_SIMT 7
 int wsl_set_option(int option, long long value);
 long long wsl_get_option(int option);
 

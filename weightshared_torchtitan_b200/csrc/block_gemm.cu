@@ -77,6 +77,7 @@ struct Region {
   signed char b2_map[kMaxSeg];
   int b2_shift[kMaxSeg];
   int swiglu;
+  int addend_map;     // tensor map of RegionDesc::addend, or -1
 };
 
 struct GemmParams {
@@ -96,10 +97,11 @@ struct GemmParams {
   // the other parts alone), 32 direct-store epilogue instead of the staged TMA store.
   int dbg;
   int stall_producer;                 // test aid: the producer never fills the ring (bounded waits)
+  int has_addend;                     // every region adds a bf16 matrix in its epilogue (RegionDesc::addend)
   unsigned long long wait_limit_ns;   // bound of every mbarrier wait
   // Row gather (factorized embedding): when set, the rows of region 0 / segment 0's A operand
   // (gather_a, K-major) or the k-rows of its B operand (gather_b, MN-major) are the rows
-  // tokens[i] of the mapped matrix, fetched by TMA tile::gather4 (1-CTA variant only).
+  // tokens[i] of the mapped matrix, fetched by TMA tile::gather4.
   const long long* gather_tokens;
   long long gather_count;
   int gather_a;
@@ -277,7 +279,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
   const int S = PAIR ? C::kStages : p.stages;
   const uint32_t stage_bytes = PAIR ? static_cast<uint32_t>(C::kStageBytes) : static_cast<uint32_t>(p.stage_bytes);
   extern __shared__ __align__(1024) uint8_t smem_dyn[];
-  __shared__ __align__(8) uint64_t bars[2 * SMAX + 4];
+  __shared__ __align__(8) uint64_t bars[2 * SMAX + 6];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
 
@@ -293,6 +295,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
   auto empty_bar = [&](int s) { return bar0 + 8u * (SMAX + s); };
   auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * SMAX + b); };
   auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * SMAX + 2 + b); };
+  auto aux_bar = [&](uint32_t b) { return bar0 + 8u * (2 * SMAX + 4 + b); };   // addend tiles landed
   volatile int* abortp = &abort_flag;
 
   if (threadIdx.x == 0) {
@@ -304,6 +307,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
       mbar_init(tempty_bar(b), PAIR ? 8 : 4);   // one arrival per epilogue warp (of both CTAs)
+      mbar_init(aux_bar(b), 1);
     }
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -353,7 +357,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       // read once per tile, not once per k-block (a dependent global load in front of every
       // stage would set the pace of the whole ring).
       int ga4[4] = {-1, -1, -1, -1};
-      if (!PAIR && !A_MN && p.gather_tokens != nullptr && p.gather_a && ti.r == 0) {
+      if (!A_MN && p.gather_tokens != nullptr && p.gather_a && ti.r == 0) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const long long row = static_cast<long long>(m0) + 4 * lane + e;
@@ -376,7 +380,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
           // 4 (l mod 16) .. +3 of every slab, so it needs four ids per k-block. They are read
           // BEFORE the wait for a free stage, which hides their latency behind the ring.
           int gb4[4] = {-1, -1, -1, -1};
-          if (!PAIR && B_MN && gather && p.gather_b) {
+          if (B_MN && gather && p.gather_b) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const long long row = static_cast<long long>(kk) + 4 * (lane & 15) + e;
@@ -400,12 +404,13 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
               if (A_MN) {
                 tma_load_2d_pair(sa, ma, fb, m0, kk);
                 tma_load_2d_pair(sa + SLAB_BYTES, ma, fb, m0 + 64, kk);
-              } else {
+              } else if (!(gather && p.gather_a)) {
                 tma_load_2d_pair(sa, ma, fb, kk, m0);
               }
               if (B_MN) {
-                for (int j = 0; j < b_slabs; ++j)
-                  tma_load_2d_pair(sb + j * SLAB_BYTES, mb, fb, n0 + 64 * j, kk);
+                if (!(gather && p.gather_b))
+                  for (int j = 0; j < b_slabs; ++j)
+                    tma_load_2d_pair(sb + j * SLAB_BYTES, mb, fb, n0 + 64 * j, kk);
               } else {
                 // (a coordinate left of the matrix, or beyond its last column, reads as zeros)
                 tma_load_2d_pair(sb, mb, fb, kk - b_kshift, n0);
@@ -428,20 +433,24 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
               }
             }
           }
-          if (!PAIR && gather && !(dbg & 2) && !p.stall_producer) {
-            // Gathered operand: every lane fetches 4 rows (512 B) per tile::gather4; a row
-            // id outside the matrix reads as zeros.
-            const uint32_t fb = full_bar(s);
+          if (gather && !(dbg & 2) && !p.stall_producer) {
+            // Gathered operand: every lane fetches 4 rows (512 B) per tile::gather4 into its own
+            // CTA's stage (in a pair the bytes count on the leader's barrier, like the tiled
+            // loads); a row id outside the matrix reads as zeros.
+            const uint32_t fb = PAIR ? map_to_cta(full_bar(s), 0) : full_bar(s);
             const uint32_t sa = smem_base + s * stage_bytes;
             const uint32_t sb = sa + A_STAGE_BYTES;
-            if (!A_MN && p.gather_a)
-              tma_gather4_2d(sa + lane * 512, ma, fb, kk, ga4[0], ga4[1], ga4[2], ga4[3]);
+            if (!A_MN && p.gather_a) {
+              if (PAIR) tma_gather4_2d_pair(sa + lane * 512, ma, fb, kk, ga4[0], ga4[1], ga4[2], ga4[3]);
+              else tma_gather4_2d(sa + lane * 512, ma, fb, kk, ga4[0], ga4[1], ga4[2], ga4[3]);
+            }
             if (B_MN && p.gather_b) {
               for (int q4 = lane; q4 < 16 * b_slabs; q4 += 32) {
                 const int j = q4 >> 4;            // slab
                 const int g4 = q4 & 15;           // group of 4 k-rows inside the slab (= lane & 15)
-                tma_gather4_2d(sb + j * SLAB_BYTES + g4 * 512, mb, fb, n0 + 64 * j, gb4[0], gb4[1], gb4[2],
-                               gb4[3]);
+                const uint32_t dst = sb + j * SLAB_BYTES + g4 * 512;
+                if (PAIR) tma_gather4_2d_pair(dst, mb, fb, n0 + 64 * j, gb4[0], gb4[1], gb4[2], gb4[3]);
+                else tma_gather4_2d(dst, mb, fb, n0 + 64 * j, gb4[0], gb4[1], gb4[2], gb4[3]);
               }
             }
           }
@@ -540,6 +549,26 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
     const uint32_t epi_base = smem_base + S * stage_bytes;
     uint32_t chunk_ctr = 0;
     int it = 0;
+    // Addend tiles (out = alpha acc + addend) are fetched into the staging buffers by TMA one
+    // 64-column chunk AHEAD of the chunk being computed; this walks the same chunk sequence.
+    int pf_u = worker, pf_c = 0;
+    uint32_t pf_ctr = 0;
+    auto prefetch_addend = [&]() {
+      if (pf_u >= units) return;
+      const TileInfo pt = decode_tile_t<PAIR>(p, pf_u);
+      const Region& PR = p.reg[pt.r];
+      const uint32_t slot = pf_ctr & 1u;
+      mbar_arrive_expect_tx(aux_bar(slot), EPI_STAGE_BYTES);
+      tma_load_2d(epi_base + slot * EPI_STAGE_BYTES, &p.maps[PR.addend_map], aux_bar(slot), pt.n0 + pf_c,
+                  pt.m0 + BM * rank);
+      ++pf_ctr;
+      pf_c += 64;
+      if (pf_c >= PR.bn) {
+        pf_c = 0;
+        pf_u += nworkers;
+      }
+    };
+    if (p.has_addend && issuer && !p.stall_producer) prefetch_addend();
     for (int u = worker; u < units; u += nworkers, ++it) {
       const int t = u;
       const TileInfo ti = decode_tile_t<PAIR>(p, u);
@@ -573,7 +602,54 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       const int row = row0 + trow;
       const uint32_t taddr =
           tmem_base + static_cast<uint32_t>(buf * BN_MAX) + (static_cast<uint32_t>(q * 32) << 16);
-      if (PAIR && R.swiglu != 0) {
+      if (p.has_addend) {
+        // ---- out = alpha * acc + addend (bf16): the addend chunk is already on its way into
+        // the staging buffer; every thread adds its row in place, then the buffer is stored.
+        const float alpha = R.alpha;
+        const uint32_t swz = static_cast<uint32_t>(trow & 7);
+        bool okc = true;
+        for (int c = 0; c < R.bn; c += 64, ++chunk_ctr) {
+          const uint32_t slot = chunk_ctr & 1u;
+          const uint32_t sbuf = epi_base + slot * EPI_STAGE_BYTES;
+          const uint32_t srow = sbuf + static_cast<uint32_t>(trow) * 128u;
+          if (issuer && !p.stall_producer) {
+            tma_wait_group_read<0>();   // the previous chunk's store has read the other buffer
+            prefetch_addend();          // ... which now takes the chunk after this one
+          }
+          okc = epi_vote_and(mbar_wait(aux_bar(slot), (chunk_ctr >> 1) & 1u, abortp, p.wait_limit_ns));
+          if (!okc) break;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + c + 32 * h, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t addr = srow + ((static_cast<uint32_t>(4 * h + j) ^ swz) << 4);
+              uint32_t w[4];
+              ld_shared_v4(addr, w);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float lo = fmaf(alpha, __uint_as_float(v[8 * j + 2 * e]), __uint_as_float(w[e] << 16));
+                const float hi =
+                    fmaf(alpha, __uint_as_float(v[8 * j + 2 * e + 1]), __uint_as_float(w[e] & 0xffff0000u));
+                w[e] = pack_bf16(lo, hi);
+              }
+              st_shared_v4(addr, w[0], w[1], w[2], w[3]);
+            }
+          }
+          fence_proxy_async_smem();
+          epi_bar_sync();
+          if (issuer && R.rows > 0) {
+            tma_store_2d(&p.maps[R.out_map], sbuf, ti.n0 + c, row0);
+            tma_commit_group();
+          }
+        }
+        if (!okc) {
+          if (issuer) record_timeout(3, t);
+          break;
+        }
+      } else if (PAIR && R.swiglu != 0) {
         // ---- gate|up tile: accumulator columns [0,128) are g, [128,256) are u for the same
         // 128 output columns. Three staged 64-column stores per half: g, u (what the backward
         // needs) and silu(g) * u computed from the bf16-rounded g and u, exactly what a
@@ -838,6 +914,7 @@ Options& options() {
       if (ms > 0 && ms <= 10000) v.wait_limit_ns = static_cast<unsigned long long>(ms) * 1000000ull;
     }
     v.reserved_sms = 0;
+    v.merge_simt = 0;
     v.profile_bits = 0;
     if ((e = getenv("WSL_DBG")) != nullptr) v.profile_bits = atoi(e);
     return v;
@@ -1126,7 +1203,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
         g.gather_count <= 0)
       return WSL_ERR_BAD_ARG;
   }
-  const bool pair = g.gather_tokens == nullptr && use_pair_tiles(g.region[0].mo, g.region[0].no);
+  const bool pair = use_pair_tiles(g.region[0].mo, g.region[0].no);
   const int bm_tile = pair ? 2 * BM : BM;
   const int bn_round = pair ? 32 : 16;
   int nmaps = 0;
@@ -1146,6 +1223,13 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       return WSL_ERR_ALIGN;
     }
     const bool swiglu = rd.mode == kEpiSwiGLU;
+    if ((rd.addend != nullptr) != (g.region[0].addend != nullptr)) return WSL_ERR_BAD_ARG;
+    if (rd.addend != nullptr) {
+      if (rd.mode != kEpiStoreBf16 || rd.transposed || rd.copy != nullptr || g.workspace != nullptr)
+        return WSL_ERR_BAD_ARG;
+      if ((reinterpret_cast<uintptr_t>(rd.addend) & 15u) != 0 || (rd.ld_addend % 8) != 0 || rd.ld_addend < rd.no)
+        return WSL_ERR_ALIGN;
+    }
     if (swiglu) {
       if (!pair || g.a_mn || g.b_mn || rd.transposed || rd.copy != nullptr || (rd.no % 128) != 0 ||
           rd.out2 == nullptr || rd.out3 == nullptr || g.workspace != nullptr)
@@ -1156,6 +1240,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     long long n_tiles = (rd.no + BN_MAX - 1) / BN_MAX;
     long long bn = (rd.no + n_tiles - 1) / n_tiles;
     bn = (bn + bn_round - 1) / bn_round * bn_round;
+    if (rd.addend != nullptr) bn = (bn + 63) / 64 * 64;   // whole 64-column staging chunks
     if (swiglu) {   // one tile = 128 output columns of g next to the same 128 of u
       n_tiles = rd.no / 128;
       bn = BN_MAX;
@@ -1176,6 +1261,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     R.transposed = rd.transposed ? 1 : 0;
     R.out_map = -1;
     R.swiglu = swiglu ? 1 : 0;
+    R.addend_map = -1;
     for (int s = 0; s < kMaxSeg; ++s) {
       R.b2_map[s] = 0;
       R.b2_shift[s] = 0;
@@ -1305,6 +1391,14 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       if (st != WSL_OK) return st;
       p.reg[r].out_map = nmaps++;
     }
+  }
+  p.has_addend = g.region[0].addend != nullptr ? 1 : 0;
+  for (int r = 0; r < g.nregion && p.has_addend; ++r) {
+    const RegionDesc& rd = g.region[r];
+    if (p.reg[r].out_map < 0 || nmaps + 1 > kMaxMaps) return WSL_ERR_BAD_ARG;
+    st = make_map_out(&p.maps[nmaps], const_cast<void*>(rd.addend), rd.mo, rd.no, rd.ld_addend, false);
+    if (st != WSL_OK) return st;
+    p.reg[r].addend_map = nmaps++;
   }
   for (int r = 0; r < g.nregion; ++r) {
     const RegionDesc& rd = g.region[r];

@@ -65,6 +65,12 @@ struct RegionDesc {
   int b2_k_shift[kMaxSeg];
   void* out2;
   void* out3;
+  // kEpiStoreBf16 only: out = alpha * acc + addend, with addend a bf16 matrix of the output's
+  // shape (pitch ld_addend). The epilogue brings the addend tile into its staging buffers by
+  // TMA one chunk ahead, adds in place and stores, so the addend is read once, in full lines.
+  // Either every region of a launch has an addend or none (W_eff = W + s B A is the user).
+  const void* addend;
+  long long ld_addend;
 };
 
 struct GemmDesc {

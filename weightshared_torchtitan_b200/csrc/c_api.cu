@@ -141,6 +141,7 @@ int wsl_set_option(int option, long long value) {
       o.reserved_sms = static_cast<int>(value);
       return WSL_OK;
     case WSL_OPT_PROFILE_BITS: o.profile_bits = static_cast<int>(value); return WSL_OK;
+    case WSL_OPT_MERGE_SIMT: o.merge_simt = value != 0; return WSL_OK;
     default: return WSL_ERR_BAD_ARG;
   }
 }
@@ -154,6 +155,7 @@ long long wsl_get_option(int option) {
     case WSL_OPT_ROW_STAGED: return o.row_staged;
     case WSL_OPT_RESERVED_SMS: return o.reserved_sms;
     case WSL_OPT_PROFILE_BITS: return o.profile_bits;
+    case WSL_OPT_MERGE_SIMT: return o.merge_simt;
     default: return WSL_ERR_BAD_ARG;
   }
 }

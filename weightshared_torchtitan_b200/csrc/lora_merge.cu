@@ -1,9 +1,13 @@
 // W_eff = W + s * B * A rounded once to bf16: a layer's effective weight, [N, K], from the
 // shared W[N, K] and the adapter factors B[N, r], A[r, K]. Used by the backward pass, where
-// dX = dY * W_eff replaces a rank-r detour through dY * B. The product has contraction length
-// r only, so the kernel is a streaming pass over W (read) and W_eff (write) with r FMAs per
-// element on the CUDA cores; A and B are a few hundred KB and stay in L1/L2. Up to
-// WSL_MAX_PROJ projections of one input width go in one launch.
+// dX = dY * W_eff replaces a rank-r detour through dY * B. Up to WSL_MAX_PROJ projections of
+// one input width go in one launch.
+//
+// Two implementations. The default runs the rank-r product on the tensor cores (one k-block
+// per tile of the block GEMM: operands B, K-major, and A, MN-major) and adds W in the
+// epilogue from tiles that TMA brings into the staging buffers, so the pass is bound by the
+// 2 * 2 * N * K bytes it has to move. The CUDA-core kernel below (r FMAs per element, issue
+// bound from r = 32 up) stays selectable with option MERGE_SIMT, for comparison.
 #include "block_gemm.cuh"
 #include "status.cuh"
 #include "../../include/wsl.h"
@@ -113,6 +117,36 @@ int launch_lora_merge(int nproj, const void* const* W, const void* const* A, con
   if ((K % 8) != 0) return WSL_ERR_ALIGN;
   if (K > 0x7fffffffLL) return WSL_ERR_TOO_LARGE;
   if (r != 8 && r != 16 && r != 32 && r != 64 && r != 128) return WSL_ERR_TOO_LARGE;
+  if (!options().merge_simt) {
+    // out_p[N_p, K] = s * B_p[N_p, r] . A_p[r, K] + W_p on the block GEMM
+    GemmDesc g = {};
+    g.a_mn = false;
+    g.b_mn = true;
+    g.nseg = 1;
+    g.seg_k[0] = static_cast<int>(r);
+    g.nregion = nproj;
+    for (int p = 0; p < nproj; ++p) {
+      if (!W[p] || !A[p] || !B[p] || !out[p] || N[p] <= 0) return WSL_ERR_BAD_ARG;
+      RegionDesc& rd = g.region[p];
+      rd.a[0].ptr = B[p];
+      rd.a[0].rows = N[p];
+      rd.a[0].cols = r;
+      rd.a[0].ld = r;
+      rd.b[0].ptr = A[p];
+      rd.b[0].rows = r;
+      rd.b[0].cols = K;
+      rd.b[0].ld = K;
+      rd.mo = N[p];
+      rd.no = K;
+      rd.out = out[p];
+      rd.ld_out = K;
+      rd.mode = kEpiStoreBf16;
+      rd.alpha = s;
+      rd.addend = W[p];
+      rd.ld_addend = K;
+    }
+    return launch_block_gemm(g, stream);
+  }
   MergeParams mp;
   mp.nproj = nproj;
   mp.K8 = static_cast<int>(K / 8);

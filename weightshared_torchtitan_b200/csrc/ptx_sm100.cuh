@@ -89,6 +89,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   return true;
 }
 
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr)
+               : "memory");
+}
+
 // --------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -251,6 +258,19 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const CUtens
       " [%0], [%1, {%3, %4}], [%2];"
       :
       : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+// Row gather of a CTA pair: four rows into THIS CTA's shared memory, bytes signalled on a
+// barrier that may live in the peer CTA.
+__device__ __forceinline__ void tma_gather4_2d_pair(uint32_t dst_smem, const CUtensorMap* m,
+                                                    uint32_t bar_cluster_addr, int c0, int r0, int r1,
+                                                    int r2, int r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      :
+      : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(r0),
+        "r"(r1), "r"(r2), "r"(r3)
       : "memory");
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {

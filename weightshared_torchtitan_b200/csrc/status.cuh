@@ -34,6 +34,7 @@ struct Options {
   unsigned long long wait_limit_ns;    // bound of every device-side wait
   int reserved_sms;                    // SMs the persistent kernels leave free (collective overlap)
   int profile_bits;                    // only honoured in builds with WSL_PROFILE_SWITCHES
+  int merge_simt;                      // 1: W + s B A on the CUDA cores instead of the block GEMM
 };
 Options& options();
 }  // namespace wsl

@@ -32,23 +32,37 @@ def _flat(x: torch.Tensor) -> torch.Tensor:
 
 # When the shared weight is trained (dW wanted together with dA and dB, bf16), the backward
 # can go through the layer's own weight gradient G = dY^T x: dB = s G A^T, dA = s B^T G and
-# dX = dY (W + s B A). That reads [N, K] matrices (merge W, copy G) instead of streaming the
-# M token rows again (pre-pass over dY, rank-r regions of the weight-gradient launch), so it
-# pays when M is large against N K / (N + K): yes for decoder layers at 32 k tokens per step
-# (M = 32768, N K <= 3 M), no for an 8B-shape MLP projection at M = 16384 (N K = 50 M).
-# "auto" decides per projection group with the measured per-element costs below; True / False
-# (environment variable WSL_DERIVED_ADAPTER_GRADS=1 / 0) force one formulation where eligible.
+# dX = dY (W + s B A). That reads [N, K] matrices (merge W, copy G, two passes over G for the
+# adapter gradients) instead of streaming the M token rows again (pre-pass over dY, rank-r
+# regions of the weight-gradient launch and of dX), so it pays when M is large against
+# N K / (N + K). "auto" decides per projection group; True / False (environment variable
+# WSL_DERIVED_ADAPTER_GRADS=1 / 0) force one formulation where eligible.
 _env = os.environ.get("WSL_DERIVED_ADAPTER_GRADS", "auto")
 DERIVED_ADAPTER_GRADS = {"0": False, "1": True}.get(_env, "auto")
-# picoseconds per element, from CUDA-event timings on B200: merging W and copying G cost about
-# 7.5 ps per weight element (+ ~15 us of launches per group); the pre-pass U costs about 0.4 ps
-# per dY element and the rank-r regions about 0.37 ps per (dY + x) element.
-_PS_PER_WEIGHT, _PS_FIXED, _PS_PER_DY, _PS_PER_ROWSTREAM = 7.5, 15e6, 0.4, 0.37
+
+# Which formulation is faster, measured on a B200 with `python bench.py --routes` (fwd+bwd of
+# the group through the autograd Function) for every projection group of the four baseline
+# configurations at their own token counts: (M, K, (N_0, ...), r) -> through the layer gradient?
+ROUTE_TABLE = {
+}
+
+# Shapes outside the table: both formulations cost HBM passes, so compare bytes. The direct
+# form streams dY once more for U = s dY B (2 M N bytes) and runs the rank-r regions, which
+# re-stream dY and x through narrow tiles at about a third of the rate of a full pass
+# (3 * 2 M (N + K) byte-equivalents); the form through G moves 4 N K (merged weight, read and
+# write) + 2 N K (bf16 copy of G) + 4 N K (two passes over G for dA, dB) bytes and pays two
+# extra launches (~20 us = 100 MB at 5 TB/s).
+_FIXED_BYTES = 100e6
 
 
-def _derived_pays(M: int, K: int, Ns) -> bool:
-    derived = _PS_FIXED + sum(_PS_PER_WEIGHT * n * K for n in Ns)
-    direct = sum(_PS_PER_DY * M * n + _PS_PER_ROWSTREAM * M * (n + K) for n in Ns)
+def derived_route_pays(M: int, K: int, Ns, r: int) -> bool:
+    """True when the backward of this projection group should go through the layer's own weight
+    gradient (see ROUTE_TABLE)."""
+    hit = ROUTE_TABLE.get((int(M), int(K), tuple(int(n) for n in Ns), int(r)))
+    if hit is not None:
+        return hit
+    derived = _FIXED_BYTES + sum(10.0 * n * K for n in Ns)
+    direct = sum(2.0 * M * n + 6.0 * M * (n + K) * min(r, 64) / 64.0 for n in Ns)
     return derived < direct
 
 
@@ -257,7 +271,7 @@ def _derived_route(x2, sinks, Ws, As) -> bool:
             and all(t[0] is not None and t[1] is not None and t[2] is not None for t in sinks)
             and all(A.shape[0] in ops.MERGE_RANKS for A in As)
             and (DERIVED_ADAPTER_GRADS is True
-                 or _derived_pays(x2.shape[0], x2.shape[1], [W.shape[0] for W in Ws])))
+                 or derived_route_pays(x2.shape[0], x2.shape[1], [W.shape[0] for W in Ws], As[0].shape[0])))
 
 
 class LoRAGateUpSwiGLUFunction(torch.autograd.Function):
