@@ -489,6 +489,13 @@ def run_rows(args):
         if what in ("all", "embed"):
             tg = time_us_flushed(torch, lambda: ops.embed_gather(tok, E), iters, warmup)
             line.update({"gather_alone_us": tg, "gather_alone_gbs": (8.0 * Me + 4.0 * Me * r_e) / tg / 1e3})
+            # the two-kernel form (row-gather kernel, then the plain GEMMs) the module takes for wide outputs
+            G = ops.embed_gather(tok, E)
+            t2f = time_us_flushed(torch, lambda: ops.linear_fwd(ops.embed_gather(tok, E), P), iters, warmup)
+            t2b = time_us_flushed(torch, lambda: ops.lora_linear_bwd_dw(dH, None, G, None, dP, None, None), iters, warmup)
+            line.update({"two_kernel_fwd_us": t2f, "two_kernel_fwd_tflops": 2.0 * Me * r_e * d / t2f / 1e6,
+                         "two_kernel_dproj_us": t2b, "two_kernel_dproj_tflops": 2.0 * Me * r_e * d / t2b / 1e6,
+                         "module_takes": "gather inside the GEMM" if ops.embed_gather_in_gemm_pays(d) else "two kernels"})
         print(json.dumps(line), flush=True)
     if what in ("all", "adamw"):
         n = 64 * 1024 * 1024 if what == "adamw" and iters == 1 else 268 * 1000 * 1000
@@ -529,18 +536,34 @@ def run_routes(args):
             sinks = [(torch.zeros(n, K, device="cuda"), torch.zeros(r, K, device="cuda"), torch.zeros(n, r, device="cuda"))
                      for n in Ns]
             line = {"config": name, "group": gname, "M": M, "K": K, "Ns": Ns, "r": r}
+
+            def run():
+                ys = Fn.lora_linear_group(x, Ws, As, Bs, 2.0, sinks)
+                torch.autograd.backward(ys, dYs)
+                x.grad = None
+
+            # the two formulations alternate rep by rep, so that both see the same clocks (the
+            # SM clock under the power cap drifts by tens of percent within seconds)
+            samples = {False: [], True: []}
             try:
-                for route, flag in (("direct_ms", False), ("through_layer_gradient_ms", True)):
+                for flag in (False, True):
                     Fn.DERIVED_ADAPTER_GRADS = flag
-
-                    def run():
-                        ys = Fn.lora_linear_group(x, Ws, As, Bs, 2.0, sinks)
-                        torch.autograd.backward(ys, dYs)
-                        x.grad = None
-
-                    line[route] = time_ms(torch, run, args.iters, 2)
+                    run()
+                torch.cuda.synchronize()
+                for _ in range(args.iters):
+                    for flag in (False, True):
+                        Fn.DERIVED_ADAPTER_GRADS = flag
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record()
+                        run()
+                        run()
+                        e1.record()
+                        torch.cuda.synchronize()
+                        samples[flag].append(e0.elapsed_time(e1) / 2)
             finally:
                 Fn.DERIVED_ADAPTER_GRADS = saved
+            line["direct_ms"] = statistics.median(samples[False])
+            line["through_layer_gradient_ms"] = statistics.median(samples[True])
             line["auto_picks_through_layer_gradient"] = bool(Fn.derived_route_pays(M, K, Ns, r))
             print(json.dumps(line), flush=True)
             del x, Ws, As, Bs, dYs, sinks
@@ -625,7 +648,7 @@ def parity_against_oracle(torch, ref):
     all the layers of the stack any bf16 implementation drifts from an fp32 one by rounding its
     activations after every operation, so beside this library's distance from the fp32 oracle
     the block gives the distance of the reference's own path on this GPU (the oracle under
-    torch.autocast(bfloat16)), and `ok` asks for no more than 1.5 times that."""
+    torch.autocast(bfloat16)), and `ok` asks for no more than twice that."""
     from weightshared_torchtitan_b200.decoder import CONFIGS, WeightSharedDecoder
     import dataclasses
     O, a, p = ref["oracle"], ref["args"], ref["params"]
@@ -666,12 +689,12 @@ def parity_against_oracle(torch, ref):
     del pe
     torch.cuda.empty_cache()
     loss_ok = abs(lg - lo) / abs(lo) <= 1e-2
-    grads_ok = all(errs[k] <= 1e-2 or errs[k] <= 1.5 * floor[k] for k in names)
+    grads_ok = all(errs[k] <= 1e-2 or (errs[k] <= 2.0 * floor[k] and floor[k] < 0.1) for k in names)
     return {"sample_tokens": ref["sample_tokens"], "loss_gpu": lg, "loss_oracle": lo,
             "loss_rel_err": abs(lg - lo) / abs(lo), "loss_bar": 1e-2,
             "grad_max_rel_err_vs_fp32_oracle": errs,
             "reference_eager_bf16_autocast_on_this_gpu_vs_fp32_oracle": floor,
-            "grad_bar": "1e-2, or 1.5 x the reference eager bf16 path's own distance (depth of the stack)",
+            "grad_bar": "1e-2, or 2 x the reference eager bf16 path's own distance (depth of the stack)",
             "ok": bool(loss_ok and grads_ok)}
 
 

@@ -161,7 +161,7 @@ def test_tiny_decoder_bf16_against_the_oracle_on_the_same_values(golden_dir, thr
     (U = s dY B) and through the layer's own weight gradient (merged weight, adapter gradients
     batched per layer). The loss is held to 1e-2 against the reference fixture; the gradients to
     the fp32 oracle evaluated on the bf16-ROUNDED parameters the GPU computes with: within 1e-2,
-    or no further from it than 1.5 times what the reference's own bf16 path (the oracle under
+    or no further from it than twice what the reference's own bf16 path (the oracle under
     torch.autocast on this GPU) is -- activations rounded after every operation of a 4-layer
     stack put any two bf16 implementations about 1e-2 apart."""
     from weightshared_torchtitan_b200 import functional as Fn
@@ -186,7 +186,7 @@ def test_tiny_decoder_bf16_against_the_oracle_on_the_same_values(golden_dir, thr
     for key in ("blocks.0.wq.weight", "blocks.1.w2.weight", "layers.0.wq.w_a", "layers.3.w2.w_b", "embed.P"):
         err = rel(_grad_of(m, key), po[key].grad)
         floor = rel(pe[key].grad, po[key].grad)
-        assert err < 1e-2 or err <= 1.5 * floor, (key, err, floor)
+        assert err < 1e-2 or (err <= 2.0 * floor and floor < 0.1), (key, err, floor)
 
 
 @pytest.mark.parametrize("flat", [True, False])

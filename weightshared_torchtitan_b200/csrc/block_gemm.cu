@@ -992,8 +992,15 @@ static int cached_map(CUtensorMap* out, const MapKey& key, Encode encode) {
   if (g_map_cache == nullptr) g_map_cache = new MapSlot[kMapSlots]();
   MapSlot& s = g_map_cache[map_hash(key, dev)];
   if (!(s.used && s.dev == dev && s.key == key)) {
-    if (encode(&s.map) != CUDA_SUCCESS) {
+    const CUresult res = encode(&s.map);
+    if (res != CUDA_SUCCESS) {
       s.used = false;
+      // the one failure of this library that depends on a driver rule the caller cannot see:
+      // say which tensor was refused
+      fprintf(stderr,
+              "wsl: cuTensorMapEncodeTiled refused a tensor (CUresult %d): ptr %p, %lld x %lld, pitch %lld "
+              "elements, box %d x %d, kind %d\n",
+              static_cast<int>(res), key.ptr, key.rows, key.cols, key.ld, key.box_cols, key.box_rows, key.kind);
       return WSL_ERR_DRIVER;
     }
     s.key = key;

@@ -236,9 +236,12 @@ class FactorizedEmbeddingFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, tokens, E, P, sinks, anchor):
-        fused = E.dtype == torch.bfloat16
+        # TMA gather inside the tcgen05 GEMM (the gathered rows never touch memory) where that
+        # pays: every one of the d / 256 column tiles of the output gathers the rows again, and
+        # a gather4 instruction moves 4 x 128 bytes where a tiled load moves 16 KiB, so for wide
+        # outputs one pass of the row-gather kernel followed by the plain GEMM is faster
+        fused = E.dtype == torch.bfloat16 and ops.embed_gather_in_gemm_pays(P.shape[0])
         if fused:
-            # TMA gather inside the tcgen05 GEMM: the gathered rows never touch memory
             h = ops.embed_fwd(tokens, E, P)
             ctx.save_for_backward(tokens, E, P)
         else:
