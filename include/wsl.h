@@ -185,6 +185,26 @@ int wsl_lora_linear_bwd_dx(int nproj, const void* const* dY, const long long* ld
                            long long lddx, long long M, long long K, int dtype, void* stream);
 
 /*
+ * Input gradient of the DOWN projection of a SwiGLU MLP with the activation's backward in its
+ * epilogue (bf16): dh[M,K] = dY[M,N] W[N,K] + U[M,r] A[r,K] stays on the SM; with the stored
+ * g and u of wsl_lora_swiglu_fwd (pitch ld_gu) the launch writes
+ *   dgate[M,K] = dh u silu'(g),   dup[M,K] = dh silu(g)      (dh rounded to bf16 first)
+ * i.e. what wsl_lora_linear_bwd_dx followed by wsl_swiglu_bwd gives, bit for bit, without dh
+ * being written and read back. K is the MLP's inner width here. r = 0 (U, A NULL) takes a W
+ * that already contains the adapter (wsl_lora_merge_weight). The g and u tiles reach the
+ * epilogue by TMA one 32-column chunk ahead of the arithmetic.
+ * wsl_swiglu_bwd_in_dx_supported() tells whether a shape can take this path (K % 64 == 0 and
+ * large enough for CTA-pair tiles).
+ * Replaces the autograd backward of w2(F.silu(w1(x)) * w3(x)) between w2's MmBackward and the
+ * SiluBackward / MulBackward pair: torchtitan/experiments/qwen3/model/model.py:251.
+ */
+int wsl_swiglu_bwd_in_dx_supported(long long M, long long N, long long K, long long r);
+int wsl_lora_linear_bwd_dx_swiglu(const void* dY, long long lddy, const void* U, long long ldu,
+                                  const void* W, const void* A, const void* g, const void* u,
+                                  void* dgate, void* dup, long long ld_gu, long long M, long long N,
+                                  long long K, long long r, void* stream);
+
+/*
  * dW[N,K] += dY^T x ;  dA[r,K] += U^T x ;  dB[N,r] += dY^T T      (all fp32, in place)
  * U and T carry the scale s already. dW is the gradient buffer of the SHARED
  * base weight: every layer that reuses W adds into the same fp32 buffer. Any of

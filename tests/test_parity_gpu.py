@@ -856,3 +856,104 @@ def test_gate_up_swiglu_function_gradients_match_the_unfused_composition(wsl):
                     assert torch.equal(ta, tb)
     finally:
         Fn.DERIVED_ADAPTER_GRADS = saved
+
+
+def test_first_library_call_of_a_fresh_thread(wsl):
+    """A thread whose very first CUDA-related action is one of this library's GEMM launches (an
+    autograd worker starting a backward pass with cached allocations) has no driver context bound
+    yet; encoding a tensor map there must bind it instead of failing."""
+    import threading
+    x, W, A, B, dY = [t.cuda().to(torch.bfloat16) for t in O.projection_inputs(5, 640, 256, 192, 16)]
+    want = wsl.linear_fwd(x, W)
+    x2 = x.clone()          # new address: its tensor map is not in the library's cache yet
+    torch.cuda.synchronize()
+    out = {}
+
+    def work():
+        try:
+            out["y"] = wsl.linear_fwd(x2, W)
+            torch.cuda.synchronize()
+        except Exception as e:      # noqa: BLE001
+            out["err"] = e
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    assert "err" not in out, out.get("err")
+    assert torch.equal(out["y"], want)
+
+
+def test_mlp_function_matches_the_unfused_composition(wsl):
+    """The whole-MLP autograd node (activation in the gate|up epilogue, its backward in the
+    epilogue of the down projection's input-gradient GEMM) against lora_gate_up_swiglu +
+    lora_linear_group + the stand-alone SwiGLU backward kernel: same output bits, same dX bits and
+    the same in-place gradients, for both backward formulations; and y against the oracle."""
+    from weightshared_torchtitan_b200 import functional as Fn
+    M, N, K, r = 1536, 768, 512, 16           # N = inner width of the MLP, K = model width
+    gen = torch.Generator().manual_seed(321)
+    bf = torch.bfloat16
+    x0 = torch.randn(M, K, generator=gen).cuda().to(bf)
+    Ws = [(torch.randn(N, K, generator=gen) * 0.05).cuda().to(bf) for _ in range(2)]
+    Ws.append((torch.randn(K, N, generator=gen) * 0.05).cuda().to(bf))
+    As = [((torch.rand(r, K, generator=gen) * 2 - 1) / K ** 0.5).cuda().to(bf) for _ in range(2)]
+    As.append(((torch.rand(r, N, generator=gen) * 2 - 1) / N ** 0.5).cuda().to(bf))
+    Bs = [(torch.randn(N, r, generator=gen) * 0.05).cuda().to(bf) for _ in range(2)]
+    Bs.append((torch.randn(K, r, generator=gen) * 0.05).cuda().to(bf))
+    dy = torch.randn(M, K, generator=gen).cuda().to(bf)
+    assert wsl.swiglu_bwd_in_dx_supported(M, K, N, r) and wsl.lora_swiglu_supported(M, N, K, r)
+
+    def sinks():
+        return [(torch.zeros(W.shape, device="cuda"), torch.zeros(A.shape, device="cuda"),
+                 torch.zeros(B.shape, device="cuda")) for W, A, B in zip(Ws, As, Bs)]
+
+    saved = Fn.DERIVED_ADAPTER_GRADS
+    try:
+        for flag in (False, True):
+            Fn.DERIVED_ADAPTER_GRADS = flag
+            res = []
+            for fused in (True, False):
+                x = x0.clone().requires_grad_(True)
+                sk = sinks()
+                if fused:
+                    y = Fn.lora_mlp(x, Ws, As, Bs, 2.0, sk)
+                else:
+                    act = Fn.lora_gate_up_swiglu(x, Ws[:2], As[:2], Bs[:2], 2.0, sk[:2])
+                    y = Fn.lora_linear_group(act, [Ws[2]], [As[2]], [Bs[2]], 2.0, sk[2:])[0]
+                y.backward(dy)
+                res.append((y.detach(), x.grad, sk))
+            (y1, dx1, s1), (y0, dx0, s0) = res
+            assert torch.equal(y1, y0) and torch.equal(dx1, dx0)
+            for a, b in zip(s1, s0):
+                for ta, tb in zip(a, b):
+                    assert torch.equal(ta, tb)
+    finally:
+        Fn.DERIVED_ADAPTER_GRADS = saved
+    xc = x0.float().cpu()
+    gate = O.lora_linear(xc, Ws[0].float().cpu(), As[0].float().cpu(), Bs[0].float().cpu())
+    up = O.lora_linear(xc, Ws[1].float().cpu(), As[1].float().cpu(), Bs[1].float().cpu())
+    want = O.lora_linear(torch.nn.functional.silu(gate) * up, Ws[2].float().cpu(), As[2].float().cpu(),
+                         Bs[2].float().cpu())
+    assert rel(y1, want) < 2 * TOL_BF16       # two roundings of the hidden activation on the way
+
+
+@pytest.mark.parametrize("M,N,K,r", [(1024, 256, 512, 16), (777, 328, 1280, 64), (2048, 1024, 3072, 0)])
+def test_dx_with_swiglu_backward_epilogue_matches_two_kernels(wsl, M, N, K, r):
+    """wsl_lora_linear_bwd_dx_swiglu against wsl_lora_linear_bwd_dx + wsl_swiglu_bwd, bit for bit;
+    ragged M, contraction not a multiple of the k-block, with and without the rank-r segment."""
+    assert wsl.swiglu_bwd_in_dx_supported(M, N, K, r)
+    gen = torch.Generator().manual_seed(55 + r)
+    bf = torch.bfloat16
+    dY = torch.randn(M, N, generator=gen).cuda().to(bf)
+    W = (torch.randn(N, K, generator=gen) * 0.05).cuda().to(bf)
+    g = torch.randn(M, K, generator=gen).cuda().to(bf)
+    u = torch.randn(M, K, generator=gen).cuda().to(bf)
+    if r:
+        U = torch.randn(M, r, generator=gen).cuda().to(bf)
+        A = (torch.randn(r, K, generator=gen) * 0.05).cuda().to(bf)
+        dg1, du1 = wsl.lora_linear_bwd_dx_swiglu(dY, U, W, A, g, u)
+        dh = wsl.lora_linear_bwd_dx([dY], [U], [W], [A])
+    else:
+        dg1, du1 = wsl.lora_linear_bwd_dx_swiglu(dY, None, W, None, g, u)
+        dh = wsl.lora_linear_bwd_dx([dY], [None], [W], [None])
+    dg0, du0 = wsl.swiglu_bwd(dh, g, u)
+    assert torch.equal(dg1, dg0) and torch.equal(du1, du0)

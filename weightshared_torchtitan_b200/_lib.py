@@ -53,6 +53,8 @@ SIGNATURES = {
     "wsl_lora_linear_fwd_group": (_i, [_i, _vp, _ll, _vpp, _vpp, _llp, _vpp, _vpp, _llp, _llp, _llp, _ll, _ll, _vp]),
     "wsl_lora_swiglu_supported": (_i, [_ll, _ll, _ll, _ll]),
     "wsl_lora_swiglu_fwd": (_i, [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _vp]),
+    "wsl_swiglu_bwd_in_dx_supported": (_i, [_ll, _ll, _ll, _ll]),
+    "wsl_lora_linear_bwd_dx_swiglu": (_i, [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _vp]),
     "wsl_lora_bwd_prepass": (_i, [_vp, _ll, _vp, _vp, _ll, _ll, _ll, _ll, _f, _i, _vp]),
     "wsl_lora_linear_bwd_dx": (_i, [_i, _vpp, _llp, _vpp, _llp, _vpp, _vpp, _llp, _llp, _vp, _ll, _ll, _ll, _i, _vp]),
     "wsl_lora_linear_bwd_dw": (_i, [_vp, _ll, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _ll, _ll, _ll,

@@ -24,6 +24,7 @@
 #include "block_gemm.cuh"
 #include "ptx_sm100.cuh"
 #include "status.cuh"
+#include "swiglu_math.cuh"
 
 #include <cuda_bf16.h>
 #include <cudaTypedefs.h>
@@ -97,7 +98,10 @@ struct GemmParams {
   // the other parts alone), 32 direct-store epilogue instead of the staged TMA store.
   int dbg;
   int stall_producer;                 // test aid: the producer never fills the ring (bounded waits)
-  int has_addend;                     // every region adds a bf16 matrix in its epilogue (RegionDesc::addend)
+  // Epilogues that read matrices of the output's shape through TMA (all regions alike):
+  // 0 none, 1 out = alpha acc + addend (64-column chunks), 2 SwiGLU backward from g = addend and
+  // u = addend2 into two outputs (32-column chunks, 64-byte swizzle).
+  int aux_mode;
   unsigned long long wait_limit_ns;   // bound of every mbarrier wait
   // Row gather (factorized embedding): when set, the rows of region 0 / segment 0's A operand
   // (gather_a, K-major) or the k-rows of its B operand (gather_b, MN-major) are the rows
@@ -558,17 +562,24 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       const TileInfo pt = decode_tile_t<PAIR>(p, pf_u);
       const Region& PR = p.reg[pt.r];
       const uint32_t slot = pf_ctr & 1u;
+      const uint32_t dst = epi_base + slot * EPI_STAGE_BYTES;
       mbar_arrive_expect_tx(aux_bar(slot), EPI_STAGE_BYTES);
-      tma_load_2d(epi_base + slot * EPI_STAGE_BYTES, &p.maps[PR.addend_map], aux_bar(slot), pt.n0 + pf_c,
-                  pt.m0 + BM * rank);
+      if (p.aux_mode == 1) {
+        tma_load_2d(dst, &p.maps[PR.addend_map], aux_bar(slot), pt.n0 + pf_c, pt.m0 + BM * rank);
+        pf_c += 64;
+      } else {   // two half-width tiles (g, u) share the slot
+        tma_load_2d(dst, &p.maps[PR.addend_map], aux_bar(slot), pt.n0 + pf_c, pt.m0 + BM * rank);
+        tma_load_2d(dst + EPI_STAGE_BYTES / 2, &p.maps[PR.addend_map + 1], aux_bar(slot), pt.n0 + pf_c,
+                    pt.m0 + BM * rank);
+        pf_c += 32;
+      }
       ++pf_ctr;
-      pf_c += 64;
       if (pf_c >= PR.bn) {
         pf_c = 0;
         pf_u += nworkers;
       }
     };
-    if (p.has_addend && issuer && !p.stall_producer) prefetch_addend();
+    if (p.aux_mode != 0 && issuer && !p.stall_producer) prefetch_addend();
     for (int u = worker; u < units; u += nworkers, ++it) {
       const int t = u;
       const TileInfo ti = decode_tile_t<PAIR>(p, u);
@@ -602,7 +613,62 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       const int row = row0 + trow;
       const uint32_t taddr =
           tmem_base + static_cast<uint32_t>(buf * BN_MAX) + (static_cast<uint32_t>(q * 32) << 16);
-      if (p.has_addend) {
+      if (p.aux_mode == 2) {
+        // ---- SwiGLU backward: dh = bf16(alpha * acc) never leaves the SM; with the g and u
+        // tiles that TMA has brought into the staging slot, every thread turns its row of 32
+        // columns into d gate and d up in place, and the two half-slots are stored.
+        const float alpha = R.alpha;
+        const uint32_t swz = static_cast<uint32_t>((trow >> 1) & 3);   // 64-byte swizzle: 16-B piece ^ row bits 1-2
+        bool okc = true;
+        for (int c = 0; c < R.bn; c += 32, ++chunk_ctr) {
+          const uint32_t slot = chunk_ctr & 1u;
+          const uint32_t sbuf = epi_base + slot * EPI_STAGE_BYTES;
+          const uint32_t grow = sbuf + static_cast<uint32_t>(trow) * 64u;
+          const uint32_t urow = grow + EPI_STAGE_BYTES / 2;
+          if (issuer && !p.stall_producer) {
+            tma_wait_group_read<0>();
+            prefetch_addend();
+          }
+          okc = epi_vote_and(mbar_wait(aux_bar(slot), (chunk_ctr >> 1) & 1u, abortp, p.wait_limit_ns));
+          if (!okc) break;
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t off = (static_cast<uint32_t>(j) ^ swz) << 4;
+            uint32_t gw[4], uw[4];
+            ld_shared_v4(grow + off, gw);
+            ld_shared_v4(urow + off, uw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float dg[2], du[2];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const float dy = __bfloat162float(__float2bfloat16_rn(alpha * __uint_as_float(v[8 * j + 2 * e + h])));
+                const float gx = __uint_as_float(h ? (gw[e] & 0xffff0000u) : (gw[e] << 16));
+                const float ux = __uint_as_float(h ? (uw[e] & 0xffff0000u) : (uw[e] << 16));
+                swiglu_bwd_elem(dy, gx, ux, dg[h], du[h]);
+              }
+              gw[e] = pack_bf16(dg[0], dg[1]);
+              uw[e] = pack_bf16(du[0], du[1]);
+            }
+            st_shared_v4(grow + off, gw[0], gw[1], gw[2], gw[3]);
+            st_shared_v4(urow + off, uw[0], uw[1], uw[2], uw[3]);
+          }
+          fence_proxy_async_smem();
+          epi_bar_sync();
+          if (issuer && R.rows > 0) {
+            tma_store_2d(&p.maps[R.out_map], sbuf, ti.n0 + c, row0);
+            tma_store_2d(&p.maps[R.out_map + 1], sbuf + EPI_STAGE_BYTES / 2, ti.n0 + c, row0);
+            tma_commit_group();
+          }
+        }
+        if (!okc) {
+          if (issuer) record_timeout(3, t);
+          break;
+        }
+      } else if (p.aux_mode == 1) {
         // ---- out = alpha * acc + addend (bf16): the addend chunk is already on its way into
         // the staging buffer; every thread adds its row in place, then the buffer is stored.
         const float alpha = R.alpha;
@@ -678,7 +744,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
                 for (int j = 0; j < 32; ++j) {
                   const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[j])));
                   const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(w[j])));
-                  v[j] = __float_as_uint(g / (1.f + __expf(-g)) * u);
+                  v[j] = __float_as_uint(swiglu_fwd_elem(g, u));
                 }
               }
 #pragma unroll
@@ -992,7 +1058,14 @@ static int cached_map(CUtensorMap* out, const MapKey& key, Encode encode) {
   if (g_map_cache == nullptr) g_map_cache = new MapSlot[kMapSlots]();
   MapSlot& s = g_map_cache[map_hash(key, dev)];
   if (!(s.used && s.dev == dev && s.key == key)) {
-    const CUresult res = encode(&s.map);
+    CUresult res = encode(&s.map);
+    if (res == CUDA_ERROR_INVALID_CONTEXT) {
+      // A thread that has made no runtime call yet (an autograd worker whose first action is
+      // one of these launches) has no context bound for the driver API: bind the device's
+      // primary context the way the runtime does, then encode again.
+      cudaFree(nullptr);
+      res = encode(&s.map);
+    }
     if (res != CUDA_SUCCESS) {
       s.used = false;
       // the one failure of this library that depends on a driver rule the caller cannot see:
@@ -1009,6 +1082,21 @@ static int cached_map(CUtensorMap* out, const MapKey& key, Encode encode) {
   }
   memcpy(out, &s.map, sizeof(CUtensorMap));
   return WSL_OK;
+}
+
+// Tensor map over a row-major bf16 matrix with a box of 32 columns (64 bytes) x 128 rows and
+// 64-byte swizzle: the half-width epilogue tiles of the SwiGLU backward.
+static int make_map_half(CUtensorMap* m, void* ptr, long long rows, long long cols, long long ld) {
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2u};
+  cuuint32_t box[2] = {32u, 128u};
+  cuuint32_t estr[2] = {1, 1};
+  const MapKey key = {ptr, rows, cols, ld, 32, 128, 3};
+  return cached_map(m, key, [&](CUtensorMap* dst) {
+    return g_encode(dst, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  });
 }
 
 static int make_map_out(CUtensorMap* m, void* ptr, long long rows, long long cols, long long ld,
@@ -1219,7 +1307,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     const RegionDesc& rd = g.region[r];
     Region& R = p.reg[r];
     if (rd.mo <= 0 || rd.no <= 0 || rd.out == nullptr) return WSL_ERR_BAD_ARG;
-    const int vec = (rd.mode == kEpiStoreBf16 || rd.mode == kEpiSwiGLU) ? 8 : 4;
+    const int vec = (rd.mode == kEpiStoreBf16 || rd.mode == kEpiSwiGLU || rd.mode == kEpiSwiGLUBwd) ? 8 : 4;
     if (rd.transposed) {
       if (rd.mode == kEpiStoreBf16) return WSL_ERR_BAD_ARG;
       if ((rd.mo % 4) != 0 || (rd.ld_out % 4) != 0 || rd.ld_out < rd.mo ||
@@ -1230,11 +1318,17 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       return WSL_ERR_ALIGN;
     }
     const bool swiglu = rd.mode == kEpiSwiGLU;
-    if ((rd.addend != nullptr) != (g.region[0].addend != nullptr)) return WSL_ERR_BAD_ARG;
+    if ((rd.addend != nullptr) != (g.region[0].addend != nullptr) || rd.mode != g.region[0].mode && rd.addend != nullptr)
+      return WSL_ERR_BAD_ARG;
+    if ((rd.mode == kEpiSwiGLUBwd) != (rd.addend2 != nullptr)) return WSL_ERR_BAD_ARG;
     if (rd.addend != nullptr) {
-      if (rd.mode != kEpiStoreBf16 || rd.transposed || rd.copy != nullptr || g.workspace != nullptr)
+      if ((rd.mode != kEpiStoreBf16 && rd.mode != kEpiSwiGLUBwd) || rd.transposed || rd.copy != nullptr ||
+          g.workspace != nullptr)
         return WSL_ERR_BAD_ARG;
       if ((reinterpret_cast<uintptr_t>(rd.addend) & 15u) != 0 || (rd.ld_addend % 8) != 0 || rd.ld_addend < rd.no)
+        return WSL_ERR_ALIGN;
+      if (rd.mode == kEpiSwiGLUBwd &&
+          (rd.out2 == nullptr || ((reinterpret_cast<uintptr_t>(rd.addend2) | reinterpret_cast<uintptr_t>(rd.out2)) & 15u) != 0))
         return WSL_ERR_ALIGN;
     }
     if (swiglu) {
@@ -1247,7 +1341,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     long long n_tiles = (rd.no + BN_MAX - 1) / BN_MAX;
     long long bn = (rd.no + n_tiles - 1) / n_tiles;
     bn = (bn + bn_round - 1) / bn_round * bn_round;
-    if (rd.addend != nullptr) bn = (bn + 63) / 64 * 64;   // whole 64-column staging chunks
+    if (rd.addend != nullptr) bn = (bn + 63) / 64 * 64;   // whole staging chunks (64 or 32 columns)
     if (swiglu) {   // one tile = 128 output columns of g next to the same 128 of u
       n_tiles = rd.no / 128;
       bn = BN_MAX;
@@ -1391,7 +1485,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     // staged TMA-store epilogue where the tile width is a whole number of 128-byte chunks
     for (int r = 0; r < g.nregion; ++r) {
       const RegionDesc& rd = g.region[r];
-      if (rd.mode == kEpiSwiGLU) continue;   // its three maps are made below
+      if (rd.mode == kEpiSwiGLU || rd.mode == kEpiSwiGLUBwd) continue;   // their maps are made below
       const bool f32 = rd.mode != kEpiStoreBf16;
       if (rd.transposed || (p.reg[r].bn % (f32 ? 32 : 64)) != 0) continue;
       st = make_map_out(&p.maps[nmaps], rd.out, rd.mo, rd.no, rd.ld_out, f32);
@@ -1399,13 +1493,26 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       p.reg[r].out_map = nmaps++;
     }
   }
-  p.has_addend = g.region[0].addend != nullptr ? 1 : 0;
-  for (int r = 0; r < g.nregion && p.has_addend; ++r) {
+  p.aux_mode = g.region[0].addend == nullptr ? 0 : (g.region[0].mode == kEpiSwiGLUBwd ? 2 : 1);
+  for (int r = 0; r < g.nregion && p.aux_mode == 1; ++r) {
     const RegionDesc& rd = g.region[r];
     if (p.reg[r].out_map < 0 || nmaps + 1 > kMaxMaps) return WSL_ERR_BAD_ARG;
     st = make_map_out(&p.maps[nmaps], const_cast<void*>(rd.addend), rd.mo, rd.no, rd.ld_addend, false);
     if (st != WSL_OK) return st;
     p.reg[r].addend_map = nmaps++;
+  }
+  for (int r = 0; r < g.nregion && p.aux_mode == 2; ++r) {
+    // g, u in and d gate, d up out: four maps over [mo, no] bf16 matrices with boxes of 32
+    // columns x 128 rows, 64-byte swizzle (two of them share a 16 KiB staging slot)
+    const RegionDesc& rd = g.region[r];
+    if (any_split || nmaps + 4 > kMaxMaps) return WSL_ERR_BAD_ARG;
+    p.reg[r].addend_map = nmaps;
+    st = make_map_half(&p.maps[nmaps++], const_cast<void*>(rd.addend), rd.mo, rd.no, rd.ld_addend);
+    if (st == WSL_OK) st = make_map_half(&p.maps[nmaps++], const_cast<void*>(rd.addend2), rd.mo, rd.no, rd.ld_addend);
+    p.reg[r].out_map = nmaps;
+    if (st == WSL_OK) st = make_map_half(&p.maps[nmaps++], rd.out, rd.mo, rd.no, rd.ld_out);
+    if (st == WSL_OK) st = make_map_half(&p.maps[nmaps++], rd.out2, rd.mo, rd.no, rd.ld_out);
+    if (st != WSL_OK) return st;
   }
   for (int r = 0; r < g.nregion; ++r) {
     const RegionDesc& rd = g.region[r];

@@ -19,6 +19,10 @@ enum EpilogueMode : int {
   // Gate and up projection of a SwiGLU MLP in one accumulator tile (see RegionDesc::b2):
   // out(bf16) = g, out2 = u, out3 = silu(g) * u with g, u rounded to bf16 first.
   kEpiSwiGLU = 3,
+  // Backward of that activation in the epilogue of the GEMM that produces dh (the input
+  // gradient of the down projection): with g = addend and u = addend2 (bf16 [mo, no]),
+  //   out(bf16) = d gate = dh u silu'(g),  out2(bf16) = d up = dh silu(g),  dh = bf16(alpha * acc).
+  kEpiSwiGLUBwd = 4,
 };
 
 // A row-major bf16 matrix in device memory: `rows` x `cols`, row pitch `ld` elements.
@@ -71,6 +75,7 @@ struct RegionDesc {
   // Either every region of a launch has an addend or none (W_eff = W + s B A is the user).
   const void* addend;
   long long ld_addend;
+  const void* addend2;   // kEpiSwiGLUBwd: the second input matrix (u), pitch ld_addend
 };
 
 struct GemmDesc {

@@ -414,6 +414,48 @@ int wsl_lora_linear_bwd_dx(int nproj, const void* const* dY, const long long* ld
   return launch_block_gemm(g, s);
 }
 
+int wsl_swiglu_bwd_in_dx_supported(long long M, long long N, long long K, long long r) {
+  return (M > 0 && N > 0 && K > 0 && r >= 0 && (K % 64) == 0 && (N % 8) == 0 && (r % 8) == 0 &&
+          use_pair_tiles(M, K)) ? 1 : 0;
+}
+
+int wsl_lora_linear_bwd_dx_swiglu(const void* dY, long long lddy, const void* U, long long ldu,
+                                  const void* W, const void* A, const void* g, const void* u,
+                                  void* dgate, void* dup, long long ld_gu, long long M, long long N,
+                                  long long K, long long r, void* stream) {
+  if (!dY || !W || !g || !u || !dgate || !dup || M <= 0 || N <= 0 || K <= 0 || r < 0) return WSL_ERR_BAD_ARG;
+  if (r > 0 && (!U || !A)) return WSL_ERR_BAD_ARG;
+  if (!wsl_swiglu_bwd_in_dx_supported(M, N, K, r)) return WSL_ERR_BAD_ARG;
+  GemmDesc gd = {};
+  gd.a_mn = false;
+  gd.b_mn = true;
+  gd.nregion = 1;
+  RegionDesc& r0 = gd.region[0];
+  int ns = 0;
+  gd.seg_k[ns] = static_cast<int>(N);
+  r0.a[ns] = mat(dY, M, N, lddy);
+  r0.b[ns] = mat(W, N, K, K);
+  ++ns;
+  if (r > 0) {
+    gd.seg_k[ns] = static_cast<int>(r);
+    r0.a[ns] = mat(U, M, r, ldu);
+    r0.b[ns] = mat(A, r, K, K);
+    ++ns;
+  }
+  gd.nseg = ns;
+  r0.mo = M;
+  r0.no = K;
+  r0.out = dgate;
+  r0.out2 = dup;
+  r0.ld_out = ld_gu;
+  r0.mode = kEpiSwiGLUBwd;
+  r0.alpha = 1.f;
+  r0.addend = g;
+  r0.addend2 = u;
+  r0.ld_addend = ld_gu;
+  return launch_block_gemm(gd, static_cast<cudaStream_t>(stream));
+}
+
 int wsl_lora_linear_bwd_dw(const void* dY, long long lddy, const void* U, long long ldu,
                            const void* x, long long ldx, const void* T, long long ldt, float* dW,
                            float* dA, float* dB, long long M, long long N, long long K,

@@ -2,6 +2,7 @@
 // softmax cross-entropy (forward + gradient in one go, in place), SwiGLU, RMSNorm with an
 // optional fused rotary embedding. Each is a plain streaming kernel: 16-byte vector
 // accesses, fp32 math, one rounding to the storage type. T is __nv_bfloat16 or float.
+#include "swiglu_math.cuh"
 #include "block_gemm.cuh"
 #include "status.cuh"
 #include "../../include/wsl.h"
@@ -174,8 +175,7 @@ swiglu_fwd_kernel(const T* __restrict__ g, const T* __restrict__ u, T* __restric
     Vec<T> o;
 #pragma unroll
     for (int e = 0; e < NV; ++e) {
-      const float x = a.get(e);
-      o.set(e, x / (1.f + __expf(-x)) * b.get(e));
+      o.set(e, swiglu_fwd_elem(a.get(e), b.get(e)));
     }
     stv<T>(out + i * NV, o);
   }
@@ -191,10 +191,10 @@ swiglu_bwd_kernel(const T* __restrict__ d, const T* __restrict__ g, const T* __r
     Vec<T> og, ou;
 #pragma unroll
     for (int e = 0; e < NV; ++e) {
-      const float x = a.get(e), dy = dd.get(e);
-      const float sg = 1.f / (1.f + __expf(-x));
-      og.set(e, dy * b.get(e) * sg * (1.f + x * (1.f - sg)));
-      ou.set(e, dy * x * sg);
+      float dgv, duv;
+      swiglu_bwd_elem(dd.get(e), a.get(e), b.get(e), dgv, duv);
+      og.set(e, dgv);
+      ou.set(e, duv);
     }
     stv<T>(dg + i * NV, og);
     stv<T>(du + i * NV, ou);

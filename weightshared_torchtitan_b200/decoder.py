@@ -284,7 +284,7 @@ class WeightSharedDecoder(nn.Module):
             p.grad = torch.zeros(p.shape, device=p.device, dtype=torch.float32)
         return p.grad
 
-    def _group(self, lyr: DecoderLayer, names, x, batch=None, swiglu: bool = False):
+    def _group(self, lyr: DecoderLayer, names, x, batch=None, mlp: bool = False):
         dt = self.compute_dtype
         Ws, As, Bs, sinks, anchors = [], [], [], [], []
         train = torch.is_grad_enabled()
@@ -299,8 +299,8 @@ class WeightSharedDecoder(nn.Module):
                 sinks.append((self._sink(W), self._sink(A), self._sink(B)))
                 anchors += [W, A, B]
         s = getattr(lyr, f"{names[0]}_offset").scale
-        if swiglu:   # names = (gate, up): the activation rides in the epilogue of their GEMM
-            return WF.lora_gate_up_swiglu(x, Ws, As, Bs, s, sinks if train else None, tuple(anchors), batch)
+        if mlp:   # names = (gate, up, down): the activation rides in the GEMM epilogues
+            return WF.lora_mlp(x, Ws, As, Bs, s, sinks if train else None, tuple(anchors), batch)
         return WF.lora_linear_group(x, Ws, As, Bs, s, sinks if train else None, tuple(anchors), batch)
 
     # ------------------------------------------------------------------------ forward
@@ -345,8 +345,7 @@ class WeightSharedDecoder(nn.Module):
                                                is_causal=True, enable_gqa=c.n_heads != c.n_kv_heads)
             o = o.transpose(1, 2).reshape(b, s, c.n_heads * c.head_dim)
             h, xn = _add_rms(lyr.ffn_norm, h, self._group(lyr, ("wo",), o, ab)[0])
-            act = self._group(lyr, ("w1", "w3"), xn, ab, swiglu=True)
-            pending = self._group(lyr, ("w2",), act, ab)[0]
+            pending = self._group(lyr, ("w1", "w3", "w2"), xn, ab, mlp=True)
         if pending is None:
             return _rms(self.norm, h)
         return _add_rms(self.norm, h, pending)[1]

@@ -313,6 +313,95 @@ class LoRAGateUpSwiGLUFunction(torch.autograd.Function):
         return _group_backward(ctx, x2, T_cat, wab, (dg, du))
 
 
+class _GroupCtx:
+    """The fields _group_backward reads, for a projection group that is part of a larger Function."""
+
+    def __init__(self, P, derived, s, sinks, batch, x_shape, need_x):
+        self.P, self.derived, self.s, self.sinks, self.batch, self.x_shape = P, derived, s, sinks, batch, x_shape
+        self.needs_input_grad = (need_x,) + (False,) * (4 + 3 * P)
+
+
+class LoRAMLPFunction(torch.autograd.Function):
+    """The whole SwiGLU MLP, y = down(silu(gate(x)) * up(x)) with a shared base weight plus a
+    per-layer adapter on each of the three projections
+    (``w2(F.silu(w1(x)) * w3(x))``, torchtitan/experiments/qwen3/model/model.py:251), as one
+    autograd node so that the activation can ride in GEMM epilogues both ways:
+
+      forward   gate|up GEMM whose epilogue writes g, u and h = silu(g) u; down GEMM on h
+      backward  the down projection's input-gradient GEMM writes d gate and d up directly (dh
+                never reaches memory), then the weight gradients of down and the backward of
+                the gate|up group
+
+    forward(ctx, x, s, sinks, anchors, batch, Wg, Ag, Bg, Wu, Au, Bu, Wd, Ad, Bd) -> y
+    ``sinks`` = three (dW, dA, dB) triples of fp32 buffers (gate, up, down), accumulated in place;
+    ``batch`` = AdapterGradBatch shared with the layer's other groups (this node reports twice).
+    Bit-identical to lora_gate_up_swiglu followed by lora_linear_group for the down projection."""
+
+    @staticmethod
+    def forward(ctx, x, s, sinks, anchors, batch, Wg, Ag, Bg, Wu, Au, Bu, Wd, Ad, Bd):
+        x2 = _flat(x)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        T_cat = ops.lora_prepass(x2, torch.cat((Ag, Au), dim=0), s)
+        g, u, h = ops.lora_swiglu_fwd(x2, Wg, Wu, T_cat, Bg, Bu)
+        T2 = ops.lora_prepass(h, Ad, s)
+        y = ops.lora_linear_fwd(h, Wd, T2, Bd)
+        ctx.s, ctx.sinks, ctx.batch, ctx.x_shape = float(s), sinks, batch, x.shape
+        ctx.derived_gu = _derived_route(x2, sinks[:2], [Wg, Wu], [Ag, Au])
+        ctx.derived_d = _derived_route(h, sinks[2:], [Wd], [Ad])
+        ctx.save_for_backward(x2, None if ctx.derived_gu else T_cat, g, u, h, None if ctx.derived_d else T2,
+                              Wg, Ag, Bg, Wu, Au, Bu, Wd, Ad, Bd)
+        return y.view(*x.shape[:-1], Wd.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, T_cat, g, u, h, T2, Wg, Ag, Bg, Wu, Au, Bu, Wd, Ad, Bd = ctx.saved_tensors
+        d = _flat(dy)
+        if d.stride(-1) != 1:
+            d = d.contiguous()
+        dWd, dAd, dBd = ctx.sinks[2]
+        if ctx.derived_d:
+            W_eff = ops.lora_merge_weight([Wd], [Ad], [Bd], ctx.s)[0]
+            dg, du = ops.lora_linear_bwd_dx_swiglu(d, None, W_eff, None, g, u)
+            dWl = ops.bwd_dw_layer_group([d], h, [dWd])
+            if ctx.batch is not None:
+                ctx.batch.add(dWl, [Ad], [Bd], [dAd], [dBd], ctx.s)
+            else:
+                ops.lora_adapter_grads_from_dw(dWl, [Ad], [Bd], [dAd], [dBd], ctx.s)
+        else:
+            if ctx.batch is not None:
+                ctx.batch.nothing_to_add()
+            U2 = ops.lora_bwd_prepass(d, Bd, ctx.s)
+            dg, du = ops.lora_linear_bwd_dx_swiglu(d, U2, Wd, Ad, g, u)
+            ops.lora_linear_bwd_dw(d, U2, h, T2, dWd, dAd, dBd)
+        gctx = _GroupCtx(2, ctx.derived_gu, ctx.s, ctx.sinks[:2], ctx.batch, ctx.x_shape, ctx.needs_input_grad[0])
+        dX = _group_backward(gctx, x2, T_cat, [Wg, Ag, Bg, Wu, Au, Bu], (dg, du))[0]
+        return (dX, None, None, None, None) + (None,) * 9
+
+
+def lora_mlp(x: torch.Tensor, Ws, As, Bs, s: float, sinks=None, anchors: Tuple[torch.Tensor, ...] = (),
+             batch: Optional[AdapterGradBatch] = None) -> torch.Tensor:
+    """down(silu(gate(x)) * up(x)) with Ws = (W_gate, W_up, W_down) etc. One autograd node with
+    the activation in the GEMM epilogues (LoRAMLPFunction) where the shapes allow it and the
+    weight gradients accumulate in place (``sinks`` complete); else the composition of
+    lora_gate_up_swiglu and lora_linear_group, which computes the same bits."""
+    x2 = _flat(x)
+    Wg, Wu, Wd = Ws
+    M = x2.shape[0]
+    r = As[0].shape[0]
+    fused = (M > 0 and x2.dtype == torch.bfloat16 and sinks is not None
+             and all(t is not None for trip in sinks for t in trip)
+             and As[1].shape[0] == r and As[2].shape[0] == r and Wg.shape == Wu.shape
+             and Wd.shape == (Wg.shape[1], Wg.shape[0])
+             and ops.lora_swiglu_supported(M, Wg.shape[0], Wg.shape[1], r)
+             and ops.swiglu_bwd_in_dx_supported(M, Wd.shape[0], Wd.shape[1], r))
+    if fused:
+        return LoRAMLPFunction.apply(x, s, sinks, _Anchor(anchors, x), batch, Wg, As[0], Bs[0], Wu, As[1], Bs[1],
+                                     Wd, As[2], Bs[2])
+    act = lora_gate_up_swiglu(x, Ws[:2], As[:2], Bs[:2], s, None if sinks is None else sinks[:2], anchors, batch)
+    return lora_linear_group(act, [Wd], [As[2]], [Bs[2]], s, None if sinks is None else sinks[2:], anchors, batch)[0]
+
+
 def lora_gate_up_swiglu(x: torch.Tensor, Ws, As, Bs, s: float, sinks=None,
                         anchors: Tuple[torch.Tensor, ...] = (),
                         batch: Optional[AdapterGradBatch] = None) -> torch.Tensor:

@@ -306,6 +306,42 @@ def lora_linear_bwd_dx(dYs: Sequence[torch.Tensor], Us: Sequence[Optional[torch.
     return dX
 
 
+def swiglu_bwd_in_dx_supported(M: int, N: int, K: int, r: int) -> bool:
+    """Whether lora_linear_bwd_dx_swiglu covers this shape (K = the MLP's inner width)."""
+    return bool(_lib.lib().wsl_swiglu_bwd_in_dx_supported(M, N, K, r))
+
+
+def lora_linear_bwd_dx_swiglu(dY: torch.Tensor, U: Optional[torch.Tensor], W: torch.Tensor,
+                              A: Optional[torch.Tensor], g: torch.Tensor, u: torch.Tensor):
+    """(d gate, d up) from dh = dY @ W + U @ A without writing dh: the down projection's input
+    gradient with the SwiGLU backward in its epilogue (wsl_lora_linear_bwd_dx_swiglu, bf16)."""
+    dY, W = _mat(dY, "dY"), _mat(W, "W").contiguous()
+    g, u = _mat(g, "g").contiguous(), _mat(u, "u").contiguous()
+    _same(WSL_BF16, dY, W, g, u)
+    M, N = dY.shape
+    K = W.shape[1]
+    if W.shape[0] != N or g.shape != (M, K) or u.shape != (M, K):
+        raise ValueError("W must be [N, K], g and u [M, K]")
+    r = 0
+    up = ap = None
+    ldu = 0
+    if U is not None:
+        U, A = _mat(U, "U"), _mat(A, "A").contiguous()
+        _same(WSL_BF16, U, A)
+        r = A.shape[0]
+        if U.shape != (M, r) or A.shape[1] != K:
+            raise ValueError("U must be [M, r] and A [r, K]")
+        up, ap, ldu = U.data_ptr(), A.data_ptr(), _ld(U)
+    dg, du = torch.empty_like(g), torch.empty_like(u)
+    _e = _tic()
+    st = _lib.lib().wsl_lora_linear_bwd_dx_swiglu(dY.data_ptr(), _ld(dY), up, ldu, W.data_ptr(), ap, g.data_ptr(),
+                                                  u.data_ptr(), dg.data_ptr(), du.data_ptr(), K, M, N, K, r,
+                                                  _stream())
+    _toc(_e, "dx", 2.0 * M * K * (N + r), 2.0 * (M * N + N * K + M * r + r * K + 4 * M * K))
+    _lib.check(st, "wsl_lora_linear_bwd_dx_swiglu")
+    return dg, du
+
+
 def lora_linear_bwd_dw(dY: torch.Tensor, U: Optional[torch.Tensor], x: torch.Tensor,
                        T: Optional[torch.Tensor], dW: Optional[torch.Tensor],
                        dA: Optional[torch.Tensor], dB: Optional[torch.Tensor]) -> None:
