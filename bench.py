@@ -366,9 +366,28 @@ def bench_projection(torch, M, N, K, r, iters, what="all", warmup=3):
             "dw_copy": lambda: ops.bwd_dw_layer_group([dY], x, [dW]),
             "adapter_grads": lambda: ops.lora_adapter_grads_from_dw(G, [A], [B], [dA], [dB], 2.0),
         }
+    # the MLP launches that carry the activation in their epilogues, with this shape as the gate / up
+    # projection (N = inner width): gate|up + SwiGLU forward, and the down projection's input gradient
+    # (contraction over K = model width, output width N) with the SwiGLU backward
+    mlp = {}
+    if ops.lora_swiglu_supported(M, N, K, r) and ops.swiglu_bwd_in_dx_supported(M, K, N, r):
+        A_cat = torch.cat((A, A))
+        T_cat = ops.lora_prepass(x, A_cat, 2.0)
+        g_, u_, _ = ops.lora_swiglu_fwd(x, W, W, T_cat, B, B)
+        Wd = W.t().contiguous()                       # [K, N]: the down projection's weight
+        dYd = dY[:, :K].contiguous()                  # its output gradient [M, K]
+        Ad = A[:, :1].expand(r, N).contiguous()       # [r, N]
+        Ud = ops.lora_bwd_prepass(dYd, B[:K], 2.0)    # [M, r]
+        mlp = {
+            "mlp_fwd": lambda: ops.lora_swiglu_fwd(x, W, W, T_cat, B, B),
+            "mlp_fwd_unfused": lambda: ops.swiglu_fwd(*ops.lora_linear_fwd_group(
+                x, [W, W], [T_cat[:, :r], T_cat[:, r:]], [B, B])),
+            "mlp_dx": lambda: ops.lora_linear_bwd_dx_swiglu(dYd, Ud, Wd, Ad, g_, u_),
+            "mlp_dx_unfused": lambda: ops.swiglu_bwd(ops.lora_linear_bwd_dx([dYd], [Ud], [Wd], [Ad]), g_, u_),
+        }
     res = {"M": M, "N": N, "K": K, "r": r}
     if what != "all":
-        res[what + "_ms"] = time_ms(torch, {**parts, **via_dw}[what], iters, warmup)
+        res[what + "_ms"] = time_ms(torch, {**parts, **via_dw, **mlp}[what], iters, warmup)
         return res
 
     def whole():
@@ -381,7 +400,7 @@ def bench_projection(torch, M, N, K, r, iters, what="all", warmup=3):
         for f in via_dw.values():
             f()
 
-    ms = {k: time_ms(torch, f, iters, warmup) for k, f in {**parts, **via_dw}.items()}
+    ms = {k: time_ms(torch, f, iters, warmup) for k, f in {**parts, **via_dw, **mlp}.items()}
     flops = 6.0 * M * N * K + 6.0 * M * r * (K + N)
     total_direct = time_ms(torch, whole, iters, warmup)
     res.update({
@@ -944,7 +963,7 @@ def main():
     ap.add_argument("--routes", action="store_true",
                     help="both backward formulations of every projection group of every configuration")
     ap.add_argument("--what", default="all", help="--op: one kernel (prepass_T, fwd, prepass_U, dx, dw, merge, "
-                    "dx_merged, dw_copy, adapter_grads); --rows: rmsnorm, swiglu, ce, adamw, embed, embed_fwd, embed_dproj")
+                    "dx_merged, dw_copy, adapter_grads, mlp_fwd, mlp_fwd_unfused, mlp_dx, mlp_dx_unfused); --rows: rmsnorm, swiglu, ce, adamw, embed, embed_fwd, embed_dproj")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--tokens", type=int, default=32768)
     ap.add_argument("--embed-tokens", type=int, default=16384)

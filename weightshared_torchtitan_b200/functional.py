@@ -44,15 +44,33 @@ DERIVED_ADAPTER_GRADS = {"0": False, "1": True}.get(_env, "auto")
 # the group through the autograd Function) for every projection group of the four baseline
 # configurations at their own token counts: (M, K, (N_0, ...), r) -> through the layer gradient?
 ROUTE_TABLE = {
+    # configuration 1 (0.6B shape, 32768 tokens, r 16): q|k|v, o, gate|up, down
+    (32768, 1024, (2048, 1024, 1024), 16): True,     # 0.82 -> 0.71 ms
+    (32768, 2048, (1024,), 16): True,                # 0.43 -> 0.43
+    (32768, 1024, (3072, 3072), 16): True,           # 1.11 -> 1.00
+    (32768, 3072, (1024,), 16): True,                # 0.66 -> 0.63
+    # configuration 2 (1.7B shape, 32768 tokens, r 32)
+    (32768, 2048, (2048, 1024, 1024), 32): True,     # 1.41 -> 1.27
+    (32768, 2048, (2048,), 32): True,                # 0.77 -> 0.74
+    (32768, 2048, (6144, 6144), 32): False,          # 3.95 = 3.95
+    (32768, 6144, (2048,), 32): True,                # 1.96 -> 1.88
+    # configuration 3 (4B shape, 32768 tokens, r 64)
+    (32768, 2560, (4096, 1024, 1024), 64): False,    # 2.43 = 2.44
+    (32768, 4096, (2560,), 64): False,               # 1.77 = 1.77
+    (32768, 2560, (9728, 9728), 64): True,           # 8.36 -> 8.15
+    (32768, 9728, (2560,), 64): False,               # 4.00 <- 4.07
+    # configuration 4 (8B shape, 16384 tokens, r 64)
+    (16384, 4096, (4096, 1024, 1024), 64): True,     # 2.27 -> 2.23
+    (16384, 4096, (4096,), 64): False,               # 1.27 <- 1.36
+    (16384, 4096, (12288, 12288), 64): True,         # 8.43 -> 8.34
+    (16384, 12288, (4096,), 64): False,              # 3.99 <- 4.07
 }
 
-# Shapes outside the table: both formulations cost HBM passes, so compare bytes. The direct
-# form streams dY once more for U = s dY B (2 M N bytes) and runs the rank-r regions, which
-# re-stream dY and x through narrow tiles at about a third of the rate of a full pass
-# (3 * 2 M (N + K) byte-equivalents); the form through G moves 4 N K (merged weight, read and
-# write) + 2 N K (bf16 copy of G) + 4 N K (two passes over G for dA, dB) bytes and pays two
-# extra launches (~20 us = 100 MB at 5 TB/s).
-_FIXED_BYTES = 100e6
+# Shapes outside the table: the form through G trades passes over M-row activations (the
+# pre-pass over dY, the rank-r regions) for passes over [N, K] matrices (merged weight, bf16
+# copy of G, two reads of G), so what decides is the token count against the input width. In
+# the table the form through G wins clearly from M / K ~ 5 upwards and loses below ~ 4.
+_MIN_TOKENS_PER_INPUT_WIDTH = 5.0
 
 
 def derived_route_pays(M: int, K: int, Ns, r: int) -> bool:
@@ -61,9 +79,7 @@ def derived_route_pays(M: int, K: int, Ns, r: int) -> bool:
     hit = ROUTE_TABLE.get((int(M), int(K), tuple(int(n) for n in Ns), int(r)))
     if hit is not None:
         return hit
-    derived = _FIXED_BYTES + sum(10.0 * n * K for n in Ns)
-    direct = sum(2.0 * M * n + 6.0 * M * (n + K) * min(r, 64) / 64.0 for n in Ns)
-    return derived < direct
+    return M >= _MIN_TOKENS_PER_INPUT_WIDTH * K
 
 
 class AdapterGradBatch:
@@ -313,6 +329,23 @@ class LoRAGateUpSwiGLUFunction(torch.autograd.Function):
         return _group_backward(ctx, x2, T_cat, wab, (dg, du))
 
 
+# The derivative of the activation can ride in the epilogue of the down projection's
+# input-gradient GEMM (ops.lora_linear_bwd_dx_swiglu) or run as its own pass over dh, g, u.
+# Measured in the configuration-4 step the epilogue form LOSES: the four epilogue warps of a
+# CTA spend ~25 instructions per element on it and the GEMM waits for them (dX launches 181 ->
+# 217 ms per step, against 12.5 ms for the stand-alone kernel). Off by default;
+# WSL_FUSE_SWIGLU_BWD=1 turns it on.
+FUSE_SWIGLU_BWD = os.environ.get("WSL_FUSE_SWIGLU_BWD", "0") == "1"
+
+
+def _down_dx_with_activation_grad(d, U2, W, A, g, u):
+    """(d gate, d up) from the down projection's output gradient."""
+    if FUSE_SWIGLU_BWD:
+        return ops.lora_linear_bwd_dx_swiglu(d, U2, W, A, g, u)
+    dh = ops.lora_linear_bwd_dx([d], [U2], [W], [A])
+    return ops.swiglu_bwd(dh, g, u)
+
+
 class _GroupCtx:
     """The fields _group_backward reads, for a projection group that is part of a larger Function."""
 
@@ -328,9 +361,10 @@ class LoRAMLPFunction(torch.autograd.Function):
     autograd node so that the activation can ride in GEMM epilogues both ways:
 
       forward   gate|up GEMM whose epilogue writes g, u and h = silu(g) u; down GEMM on h
-      backward  the down projection's input-gradient GEMM writes d gate and d up directly (dh
-                never reaches memory), then the weight gradients of down and the backward of
-                the gate|up group
+      backward  the down projection's input gradient, then d gate and d up (as one launch whose
+                epilogue applies the activation's derivative when FUSE_SWIGLU_BWD is set, else
+                the GEMM followed by the stand-alone kernel), the weight gradients of down and
+                the backward of the gate|up group
 
     forward(ctx, x, s, sinks, anchors, batch, Wg, Ag, Bg, Wu, Au, Bu, Wd, Ad, Bd) -> y
     ``sinks`` = three (dW, dA, dB) triples of fp32 buffers (gate, up, down), accumulated in place;
@@ -362,7 +396,7 @@ class LoRAMLPFunction(torch.autograd.Function):
         dWd, dAd, dBd = ctx.sinks[2]
         if ctx.derived_d:
             W_eff = ops.lora_merge_weight([Wd], [Ad], [Bd], ctx.s)[0]
-            dg, du = ops.lora_linear_bwd_dx_swiglu(d, None, W_eff, None, g, u)
+            dg, du = _down_dx_with_activation_grad(d, None, W_eff, None, g, u)
             dWl = ops.bwd_dw_layer_group([d], h, [dWd])
             if ctx.batch is not None:
                 ctx.batch.add(dWl, [Ad], [Bd], [dAd], [dBd], ctx.s)
@@ -372,7 +406,7 @@ class LoRAMLPFunction(torch.autograd.Function):
             if ctx.batch is not None:
                 ctx.batch.nothing_to_add()
             U2 = ops.lora_bwd_prepass(d, Bd, ctx.s)
-            dg, du = ops.lora_linear_bwd_dx_swiglu(d, U2, Wd, Ad, g, u)
+            dg, du = _down_dx_with_activation_grad(d, U2, Wd, Ad, g, u)
             ops.lora_linear_bwd_dw(d, U2, h, T2, dWd, dAd, dBd)
         gctx = _GroupCtx(2, ctx.derived_gu, ctx.s, ctx.sinks[:2], ctx.batch, ctx.x_shape, ctx.needs_input_grad[0])
         dX = _group_backward(gctx, x2, T_cat, [Wg, Ag, Bg, Wu, Au, Bu], (dg, du))[0]
