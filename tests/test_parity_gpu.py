@@ -906,10 +906,11 @@ def test_mlp_function_matches_the_unfused_composition(wsl):
         return [(torch.zeros(W.shape, device="cuda"), torch.zeros(A.shape, device="cuda"),
                  torch.zeros(B.shape, device="cuda")) for W, A, B in zip(Ws, As, Bs)]
 
-    saved = Fn.DERIVED_ADAPTER_GRADS
+    saved, saved_fuse = Fn.DERIVED_ADAPTER_GRADS, Fn.FUSE_SWIGLU_BWD
     try:
         for flag in (False, True):
             Fn.DERIVED_ADAPTER_GRADS = flag
+            Fn.FUSE_SWIGLU_BWD = True          # the epilogue form, whatever "auto" would pick at this width
             res = []
             for fused in (True, False):
                 x = x0.clone().requires_grad_(True)
@@ -927,7 +928,7 @@ def test_mlp_function_matches_the_unfused_composition(wsl):
                 for ta, tb in zip(a, b):
                     assert torch.equal(ta, tb)
     finally:
-        Fn.DERIVED_ADAPTER_GRADS = saved
+        Fn.DERIVED_ADAPTER_GRADS, Fn.FUSE_SWIGLU_BWD = saved, saved_fuse
     xc = x0.float().cpu()
     gate = O.lora_linear(xc, Ws[0].float().cpu(), As[0].float().cpu(), Bs[0].float().cpu())
     up = O.lora_linear(xc, Ws[1].float().cpu(), As[1].float().cpu(), Bs[1].float().cpu())

@@ -102,6 +102,10 @@ struct GemmParams {
   // 0 none, 1 out = alpha acc + addend (64-column chunks), 2 SwiGLU backward from g = addend and
   // u = addend2 into two outputs (32-column chunks, 64-byte swizzle).
   int aux_mode;
+  // Staging slots of 16 KiB the epilogue owns behind the operand ring: 2 normally; the
+  // weight-merge launch (one k-block per tile, so a short ring) runs with 8, which lets the
+  // addend tiles be fetched six chunks ahead instead of one.
+  int epi_slots;
   unsigned long long wait_limit_ns;   // bound of every mbarrier wait
   // Row gather (factorized embedding): when set, the rows of region 0 / segment 0's A operand
   // (gather_a, K-major) or the k-rows of its B operand (gather_b, MN-major) are the rows
@@ -283,7 +287,8 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
   const int S = PAIR ? C::kStages : p.stages;
   const uint32_t stage_bytes = PAIR ? static_cast<uint32_t>(C::kStageBytes) : static_cast<uint32_t>(p.stage_bytes);
   extern __shared__ __align__(1024) uint8_t smem_dyn[];
-  __shared__ __align__(8) uint64_t bars[2 * SMAX + 6];
+  constexpr int kMaxEpiSlots = 8;
+  __shared__ __align__(8) uint64_t bars[2 * SMAX + 4 + kMaxEpiSlots];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
 
@@ -311,8 +316,8 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
       mbar_init(tempty_bar(b), PAIR ? 8 : 4);   // one arrival per epilogue warp (of both CTAs)
-      mbar_init(aux_bar(b), 1);
     }
+    for (int b = 0; b < kMaxEpiSlots; ++b) mbar_init(aux_bar(b), 1);
     fence_barrier_init();
     fence_proxy_async_smem();
   }
@@ -557,11 +562,16 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
     // 64-column chunk AHEAD of the chunk being computed; this walks the same chunk sequence.
     int pf_u = worker, pf_c = 0;
     uint32_t pf_ctr = 0;
+    const uint32_t n_slots = static_cast<uint32_t>(p.epi_slots);
+    // With more than two slots the fetch runs n_slots - 2 chunks ahead and a slot is reused
+    // two stores after it was handed to TMA, so the issuer never waits for the store it has
+    // just issued; with two slots it runs one chunk ahead and has to.
+    const int pf_dist = n_slots > 2 ? static_cast<int>(n_slots) - 2 : 1;
     auto prefetch_addend = [&]() {
       if (pf_u >= units) return;
       const TileInfo pt = decode_tile_t<PAIR>(p, pf_u);
       const Region& PR = p.reg[pt.r];
-      const uint32_t slot = pf_ctr & 1u;
+      const uint32_t slot = pf_ctr % n_slots;
       const uint32_t dst = epi_base + slot * EPI_STAGE_BYTES;
       mbar_arrive_expect_tx(aux_bar(slot), EPI_STAGE_BYTES);
       if (p.aux_mode == 1) {
@@ -579,7 +589,8 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
         pf_u += nworkers;
       }
     };
-    if (p.aux_mode != 0 && issuer && !p.stall_producer) prefetch_addend();
+    if (p.aux_mode != 0 && issuer && !p.stall_producer)
+      for (int i = 0; i < pf_dist; ++i) prefetch_addend();
     for (int u = worker; u < units; u += nworkers, ++it) {
       const int t = u;
       const TileInfo ti = decode_tile_t<PAIR>(p, u);
@@ -675,14 +686,17 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t swz = static_cast<uint32_t>(trow & 7);
         bool okc = true;
         for (int c = 0; c < R.bn; c += 64, ++chunk_ctr) {
-          const uint32_t slot = chunk_ctr & 1u;
+          const uint32_t slot = chunk_ctr % n_slots;
           const uint32_t sbuf = epi_base + slot * EPI_STAGE_BYTES;
           const uint32_t srow = sbuf + static_cast<uint32_t>(trow) * 128u;
           if (issuer && !p.stall_producer) {
-            tma_wait_group_read<0>();   // the previous chunk's store has read the other buffer
-            prefetch_addend();          // ... which now takes the chunk after this one
+            // the slot the next fetch goes to was last stored from one (two slots) or two
+            // (more slots) chunks ago: that store must have read it
+            if (n_slots > 2) tma_wait_group_read<1>();
+            else tma_wait_group_read<0>();
+            prefetch_addend();
           }
-          okc = epi_vote_and(mbar_wait(aux_bar(slot), (chunk_ctr >> 1) & 1u, abortp, p.wait_limit_ns));
+          okc = epi_vote_and(mbar_wait(aux_bar(slot), (chunk_ctr / n_slots) & 1u, abortp, p.wait_limit_ns));
           if (!okc) break;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
@@ -1298,7 +1312,13 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
         g.gather_count <= 0)
       return WSL_ERR_BAD_ARG;
   }
-  const bool pair = use_pair_tiles(g.region[0].mo, g.region[0].no);
+  // The weight-merge launch (out = alpha acc + addend, one or two k-blocks per tile) is a
+  // streaming pass bound by how far ahead its addend tiles are fetched: it runs on single
+  // CTAs with a 2-stage operand ring and 8 staging slots instead of 4 stages and 2 slots.
+  int kb_all = 0;
+  for (int sgi = 0; sgi < g.nseg; ++sgi) kb_all += (g.seg_k[sgi] + BK - 1) / BK;
+  const bool deep_epilogue = g.region[0].addend != nullptr && g.region[0].mode == kEpiStoreBf16 && kb_all <= 4;
+  const bool pair = !deep_epilogue && use_pair_tiles(g.region[0].mo, g.region[0].no);
   const int bm_tile = pair ? 2 * BM : BM;
   const int bn_round = pair ? 32 : 16;
   int nmaps = 0;
@@ -1439,6 +1459,12 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
     const bool narrow = !pair && max_bn <= NARROW_BN;
     p.stages = narrow ? NARROW_STAGES : Cfg<false>::kStages;
     p.stage_bytes = narrow ? NARROW_STAGE_BYTES : Cfg<false>::kStageBytes;
+    p.epi_slots = 2;
+    if (deep_epilogue) {
+      p.stages = 2;
+      p.stage_bytes = Cfg<false>::kStageBytes;
+      p.epi_slots = (Cfg<false>::kStages - 2) * Cfg<false>::kStageBytes / EPI_STAGE_BYTES + 2;   // 8
+    }
   }
   p.workspace = nullptr;
   int plan[kMaxRegion];

@@ -331,16 +331,20 @@ class LoRAGateUpSwiGLUFunction(torch.autograd.Function):
 
 # The derivative of the activation can ride in the epilogue of the down projection's
 # input-gradient GEMM (ops.lora_linear_bwd_dx_swiglu) or run as its own pass over dh, g, u.
-# Measured in the configuration-4 step the epilogue form LOSES: the four epilogue warps of a
-# CTA spend ~25 instructions per element on it and the GEMM waits for them (dX launches 181 ->
-# 217 ms per step, against 12.5 ms for the stand-alone kernel). Off by default;
-# WSL_FUSE_SWIGLU_BWD=1 turns it on.
-FUSE_SWIGLU_BWD = os.environ.get("WSL_FUSE_SWIGLU_BWD", "0") == "1"
+# The four epilogue warps of a CTA spend ~16 instructions per element on it, which the main
+# loop hides only when the contraction (the model width d) is long: measured on B200 at the
+# configuration-4 MLP shape (d = 4096, 16384 tokens) 1.23 ms against 1.58 ms for GEMM + kernel,
+# at the configuration-1 shape (d = 1024, 32768 tokens) 0.33 ms against 0.30 ms. "auto" takes
+# the epilogue form from d = 4096; WSL_FUSE_SWIGLU_BWD=0 / 1 forces one.
+_env_fuse = os.environ.get("WSL_FUSE_SWIGLU_BWD", "auto")
+FUSE_SWIGLU_BWD = {"0": False, "1": True}.get(_env_fuse, "auto")
+_FUSE_SWIGLU_BWD_MIN_WIDTH = 4096
 
 
 def _down_dx_with_activation_grad(d, U2, W, A, g, u):
-    """(d gate, d up) from the down projection's output gradient."""
-    if FUSE_SWIGLU_BWD:
+    """(d gate, d up) from the down projection's output gradient d [M, width]."""
+    fuse = FUSE_SWIGLU_BWD if FUSE_SWIGLU_BWD != "auto" else d.shape[1] >= _FUSE_SWIGLU_BWD_MIN_WIDTH
+    if fuse:
         return ops.lora_linear_bwd_dx_swiglu(d, U2, W, A, g, u)
     dh = ops.lora_linear_bwd_dx([d], [U2], [W], [A])
     return ops.swiglu_bwd(dh, g, u)
