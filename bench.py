@@ -733,9 +733,11 @@ def run_ours(args):
     torch.cuda.set_device(local)
     if world > 1:
         opts = None
-        if args.nccl_ctas > 0 and args.allreduce == "overlap":
+        if args.allreduce == "overlap":
+            # the buckets run beside the backward kernels: give their stream priority
             opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
-            opts.config.max_ctas = args.nccl_ctas
+            if args.nccl_ctas > 0:
+                opts.config.max_ctas = args.nccl_ctas
         dist.init_process_group("nccl", device_id=torch.device("cuda", local), pg_options=opts)
     _lib.lib()
     peaks = load_peaks()
@@ -951,9 +953,9 @@ def main():
     ap.add_argument("--allreduce", default="overlap", choices=["overlap", "blocking"],
                     help="N > 1: exchange gradients in buckets during backward, or once after it")
     ap.add_argument("--bucket-mb", type=int, default=256)
-    ap.add_argument("--reserve-sms", type=int, default=16,
-                    help="SMs the persistent kernels leave free while a bucket is in flight")
-    ap.add_argument("--nccl-ctas", type=int, default=8, help="NCCL max CTAs per collective (0 = NCCL's default)")
+    ap.add_argument("--reserve-sms", type=int, default=0,
+                    help="SMs the library's kernels leave free while a bucket is in flight (0 = none)")
+    ap.add_argument("--nccl-ctas", type=int, default=0, help="NCCL max CTAs per collective (0 = NCCL's default)")
     ap.add_argument("--link-gbs", type=float, default=300.0,
                     help="all-reduce rate (GB/s of arena bytes) assumed when sizing the reservation window")
     # kernel-level modes

@@ -85,6 +85,11 @@ int wsl_reset_status(void);
  *                   runs beside them on another stream (the gradient all-reduce overlapped
  *                   with the backward pass; the reference overlaps by DDP buckets,
  *                   torchtitan/models/llama3/infra/parallelize.py:428-444)
+ *   GRID_WAVES      GEMM grids of up to this many times the CTAs that fit at once: 1 = persistent (one
+ *                   CTA or pair per SM walks its share of the tiles), 2..8 = that many waves of
+ *                   shorter-lived CTAs which the hardware deals to SMs as they free up (evens out
+ *                   unequal tile times and SMs held by another kernel), 0 (default) = two waves for
+ *                   launches with long tiles and at least four tiles per CTA, else one
  *   MERGE_SIMT      1 runs wsl_lora_merge_weight on the CUDA cores instead of the tensor cores
  *   PROFILE_BITS    only honoured by builds compiled with -DWSL_PROFILE_SWITCHES
  * No counterpart in the reference (its knobs are Python config fields).
@@ -96,6 +101,7 @@ int wsl_reset_status(void);
 #define WSL_OPT_RESERVED_SMS 5
 #define WSL_OPT_PROFILE_BITS 6
 #define WSL_OPT_MERGE_SIMT 7
+#define WSL_OPT_GRID_WAVES 8
 int wsl_set_option(int option, long long value);
 long long wsl_get_option(int option);
 
@@ -388,8 +394,9 @@ int wsl_swiglu_bwd(const void* dout, const void* gate, const void* up, void* dga
  * written for the backward (may be NULL). With rope_cos / rope_sin ([seq, D] fp32, both or
  * neither) the normalised row is rotated: y = n*cos + rotate_half(n)*sin at position
  * (r / heads) % seq -- the q/k head norm followed by the rotary embedding in one pass.
- * Supported widths: D/vec a power of two <= 32 or D a multiple of 32*vec up to 8*32*vec
- * (vec = 8 for bf16, 4 for fp32), i.e. D <= 2048 in bf16; other widths return
+ * Supported widths: D/vec a power of two <= 32, or D = {1, 2, 4, 8} * 32 * vec (vec = 8 for
+ * bf16, 4 for fp32: up to 2048 / 1024), or, in bf16 with dense rows (pitch = D), D = 2560
+ * and 4096 ({10, 16} * 32 * vec, the hidden sizes of the 4B and 8B shapes); other widths return
  * WSL_ERR_TOO_LARGE. Rotary needs D <= 32*vec. w and dw are fp32 [D]; dw is accumulated
  * (+=, atomics) and may be NULL.
  * Replaces nn.RMSNorm and apply_rotary_emb:

@@ -344,3 +344,25 @@ def test_state_dict_round_trip_with_the_converted_reference_layout():
     bad["layers.2.attention.wq.base.weight"] += 1.0
     with pytest.raises(ValueError):
         A.from_reference(WeightSharedDecoder(c), bad)
+
+
+def test_route_table_covers_the_baseline_configurations():
+    """Every projection group (q|k|v, o, gate|up, down) of baseline configurations 1-4 at its own
+    token count has a measured entry in functional.ROUTE_TABLE (so the step never decides by the
+    fallback rule there), the entries reproduce through derived_route_pays, and the fallback rule
+    separates the table's clear cases."""
+    from weightshared_torchtitan_b200 import functional as Fn
+    from weightshared_torchtitan_b200.decoder import CONFIGS, proj_shapes
+    tokens = {"qwen3-0.6b-ws": 8 * 4096, "qwen3-1.7b-ws": 8 * 4096, "qwen3-4b-ws": 4 * 8192, "qwen3-8b-ws": 2 * 8192}
+    seen = set()
+    for name, c in CONFIGS.items():
+        shp = proj_shapes(c)
+        for names in (("wq", "wk", "wv"), ("wo",), ("w1", "w3"), ("w2",)):
+            key = (tokens[name], shp[names[0]][1], tuple(shp[n][0] for n in names), c.rank)
+            assert key in Fn.ROUTE_TABLE, (name, names, key)
+            assert Fn.derived_route_pays(*key) is Fn.ROUTE_TABLE[key]
+            seen.add(key)
+    assert seen == set(Fn.ROUTE_TABLE)
+    # outside the table: many tokens per input width -> through the layer gradient, few -> direct
+    assert Fn.derived_route_pays(65536, 1024, (1024,), 16) is True
+    assert Fn.derived_route_pays(4096, 4096, (4096,), 64) is False

@@ -142,6 +142,10 @@ int wsl_set_option(int option, long long value) {
       return WSL_OK;
     case WSL_OPT_PROFILE_BITS: o.profile_bits = static_cast<int>(value); return WSL_OK;
     case WSL_OPT_MERGE_SIMT: o.merge_simt = value != 0; return WSL_OK;
+    case WSL_OPT_GRID_WAVES:
+      if (value < 0 || value > 8) return WSL_ERR_BAD_ARG;
+      o.grid_waves = static_cast<int>(value);
+      return WSL_OK;
     default: return WSL_ERR_BAD_ARG;
   }
 }
@@ -156,6 +160,7 @@ long long wsl_get_option(int option) {
     case WSL_OPT_RESERVED_SMS: return o.reserved_sms;
     case WSL_OPT_PROFILE_BITS: return o.profile_bits;
     case WSL_OPT_MERGE_SIMT: return o.merge_simt;
+    case WSL_OPT_GRID_WAVES: return o.grid_waves;
     default: return WSL_ERR_BAD_ARG;
   }
 }

@@ -33,6 +33,7 @@ struct Options {
   int stall_producer;                  // 1: producers never fill their rings (bounded-wait tests)
   unsigned long long wait_limit_ns;    // bound of every device-side wait
   int reserved_sms;                    // SMs the persistent kernels leave free (collective overlap)
+  int grid_waves;                      // GEMM grids up to this many times the co-resident CTAs (0 = by launch)
   int profile_bits;                    // only honoured in builds with WSL_PROFILE_SWITCHES
   int merge_simt;                      // 1: W + s B A on the CUDA cores instead of the block GEMM
 };
