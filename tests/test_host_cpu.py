@@ -366,3 +366,29 @@ def test_route_table_covers_the_baseline_configurations():
     # outside the table: many tokens per input width -> through the layer gradient, few -> direct
     assert Fn.derived_route_pays(65536, 1024, (1024,), 16) is True
     assert Fn.derived_route_pays(4096, 4096, (4096,), 64) is False
+
+
+def test_runtime_options_round_trip():
+    """wsl_set_option / wsl_get_option need no device: values come back, out-of-range values and
+    unknown keys are refused, and the defaults are the documented ones."""
+    from weightshared_torchtitan_b200 import _lib
+    lib = _lib.lib()
+    assert _lib.get_option(_lib.OPT_RESERVED_SMS) == 0 and _lib.get_option(_lib.OPT_GRID_WAVES) == 0
+    assert _lib.get_option(_lib.OPT_STALL_PRODUCER) == 0 and _lib.get_option(_lib.OPT_MERGE_SIMT) == 0
+    old = _lib.get_option(_lib.OPT_WAIT_LIMIT_MS)
+    assert old == 2000 or "WSL_WAIT_LIMIT_MS" in __import__("os").environ
+    try:
+        _lib.set_option(_lib.OPT_WAIT_LIMIT_MS, 250)
+        assert _lib.get_option(_lib.OPT_WAIT_LIMIT_MS) == 250
+        _lib.set_option(_lib.OPT_RESERVED_SMS, 16)
+        assert _lib.get_option(_lib.OPT_RESERVED_SMS) == 16
+        _lib.set_option(_lib.OPT_GRID_WAVES, 2)
+        assert _lib.get_option(_lib.OPT_GRID_WAVES) == 2
+        assert lib.wsl_set_option(_lib.OPT_WAIT_LIMIT_MS, 0) == _lib.WSL_ERR_BAD_ARG
+        assert lib.wsl_set_option(_lib.OPT_RESERVED_SMS, 1000) == _lib.WSL_ERR_BAD_ARG
+        assert lib.wsl_set_option(_lib.OPT_GRID_WAVES, 9) == _lib.WSL_ERR_BAD_ARG
+        assert lib.wsl_set_option(99, 1) == _lib.WSL_ERR_BAD_ARG
+    finally:
+        _lib.set_option(_lib.OPT_WAIT_LIMIT_MS, old)
+        _lib.set_option(_lib.OPT_RESERVED_SMS, 0)
+        _lib.set_option(_lib.OPT_GRID_WAVES, 0)
