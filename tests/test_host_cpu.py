@@ -1,6 +1,7 @@
 """CPU tests: the C-ABI library loads and exports every symbol include/wsl.h declares (no
 compute without a GPU), host-side logic (modules' structure, converter, arena, cache), and
 the product's refusal to run without its CUDA library or on CPU tensors."""
+import json
 import os
 import re
 import types
@@ -392,3 +393,53 @@ def test_runtime_options_round_trip():
         _lib.set_option(_lib.OPT_WAIT_LIMIT_MS, old)
         _lib.set_option(_lib.OPT_RESERVED_SMS, 0)
         _lib.set_option(_lib.OPT_GRID_WAVES, 0)
+
+
+def test_checkpoint_round_trip_in_the_reference_folder_layout(tmp_path):
+    """step-N folders with model.safetensors (every shared base weight once, alias table), an index
+    whose weight_map lists every reference key, and the optimizer state of a TrainStep; the files
+    are plain safetensors (cross-read with the safetensors package when it is installed)."""
+    from weightshared_torchtitan_b200 import checkpoint as C
+    from weightshared_torchtitan_b200 import state_dict_adapter as SDA
+    from weightshared_torchtitan_b200.decoder import DecoderConfig, WeightSharedDecoder
+    from weightshared_torchtitan_b200.train_step import TrainStep
+    cfg = DecoderConfig(dim=32, hidden_dim=64, n_layers=4, n_unique=2, n_heads=2, n_kv_heads=1, head_dim=16, rank=8,
+                        vocab_size=64, embed_rank=16, max_seq_len=8)
+    torch.manual_seed(0)
+    m = WeightSharedDecoder(cfg)
+    st = TrainStep(m, lr=1e-3)                    # CPU: torch AdamW over the flat arena
+    st.arena.buffer.normal_()                     # stand-in gradients, then one optimizer step for non-trivial state
+    st.optimizer.step()
+    st.steps = 7
+    folder = str(tmp_path / "checkpoint")
+    assert C.latest_step(folder) == -1
+    out = C.save_checkpoint(folder, 7, m, st)
+    C.save_checkpoint(folder, 3, m)
+    assert C.latest_step(folder) == 7 and out.endswith("step-7")
+    index = json.load(open(os.path.join(out, "model.safetensors.index.json")))
+    full = SDA.to_reference(m)
+    assert sorted(index["weight_map"]) == sorted(full)
+    tensors, meta = C.read_safetensors(os.path.join(out, "model.safetensors"))
+    aliases = json.loads(meta["aliases"])
+    assert len(tensors) == len(list(m.parameters())) and len(tensors) + len(aliases) == len(full)
+    assert aliases["layers.2.attention.wq.base.weight"] == "layers.0.attention.wq.base.weight"
+    try:
+        from safetensors.torch import load_file
+        other = load_file(os.path.join(out, "model.safetensors"))
+        assert sorted(other) == sorted(tensors) and all(torch.equal(other[k], tensors[k]) for k in tensors)
+    except ImportError:
+        pass
+    torch.manual_seed(1)
+    m2 = WeightSharedDecoder(cfg)
+    st2 = TrainStep(m2, lr=5e-4)
+    assert C.load_checkpoint(folder, m2, st2) == 7
+    for (n1, p1), (n2, p2) in zip(m.named_parameters(), m2.named_parameters()):
+        assert n1 == n2 and torch.equal(p1, p2)
+    assert st2.steps == 7 and st2.lr == 1e-3
+    sd1, sd2 = st.state_dict(), st2.state_dict()
+    moments = [k for k in sd1 if k.startswith("exp_avg")]
+    assert len(moments) == 2 * len(list(m.parameters())) and sd1["exp_avg.output.weight"].abs().max() > 0
+    assert all(torch.equal(sd1[k], sd2[k]) for k in moments)
+    assert all(float(s["step"]) == 7.0 for s in st2.optimizer.state.values())
+    with pytest.raises(FileNotFoundError):
+        C.load_checkpoint(str(tmp_path / "nothing"), m2)

@@ -1,7 +1,8 @@
 """The converter on the reference's REAL Qwen3Model (meta device), when the reference checkout
 is present: parameter names and sharing must be exactly what state_dict_adapter maps to, the
-converter must sit in the trainer's own registry, and the ``shared_lora`` section must merge
-into the reference's JobConfig through its custom_args_module mechanism.
+converter and the ``qwen3_shared_lora`` TrainSpec must sit in the trainer's own registries, and
+the ``shared_lora`` section must merge into the reference's JobConfig through its
+custom_args_module mechanism.
 
 Runs in a child process (importing torchtitan takes seconds and must see the reference
 checkout, not another torchtitan that may be installed, first on sys.path). Skipped where the
@@ -25,6 +26,8 @@ from torchtitan.experiments.qwen3.model.model import Qwen3Model
 from torchtitan.protocols import model_converter as mc
 from torchtitan.config.manager import ConfigManager
 from weightshared_torchtitan_b200 import converter as C
+from weightshared_torchtitan_b200 import train_spec as TS
+from torchtitan.protocols.train_spec import get_train_spec
 from weightshared_torchtitan_b200 import state_dict_adapter as SDA
 from weightshared_torchtitan_b200.decoder import DecoderConfig, WeightSharedDecoder
 
@@ -58,6 +61,19 @@ L = model.layers
 out["shared_objects"] = all(L[str(l)].attention.wq.base is L[str(l % 2)].attention.wq.base and
                             L[str(l)].feed_forward.w2.base is L[str(l % 2)].feed_forward.w2.base for l in range(4))
 out["adapters_distinct"] = len({id(L[str(l)].attention.wq.offset) for l in range(4)}) == 4
+# the TrainSpec the trainer would pick with --model.name qwen3_shared_lora
+spec = get_train_spec(TS.SPEC_NAME)
+out["spec"] = [spec.name, spec.model_cls is Qwen3Model, sorted(spec.model_args)[:2], spec.parallelize_fn is TS.parallelize_shared_lora]
+class _PD:                                   # single process: nothing to wrap
+    dp_replicate_enabled = tp_enabled = cp_enabled = pp_enabled = dp_shard_enabled = ep_enabled = False
+out["parallelize_identity"] = spec.parallelize_fn(model, _PD(), cfg) is model
+class _TP(_PD):
+    tp_enabled = True
+try:
+    spec.parallelize_fn(model, _TP(), cfg)
+    out["refuses_tp"] = False
+except NotImplementedError:
+    out["refuses_tp"] = True
 print("RESULT " + json.dumps(out))
 """
 
@@ -77,3 +93,5 @@ def test_converter_on_the_reference_qwen3_model():
     assert out["same_shapes"]
     assert out["named_parameters_are_the_unique_ones"]
     assert out["shared_objects"] and out["adapters_distinct"]
+    assert out["spec"] == ["qwen3_shared_lora", True, ["0.6B", "1.7B"], True]
+    assert out["parallelize_identity"] and out["refuses_tp"]

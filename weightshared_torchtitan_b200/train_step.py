@@ -99,20 +99,45 @@ class TrainStep:
             raise _lib.WslError(st, f"device status words {words} (role, block, unit)")
 
     # ------------------------------------------------------------------ checkpoint state
-    def state_dict(self) -> Dict[str, object]:
-        """Optimizer state of the step: the step count (bias correction) and, per parameter
-        under its arena name, the two AdamW moments -- the content of torch.optim.AdamW's
-        state ('step', 'exp_avg', 'exp_avg_sq'), so a run resumes with warm moments as the
-        reference does through OptimizersContainer (torchtitan/components/optimizer.py) and
-        its checkpointer."""
-        out: Dict[str, object] = {"steps": self.steps, "lr": None if callable(self.lr) else float(self.lr)}
-        if self.fused_update:
+    def _torch_moments(self, p: torch.Tensor):
+        """(exp_avg, exp_avg_sq) of torch.optim.AdamW for parameter `p`, created as zeros when the
+        optimizer has not stepped yet."""
+        st = self.optimizer.state[p]
+        if "exp_avg" not in st:
+            fused = self.arena.buffer.is_cuda
+            st["step"] = (torch.zeros((), dtype=torch.float32, device=p.device) if fused
+                          else torch.tensor(0.0, dtype=torch.float32))
+            st["exp_avg"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+            st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+        return st["exp_avg"], st["exp_avg_sq"]
+
+    def _moment_views(self):
+        """name -> (exp_avg, exp_avg_sq) views per parameter, whatever the optimizer's layout."""
+        out = {}
+        if self.fused_update or self.flat:
+            if self.fused_update:
+                m, v = self.exp_avg, self.exp_avg_sq
+            else:
+                m, v = self._torch_moments(self._flat_param)
             for n, p, off in zip(self.arena.names, self.arena.params, self.arena.offsets):
                 k = p.numel()
-                out[f"exp_avg.{n}"] = self.exp_avg[off:off + k].view(p.shape)
-                out[f"exp_avg_sq.{n}"] = self.exp_avg_sq[off:off + k].view(p.shape)
+                out[n] = (m[off:off + k].view(p.shape), v[off:off + k].view(p.shape))
         else:
-            out["optimizer"] = self.optimizer.state_dict()
+            for n, p in zip(self.arena.names, self.arena.params):
+                out[n] = self._torch_moments(p)
+        return out
+
+    def state_dict(self) -> Dict[str, object]:
+        """Optimizer state of the step in one layout for all three optimizer paths: the step
+        count (bias correction), the learning rate when it is a constant and, per parameter
+        under its arena name, the two AdamW moments -- the content of torch.optim.AdamW's state
+        ('step', 'exp_avg', 'exp_avg_sq'), so a run resumes with warm moments as the reference
+        does through OptimizersContainer (torchtitan/components/optimizer.py) and its
+        checkpointer. The tensors are views of the live state."""
+        out: Dict[str, object] = {"steps": self.steps, "lr": None if callable(self.lr) else float(self.lr)}
+        for n, (m, v) in self._moment_views().items():
+            out[f"exp_avg.{n}"] = m
+            out[f"exp_avg_sq.{n}"] = v
         return out
 
     @torch.no_grad()
@@ -120,13 +145,13 @@ class TrainStep:
         self.steps = int(sd["steps"])
         if sd.get("lr") is not None and not callable(self.lr):
             self.lr = float(sd["lr"])
-        if self.fused_update:
-            for n, p, off in zip(self.arena.names, self.arena.params, self.arena.offsets):
-                k = p.numel()
-                self.exp_avg[off:off + k].view(p.shape).copy_(sd[f"exp_avg.{n}"])
-                self.exp_avg_sq[off:off + k].view(p.shape).copy_(sd[f"exp_avg_sq.{n}"])
-        else:
-            self.optimizer.load_state_dict(sd["optimizer"])
+        for n, (m, v) in self._moment_views().items():
+            m.copy_(sd[f"exp_avg.{n}"])
+            v.copy_(sd[f"exp_avg_sq.{n}"])
+        if self.optimizer is not None:
+            for st in self.optimizer.state.values():
+                if "step" in st:
+                    st["step"].fill_(float(self.steps))
 
     # ------------------------------------------------------------------------ the step
     def _bucket_launched(self, nbytes: int) -> None:
