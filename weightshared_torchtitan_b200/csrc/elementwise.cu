@@ -546,7 +546,7 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const void* res, void* h_ou
     const int s_kv = cs ? 2 : kvn;
     const int s_lpr = cs ? static_cast<int>(D / (2 * (is_f32 ? 4 : 8))) : lpr;
     const int cw = rn_fwd_compute_warps(s_kv);
-    const long long tile_rows = rn_tile_rows(cw, s_kv, 32 / s_lpr);
+    const long long tile_rows = static_cast<long long>(cw) * (32 / s_lpr) * rn_rows_per_group(s_kv);
     const long long n_tiles = (rows + tile_rows - 1) / tile_rows;
     const unsigned sgb = static_cast<unsigned>(n_tiles < device_sm_count() ? n_tiles : device_sm_count());
     const size_t ssmem = rn_fwd_staged_smem(d, fused);
@@ -649,7 +649,7 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
     const int s_lpr = cs ? static_cast<int>(D / (2 * (is_f32 ? 4 : 8))) : lpr;
     const int rpg = rn_rows_per_group(s_kv);
     const int cw = rn_compute_warps(s_kv, s_kv * (is_f32 ? 4 : 8), cs != nullptr);
-    const long long tile_rows = rn_tile_rows(cw, s_kv, 32 / s_lpr);
+    const long long tile_rows = static_cast<long long>(cw) * (32 / s_lpr) * rpg;
     const long long n_tiles = (rows + tile_rows - 1) / tile_rows;
     const unsigned sgb = static_cast<unsigned>(n_tiles < device_sm_count() ? n_tiles : device_sm_count());
     const size_t ssmem = rn_staged_smem(d, fused);

@@ -40,52 +40,15 @@ struct RnKnobs {
 // they run 7 compute warps (8 warps in all: 255 registers)
 // Rows wider than 8 vectors per lane (KV = 10, 16: hidden sizes 2560 and 4096 in bf16) take one
 // row per warp and tile, and as many compute warps as fit a 32 KB tile (512 KV bytes per row).
-// Such a row is SPLIT between two warps (rn_halves = 2): each holds half of its vectors in
-// registers and the two exchange their partial row sums through shared memory, so a 32 KB tile
-// of 4 (6) rows keeps 8 (12) compute warps busy instead of 4 (6) -- these loops are bound by
-// issue slots and shared-memory latency, not by bytes, and one warp per scheduler hides neither.
-__host__ __device__ constexpr int rn_halves(int kv) { return kv > 8 ? 2 : 1; }
 __host__ __device__ constexpr int rn_rows_per_group(int kv) { return kv <= 8 ? 8 / kv : 1; }
-__host__ __device__ constexpr int rn_fwd_compute_warps(int kv) { return kv <= 8 ? 8 : 2 * (64 / kv); }
+__host__ __device__ constexpr int rn_fwd_compute_warps(int kv) { return kv <= 8 ? 8 : 64 / kv; }
 __host__ __device__ constexpr int rn_compute_warps(int kv, int elems_per_lane, bool rope) {
-  return kv > 8 ? 2 * (64 / kv) : ((elems_per_lane >= 32 || rope) ? 7 : 8);
-}
-// rows of one tile
-__host__ __device__ constexpr int rn_tile_rows(int cw, int kv, int rpw) {
-  return cw / rn_halves(kv) * rpw * rn_rows_per_group(kv);
+  return kv > 8 ? 64 / kv : ((elems_per_lane >= 32 || rope) ? 7 : 8);
 }
 
-// Sum of the two partial row sums of a split row. Warps 2i and 2i + 1 share row i. Each warp
-// posts its partial in one of two slots (alternating, so a value is not overwritten before the
-// partner has read it: the partner can be at most one exchange ahead) and then its exchange
-// count; it reads the partner's slot once the partner's count has caught up. The wait is a
-// bounded spin that also leaves when the CTA's abort flag is up, so a warp whose partner left
-// after a wait ran out cannot hang (its result is then garbage that nothing stores: the status
-// word already says WSL_ERR_TIMEOUT).
-struct PairExchange {
-  volatile float* vals;   // [2 * warps]
-  volatile int* seqs;     // [warps]
-  int seq;
-};
-__device__ __forceinline__ float pair_sum(float v, PairExchange& px, int warp, int lane, volatile int* abortp) {
-  const int seq = ++px.seq;
-  if (lane == 0) {
-    px.vals[2 * warp + (seq & 1)] = v;
-    __threadfence_block();
-    px.seqs[warp] = seq;
-    int spins = 0;
-    while (px.seqs[warp ^ 1] < seq && *abortp == 0 && ++spins < (1 << 24)) {
-    }
-    __threadfence_block();
-  }
-  __syncwarp();
-  return v + px.vals[2 * (warp ^ 1) + (seq & 1)];
-}
-
-// shared memory: stages | barriers (full[S], empty[S]) | abort, drain words (16 B) | pair
-// exchange: 32 floats + 16 counters (up to 13 warps; 240 B) | w[D] | dw[D]
+// shared memory: stages | barriers (full[S], empty[S]) | abort, drain words | w[D] | dw[D]
 __host__ __device__ constexpr size_t rn_head_bytes(int stages, int nops) {
-  return static_cast<size_t>(stages) * nops * RN_TILE_BYTES + 2 * stages * sizeof(uint64_t) + 16 + 240;
+  return static_cast<size_t>(stages) * nops * RN_TILE_BYTES + 2 * stages * sizeof(uint64_t) + 16;
 }
 // backward: dy, x (+ the gradient of the residual stream); forward: x (+ the residual addend)
 __host__ __device__ constexpr size_t rn_staged_smem(int D, bool dres) {
@@ -203,11 +166,11 @@ __device__ __forceinline__ void rn_producer_loop(const unsigned char* src0, cons
 // Zero the rows [first_missing, RPG) of this lane group's slice of a tile (ragged last tile).
 template <typename T, int KV>
 __device__ __forceinline__ void zero_missing_rows(unsigned char* tile, int g, int rpg, int first_missing,
-                                                  size_t row_bytes, int lpr, int l, int kbase = 0) {
+                                                  size_t row_bytes, int lpr, int l) {
   constexpr int NV = Vec<T>::N;
   for (int r = first_missing; r < rpg; ++r)
 #pragma unroll
-    for (int k = kbase; k < kbase + KV; ++k)
+    for (int k = 0; k < KV; ++k)
       *reinterpret_cast<uint4*>(tile + static_cast<size_t>(g * rpg + r) * row_bytes +
                                 static_cast<size_t>(k * lpr + l) * NV * sizeof(T)) = make_uint4(0, 0, 0, 0);
 }
@@ -231,24 +194,20 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
   constexpr int CW = rn_fwd_compute_warps(KV);
   constexpr int THREADS = (CW + 1) * 32;
   constexpr int NOPS = RES ? 2 : 1;
-  // rows wider than 8 vectors per lane are split between two warps (rn_halves)
-  constexpr int H = rn_halves(KV);
-  constexpr int KH = KV / H;
-  // what a warp holds of a row must fit in registers, else it is read from shared memory twice
-  constexpr bool PACKED = KH * NV > 64;
-  constexpr int KF = PACKED ? 1 : KH;
+  // very wide rows do not fit in registers: they are read from shared memory twice
+  constexpr bool PACKED = KV * NV > 64;
+  constexpr int KF = PACKED ? 1 : KV;
   constexpr int S = rn_stages(NOPS);
   extern __shared__ __align__(128) unsigned char rn_smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(rn_smem + S * NOPS * RN_TILE_BYTES);
   volatile int* abortp = reinterpret_cast<volatile int*>(bars + 2 * S);
   volatile int* drainp = abortp + 1;   // stays 0: the flag of the tear-down waits
-  PairExchange px = {reinterpret_cast<volatile float*>(abortp + 4), abortp + 4 + 32, 0};
   float* w_s = reinterpret_cast<float*>(rn_smem + rn_head_bytes(S, NOPS));
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int rpw = 32 / lpr;
   const int l = lane % lpr;
-  const int tile_rows = rn_tile_rows(CW, KV, rpw);
+  const int tile_rows = CW * rpw * RPG;
   const uint32_t stage0 = smem_u32(rn_smem);
   const uint32_t bar0 = smem_u32(bars);
   if (threadIdx.x == 0) {
@@ -258,7 +217,6 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
     }
     *abortp = 0;
     *drainp = 0;
-    for (int i = 0; i < 16; ++i) abortp[4 + 32 + i] = 0;   // pair-exchange counters
     fence_barrier_init();
   }
   for (int j = threadIdx.x; j < D; j += THREADS) w_s[scale_slot<NV>(j, lpr)] = w[j];
@@ -272,8 +230,7 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
     return;
   }
   const float inv_D = 1.0f / static_cast<float>(D);
-  const int g = (warp / H) * rpw + lane / lpr;   // lane group (row slot) within the CTA
-  const int kbase = (warp % H) * KH;             // first vector of the row this warp holds
+  const int g = warp * rpw + lane / lpr;   // lane group within the CTA
   static_assert(!ROPE || KV == 2, "rotary rows are held as two half-row vectors per lane");
   constexpr int KR = ROPE ? KV : 1;
   float cr_n[KR][NV], sr_n[KR][NV];
@@ -320,8 +277,8 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
                            static_cast<long long>(g) * RPG;
     const int have = static_cast<int>(min(static_cast<long long>(RPG), max(rows - row0, 0ll)));
     if (have < RPG) {
-      zero_missing_rows<T, KH>(sx, g, RPG, have, row_bytes, lpr, l, kbase);
-      if (RES) zero_missing_rows<T, KH>(sx + RN_TILE_BYTES, g, RPG, have, row_bytes, lpr, l, kbase);
+      zero_missing_rows<T, KV>(sx, g, RPG, have, row_bytes, lpr, l);
+      if (RES) zero_missing_rows<T, KV>(sx + RN_TILE_BYTES, g, RPG, have, row_bytes, lpr, l);
     }
     const unsigned char* srow = sx + static_cast<size_t>(g * RPG) * row_bytes + static_cast<size_t>(l) * NV * sizeof(T);
     T* yrow = y + row0 * ldy + l * NV;
@@ -330,8 +287,7 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
     for (int r = 0; r < RPG; ++r) {
       float f_[KF][NV];
       // vector k of the row (x, or x + res rounded to the storage type) as floats
-      auto load_vec = [&](int kk, float (&f)[NV], bool store_h) {
-        const int k = kbase + kk;
+      auto load_vec = [&](int k, float (&f)[NV], bool store_h) {
         const Vec<T> v = ldv<T>(reinterpret_cast<const T*>(srow + r * row_bytes) + k * lpr * NV);
         unpack<T>(v, f);
         if (RES) {
@@ -346,7 +302,7 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
       };
       float ss = 0.f;
 #pragma unroll
-      for (int k = 0; k < KH; ++k) {
+      for (int k = 0; k < KV; ++k) {
         float (&f)[NV] = f_[PACKED ? 0 : k];
         load_vec(k, f, true);
 #pragma unroll
@@ -354,11 +310,10 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
       }
       if (PACKED) asm volatile("" ::: "memory");   // keep the second read a read, not 128 live registers
       ss = group_sum(ss, lpr);
-      if (H == 2) ss = pair_sum(ss, px, warp, lane, abortp);
       const float rstd = rsqrt_refined(fmaf(ss, inv_D, eps));
-      if (r < have && l == 0 && kbase == 0 && rstd_out) rstd_out[row0 + r] = rstd;
+      if (r < have && l == 0 && rstd_out) rstd_out[row0 + r] = rstd;
 #pragma unroll
-      for (int k = 0; k < KH; ++k) {
+      for (int k = 0; k < KV; ++k) {
         float o[NV];
         if (ROPE) {
 #pragma unroll
@@ -369,11 +324,11 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
           float (&f)[NV] = f_[PACKED ? 0 : k];
           if (PACKED) load_vec(k, f, false);
           float wk[NV];
-          load_scale<NV>(w_s, kbase + k, lpr, l, wk);
+          load_scale<NV>(w_s, k, lpr, l, wk);
 #pragma unroll
           for (int e = 0; e < NV; ++e) o[e] = f[e] * rstd * wk[e];
         }
-        if (r < have) stv<T>(yrow + r * ldy + (kbase + k) * lpr * NV, pack<T>(o));
+        if (r < have) stv<T>(yrow + r * ldy + k * lpr * NV, pack<T>(o));
       }
     }
     __syncwarp();
@@ -403,21 +358,18 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
   constexpr int THREADS = (CW + 1) * 32;
   constexpr int NOPS = DRES ? 3 : 2;
   constexpr int S = rn_stages(NOPS);
-  constexpr int H = rn_halves(KV);   // rows wider than 8 vectors per lane: two warps per row
-  constexpr int KH = KV / H;
   static_assert(!(ROPE && DRES), "the residual stream meets hidden-size norms only");
   extern __shared__ __align__(128) unsigned char rn_smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(rn_smem + S * NOPS * RN_TILE_BYTES);
   volatile int* abortp = reinterpret_cast<volatile int*>(bars + 2 * S);
   volatile int* drainp = abortp + 1;
-  PairExchange px = {reinterpret_cast<volatile float*>(abortp + 4), abortp + 4 + 32, 0};
   float* w_s = reinterpret_cast<float*>(rn_smem + rn_head_bytes(S, NOPS));
   float* dw_part = w_s + D;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int rpw = 32 / lpr;
   const int l = lane % lpr;
-  const int tile_rows = rn_tile_rows(CW, KV, rpw);
+  const int tile_rows = CW * rpw * RPG;
   const uint32_t stage0 = smem_u32(rn_smem);
   const uint32_t bar0 = smem_u32(bars);
   if (threadIdx.x == 0) {
@@ -427,7 +379,6 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
     }
     *abortp = 0;
     *drainp = 0;
-    for (int i = 0; i < 16; ++i) abortp[4 + 32 + i] = 0;   // pair-exchange counters
     fence_barrier_init();
   }
   for (int j = threadIdx.x; j < D; j += THREADS) {
@@ -445,11 +396,10 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
                               my_tiles, stage0, bar0, abortp, drainp, lane, knobs);
   } else {
     const float inv_D = 1.0f / static_cast<float>(D);
-    const int g = (warp / H) * rpw + lane / lpr;
-    const int kbase = (warp % H) * KH;   // first vector of the row this warp holds
-    float dwacc[KH][NV];
+    const int g = warp * rpw + lane / lpr;
+    float dwacc[KV][NV];
 #pragma unroll
-    for (int k = 0; k < KH; ++k)
+    for (int k = 0; k < KV; ++k)
 #pragma unroll
       for (int e = 0; e < NV; ++e) dwacc[k][e] = 0.f;
     static_assert(!ROPE || KV == 2, "rotary rows are held as two half-row vectors per lane");
@@ -508,9 +458,9 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
                              static_cast<long long>(g) * RPG;
       const int have = static_cast<int>(min(static_cast<long long>(RPG), max(rows - row0, 0ll)));
       if (have < RPG) {
-        zero_missing_rows<T, KH>(sdy, g, RPG, have, row_bytes, lpr, l, kbase);
-        zero_missing_rows<T, KH>(sx, g, RPG, have, row_bytes, lpr, l, kbase);
-        if (DRES) zero_missing_rows<T, KH>(sdr, g, RPG, have, row_bytes, lpr, l, kbase);
+        zero_missing_rows<T, KV>(sdy, g, RPG, have, row_bytes, lpr, l);
+        zero_missing_rows<T, KV>(sx, g, RPG, have, row_bytes, lpr, l);
+        if (DRES) zero_missing_rows<T, KV>(sdr, g, RPG, have, row_bytes, lpr, l);
       }
       const size_t goff = static_cast<size_t>(g * RPG) * row_bytes + static_cast<size_t>(l) * NV * sizeof(T);
       T* dxrow = dx + row0 * lddx + l * NV;
@@ -519,22 +469,22 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
         const float rstd = rs[r];
         // very wide rows do not fit in registers next to the dw accumulators: they read the
         // row from shared memory a second time for the outputs
-        constexpr bool PACKED = KH * NV > 32;
-        constexpr int KF = PACKED ? 1 : KH;
+        constexpr bool PACKED = KV * NV > 32;
+        constexpr int KF = PACKED ? 1 : KV;
         float dn_[KF][NV], xf_[KF][NV];
         float dot = 0.f;
 #pragma unroll
-        for (int k = 0; k < KH; ++k) {
+        for (int k = 0; k < KV; ++k) {
           float (&dn)[NV] = dn_[PACKED ? 0 : k];
           float (&xf)[NV] = xf_[PACKED ? 0 : k];
-          const size_t off = goff + r * row_bytes + static_cast<size_t>(kbase + k) * lpr * NV * sizeof(T);
+          const size_t off = goff + r * row_bytes + static_cast<size_t>(k) * lpr * NV * sizeof(T);
           const Vec<T> dv = ldv<T>(reinterpret_cast<const T*>(sdy + off));
           const Vec<T> xv = ldv<T>(reinterpret_cast<const T*>(sx + off));
           unpack<T>(dv, dn);
           unpack<T>(xv, xf);
           if (!ROPE) {
             float wk[NV];
-            load_scale<NV>(w_s, kbase + k, lpr, l, wk);
+            load_scale<NV>(w_s, k, lpr, l, wk);
 #pragma unroll
             for (int e = 0; e < NV; ++e) {
               const float p = dn[e] * xf[e];
@@ -561,32 +511,31 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
             }
         }
         dot = group_sum(dot, lpr);
-        if (H == 2) dot = pair_sum(dot, px, warp, lane, abortp);
         if (PACKED) asm volatile("" ::: "memory");   // keep the second read a read, not 128 live registers
         const float c3 = dot * inv_D * rstd * rstd * rstd;
 #pragma unroll
-        for (int k = 0; k < KH; ++k) {
+        for (int k = 0; k < KV; ++k) {
           float (&dn)[NV] = dn_[PACKED ? 0 : k];
           float (&xf)[NV] = xf_[PACKED ? 0 : k];
           if (PACKED) {
-            const size_t off = goff + r * row_bytes + static_cast<size_t>(kbase + k) * lpr * NV * sizeof(T);
+            const size_t off = goff + r * row_bytes + static_cast<size_t>(k) * lpr * NV * sizeof(T);
             unpack<T>(ldv<T>(reinterpret_cast<const T*>(sdy + off)), dn);
             unpack<T>(ldv<T>(reinterpret_cast<const T*>(sx + off)), xf);
           }
           float wk[NV];
-          if (!ROPE) load_scale<NV>(w_s, kbase + k, lpr, l, wk);
+          if (!ROPE) load_scale<NV>(w_s, k, lpr, l, wk);
           float o[NV];
 #pragma unroll
           for (int e = 0; e < NV; ++e)
             o[e] = fmaf(dn[e] * (ROPE ? w_own[ROPE ? k : 0][e] : wk[e]), rstd, -(xf[e] * c3));
           if (DRES) {
             float a[NV];
-            const size_t off = goff + r * row_bytes + static_cast<size_t>(kbase + k) * lpr * NV * sizeof(T);
+            const size_t off = goff + r * row_bytes + static_cast<size_t>(k) * lpr * NV * sizeof(T);
             unpack<T>(ldv<T>(reinterpret_cast<const T*>(sdr + off)), a);
 #pragma unroll
             for (int e = 0; e < NV; ++e) o[e] += a[e];
           }
-          if (r < have) stv<T>(dxrow + r * lddx + (kbase + k) * lpr * NV, pack<T>(o));
+          if (r < have) stv<T>(dxrow + r * lddx + k * lpr * NV, pack<T>(o));
         }
       }
       __syncwarp();
@@ -598,9 +547,9 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
     }
     if (dw != nullptr) {
 #pragma unroll
-      for (int k = 0; k < KH; ++k)
+      for (int k = 0; k < KV; ++k)
 #pragma unroll
-        for (int e = 0; e < NV; ++e) atomicAdd(&dw_part[((kbase + k) * lpr + l) * NV + e], dwacc[k][e]);
+        for (int e = 0; e < NV; ++e) atomicAdd(&dw_part[(k * lpr + l) * NV + e], dwacc[k][e]);
     }
   }
   __syncthreads();
