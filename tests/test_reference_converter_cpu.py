@@ -15,7 +15,8 @@ import sys
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REFERENCE = os.environ.get("WSL_REFERENCE_CHECKOUT", "/root/reference")
+# the reference checkout: WSL_REFERENCE_CHECKOUT, else a directory `reference` beside this repository
+REFERENCE = os.environ.get("WSL_REFERENCE_CHECKOUT", os.path.join(os.path.dirname(ROOT), "reference"))
 
 CHILD = r"""
 import json, sys
