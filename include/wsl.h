@@ -335,7 +335,10 @@ int wsl_embed_gather(const long long* tokens, const void* E_small, void* G, long
  * The factorized embedding in one kernel: the TMA producer of the tcgen05 GEMM fetches the
  * rows E_small[tokens[m]] with tile::gather4 straight into the swizzled operand tile, so the
  * gathered matrix is never written to memory. A token id outside [0, V) contributes a zero
- * row.
+ * row. Every 256-column tile of h gathers the rows again and a gather4 instruction moves 4 x 128
+ * bytes, so for wide outputs (d above ~1024) wsl_embed_gather followed by wsl_linear_fwd is
+ * faster (measured 107 against 288 us at 16384 tokens, r_e = 1024, d = 4096); the results are
+ * the same bits.
  * Replaces nn.Embedding (torchtitan/experiments/qwen3/model/model.py:350,441); the
  * factorization itself (E_small, P) is not in the reference.
  */
