@@ -90,6 +90,8 @@ int wsl_reset_status(void);
  *                   shorter-lived CTAs which the hardware deals to SMs as they free up (evens out
  *                   unequal tile times and SMs held by another kernel), 0 (default) = two waves for
  *                   launches with long tiles and at least four tiles per CTA, else one
+ *   SPLIT_TAIL      0 keeps weight-gradient launches from cutting the tiles of their last, partial round
+ *                   of work into split-K units (see wsl_lora_linear_bwd_dw); default 1
  *   MERGE_SIMT      1 runs wsl_lora_merge_weight on the CUDA cores instead of the tensor cores
  *   PROFILE_BITS    only honoured by builds compiled with -DWSL_PROFILE_SWITCHES
  * No counterpart in the reference (its knobs are Python config fields).
@@ -102,6 +104,7 @@ int wsl_reset_status(void);
 #define WSL_OPT_PROFILE_BITS 6
 #define WSL_OPT_MERGE_SIMT 7
 #define WSL_OPT_GRID_WAVES 8
+#define WSL_OPT_SPLIT_TAIL 9
 int wsl_set_option(int option, long long value);
 long long wsl_get_option(int option);
 
@@ -219,8 +222,10 @@ int wsl_lora_linear_bwd_dx_swiglu(const void* dY, long long lddy, const void* U,
  * When the [N,K] tile grid is too small to fill the GPU (short weight matrices, long
  * token count) the token contraction is split across CTAs, partial sums go to the
  * workspace and a second kernel adds them into dW/dA/dB in a fixed order, so results stay
- * bit-reproducible. wsl_bwd_dw_workspace_bytes() gives the size that allows the best
- * split; a smaller or absent workspace only costs speed. The workspace contents are
+ * bit-reproducible. When the grid is large but its last round of tiles is only partly
+ * full (every tile contracts over all M tokens, so an idle round is long), just the tiles
+ * of that round are split that way. wsl_bwd_dw_workspace_bytes() gives the size that allows
+ * the best split; a smaller or absent workspace only costs speed. The workspace contents are
  * garbage afterwards; calls that overlap on the GPU need separate workspaces.
  * Replaces the MmBackward weight gradients and AccumulateGrad of
  * torchtitan/models/llama3/model/model.py:191,392-394 (one dW per use, cast and

@@ -366,6 +366,55 @@ def test_split_contraction_for_small_weight_grads(wsl):
         assert rel(got, w) < 1e-4 and rel(unsplit, w) < 1e-4
 
 
+def test_split_tail_of_a_large_weight_gradient(wsl):
+    """Large tile grid whose last round is only partly full (242 tile pairs on 74 CTA pairs):
+    the launch cuts only the tiles of that round into split-K units. The workspace is then a
+    fraction of the output; results match the oracle, are bit-reproducible, agree with the
+    launch without a tail to fp32 rounding, and the grouped launch's bf16 copy G comes out of
+    the folded sums. Ragged N so that the tail holds a partial tile. Launches that carry the
+    narrow rank-r regions as well take no tail."""
+    from weightshared_torchtitan_b200 import _lib
+    lib = _lib.lib()
+    M, N, K, r = 8192, 5632 - 24, 2816, 16
+    ws = lib.wsl_bwd_dw_workspace_bytes(M, N, K, 0, 1, 0, 0)
+    assert 0 < ws < N * K * 4                                   # a tail, not a split of everything
+    assert lib.wsl_bwd_dw_workspace_bytes(M, N, K, r, 1, 1, 1) == 0
+    g = torch.Generator().manual_seed(77)
+    x = (torch.randn(M, K, generator=g) * 0.5).cuda().to(torch.bfloat16)
+    dY = (torch.randn(M, N, generator=g) * 0.5).cuda().to(torch.bfloat16)
+    want_dW = dY.float().T @ x.float()
+
+    def run():
+        dW = torch.ones(N, K, device="cuda")
+        wsl.lora_linear_bwd_dw(dY, None, x, None, dW, None, None)
+        return dW
+
+    a, b = run(), run()
+    assert torch.equal(a, b)
+    _lib.set_option(_lib.OPT_SPLIT_TAIL, 0)
+    try:
+        assert lib.wsl_bwd_dw_workspace_bytes(M, N, K, 0, 1, 0, 0) == 0
+        plain = run()
+    finally:
+        _lib.set_option(_lib.OPT_SPLIT_TAIL, 1)
+    assert rel(a, 1 + want_dW) < 1e-4 and rel(plain, 1 + want_dW) < 1e-4 and rel(a, plain) < 1e-5
+    assert not torch.equal(a, plain)                            # the tail did sum in another order
+    # grouped launch with the bf16 copy: two projections reading the same x
+    Ns = (3072, N - 3072)
+    ll = ctypes.c_longlong * 2
+    assert 0 < lib.wsl_bwd_dw_group_workspace_bytes(2, ll(*Ns), ll(0, 0), M, K) < N * K * 4
+    dYs = [dY[:, :Ns[0]].contiguous(), dY[:, Ns[0]:].contiguous()]
+    dWs = [torch.ones(n, K, device="cuda") for n in Ns]
+    Gs = wsl.bwd_dw_layer_group(dYs, x, dWs)
+    off = 0
+    for n, dWp, G in zip(Ns, dWs, Gs):
+        w = want_dW[off:off + n]
+        assert rel(dWp, 1 + w) < 1e-4
+        assert rel(G.float(), w) < TOL_BF16
+        assert torch.equal(G, (dWp - 1).to(torch.bfloat16)) or rel(G.float(), dWp - 1) < 4e-3
+        off += n
+
+
 def test_fused_embedding_gathers_exact_rows(wsl):
     """The TMA-gather GEMM (wsl_embed_fwd) with P = [I ; 0]: h[:, :r_e] must be E_small[tokens]
     bit for bit (indices exact), ragged token count, repeated ids, full vocabulary size."""

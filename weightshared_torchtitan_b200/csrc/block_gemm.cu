@@ -69,7 +69,14 @@ struct Region {
   int out_map;        // tensor map of the output for the TMA-store epilogue, or -1
   int group;          // rasterisation: M-tiles per group (their A rows stay L2-resident)
   int splits;         // split-K factor of this region (1 = none)
-  int unit_begin;     // first work unit of this region (units = tiles * splits)
+  int unit_begin;     // first work unit of this region (units = tile_count * splits)
+  // The tiles of the region's rasterisation this entry covers: all of them, except where a
+  // launch ends with a split TAIL -- then the parent entry stops short (tile_count < tiles)
+  // and a copy of it at the end of the launch covers the rest (tile_off > 0, splits > 1),
+  // its partials packed tile by tile into the workspace (see SplitPlan).
+  int tile_off;
+  int tile_count;
+  int tail;           // 1 for such a tail entry
   void* copy;         // bf16 copy of alpha * acc (RegionDesc::copy), or nullptr
   long long ld_copy;
   // kEpiSwiGLU regions (pair launches): the second CTA of a pair loads its half of the B tile
@@ -260,9 +267,9 @@ __device__ __forceinline__ TileInfo decode_tile_t(const GemmParams& p, int u) {
   while (r + 1 < p.nregion && u >= p.reg[r + 1].unit_begin) ++r;
   const Region& R = p.reg[r];
   const int ul = u - R.unit_begin;
-  const int tiles_r = R.m_tiles * R.n_tiles;
+  const int tiles_r = R.tile_count;
   const int split = ul / tiles_r;
-  const int lt = ul - split * tiles_r;
+  const int lt = ul - split * tiles_r + R.tile_off;
   const int G = R.group;
   const int per_group = G * R.n_tiles;
   const int g = lt / per_group;
@@ -599,8 +606,17 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
       if (R.splits > 1) {
         // partial sums go to this split's slice of the workspace; splitk_reduce_kernel folds
         // them into the real output in a fixed order afterwards
-        R.out = p.workspace + R.ws_off + static_cast<long long>(split) * R.rows * R.cols;
-        R.ld = R.transposed ? R.rows : R.cols;
+        if (R.tail) {
+          // packed: one dense [tile rows x BN_MAX] block per (split, tile) of the tail; the
+          // base is moved back by the tile's origin so that (row, col) indexing still works
+          const long long blk = static_cast<long long>(split) * R.tile_count + (u - R.unit_begin - split * R.tile_count);
+          R.out = p.workspace + R.ws_off + blk * (C::kTileM * BN_MAX) -
+                  (static_cast<long long>(ti.m0) * BN_MAX + ti.n0);
+          R.ld = BN_MAX;
+        } else {
+          R.out = p.workspace + R.ws_off + static_cast<long long>(split) * R.rows * R.cols;
+          R.ld = R.transposed ? R.rows : R.cols;
+        }
         R.mode = kEpiStoreF32;
         R.alpha = 1.f;
         R.out_map = -1;
@@ -942,6 +958,66 @@ splitk_reduce_kernel(const __grid_constant__ ReduceParams rp) {
   }
 }
 
+// Fold of a split tail (see SplitPlan): for tile j of the tail entry `tr`,
+//   out[tile j] (op)= alpha * (block(0, j) + ... + block(S-1, j)),
+// the blocks being the dense [tile rows x BN_MAX] partials the main kernel left in the
+// workspace. `parts` blocks of 256 threads share a tile by rows.
+template <bool PAIR>
+__global__ void __launch_bounds__(256)
+tail_reduce_kernel(const __grid_constant__ GemmParams p, int tr, int parts) {
+  constexpr int TM = Cfg<PAIR>::kTileM;
+  const Region& R = p.reg[tr];
+  const int j = static_cast<int>(blockIdx.x) / parts;
+  const int part = static_cast<int>(blockIdx.x) % parts;
+  const TileInfo ti = decode_tile_t<PAIR>(p, R.unit_begin + j);   // split 0 of tile j
+  const int rows_per = TM / parts;
+  const int c4n = R.bn / 4;
+  const long long blk = static_cast<long long>(TM) * BN_MAX;
+  const float* ws = p.workspace + R.ws_off;
+  for (int idx = threadIdx.x; idx < rows_per * c4n; idx += 256) {
+    const int lr = part * rows_per + idx / c4n;
+    const int lc = (idx % c4n) * 4;
+    const long long row = ti.m0 + lr;
+    const int col = ti.n0 + lc;
+    if (row >= R.rows || col >= R.cols) continue;
+    const float* src = ws + j * blk + static_cast<long long>(lr) * BN_MAX + lc;
+    float4 a = *reinterpret_cast<const float4*>(src);
+    for (int s = 1; s < R.splits; ++s) {
+      const float4 b = *reinterpret_cast<const float4*>(src + static_cast<long long>(s) * R.tile_count * blk);
+      a.x += b.x;
+      a.y += b.y;
+      a.z += b.z;
+      a.w += b.w;
+    }
+    a.x *= R.alpha;
+    a.y *= R.alpha;
+    a.z *= R.alpha;
+    a.w *= R.alpha;
+    if (R.copy != nullptr || R.mode == kEpiStoreBf16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(a.z, a.w);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      if (R.copy != nullptr)
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(R.copy) + row * R.ld_copy + col) = pk;
+      if (R.mode == kEpiStoreBf16)
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(R.out) + row * R.ld + col) = pk;
+    }
+    if (R.mode != kEpiStoreBf16) {
+      float4* dst = reinterpret_cast<float4*>(static_cast<float*>(R.out) + row * R.ld + col);
+      if (R.mode == kEpiAccumF32) {
+        const float4 o = *dst;
+        a.x += o.x;
+        a.y += o.y;
+        a.z += o.z;
+        a.w += o.w;
+      }
+      *dst = a;
+    }
+  }
+}
+
 // ============================================================== host side
 unsigned long long g_launch_count = 0;
 
@@ -996,6 +1072,7 @@ Options& options() {
     v.reserved_sms = 0;
     v.grid_waves = 0;
     v.merge_simt = 0;
+    v.split_tail = 1;
     v.profile_bits = 0;
     if ((e = getenv("WSL_DBG")) != nullptr) v.profile_bits = atoi(e);
     return v;
@@ -1221,16 +1298,6 @@ size_t plan_splits(int nregion, const long long* tiles, const double* weight, co
   return best_bytes;
 }
 
-// The launch uses CTA pairs (256-row tiles) when its first region is large enough.
-bool use_pair_tiles(long long mo0, long long no0);
-
-long long region_tiles(bool pair, long long mo, long long no) {
-  const long long tm = pair ? 2 * BM : BM;
-  return ((mo + tm - 1) / tm) * ((no + BN_MAX - 1) / BN_MAX);
-}
-int split_workers(bool pair, int num_sms) { return pair ? num_sms / 2 : num_sms; }
-int kblocks(long long k) { return static_cast<int>((k + BK - 1) / BK); }
-
 // How many times the co-resident CTA count a grid may have. One wave = the persistent form:
 // every CTA (pair) walks its share of the statically dealt work units. With long tiles (many
 // k-blocks) and several units per worker, TWO waves of half-as-long-lived CTAs let the
@@ -1243,6 +1310,225 @@ static int auto_grid_waves(int kb_total, long long units, long long cap) {
   if (opt >= 1) return opt;
   return (kb_total >= 56 && units >= 4 * cap) ? 2 : 1;
 }
+
+
+// Makespan, in k-block units, of a launch whose work units come in `nseg` runs of `count[i]`
+// units costing `cost[i]` each, dealt the way the kernel deals them: unit u belongs to CTA
+// (pair) u % n_cta, n_cta = min(units, workers x grid waves); when the grid holds more CTAs
+// than fit at once they start in index order, each as soon as an earlier one has finished.
+static double simulate_makespan(int nseg, const long long* count, const double* cost, int kb_total,
+                                int workers) {
+  long long units = 0;
+  for (int i = 0; i < nseg; ++i) units += count[i];
+  if (units <= 0 || workers <= 0) return 0.0;
+  const long long cap = static_cast<long long>(workers) * auto_grid_waves(kb_total, units, workers);
+  const int n_cta = static_cast<int>(units < cap ? units : cap);
+  constexpr int kMaxCta = 1024;
+  if (n_cta > kMaxCta) return 1e30;
+  double load[kMaxCta];
+  for (int c = 0; c < n_cta; ++c) load[c] = 0.0;
+  long long u = 0;
+  for (int i = 0; i < nseg; ++i) {
+    // whole rounds of the run cost every CTA the same; only the ragged ends go one by one
+    long long left = count[i];
+    while (left > 0 && (u % n_cta) != 0) { load[u % n_cta] += cost[i]; ++u; --left; }
+    const long long rounds = left / n_cta;
+    if (rounds > 0) {
+      for (int c = 0; c < n_cta; ++c) load[c] += cost[i] * static_cast<double>(rounds);
+      u += rounds * n_cta;
+      left -= rounds * n_cta;
+    }
+    while (left > 0) { load[u % n_cta] += cost[i]; ++u; --left; }
+  }
+  double mk = 0.0;
+  if (n_cta <= workers) {
+    for (int c = 0; c < n_cta; ++c) mk = load[c] > mk ? load[c] : mk;
+    return mk;
+  }
+  // min-heap of the times at which the `workers` places become free
+  double slot[kMaxCta];
+  for (int w = 0; w < workers; ++w) slot[w] = 0.0;
+  for (int c = 0; c < n_cta; ++c) {
+    const double t = slot[0] + load[c];
+    mk = t > mk ? t : mk;
+    int i = 0;
+    for (;;) {   // replace the root by t and sift it down
+      const int l = 2 * i + 1, r = l + 1;
+      int m = i;
+      double mv = t;
+      if (l < workers && slot[l] < mv) { m = l; mv = slot[l]; }
+      if (r < workers && slot[r] < mv) { m = r; mv = slot[r]; }
+      if (m == i) break;
+      slot[i] = slot[m];
+      i = m;
+    }
+    slot[i] = t;
+  }
+  return mk;
+}
+
+// What launch_block_gemm does with the contraction of a launch that was given a workspace.
+// Either nothing, or every region is split (`splits`, the plan of plan_splits: launches with
+// few tiles), or a TAIL: the last `tail_tiles` tiles (in rasterisation order) of region
+// `tail_parent` leave their place in the launch order and run at its very end, each split
+// `tail_splits` ways. A launch of many long tiles (a weight gradient contracts over every
+// token) otherwise ends with a partial round in which most CTAs idle for a whole tile time:
+// 384 tile pairs on 74 CTA pairs take 6 rounds for 5.2 rounds of work. With the tail's tiles
+// cut into short units the last round is short too. Only the tail goes through the
+// workspace (one dense [tile rows x 256] fp32 block per split and tile); everything else keeps
+// its in-place epilogue, and the fixed-order fold keeps results bit-reproducible.
+constexpr double kTailParentWeight = 0.75;   // only (nearly) full-width tiles are worth a tail
+struct SplitPlan {
+  int splits[kMaxRegion];   // per region of the launch (uniform plan), all 1 with a tail
+  int tail_parent;          // -1: no tail
+  int tail_tiles;
+  int tail_splits;
+  size_t bytes;             // workspace the plan needs
+};
+
+struct PlanKey {
+  long long mo[kMaxRegion], no[kMaxRegion];
+  size_t ws_limit;
+  int nregion, kb_total, workers, pair, allow_tail, waves_opt, tail_opt;
+};
+struct PlanSlot {
+  bool used;
+  PlanKey key;
+  SplitPlan plan;
+};
+constexpr int kPlanSlots = 256;
+static PlanSlot g_plans[kPlanSlots] = {};
+static std::mutex g_plan_mutex;
+
+static SplitPlan plan_launch_uncached(int nregion, const long long* mo, const long long* no, int kb_total,
+                                      size_t ws_limit, int workers, bool pair, bool allow_tail) {
+  SplitPlan out;
+  for (int i = 0; i < kMaxRegion; ++i) out.splits[i] = 1;
+  out.tail_parent = -1;
+  out.tail_tiles = 0;
+  out.tail_splits = 1;
+  out.bytes = 0;
+  if (nregion < 1 || nregion > kMaxRegion || workers <= 0) return out;
+  long long tiles[kMaxRegion], elems[kMaxRegion];
+  double weight[kMaxRegion];
+  const long long th = pair ? 2 * BM : BM;
+  for (int i = 0; i < nregion; ++i) {
+    tiles[i] = ((mo[i] + th - 1) / th) * ((no[i] + BN_MAX - 1) / BN_MAX);
+    weight[i] = tile_weight(no[i]);
+    elems[i] = mo[i] * no[i];
+  }
+  out.bytes = plan_splits(nregion, tiles, weight, elems, kb_total, ws_limit, workers, out.splits);
+  if (!allow_tail || !options().split_tail || nregion + 1 > kMaxRegion || kb_total < 64) return out;
+  // time of the plan so far, by the same clock as the candidates below
+  long long cnt[kMaxRegion + 1];
+  double cst[kMaxRegion + 1];
+  for (int i = 0; i < nregion; ++i) {
+    cnt[i] = tiles[i] * out.splits[i];
+    cst[i] = static_cast<double>((kb_total + out.splits[i] - 1) / out.splits[i]) * weight[i] + 6.0;
+  }
+  double best = simulate_makespan(nregion, cnt, cst, kb_total, workers) * 0.27;
+  if (out.bytes > 0) best += 2.0 * static_cast<double>(out.bytes) / 6.5e6 + 4.0;
+  // The tail comes off the region with the most tiles. Launches that also carry narrow
+  // regions (the rank-r products dB, dA beside dW) are left alone: their cheap units already
+  // fill most of the last round, and a tail measured between +9 % and -4 % on them.
+  int parent = -1;
+  for (int i = 0; i < nregion; ++i) {
+    if (weight[i] < kTailParentWeight) return out;
+    if (tiles[i] >= 2 && (parent < 0 || tiles[i] >= tiles[parent])) parent = i;
+  }
+  if (parent < 0) return out;
+  long long t_max = workers + workers / 4;   // a round of tiles and a little more
+  if (t_max > tiles[parent] - 1) t_max = tiles[parent] - 1;
+  static const int kTailSplits[] = {2, 3, 4, 5, 6, 8};
+  const int s_cap = kb_total / 8 < 8 ? kb_total / 8 : 8;
+  const size_t block_bytes = static_cast<size_t>(th) * BN_MAX * 4;
+  double best_tail = 1e30;
+  long long best_t = 0;
+  int best_s = 1;
+  for (long long t = 1; t <= t_max; ++t) {
+    for (int si = 0; si < 6 && kTailSplits[si] <= s_cap; ++si) {
+      const int S = kTailSplits[si];
+      const size_t bytes = static_cast<size_t>(S) * t * block_bytes;
+      if (bytes > ws_limit) break;
+      for (int i = 0; i < nregion; ++i) {
+        cnt[i] = i == parent ? tiles[i] - t : tiles[i];
+        cst[i] = static_cast<double>(kb_total) * weight[i] + 6.0;
+      }
+      cnt[nregion] = t * S;
+      cst[nregion] = static_cast<double>((kb_total + S - 1) / S) * weight[parent] + 6.0;
+      const double tm = simulate_makespan(nregion + 1, cnt, cst, kb_total, workers) * 0.27 +
+                        2.0 * static_cast<double>(bytes) / 6.5e6 + 4.0;
+      if (tm < best_tail) {
+        best_tail = tm;
+        best_t = t;
+        best_s = S;
+      }
+    }
+  }
+  // (measured gains are about half of what this model predicts: idle SMs in a partial round
+  // are not a pure loss on a power-capped part, the busy ones clock higher meanwhile)
+  if (best_tail < 0.95 * best) {
+    for (int i = 0; i < kMaxRegion; ++i) out.splits[i] = 1;
+    out.tail_parent = parent;
+    out.tail_tiles = static_cast<int>(best_t);
+    out.tail_splits = best_s;
+    out.bytes = static_cast<size_t>(best_s) * best_t * block_bytes;
+  }
+  return out;
+}
+
+// Plans repeat launch after launch (the same few shapes every layer, every step): a small
+// table keyed by everything the plan depends on saves the search.
+SplitPlan plan_launch(int nregion, const long long* mo, const long long* no, int kb_total, size_t ws_limit,
+                      int workers, bool pair, bool allow_tail) {
+  PlanKey key;
+  std::memset(&key, 0, sizeof(key));
+  for (int i = 0; i < nregion && i < kMaxRegion; ++i) {
+    key.mo[i] = mo[i];
+    key.no[i] = no[i];
+  }
+  key.ws_limit = ws_limit;
+  key.nregion = nregion;
+  key.kb_total = kb_total;
+  key.workers = workers;
+  key.pair = pair ? 1 : 0;
+  key.allow_tail = allow_tail ? 1 : 0;
+  key.waves_opt = options().grid_waves;
+  key.tail_opt = options().split_tail;
+  unsigned long long h = 1469598103934665603ull;
+  const unsigned char* kb = reinterpret_cast<const unsigned char*>(&key);
+  for (size_t i = 0; i < sizeof(key); ++i) h = (h ^ kb[i]) * 1099511628211ull;
+  // open addressing over a few neighbouring slots; a full neighbourhood overwrites its first
+  constexpr int kProbe = 8;
+  const unsigned home = static_cast<unsigned>(h % kPlanSlots);
+  {
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    for (int i = 0; i < kProbe; ++i) {
+      const PlanSlot& sl = g_plans[(home + i) % kPlanSlots];
+      if (sl.used && std::memcmp(&sl.key, &key, sizeof(key)) == 0) return sl.plan;
+    }
+  }
+  const SplitPlan plan = plan_launch_uncached(nregion, mo, no, kb_total, ws_limit, workers, pair, allow_tail);
+  std::lock_guard<std::mutex> lock(g_plan_mutex);
+  int put = 0;
+  for (int i = 0; i < kProbe; ++i)
+    if (!g_plans[(home + i) % kPlanSlots].used) { put = i; break; }
+  PlanSlot& slot = g_plans[(home + put) % kPlanSlots];
+  slot.used = true;
+  slot.key = key;
+  slot.plan = plan;
+  return plan;
+}
+
+// The launch uses CTA pairs (256-row tiles) when its first region is large enough.
+bool use_pair_tiles(long long mo0, long long no0);
+
+long long region_tiles(bool pair, long long mo, long long no) {
+  const long long tm = pair ? 2 * BM : BM;
+  return ((mo + tm - 1) / tm) * ((no + BN_MAX - 1) / BN_MAX);
+}
+int split_workers(bool pair, int num_sms) { return pair ? num_sms / 2 : num_sms; }
+int kblocks(long long k) { return static_cast<int>((k + BK - 1) / BK); }
 
 template <bool A_MN, bool B_MN, bool PAIR>
 static int launch_variant(const GemmParams& p, long long units, cudaStream_t stream) {
@@ -1337,6 +1623,24 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   const bool pair = !deep_epilogue && use_pair_tiles(g.region[0].mo, g.region[0].no);
   const int bm_tile = pair ? 2 * BM : BM;
   const int bn_round = pair ? 32 : 16;
+  // Split plan of a launch that brought a workspace.
+  SplitPlan plan;
+  for (int r = 0; r < kMaxRegion; ++r) plan.splits[r] = 1;
+  plan.tail_parent = -1;
+  plan.tail_tiles = 0;
+  plan.tail_splits = 1;
+  plan.bytes = 0;
+  if (g.workspace != nullptr) {
+    long long pmo[kMaxRegion], pno[kMaxRegion];
+    bool plain = g.gather_tokens == nullptr;   // a tail needs ordinary regions
+    for (int r = 0; r < g.nregion; ++r) {
+      const RegionDesc& rd = g.region[r];
+      pmo[r] = rd.mo;
+      pno[r] = rd.no;
+      plain = plain && rd.addend == nullptr && !rd.transposed && rd.mode >= kEpiStoreBf16 && rd.mode <= kEpiAccumF32;
+    }
+    plan = plan_launch(g.nregion, pmo, pno, kb_all, g.workspace_bytes, split_workers(pair, g_num_sms), pair, plain);
+  }
   int nmaps = 0;
   long long tiles = 0;
   for (int r = 0; r < g.nregion; ++r) {
@@ -1482,34 +1786,46 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       p.epi_slots = (Cfg<false>::kStages - 2) * Cfg<false>::kStageBytes / EPI_STAGE_BYTES + 2;   // 8
     }
   }
-  p.workspace = nullptr;
-  int plan[kMaxRegion];
-  for (int r = 0; r < kMaxRegion; ++r) plan[r] = 1;
-  if (g.workspace != nullptr) {
-    long long rt[kMaxRegion], re[kMaxRegion];
-    double rw[kMaxRegion];
-    for (int r = 0; r < g.nregion; ++r) {
-      rt[r] = static_cast<long long>(p.reg[r].m_tiles) * p.reg[r].n_tiles;
-      rw[r] = tile_weight(g.region[r].no);
-      re[r] = g.region[r].mo * g.region[r].no;
-    }
-    if (plan_splits(g.nregion, rt, rw, re, kb_total, g.workspace_bytes, split_workers(pair, g_num_sms),
-                    plan) > 0)
-      p.workspace = g.workspace;
-  }
+  p.workspace = plan.bytes > 0 ? g.workspace : nullptr;
   bool any_split = false;
+  int tail_region = -1;
   {
+    // regions that are split keep their partials in the workspace one after the other;
+    // the others write their outputs themselves
     long long off = 0, ub = 0;
     for (int r = 0; r < g.nregion; ++r) {
       Region& R = p.reg[r];
-      R.splits = plan[r];
+      R.splits = plan.splits[r];
       R.unit_begin = static_cast<int>(ub);
       R.ws_off = off;
-      any_split = any_split || plan[r] > 1;
-      off += static_cast<long long>(plan[r]) * g.region[r].mo * g.region[r].no;
-      ub += static_cast<long long>(R.m_tiles) * R.n_tiles * plan[r];
+      R.tile_off = 0;
+      R.tile_count = R.m_tiles * R.n_tiles;
+      R.tail = 0;
+      if (r == plan.tail_parent) R.tile_count -= plan.tail_tiles;
+      any_split = any_split || R.splits > 1;
+      if (R.splits > 1) off += static_cast<long long>(R.splits) * g.region[r].mo * g.region[r].no;
+      ub += static_cast<long long>(R.tile_count) * R.splits;
+    }
+    if (plan.tail_parent >= 0) {
+      // the tail: a second entry for the parent region, last in the launch order
+      if (g.nregion + 1 > kMaxRegion || any_split || plan.tail_tiles < 1 ||
+          plan.tail_tiles >= p.reg[plan.tail_parent].m_tiles * p.reg[plan.tail_parent].n_tiles)
+        return WSL_ERR_BAD_ARG;
+      tail_region = g.nregion;
+      Region& T = p.reg[tail_region];
+      T = p.reg[plan.tail_parent];
+      T.tile_off = p.reg[plan.tail_parent].tile_count;
+      T.tile_count = plan.tail_tiles;
+      T.tail = 1;
+      T.splits = plan.tail_splits;
+      T.unit_begin = static_cast<int>(ub);
+      T.ws_off = 0;
+      off = static_cast<long long>(T.splits) * T.tile_count * bm_tile * BN_MAX;
+      ub += static_cast<long long>(T.tile_count) * T.splits;
+      p.nregion = g.nregion + 1;
     }
     if (ub > 0x7fffffffLL) return WSL_ERR_TOO_LARGE;
+    if (off > 0 && static_cast<size_t>(off) * 4 > g.workspace_bytes) return WSL_ERR_BAD_ARG;
     p.total_units = static_cast<int>(ub);
   }
   p.gather_tokens = g.gather_tokens;
@@ -1523,10 +1839,12 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
 #ifndef WSL_PROFILE_SWITCHES
   p.dbg = 0;
 #endif
-  if (!any_split && !(p.dbg & 32)) {
+  if (!(p.dbg & 32)) {
     // staged TMA-store epilogue where the tile width is a whole number of 128-byte chunks
+    // (split regions write fp32 partials to the workspace with plain stores instead)
     for (int r = 0; r < g.nregion; ++r) {
       const RegionDesc& rd = g.region[r];
+      if (p.reg[r].splits > 1) continue;
       if (rd.mode == kEpiSwiGLU || rd.mode == kEpiSwiGLUBwd) continue;   // their maps are made below
       const bool f32 = rd.mode != kEpiStoreBf16;
       if (rd.transposed || (p.reg[r].bn % (f32 ? 32 : 64)) != 0) continue;
@@ -1575,16 +1893,27 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   else if (!g.a_mn && !g.b_mn) st = WSL_LAUNCH(false, false);
   else st = WSL_LAUNCH(true, false);
 #undef WSL_LAUNCH
-  if (st != WSL_OK || !any_split) return st;
+  if (st != WSL_OK) return st;
+  if (tail_region >= 0) {
+    constexpr int kParts = 4;   // blocks per tail tile
+    const unsigned blocks = static_cast<unsigned>(p.reg[tail_region].tile_count) * kParts;
+    if (pair) tail_reduce_kernel<true><<<blocks, 256, 0, stream>>>(p, tail_region, kParts);
+    else tail_reduce_kernel<false><<<blocks, 256, 0, stream>>>(p, tail_region, kParts);
+    if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
+    ++g_launch_count;
+    return WSL_OK;
+  }
+  if (!any_split) return st;
   ReduceParams rp;
-  rp.nregion = g.nregion;
+  rp.nregion = 0;
   long long total = 0;
   for (int r = 0; r < g.nregion; ++r) {
+    if (p.reg[r].splits < 2) continue;
     const RegionDesc& rd = g.region[r];
     // output orientation: a transposed region's result matrix is [no, mo]
     const long long orows = rd.transposed ? rd.no : rd.mo;
     const long long ocols = rd.transposed ? rd.mo : rd.no;
-    ReduceRegion& R = rp.reg[r];
+    ReduceRegion& R = rp.reg[rp.nregion++];
     R.ws = reinterpret_cast<const float4*>(p.workspace + p.reg[r].ws_off);
     R.out = rd.out;
     R.ld = rd.ld_out;

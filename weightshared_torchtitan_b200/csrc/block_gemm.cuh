@@ -10,7 +10,7 @@ namespace wsl {
 
 constexpr int kMaxMaps = 32;    // tensor maps carried in the kernel parameters
 constexpr int kMaxSeg = 6;      // contraction segments (K-concatenation)
-constexpr int kMaxRegion = 9;   // output regions sharing one launch (3 projections x dW, dB, dA)
+constexpr int kMaxRegion = 10;  // output regions sharing one launch (3 projections x dW, dB, dA, + a split tail)
 
 enum EpilogueMode : int {
   kEpiStoreBf16 = 0,   // out(bf16)  = alpha * acc

@@ -146,6 +146,7 @@ int wsl_set_option(int option, long long value) {
       if (value < 0 || value > 8) return WSL_ERR_BAD_ARG;
       o.grid_waves = static_cast<int>(value);
       return WSL_OK;
+    case WSL_OPT_SPLIT_TAIL: o.split_tail = value != 0; return WSL_OK;
     default: return WSL_ERR_BAD_ARG;
   }
 }
@@ -161,6 +162,7 @@ long long wsl_get_option(int option) {
     case WSL_OPT_PROFILE_BITS: return o.profile_bits;
     case WSL_OPT_MERGE_SIMT: return o.merge_simt;
     case WSL_OPT_GRID_WAVES: return o.grid_waves;
+    case WSL_OPT_SPLIT_TAIL: return o.split_tail;
     default: return WSL_ERR_BAD_ARG;
   }
 }
@@ -625,36 +627,32 @@ int wsl_lora_merge_weight(int nproj, const void* const* W, const void* const* A,
 unsigned long long wsl_bwd_dw_group_workspace_bytes(int nproj, const long long* N, const long long* r,
                                                     long long M, long long K) {
   if (nproj < 1 || nproj > WSL_MAX_PROJ || !N || !r || M <= 0 || K <= 0) return 0;
-  long long rt[kMaxRegion], re[kMaxRegion];
-  double rw[kMaxRegion];
+  // same region order and tiling rule as the launch itself
+  long long mo[kMaxRegion], no[kMaxRegion];
   int nr = 0;
   const bool pair = use_pair_tiles(N[0], K);
-  for (int p = 0; p < nproj; ++p) { rt[nr] = region_tiles(pair, N[p], K); rw[nr] = tile_weight(K); re[nr++] = N[p] * K; }
+  for (int p = 0; p < nproj; ++p) { mo[nr] = N[p]; no[nr++] = K; }
   for (int p = 0; p < nproj; ++p)
-    if (r[p] > 0) { rt[nr] = region_tiles(pair, N[p], r[p]); rw[nr] = tile_weight(r[p]); re[nr++] = N[p] * r[p]; }
+    if (r[p] > 0) { mo[nr] = N[p]; no[nr++] = r[p]; }
   for (int p = 0; p < nproj; ++p)
-    if (r[p] > 0) { rt[nr] = region_tiles(pair, K, r[p]); rw[nr] = tile_weight(r[p]); re[nr++] = r[p] * K; }
+    if (r[p] > 0) { mo[nr] = K; no[nr++] = r[p]; }
   const int sms = device_check() == WSL_OK ? device_sm_count() : 148;
-  int plan[kMaxRegion];
-  return plan_splits(nr, rt, rw, re, kblocks(M), ~static_cast<size_t>(0), split_workers(pair, sms), plan);
+  return plan_launch(nr, mo, no, kblocks(M), ~static_cast<size_t>(0), split_workers(pair, sms), pair, true).bytes;
 }
 
 unsigned long long wsl_bwd_dw_workspace_bytes(long long M, long long N, long long K, long long r,
                                               int want_dW, int want_dA, int want_dB) {
   if (M <= 0 || N <= 0 || K <= 0 || r < 0) return 0;
-  long long rt[3], re[3];
-  double rw[3];
+  long long mo[3], no[3];
   int nr = 0;
-  // same region order and tiling rule as the launch itself
   const bool pair = want_dW ? use_pair_tiles(N, K)
                             : (want_dB && r > 0 ? use_pair_tiles(N, r) : use_pair_tiles(K, r));
-  if (want_dW) { rt[nr] = region_tiles(pair, N, K); rw[nr] = tile_weight(K); re[nr++] = N * K; }
-  if (want_dB && r > 0) { rt[nr] = region_tiles(pair, N, r); rw[nr] = tile_weight(r); re[nr++] = N * r; }
-  if (want_dA && r > 0) { rt[nr] = region_tiles(pair, K, r); rw[nr] = tile_weight(r); re[nr++] = r * K; }
+  if (want_dW) { mo[nr] = N; no[nr++] = K; }
+  if (want_dB && r > 0) { mo[nr] = N; no[nr++] = r; }
+  if (want_dA && r > 0) { mo[nr] = K; no[nr++] = r; }
   if (nr == 0) return 0;
   const int sms = device_check() == WSL_OK ? device_sm_count() : 148;
-  int plan[3];
-  return plan_splits(nr, rt, rw, re, kblocks(M), ~static_cast<size_t>(0), split_workers(pair, sms), plan);
+  return plan_launch(nr, mo, no, kblocks(M), ~static_cast<size_t>(0), split_workers(pair, sms), pair, true).bytes;
 }
 
 int wsl_embed_gather(const long long* tokens, const void* E_small, void* G, long long M,

@@ -36,6 +36,7 @@ struct Options {
   int grid_waves;                      // GEMM grids up to this many times the co-resident CTAs (0 = by launch)
   int profile_bits;                    // only honoured in builds with WSL_PROFILE_SWITCHES
   int merge_simt;                      // 1: W + s B A on the CUDA cores instead of the block GEMM
+  int split_tail;                      // 1: launches of long tiles may end with a split tail (see SplitPlan)
 };
 Options& options();
 }  // namespace wsl

@@ -52,13 +52,13 @@ ROUTE_TABLE = {
     # configuration 2 (1.7B shape, 32768 tokens, r 32)
     (32768, 2048, (2048, 1024, 1024), 32): True,     # 1.41 -> 1.27
     (32768, 2048, (2048,), 32): True,                # 0.77 -> 0.74
-    (32768, 2048, (6144, 6144), 32): False,          # 3.95 = 3.95
+    (32768, 2048, (6144, 6144), 32): True,           # 4.12 -> 3.80
     (32768, 6144, (2048,), 32): True,                # 1.96 -> 1.88
     # configuration 3 (4B shape, 32768 tokens, r 64)
-    (32768, 2560, (4096, 1024, 1024), 64): False,    # 2.43 = 2.44
-    (32768, 4096, (2560,), 64): False,               # 1.77 = 1.77
+    (32768, 2560, (4096, 1024, 1024), 64): True,     # 2.56 -> 2.45
+    (32768, 4096, (2560,), 64): True,                # 1.91 -> 1.80
     (32768, 2560, (9728, 9728), 64): True,           # 8.36 -> 8.15
-    (32768, 9728, (2560,), 64): False,               # 4.00 <- 4.07
+    (32768, 9728, (2560,), 64): True,                # 3.96 -> 3.91
     # configuration 4 (8B shape, 16384 tokens, r 64)
     (16384, 4096, (4096, 1024, 1024), 64): True,     # 2.27 -> 2.23
     (16384, 4096, (4096,), 64): False,               # 1.27 <- 1.36
