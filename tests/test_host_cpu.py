@@ -395,6 +395,32 @@ def test_runtime_options_round_trip():
         _lib.set_option(_lib.OPT_GRID_WAVES, 0)
 
 
+def test_split_plan_of_weight_gradient_launches():
+    """The workspace a weight-gradient launch asks for tells its split plan (host code, no device):
+    nothing for a grid that fills its rounds, the whole output times S for a small grid, and a few
+    tile blocks (S x T x 256 KiB) for a large grid with a partly filled last round; launches that
+    carry the narrow rank-r regions, and contractions too short to pay, take no tail."""
+    from weightshared_torchtitan_b200 import _lib
+    lib = _lib.lib()
+    blk = 256 * 256 * 4
+    assert _lib.get_option(_lib.OPT_SPLIT_TAIL) == 1
+    # configuration 4: q|k|v 384 tile pairs = 5.19 rounds -> a tail; gate|up 1536 = 20.76 rounds -> none
+    ws = lib.wsl_bwd_dw_workspace_bytes(16384, 6144, 4096, 0, 1, 0, 0)
+    assert 0 < ws < 6144 * 4096 * 4 // 4 and ws % blk == 0
+    assert lib.wsl_bwd_dw_workspace_bytes(16384, 24576, 4096, 0, 1, 0, 0) == 0
+    assert lib.wsl_bwd_dw_workspace_bytes(16384, 6144, 4096, 64, 1, 1, 1) == 0       # with dB, dA regions
+    assert lib.wsl_bwd_dw_workspace_bytes(2048, 6144, 4096, 0, 1, 0, 0) == 0         # 32 k-blocks per tile
+    # a small grid splits every tile: S x the whole output
+    small = lib.wsl_bwd_dw_workspace_bytes(32768, 256, 512, 0, 1, 0, 0)
+    assert small >= 2 * 256 * 512 * 4 and small % (256 * 512 * 4) == 0
+    _lib.set_option(_lib.OPT_SPLIT_TAIL, 0)
+    try:
+        assert lib.wsl_bwd_dw_workspace_bytes(16384, 6144, 4096, 0, 1, 0, 0) == 0
+        assert lib.wsl_bwd_dw_workspace_bytes(32768, 256, 512, 0, 1, 0, 0) == small
+    finally:
+        _lib.set_option(_lib.OPT_SPLIT_TAIL, 1)
+
+
 def test_checkpoint_round_trip_in_the_reference_folder_layout(tmp_path):
     """step-N folders with model.safetensors (every shared base weight once, alias table), an index
     whose weight_map lists every reference key, and the optimizer state of a TrainStep; the files
