@@ -74,7 +74,7 @@ int wsl_reset_status(void);
 /*
  * Run-time options of the library (process-wide). Initial values come from the environment,
  * read once when the library is first used: WSL_PAIR (PAIR_TILES), WSL_ROW_STAGED
- * (ROW_STAGED), WSL_WAIT_LIMIT_MS (WAIT_LIMIT_MS). wsl_set_option returns WSL_OK or
+ * (ROW_STAGED), WSL_WAIT_LIMIT_MS (WAIT_LIMIT_MS), WSL_SPLIT_TAIL (SPLIT_TAIL). wsl_set_option returns WSL_OK or
  * WSL_ERR_BAD_ARG; wsl_get_option returns the value.
  *   WAIT_LIMIT_MS   bound of every device-side wait, 1..10000 ms (default 2000)
  *   STALL_PRODUCER  test aid: the copy-issuing warps never fill their rings, so the waits

@@ -1072,7 +1072,8 @@ Options& options() {
     v.reserved_sms = 0;
     v.grid_waves = 0;
     v.merge_simt = 0;
-    v.split_tail = 1;
+    e = getenv("WSL_SPLIT_TAIL");
+    v.split_tail = (e && e[0] == '0') ? 0 : 1;
     v.profile_bits = 0;
     if ((e = getenv("WSL_DBG")) != nullptr) v.profile_bits = atoi(e);
     return v;

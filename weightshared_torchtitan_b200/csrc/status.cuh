@@ -25,7 +25,7 @@ int device_sm_count();   // SMs of the current device that launches may fill (al
                          // ones); 0 when device_check() fails
 
 // Run-time options. Initial values come from the environment, read ONCE when the library is
-// first used (WSL_PAIR, WSL_ROW_STAGED, WSL_WAIT_LIMIT_MS); afterwards wsl_set_option()
+// first used (WSL_PAIR, WSL_ROW_STAGED, WSL_WAIT_LIMIT_MS, WSL_SPLIT_TAIL); afterwards wsl_set_option()
 // changes them. Launch paths read this struct, never the environment.
 struct Options {
   int pair_tiles;                      // 1: large GEMMs run on CTA pairs (cta_group::2)
