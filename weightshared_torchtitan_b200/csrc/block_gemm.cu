@@ -1896,7 +1896,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
 #undef WSL_LAUNCH
   if (st != WSL_OK) return st;
   if (tail_region >= 0) {
-    constexpr int kParts = 4;   // blocks per tail tile
+    constexpr int kParts = 16;   // blocks per tail tile: a few hundred blocks for 10-90 tiles
     const unsigned blocks = static_cast<unsigned>(p.reg[tail_region].tile_count) * kParts;
     if (pair) tail_reduce_kernel<true><<<blocks, 256, 0, stream>>>(p, tail_region, kParts);
     else tail_reduce_kernel<false><<<blocks, 256, 0, stream>>>(p, tail_region, kParts);
