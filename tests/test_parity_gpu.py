@@ -413,6 +413,15 @@ def test_split_tail_of_a_large_weight_gradient(wsl):
         assert rel(G.float(), w) < TOL_BF16
         assert torch.equal(G, (dWp - 1).to(torch.bfloat16)) or rel(G.float(), dWp - 1) < 4e-3
         off += n
+    # a weight too short for CTA pairs (N < 512): 192 single-CTA tiles on 148 SMs, same treatment
+    M2, N2, K2 = 8192, 448, 12288
+    ws2 = lib.wsl_bwd_dw_workspace_bytes(M2, N2, K2, 0, 1, 0, 0)
+    assert 0 < ws2 and ws2 % (N2 * K2 * 4) != 0 and ws2 % (128 * 256 * 4) == 0
+    x2 = (torch.randn(M2, K2, generator=g) * 0.5).cuda().to(torch.bfloat16)
+    dY2 = (torch.randn(M2, N2, generator=g) * 0.5).cuda().to(torch.bfloat16)
+    dW2 = torch.ones(N2, K2, device="cuda")
+    wsl.lora_linear_bwd_dw(dY2, None, x2, None, dW2, None, None)
+    assert rel(dW2, 1 + dY2.float().T @ x2.float()) < 1e-4
 
 
 def test_fused_embedding_gathers_exact_rows(wsl):
