@@ -74,7 +74,7 @@ int wsl_reset_status(void);
 /*
  * Run-time options of the library (process-wide). Initial values come from the environment,
  * read once when the library is first used: WSL_PAIR (PAIR_TILES), WSL_ROW_STAGED
- * (ROW_STAGED), WSL_WAIT_LIMIT_MS (WAIT_LIMIT_MS), WSL_SPLIT_TAIL (SPLIT_TAIL). wsl_set_option returns WSL_OK or
+ * (ROW_STAGED), WSL_WAIT_LIMIT_MS (WAIT_LIMIT_MS), WSL_SPLIT_TAIL (SPLIT_TAIL), WSL_DEPENDENT_LAUNCH (DEPENDENT_LAUNCH). wsl_set_option returns WSL_OK or
  * WSL_ERR_BAD_ARG; wsl_get_option returns the value.
  *   WAIT_LIMIT_MS   bound of every device-side wait, 1..10000 ms (default 2000)
  *   STALL_PRODUCER  test aid: the copy-issuing warps never fill their rings, so the waits
@@ -92,6 +92,10 @@ int wsl_reset_status(void);
  *                   launches with long tiles and at least four tiles per CTA, else one
  *   SPLIT_TAIL      0 keeps weight-gradient launches from cutting the tiles of their last, partial round
  *                   of work into split-K units (see wsl_lora_linear_bwd_dw); default 1
+ *   DEPENDENT_LAUNCH 0 launches every kernel with plain stream ordering; 1 (default) launches the GEMM, RMSNorm
+ *                   and fold kernels with programmatic stream serialization: their CTAs take SMs and set
+ *                   themselves up while the kernel before them in the stream drains, and wait for it
+ *                   (griddepcontrol.wait) before they touch global memory
  *   MERGE_SIMT      1 runs wsl_lora_merge_weight on the CUDA cores instead of the tensor cores
  *   PROFILE_BITS    only honoured by builds compiled with -DWSL_PROFILE_SWITCHES
  * No counterpart in the reference (its knobs are Python config fields).
@@ -105,6 +109,7 @@ int wsl_reset_status(void);
 #define WSL_OPT_MERGE_SIMT 7
 #define WSL_OPT_GRID_WAVES 8
 #define WSL_OPT_SPLIT_TAIL 9
+#define WSL_OPT_DEPENDENT_LAUNCH 10
 int wsl_set_option(int option, long long value);
 long long wsl_get_option(int option);
 

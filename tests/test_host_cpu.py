@@ -376,6 +376,7 @@ def test_runtime_options_round_trip():
     lib = _lib.lib()
     assert _lib.get_option(_lib.OPT_RESERVED_SMS) == 0 and _lib.get_option(_lib.OPT_GRID_WAVES) == 0
     assert _lib.get_option(_lib.OPT_STALL_PRODUCER) == 0 and _lib.get_option(_lib.OPT_MERGE_SIMT) == 0
+    assert _lib.get_option(_lib.OPT_SPLIT_TAIL) == 1 and _lib.get_option(_lib.OPT_DEPENDENT_LAUNCH) == 1
     old = _lib.get_option(_lib.OPT_WAIT_LIMIT_MS)
     assert old == 2000 or "WSL_WAIT_LIMIT_MS" in __import__("os").environ
     try:

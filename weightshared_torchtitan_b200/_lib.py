@@ -32,6 +32,7 @@ OPT_PROFILE_BITS = 6
 OPT_MERGE_SIMT = 7
 OPT_GRID_WAVES = 8
 OPT_SPLIT_TAIL = 9
+OPT_DEPENDENT_LAUNCH = 10
 
 _vp = ctypes.c_void_p
 _ll = ctypes.c_longlong

@@ -343,6 +343,12 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_base_smem);
   const int units = p.total_units;
+  // Barriers and tensor memory are set up; from here on the kernel reads and writes global
+  // memory, which has to wait for the kernel before it in the stream. The one after it may
+  // be staged already: its CTAs take the SMs as this grid's CTAs leave them and do their own
+  // set-up while the last tiles here are still running.
+  grid_dep_wait();
+  grid_dep_launch();
 #ifdef WSL_PROFILE_SWITCHES
   const int dbg = p.dbg;
 #else
@@ -909,6 +915,8 @@ struct ReduceParams {
 
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const __grid_constant__ ReduceParams rp) {
+  grid_dep_wait();
+  grid_dep_launch();
   for (long long gi = blockIdx.x * 256ll + threadIdx.x; gi < rp.total; gi += gridDim.x * 256ll) {
     int r = 0;
     while (r + 1 < rp.nregion && gi >= rp.reg[r + 1].begin) ++r;
@@ -966,6 +974,8 @@ template <bool PAIR>
 __global__ void __launch_bounds__(256)
 tail_reduce_kernel(const __grid_constant__ GemmParams p, int tr, int parts) {
   constexpr int TM = Cfg<PAIR>::kTileM;
+  grid_dep_wait();
+  grid_dep_launch();
   const Region& R = p.reg[tr];
   const int j = static_cast<int>(blockIdx.x) / parts;
   const int part = static_cast<int>(blockIdx.x) % parts;
@@ -1072,6 +1082,8 @@ Options& options() {
     v.reserved_sms = 0;
     v.grid_waves = 0;
     v.merge_simt = 0;
+    e = getenv("WSL_DEPENDENT_LAUNCH");
+    v.dependent_launch = (e && e[0] == '0') ? 0 : 1;
     e = getenv("WSL_SPLIT_TAIL");
     v.split_tail = (e && e[0] == '0') ? 0 : 1;
     v.profile_bits = 0;
@@ -1547,13 +1559,15 @@ static int launch_variant(const GemmParams& p, long long units, cudaStream_t str
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = PAIR ? 2 : 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = options().dependent_launch ? 2 : 1;
   cfg.blockDim = dim3(NUM_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -1589,7 +1603,8 @@ static int launch_variant(const GemmParams& p, long long units, cudaStream_t str
 static bool pair_mode_enabled() { return options().pair_tiles != 0; }
 
 bool use_pair_tiles(long long mo0, long long no0) {
-  return pair_mode_enabled() && mo0 >= 512 && no0 >= 128;
+  static const long long min_n = getenv("WSL_PAIR_MIN_N") ? atoll(getenv("WSL_PAIR_MIN_N")) : 128;   // EXPERIMENT
+  return pair_mode_enabled() && mo0 >= 512 && no0 >= min_n;
 }
 
 int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
@@ -1898,8 +1913,8 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   if (tail_region >= 0) {
     constexpr int kParts = 16;   // blocks per tail tile: a few hundred blocks for 10-90 tiles
     const unsigned blocks = static_cast<unsigned>(p.reg[tail_region].tile_count) * kParts;
-    if (pair) tail_reduce_kernel<true><<<blocks, 256, 0, stream>>>(p, tail_region, kParts);
-    else tail_reduce_kernel<false><<<blocks, 256, 0, stream>>>(p, tail_region, kParts);
+    if (pair) launch_dependent(tail_reduce_kernel<true>, dim3(blocks), dim3(256), 0, stream, p, tail_region, kParts);
+    else launch_dependent(tail_reduce_kernel<false>, dim3(blocks), dim3(256), 0, stream, p, tail_region, kParts);
     if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
     ++g_launch_count;
     return WSL_OK;
@@ -1931,7 +1946,7 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   rp.total = total;
   long long blocks = (total + 255) / 256;
   if (blocks > 8ll * g_num_sms) blocks = 8ll * g_num_sms;
-  splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(rp);
+  launch_dependent(splitk_reduce_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, rp);
   if (cudaGetLastError() != cudaSuccess) return WSL_ERR_CUDA;
   ++g_launch_count;
   return WSL_OK;

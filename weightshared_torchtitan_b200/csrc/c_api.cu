@@ -147,6 +147,7 @@ int wsl_set_option(int option, long long value) {
       o.grid_waves = static_cast<int>(value);
       return WSL_OK;
     case WSL_OPT_SPLIT_TAIL: o.split_tail = value != 0; return WSL_OK;
+    case WSL_OPT_DEPENDENT_LAUNCH: o.dependent_launch = value != 0; return WSL_OK;
     default: return WSL_ERR_BAD_ARG;
   }
 }
@@ -163,6 +164,7 @@ long long wsl_get_option(int option) {
     case WSL_OPT_MERGE_SIMT: return o.merge_simt;
     case WSL_OPT_GRID_WAVES: return o.grid_waves;
     case WSL_OPT_SPLIT_TAIL: return o.split_tail;
+    case WSL_OPT_DEPENDENT_LAUNCH: return o.dependent_launch;
     default: return WSL_ERR_BAD_ARG;
   }
 }

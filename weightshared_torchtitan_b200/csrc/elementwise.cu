@@ -562,7 +562,7 @@ int launch_rmsnorm_fwd(const void* x, long long ldx, const void* res, void* h_ou
         return WSL_ERR_CUDA;                                                                       \
       attr_set_dev[dev_i] = true;                                                                  \
     }                                                                                              \
-    rmsnorm_fwd_staged_kernel<T, R, KVN, RES><<<sgb, (cw + 1) * 32, ssmem, s>>>(                   \
+    launch_dependent(rmsnorm_fwd_staged_kernel<T, R, KVN, RES>, dim3(sgb), dim3((cw + 1) * 32), ssmem, s,  \
         static_cast<const T*>(x), static_cast<const T*>(res), static_cast<T*>(h_out), w,           \
         static_cast<T*>(y), ldy, rstd, rows, d, s_lpr, eps, cs, sn, h, sq, n_tiles, rn_knobs());   \
   } while (0)
@@ -665,7 +665,7 @@ int launch_rmsnorm_bwd(const void* dy, long long lddy, const void* x, long long 
         return WSL_ERR_CUDA;                                                                       \
       attr_set_dev[dev_i] = true;                                                                  \
     }                                                                                              \
-    rmsnorm_bwd_staged_kernel<T, R, KVN, DRES><<<sgb, (cw + 1) * 32, ssmem, s>>>(                  \
+    launch_dependent(rmsnorm_bwd_staged_kernel<T, R, KVN, DRES>, dim3(sgb), dim3((cw + 1) * 32), ssmem, s, \
         static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(dres), w, rstd, \
         static_cast<T*>(dx), lddx, dw, rows, d, s_lpr, cs, sn, h, sq, n_tiles, rn_knobs());        \
   } while (0)

@@ -96,6 +96,15 @@ __device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t (&r)[4]) {
                : "memory");
 }
 
+// ------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it in the stream is still running. grid_dep_wait() blocks until that earlier
+// grid has completed and its memory operations are visible (a no-op for a normal launch);
+// everything that touches global memory comes after it. grid_dep_launch() tells the hardware
+// that the NEXT kernel in the stream may be started as far as this CTA is concerned.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // --------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -219,6 +219,8 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const T* __restrict__ res, T*
     *drainp = 0;
     fence_barrier_init();
   }
+  grid_dep_wait();     // global memory is touched from here on (see ptx_sm100.cuh)
+  grid_dep_launch();
   for (int j = threadIdx.x; j < D; j += THREADS) w_s[scale_slot<NV>(j, lpr)] = w[j];
   __syncthreads();
   const int my_tiles = static_cast<int>((n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
@@ -381,6 +383,8 @@ rmsnorm_bwd_staged_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
     *drainp = 0;
     fence_barrier_init();
   }
+  grid_dep_wait();     // global memory is touched from here on (see ptx_sm100.cuh)
+  grid_dep_launch();
   for (int j = threadIdx.x; j < D; j += THREADS) {
     dw_part[j] = 0.f;
     w_s[scale_slot<NV>(j, lpr)] = w[j];

@@ -25,7 +25,8 @@ int device_sm_count();   // SMs of the current device that launches may fill (al
                          // ones); 0 when device_check() fails
 
 // Run-time options. Initial values come from the environment, read ONCE when the library is
-// first used (WSL_PAIR, WSL_ROW_STAGED, WSL_WAIT_LIMIT_MS, WSL_SPLIT_TAIL); afterwards wsl_set_option()
+// first used (WSL_PAIR, WSL_ROW_STAGED, WSL_WAIT_LIMIT_MS, WSL_SPLIT_TAIL,
+// WSL_DEPENDENT_LAUNCH); afterwards wsl_set_option()
 // changes them. Launch paths read this struct, never the environment.
 struct Options {
   int pair_tiles;                      // 1: large GEMMs run on CTA pairs (cta_group::2)
@@ -36,7 +37,27 @@ struct Options {
   int grid_waves;                      // GEMM grids up to this many times the co-resident CTAs (0 = by launch)
   int profile_bits;                    // only honoured in builds with WSL_PROFILE_SWITCHES
   int merge_simt;                      // 1: W + s B A on the CUDA cores instead of the block GEMM
+  int dependent_launch;                // 1: GEMM launches may start while the kernel before them drains
   int split_tail;                      // 1: launches of long tiles may end with a split tail (see SplitPlan)
 };
 Options& options();
+
+// Launch of a kernel that calls grid_dep_wait() before its first access to global memory:
+// with the option on it carries the programmatic-stream-serialization attribute, so its CTAs
+// may take SMs and set themselves up while the kernel before it in the stream drains.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = options().dependent_launch ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 }  // namespace wsl
