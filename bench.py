@@ -14,8 +14,9 @@ over one batch. Synthetic token ids stand in for the C4 stream the reference tra
 One JSON line on stdout (rank 0). `value` = whole-job tokens/s with tokens already resident
 in HBM; `e2e` = the same step driven from pinned host buffers (H2D of tokens/labels and D2H
 of the loss inside the timed region); `roofline` = the dominant kernel of this library by
-device time inside the timed region (CUDA events on the launching stream), against the
-measured bf16 tensor peak; `op_headline` = the isolated fused projection fwd+bwd at the
+device time inside the timed region (CUDA events on the launching stream around every launch
+of one step in four: events between kernels switch their programmatic overlap off, so the
+other steps run without them), against the measured bf16 tensor peak; `op_headline` = the isolated fused projection fwd+bwd at the
 configuration-4 MLP shapes (M = 16384) with its own clock record; `gpu_eager_baseline` = the
 reference's eager composition (nn.Linear + LoRA + add under bf16 autocast) at the same shape
 on the same GPU; `cpu_baseline` = the CPU oracle (eager PyTorch restatement of the reference
@@ -53,6 +54,7 @@ WORKLOAD = "qwen3-8b-ws"
 SEQ_LEN, MICRO_BATCH, CONFIG_NO = WORKLOAD_SHAPES[WORKLOAD]
 METRIC = "step_tokens_per_s"
 UNIT = "tokens/s"
+TIMING_EVERY = 4             # steps between two steps that carry per-launch CUDA events
 PEAK_NOMINAL_TF = 2250.0     # B200 dense bf16, the constant the reference's MFU uses (torchtitan/tools/utils.py:96-98)
 
 # Measured DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) over algorithmic bytes
@@ -780,14 +782,19 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    # A pair of CUDA events around every launch of this library sits between consecutive
+    # kernels and so switches their programmatic overlap off; one step in TIMING_EVERY carries
+    # them (the sample the kernel table and the roofline are computed from), the others run as
+    # a user's step does.
     records = []
-    ops.set_timing(records)
+    instrumented = [i for i in range(args.steps) if i % TIMING_EVERY == 0]
     step.timing = {}
     n0 = _lib.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
     e0.record()
     for i in range(args.steps):
+        ops.set_timing(records if i % TIMING_EVERY == 0 else None)
         loss = step(*dev[i % nbatch])
     e1.record()
     sync_all()
@@ -867,12 +874,13 @@ def run_ours(args):
                     "h2d_bytes_per_step": 2 * MICRO_BATCH * SEQ_LEN * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches) * world,
             "roofline": roofline,
-            "kernels": {k: {"launches": v["launches"], "ms_per_step": v["ms"] / args.steps,
+            "kernels_timed_in_steps": instrumented,
+            "kernels": {k: {"launches": v["launches"], "ms_per_step": v["ms"] / len(instrumented),
                             "tflops": v["flops"] / v["ms"] / 1e9 if v["flops"] else None,
                             "gbs": v["bytes"] / v["ms"] / 1e6} for k, v in sorted(kinds.items())},
-            "wsl_kernel_share_of_step": kernel_ms / ms_dev,
+            "wsl_kernel_share_of_step": (kernel_ms / len(instrumented)) / (ms_dev / args.steps),
             "model_tflops_per_gpu": fpt["total"] * tps_gpu / 1e12,
-            "linear_tflops_per_gpu_in_step": fpt["linear"] * tokens_per_step * args.steps / (kernel_ms / 1e3) / 1e12,
+            "linear_tflops_per_gpu_in_step": fpt["linear"] * tokens_per_step * len(instrumented) / (kernel_ms / 1e3) / 1e12,
             # executed algorithmic FLOPs per token (every layer's projections counted, shared or
             # not) against the nominal dense bf16 peak, linears alone and the full step
             "step_roofline": {

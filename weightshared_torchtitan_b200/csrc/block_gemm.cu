@@ -328,6 +328,8 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
     fence_barrier_init();
     fence_proxy_async_smem();
   }
+  if (warp == 0 && elect_one())   // the operand maps live in the kernel parameters: nothing to wait for
+    for (int i = 0; i < p.nregion * p.nseg * 2 && i < kMaxMaps; ++i) tma_prefetch_desc(&p.maps[i]);
   if (warp == 1) {
     if (PAIR) {
       tmem_alloc_pair(smem_u32(&tmem_base_smem), TMEM_COLS);
@@ -357,8 +359,6 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (elect_one())
-      for (int i = 0; i < p.nregion * p.nseg * 2 && i < kMaxMaps; ++i) tma_prefetch_desc(&p.maps[i]);
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
