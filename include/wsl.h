@@ -90,7 +90,7 @@ int wsl_reset_status(void);
  *                   shorter-lived CTAs which the hardware deals to SMs as they free up (evens out
  *                   unequal tile times and SMs held by another kernel), 0 (default) = two waves for
  *                   launches with long tiles and at least four tiles per CTA, else one
- *   SPLIT_TAIL      0 keeps weight-gradient launches from cutting the tiles of their last, partial round
+ *   SPLIT_TAIL      0 keeps weight-gradient launches from cutting the tiles of their last, partial wave
  *                   of work into split-K units (see wsl_lora_linear_bwd_dw); default 1
  *   DEPENDENT_LAUNCH 0 launches every kernel with plain stream ordering; 1 (default) launches the GEMM, RMSNorm
  *                   and fold kernels with programmatic stream serialization: their CTAs take SMs and set
@@ -227,9 +227,9 @@ int wsl_lora_linear_bwd_dx_swiglu(const void* dY, long long lddy, const void* U,
  * When the [N,K] tile grid is too small to fill the GPU (short weight matrices, long
  * token count) the token contraction is split across CTAs, partial sums go to the
  * workspace and a second kernel adds them into dW/dA/dB in a fixed order, so results stay
- * bit-reproducible. When the grid is large but its last round of tiles is only partly
- * full (every tile contracts over all M tokens, so an idle round is long), just the tiles
- * of that round are split that way. wsl_bwd_dw_workspace_bytes() gives the size that allows
+ * bit-reproducible. When the grid is large but its last wave of tiles is only partly
+ * full (every tile contracts over all M tokens, so an idle wave is long), just the tiles
+ * of that wave are split that way. wsl_bwd_dw_workspace_bytes() gives the size that allows
  * the best split; a smaller or absent workspace only costs speed. The workspace contents are
  * garbage afterwards; calls that overlap on the GPU need separate workspaces.
  * Replaces the MmBackward weight gradients and AccumulateGrad of

@@ -398,14 +398,14 @@ def test_runtime_options_round_trip():
 
 def test_split_plan_of_weight_gradient_launches():
     """The workspace a weight-gradient launch asks for tells its split plan (host code, no device):
-    nothing for a grid that fills its rounds, the whole output times S for a small grid, and a few
-    tile blocks (S x T x 256 KiB) for a large grid with a partly filled last round; launches that
+    nothing for a grid that fills its waves, the whole output times S for a small grid, and a few
+    tile blocks (S x T x 256 KiB) for a large grid with a partly filled last wave; launches that
     carry the narrow rank-r regions, and contractions too short to pay, take no tail."""
     from weightshared_torchtitan_b200 import _lib
     lib = _lib.lib()
     blk = 256 * 256 * 4
     assert _lib.get_option(_lib.OPT_SPLIT_TAIL) == 1
-    # configuration 4: q|k|v 384 tile pairs = 5.19 rounds -> a tail; gate|up 1536 = 20.76 rounds -> none
+    # configuration 4: q|k|v 384 tile pairs = 5.19 waves -> a tail; gate|up 1536 = 20.76 waves -> none
     ws = lib.wsl_bwd_dw_workspace_bytes(16384, 6144, 4096, 0, 1, 0, 0)
     assert 0 < ws < 6144 * 4096 * 4 // 4 and ws % blk == 0
     assert lib.wsl_bwd_dw_workspace_bytes(16384, 24576, 4096, 0, 1, 0, 0) == 0

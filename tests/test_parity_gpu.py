@@ -367,8 +367,8 @@ def test_split_contraction_for_small_weight_grads(wsl):
 
 
 def test_split_tail_of_a_large_weight_gradient(wsl):
-    """Large tile grid whose last round is only partly full (242 tile pairs on 74 CTA pairs):
-    the launch cuts only the tiles of that round into split-K units. The workspace is then a
+    """Large tile grid whose last wave is only partly full (242 tile pairs on 74 CTA pairs):
+    the launch cuts only the tiles of that wave into split-K units. The workspace is then a
     fraction of the output; results match the oracle, are bit-reproducible, agree with the
     launch without a tail to fp32 rounding, and the grouped launch's bf16 copy G comes out of
     the folded sums. Ragged N so that the tail holds a partial tile. Launches that carry the

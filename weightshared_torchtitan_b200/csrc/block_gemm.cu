@@ -1342,14 +1342,14 @@ static double simulate_makespan(int nseg, const long long* count, const double* 
   for (int c = 0; c < n_cta; ++c) load[c] = 0.0;
   long long u = 0;
   for (int i = 0; i < nseg; ++i) {
-    // whole rounds of the run cost every CTA the same; only the ragged ends go one by one
+    // whole passes over the CTAs cost every CTA the same; only the ragged ends go one by one
     long long left = count[i];
     while (left > 0 && (u % n_cta) != 0) { load[u % n_cta] += cost[i]; ++u; --left; }
-    const long long rounds = left / n_cta;
-    if (rounds > 0) {
-      for (int c = 0; c < n_cta; ++c) load[c] += cost[i] * static_cast<double>(rounds);
-      u += rounds * n_cta;
-      left -= rounds * n_cta;
+    const long long passes = left / n_cta;
+    if (passes > 0) {
+      for (int c = 0; c < n_cta; ++c) load[c] += cost[i] * static_cast<double>(passes);
+      u += passes * n_cta;
+      left -= passes * n_cta;
     }
     while (left > 0) { load[u % n_cta] += cost[i]; ++u; --left; }
   }
@@ -1385,9 +1385,9 @@ static double simulate_makespan(int nseg, const long long* count, const double* 
 // few tiles), or a TAIL: the last `tail_tiles` tiles (in rasterisation order) of region
 // `tail_parent` leave their place in the launch order and run at its very end, each split
 // `tail_splits` ways. A launch of many long tiles (a weight gradient contracts over every
-// token) otherwise ends with a partial round in which most CTAs idle for a whole tile time:
-// 384 tile pairs on 74 CTA pairs take 6 rounds for 5.2 rounds of work. With the tail's tiles
-// cut into short units the last round is short too. Only the tail goes through the
+// token) otherwise ends with a partial wave in which most CTAs idle for a whole tile time:
+// 384 tile pairs on 74 CTA pairs take 6 waves for 5.2 waves of work. With the tail's tiles
+// cut into short units the last wave is short too. Only the tail goes through the
 // workspace (one dense [tile rows x 256] fp32 block per split and tile); everything else keeps
 // its in-place epilogue, and the fixed-order fold keeps results bit-reproducible.
 constexpr double kTailParentWeight = 0.75;   // only (nearly) full-width tiles are worth a tail
@@ -1443,14 +1443,14 @@ static SplitPlan plan_launch_uncached(int nregion, const long long* mo, const lo
   if (out.bytes > 0) best += 2.0 * static_cast<double>(out.bytes) / 6.5e6 + 4.0;
   // The tail comes off the region with the most tiles. Launches that also carry narrow
   // regions (the rank-r products dB, dA beside dW) are left alone: their cheap units already
-  // fill most of the last round, and a tail measured between +9 % and -4 % on them.
+  // fill most of the last wave, and a tail measured between +9 % and -4 % on them.
   int parent = -1;
   for (int i = 0; i < nregion; ++i) {
     if (weight[i] < kTailParentWeight) return out;
     if (tiles[i] >= 2 && (parent < 0 || tiles[i] >= tiles[parent])) parent = i;
   }
   if (parent < 0) return out;
-  long long t_max = workers + workers / 4;   // a round of tiles and a little more
+  long long t_max = workers + workers / 4;   // a wave of tiles and a little more
   if (t_max > tiles[parent] - 1) t_max = tiles[parent] - 1;
   static const int kTailSplits[] = {2, 3, 4, 5, 6, 8};
   const int s_cap = kb_total / 8 < 8 ? kb_total / 8 : 8;
@@ -1478,7 +1478,7 @@ static SplitPlan plan_launch_uncached(int nregion, const long long* mo, const lo
       }
     }
   }
-  // (measured gains are about half of what this model predicts: idle SMs in a partial round
+  // (measured gains are about half of what this model predicts: idle SMs in a partial wave
   // are not a pure loss on a power-capped part, the busy ones clock higher meanwhile)
   if (best_tail < 0.95 * best) {
     for (int i = 0; i < kMaxRegion; ++i) out.splits[i] = 1;
