@@ -77,6 +77,10 @@ struct Region {
   int tile_off;
   int tile_count;
   int tail;           // 1 for such a tail entry
+  // k-blocks this region really has: the launch's kb_total, except where regions of different
+  // contraction lengths share a launch (one segment, GemmDesc::ragged_k) -- then a region's
+  // splits divide ITS blocks and nothing is spent on the zeros beyond its end
+  int kb_own;
   void* copy;         // bf16 copy of alpha * acc (RegionDesc::copy), or nullptr
   long long ld_copy;
   // kEpiSwiGLU regions (pair launches): the second CTA of a pair loads its half of the B tile
@@ -395,7 +399,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
         const int klen = p.seg_k[sg];
         const int nkb = (klen + BK - 1) / BK;
         int lo, hi;
-        split_range(p.kb_total, R.splits, split, kb_base, nkb, lo, hi);
+        split_range(R.kb_own, R.splits, split, kb_base, min(nkb, R.kb_own - kb_base), lo, hi);
         kb_base += nkb;
         for (int kk = lo * BK; kk < hi * BK; kk += BK) {
           // Gathered B operand: the k-rows of this block are 64 token ids; lane l fetches rows
@@ -519,7 +523,7 @@ block_gemm_kernel(const __grid_constant__ GemmParams p) {
           const int klen = p.seg_k[sg];
           const int nkb = (klen + BK - 1) / BK;
           int lo, hi;
-          split_range(p.kb_total, R.splits, split, kb_base, nkb, lo, hi);
+          split_range(R.kb_own, R.splits, split, kb_base, min(nkb, R.kb_own - kb_base), lo, hi);
           kb_base += nkb;
           for (int kk = lo * BK; kk < hi * BK; kk += BK) {
             ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, abortp, p.wait_limit_ns));
@@ -1253,8 +1257,12 @@ double tile_weight(long long no) {
 // smallest simulated makespan wins, charging the workspace round trip (partials written and
 // read once at ~6.5 MB/us) and the reduce launch. One k-block of a full tile ~ 0.27 us.
 // Returns the workspace bytes the plan needs (0 = no split anywhere).
+// `kb_own` (may be null): the k-blocks region i really has when regions of different
+// contraction lengths share a launch (kb_total = the longest). Such a region is split in
+// proportion to its length, so that units stay about equally long, and a region that stays
+// whole writes its output itself while the others go through the workspace.
 size_t plan_splits(int nregion, const long long* tiles, const double* weight, const long long* elems,
-                   int kb_total, size_t ws_limit_bytes, int workers, int* splits_out) {
+                   int kb_total, size_t ws_limit_bytes, int workers, int* splits_out, const int* kb_own = nullptr) {
   for (int i = 0; i < nregion; ++i) splits_out[i] = 1;
   long long total = 0;
   for (int i = 0; i < nregion; ++i) total += tiles[i];
@@ -1277,24 +1285,32 @@ size_t plan_splits(int nregion, const long long* tiles, const double* weight, co
         if (fine > s_cap) fine = s_cap;
         if (fine > sr[i]) sr[i] = static_cast<int>(fine);
       }
+      if (kb_own != nullptr) {
+        // in proportion to the region's own length, never more splits than it has 8-block runs
+        long long own = (static_cast<long long>(sr[i]) * kb_own[i] + kb_total / 2) / kb_total;
+        const long long cap_i = kb_own[i] / 8 < 1 ? 1 : kb_own[i] / 8;
+        if (own > cap_i) own = cap_i;
+        sr[i] = own < 1 ? 1 : static_cast<int>(own);
+      }
       if (sr[i] > 1) {
         bytes += static_cast<size_t>(sr[i]) * elems[i] * 4;
         any = true;
       }
     }
-    if (any) {
-      // either every region goes through the workspace or none (one reduce launch)
+    if (any && kb_own == nullptr) {
+      // regions of one length: either every region goes through the workspace or none
       bytes = 0;
       for (int i = 0; i < nregion; ++i) {
         if (sr[i] < 2) sr[i] = 2 <= s_cap ? 2 : 1;
         bytes += static_cast<size_t>(sr[i]) * elems[i] * 4;
       }
-      if (bytes > ws_limit_bytes) break;
     }
+    if (any && bytes > ws_limit_bytes) break;
     for (int w = 0; w < W; ++w) load[w] = 0.0;
     long long u = 0;
     for (int i = 0; i < nregion; ++i) {
-      const double kb = static_cast<double>((kb_total + sr[i] - 1) / sr[i]);
+      const int kbi = kb_own != nullptr ? kb_own[i] : kb_total;
+      const double kb = static_cast<double>((kbi + sr[i] - 1) / sr[i]);
       for (long long j = 0; j < tiles[i] * sr[i]; ++j, ++u) load[u % W] += kb * weight[i] + 6.0;
     }
     double mk = 0.0;
@@ -1401,6 +1417,7 @@ struct SplitPlan {
 
 struct PlanKey {
   long long mo[kMaxRegion], no[kMaxRegion];
+  int kb_own[kMaxRegion];
   size_t ws_limit;
   int nregion, kb_total, workers, pair, allow_tail, waves_opt, tail_opt;
 };
@@ -1414,7 +1431,8 @@ static PlanSlot g_plans[kPlanSlots] = {};
 static std::mutex g_plan_mutex;
 
 static SplitPlan plan_launch_uncached(int nregion, const long long* mo, const long long* no, int kb_total,
-                                      size_t ws_limit, int workers, bool pair, bool allow_tail) {
+                                      size_t ws_limit, int workers, bool pair, bool allow_tail,
+                                      const int* kb_own) {
   SplitPlan out;
   for (int i = 0; i < kMaxRegion; ++i) out.splits[i] = 1;
   out.tail_parent = -1;
@@ -1430,7 +1448,8 @@ static SplitPlan plan_launch_uncached(int nregion, const long long* mo, const lo
     weight[i] = tile_weight(no[i]);
     elems[i] = mo[i] * no[i];
   }
-  out.bytes = plan_splits(nregion, tiles, weight, elems, kb_total, ws_limit, workers, out.splits);
+  out.bytes = plan_splits(nregion, tiles, weight, elems, kb_total, ws_limit, workers, out.splits, kb_own);
+  if (kb_own != nullptr) return out;   // regions of different lengths: all narrow, no tail
   if (!allow_tail || !options().split_tail || nregion + 1 > kMaxRegion || kb_total < 64) return out;
   // time of the plan so far, by the same clock as the candidates below
   long long cnt[kMaxRegion + 1];
@@ -1493,12 +1512,13 @@ static SplitPlan plan_launch_uncached(int nregion, const long long* mo, const lo
 // Plans repeat launch after launch (the same few shapes every layer, every step): a small
 // table keyed by everything the plan depends on saves the search.
 SplitPlan plan_launch(int nregion, const long long* mo, const long long* no, int kb_total, size_t ws_limit,
-                      int workers, bool pair, bool allow_tail) {
+                      int workers, bool pair, bool allow_tail, const int* kb_own = nullptr) {
   PlanKey key;
   std::memset(&key, 0, sizeof(key));
   for (int i = 0; i < nregion && i < kMaxRegion; ++i) {
     key.mo[i] = mo[i];
     key.no[i] = no[i];
+    key.kb_own[i] = kb_own != nullptr ? kb_own[i] : -1;
   }
   key.ws_limit = ws_limit;
   key.nregion = nregion;
@@ -1521,7 +1541,7 @@ SplitPlan plan_launch(int nregion, const long long* mo, const long long* no, int
       if (sl.used && std::memcmp(&sl.key, &key, sizeof(key)) == 0) return sl.plan;
     }
   }
-  const SplitPlan plan = plan_launch_uncached(nregion, mo, no, kb_total, ws_limit, workers, pair, allow_tail);
+  const SplitPlan plan = plan_launch_uncached(nregion, mo, no, kb_total, ws_limit, workers, pair, allow_tail, kb_own);
   std::lock_guard<std::mutex> lock(g_plan_mutex);
   int put = 0;
   for (int i = 0; i < kProbe; ++i)
@@ -1646,6 +1666,15 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
   plan.tail_tiles = 0;
   plan.tail_splits = 1;
   plan.bytes = 0;
+  // regions of different contraction lengths in one launch: each one's own k-blocks
+  const bool ragged = g.ragged_k && g.nseg == 1;
+  int kb_own[kMaxRegion];
+  for (int r = 0; r < g.nregion; ++r) {
+    const long long ak = g.a_mn ? g.region[r].a[0].rows : g.region[r].a[0].cols;
+    long long kb = (ak + BK - 1) / BK;
+    kb = kb < 1 ? 1 : (kb > kb_all ? kb_all : kb);
+    kb_own[r] = ragged ? static_cast<int>(kb) : kb_all;
+  }
   if (g.workspace != nullptr) {
     long long pmo[kMaxRegion], pno[kMaxRegion];
     bool plain = g.gather_tokens == nullptr;   // a tail needs ordinary regions
@@ -1655,7 +1684,8 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       pno[r] = rd.no;
       plain = plain && rd.addend == nullptr && !rd.transposed && rd.mode >= kEpiStoreBf16 && rd.mode <= kEpiAccumF32;
     }
-    plan = plan_launch(g.nregion, pmo, pno, kb_all, g.workspace_bytes, split_workers(pair, g_num_sms), pair, plain);
+    plan = plan_launch(g.nregion, pmo, pno, kb_all, g.workspace_bytes, split_workers(pair, g_num_sms), pair, plain,
+                       ragged ? kb_own : nullptr);
   }
   int nmaps = 0;
   long long tiles = 0;
@@ -1817,6 +1847,8 @@ int launch_block_gemm(const GemmDesc& g, cudaStream_t stream) {
       R.tile_off = 0;
       R.tile_count = R.m_tiles * R.n_tiles;
       R.tail = 0;
+      R.kb_own = kb_own[r];
+      if (R.splits > R.kb_own) return WSL_ERR_BAD_ARG;   // every split owns at least one block
       if (r == plan.tail_parent) R.tile_count -= plan.tail_tiles;
       any_split = any_split || R.splits > 1;
       if (R.splits > 1) off += static_cast<long long>(R.splits) * g.region[r].mo * g.region[r].no;
