@@ -334,11 +334,13 @@ class LoRAGateUpSwiGLUFunction(torch.autograd.Function):
 # The four epilogue warps of a CTA spend ~16 instructions per element on it, which the main
 # loop hides only when the contraction (the model width d) is long: measured on B200 at the
 # configuration-4 MLP shape (d = 4096, 16384 tokens) 1.23 ms against 1.58 ms for GEMM + kernel,
-# at the configuration-1 shape (d = 1024, 32768 tokens) 0.33 ms against 0.30 ms. "auto" takes
-# the epilogue form from d = 4096; WSL_FUSE_SWIGLU_BWD=0 / 1 forces one.
+# at the configuration-3 shape (d = 2560, 32768 tokens) 1.59 against 1.80 ms, at the
+# configuration-2 shape (d = 2048) 1.00 against 0.97 ms and at the configuration-1 shape
+# (d = 1024) 0.33 against 0.30 ms. "auto" takes the epilogue form from d = 2560;
+# WSL_FUSE_SWIGLU_BWD=0 / 1 forces one.
 _env_fuse = os.environ.get("WSL_FUSE_SWIGLU_BWD", "auto")
 FUSE_SWIGLU_BWD = {"0": False, "1": True}.get(_env_fuse, "auto")
-_FUSE_SWIGLU_BWD_MIN_WIDTH = 4096
+_FUSE_SWIGLU_BWD_MIN_WIDTH = 2560
 
 
 def _down_dx_with_activation_grad(d, U2, W, A, g, u):
