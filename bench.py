@@ -372,7 +372,7 @@ def bench_projection(torch, M, N, K, r, iters, what="all", warmup=3):
     # projection (N = inner width): gate|up + SwiGLU forward, and the down projection's input gradient
     # (contraction over K = model width, output width N) with the SwiGLU backward
     mlp = {}
-    if ops.lora_swiglu_supported(M, N, K, r) and ops.swiglu_bwd_in_dx_supported(M, K, N, r):
+    if N >= K and ops.lora_swiglu_supported(M, N, K, r) and ops.swiglu_bwd_in_dx_supported(M, K, N, r):
         A_cat = torch.cat((A, A))
         T_cat = ops.lora_prepass(x, A_cat, 2.0)
         g_, u_, _ = ops.lora_swiglu_fwd(x, W, W, T_cat, B, B)

@@ -363,7 +363,9 @@ def test_route_table_covers_the_baseline_configurations():
             assert key in Fn.ROUTE_TABLE, (name, names, key)
             assert Fn.derived_route_pays(*key) is Fn.ROUTE_TABLE[key]
             seen.add(key)
-    assert seen == set(Fn.ROUTE_TABLE)
+    # plus the isolated-op headline shape (one gate projection of configuration 4 on its own)
+    headline = (16384, 4096, (12288,), 64)
+    assert seen | {headline} == set(Fn.ROUTE_TABLE)
     # outside the table: many tokens per input width -> through the layer gradient, few -> direct
     assert Fn.derived_route_pays(65536, 1024, (1024,), 16) is True
     assert Fn.derived_route_pays(4096, 4096, (4096,), 64) is False
